@@ -1,0 +1,158 @@
+/* C ABI of the sm_100a kernel library (libincin_sm100.so).
+ *
+ * Every entry point takes raw device pointers plus the CUDA stream to launch on
+ * (a cudaStream_t passed as void*), returns an incin_status code and never
+ * synchronises the device.  Unless a function says otherwise it allocates
+ * nothing: outputs and scratch buffers are owned by the caller (the Python
+ * layer hands in torch-allocated storage), so every launch is capturable in a
+ * CUDA graph and replays with no host work.
+ *
+ * bf16 tensors are `uint16_t`-sized elements in device memory; fp32 tensors are
+ * `float`.  "rows" always means the flattened leading dimensions.
+ */
+#ifndef INCIN_B200_H
+#define INCIN_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum incin_status {
+  INCIN_OK = 0,
+  INCIN_ERR_ARGUMENT = 1,
+  INCIN_ERR_ALIGNMENT = 2,
+  INCIN_ERR_DRIVER = 3,
+  INCIN_ERR_TENSOR_MAP = 4,
+  INCIN_ERR_LAUNCH = 5,
+  INCIN_ERR_UNSUPPORTED = 6,
+  INCIN_ERR_TOO_LARGE = 7,
+  INCIN_ERR_PEER = 8
+} incin_status;
+
+/* epilogue activations of incin_gemm_bf16 */
+enum {
+  INCIN_ACT_NONE = 0,
+  INCIN_ACT_GELU = 1,  /* exact erf GELU; optional pre-activation copy to aux */
+  INCIN_ACT_SILU = 2,
+  INCIN_ACT_DGELU = 3, /* multiply by GELU'(aux): activation backward fused into a data-gradient GEMM */
+  INCIN_ACT_DSILU = 4
+};
+
+/* C[b][m][n] = epi(alpha * sum_k A[b][m][k] * B[b][n][k]); all strides in elements.
+ * a_mn_major = 0: A is stored [M][lda] (k contiguous);  1: stored [K][lda] (m contiguous).
+ * b_mn_major = 0: B is stored [N][ldb] (k contiguous);  1: stored [K][ldb] (n contiguous).
+ * batch index b in [0, batch_lo*batch_hi) splits into (b % batch_lo, b / batch_lo) with one
+ * stride each, so heads inside a [B, T, 3, H, D] buffer are addressable without a copy. */
+typedef struct incin_gemm_desc {
+  const void* A;
+  const void* B;
+  void* C;
+  int M, N, K;
+  long long lda, ldb, ldc;
+  int a_mn_major, b_mn_major;
+  int batch_lo, batch_hi;
+  long long a_stride_lo, a_stride_hi, b_stride_lo, b_stride_hi, c_stride_lo, c_stride_hi;
+  int out_fp32;    /* C is float instead of bf16 */
+  int accumulate;  /* fp32 only: C += result (atomic), needed for split-K */
+  float alpha;
+  const void* bias;     /* bf16 [N] or NULL */
+  const void* residual; /* bf16, same layout as C, or NULL */
+  int act;
+  void* aux;     /* bf16, same layout as C: GELU/SILU pre-activation out, DGELU/DSILU pre-activation in */
+  int splits;    /* split-K factor (>1 requires out_fp32 && accumulate) */
+  int tile_n;    /* 0 = heuristic, else 64/128/192/256 */
+  int max_ctas;  /* 0 = all SMs; smaller leaves SMs to a concurrent communication kernel */
+  void* status;  /* optional int32 device word: receives a KernelStatus code if a wait timed out */
+} incin_gemm_desc;
+
+int incin_gemm_bf16(const incin_gemm_desc* desc, void* stream);
+
+/* ---- normalisation ------------------------------------------------------------------------ */
+/* y = (x - mean) * rstd * gamma + beta over the last dim C; bf16 io, fp32 statistics.
+ * beta may be NULL.  mean/rstd are fp32 [rows] and are kept for the backward pass. */
+int incin_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                        long long rows, int C, float eps, void* stream);
+/* dx = LN'(dy) (+ dx_add when not NULL: the residual-stream gradient, fused);
+ * dgamma/dbeta are fp32 and are ACCUMULATED into (they are slices of the flat gradient buffer).
+ * scratch: fp32, at least incin_layernorm_bwd_scratch_floats(rows, C) elements. */
+long long incin_layernorm_bwd_scratch_floats(long long rows, int C);
+int incin_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                        const void* dx_add, void* dx, float* dgamma, float* dbeta, float* scratch, long long rows,
+                        int C, void* stream);
+/* RMSNorm: y = x * rsqrt(mean(x^2) + eps) * gamma */
+int incin_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd, long long rows, int C, float eps,
+                      void* stream);
+int incin_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rstd, const void* dx_add,
+                      void* dx, float* dgamma, float* scratch, long long rows, int C, void* stream);
+
+/* ---- embedding ------------------------------------------------------------------------------ */
+/* out[b,t,:] = wte[tok[b,t],:] + wpe[t,:] (wpe may be NULL); tokens are int64 */
+int incin_embedding_fwd(const int64_t* tokens, const void* wte, const void* wpe, void* out, long long B, int T, int C,
+                        void* stream);
+/* dwte/dwpe are fp32 and accumulated into with atomics */
+int incin_embedding_bwd(const void* dout, const int64_t* tokens, float* dwte, float* dwpe, long long B, int T, int C,
+                        void* stream);
+
+/* ---- softmax cross-entropy -------------------------------------------------------------------- */
+/* logits: bf16 [rows][ld], only the first V columns are classes.  Writes per-row loss and log-sum-exp. */
+int incin_xent_fwd(const void* logits, const int64_t* targets, float* loss, float* lse, long long rows, int V,
+                   long long ld, void* stream);
+/* dlogits = (softmax - onehot) * (*dloss) * scale, written in place over logits (columns >= V get 0) */
+int incin_xent_bwd(void* logits, const int64_t* targets, const float* lse, const float* dloss, float scale,
+                   long long rows, int V, long long ld, void* stream);
+/* out[0] = mean(x[0..n)) : deterministic single-block tree reduction */
+int incin_mean_f32(const float* x, float* out, long long n, void* stream);
+
+/* ---- causal softmax for the composed (materialised-scores) attention path ---------------------- */
+/* in place over bf16 scores [batch][T][T]: p = softmax(scale * s + causal mask) */
+int incin_causal_softmax_fwd(void* scores, long long batch, int T, float scale, void* stream);
+/* in place over dP given P: dS = P * (dP - sum(dP * P)) * scale, zero above the diagonal */
+int incin_causal_softmax_bwd(void* dp, const void* p, long long batch, int T, float scale, void* stream);
+
+/* ---- reductions / misc ------------------------------------------------------------------------- */
+/* dbias[n] += sum_m dy[m][n]  (fp32 accumulate into the flat gradient buffer) */
+int incin_colsum_accum(const void* dy, float* dbias, long long rows, int N, long long ld, void* stream);
+/* out[0] += sum(x^2); out[1] = 1.0 if any element is NaN/Inf (device-side gradient check, no D2H of tensors) */
+int incin_sumsq_nonfinite_f32(const float* x, long long n, float* out, void* stream);
+int incin_fill_f32(float* x, float value, long long n, void* stream);
+int incin_cast_f32_to_bf16(const float* x, void* y, long long n, void* stream);
+int incin_cast_bf16_to_f32(const void* x, float* y, long long n, void* stream);
+/* y = act'(pre) * dy,  y = act(x) elementwise (bf16) for modules that do not fuse into a GEMM */
+int incin_act_fwd(const void* x, void* y, long long n, int act, void* stream);
+int incin_act_bwd(const void* dy, const void* pre, void* dx, long long n, int act, void* stream);
+/* SwiGLU: y = silu(gate) * up, inputs are the two halves [rows][2F] -> [rows][F] */
+int incin_swiglu_fwd(const void* gate_up, void* y, long long rows, int F, void* stream);
+int incin_swiglu_bwd(const void* dy, const void* gate_up, void* dgate_up, long long rows, int F, void* stream);
+/* rotary embedding in place on [B][T][H][D] slices with row stride `ld`; inverse=1 applies the transpose (backward) */
+int incin_rope(void* x, long long B, int T, int H, int D, long long stride_b, long long stride_t, long long stride_h,
+               float theta, int inverse, void* stream);
+
+/* ---- optimiser --------------------------------------------------------------------------------- */
+/* hyper (device, 8 floats): {lr, beta1, beta2, eps, weight_decay, step, grad_scale, unused}.
+ * Bias-corrected, decoupled weight decay on the first n_decay elements only.
+ * Updates fp32 master weights and moments and writes the bf16 shadow copy used by the forward pass. */
+int incin_adamw_flat(float* master, float* m, float* v, const float* grad, void* shadow_bf16, long long n,
+                     long long n_decay, const float* hyper, void* stream);
+/* hyper: {lr, momentum, unused, unused, weight_decay, ...}; mom may be NULL */
+int incin_sgd_flat(float* master, float* mom, const float* grad, void* shadow_bf16, long long n, long long n_decay,
+                   const float* hyper, void* stream);
+
+/* ---- device RNG (Philox4x32-10) ---------------------------------------------------------------- */
+int incin_philox_uniform_f32(float* out, long long n, uint64_t seed, uint64_t offset, void* stream);
+int incin_philox_normal_f32(float* out, long long n, uint64_t seed, uint64_t offset, float mean, float std,
+                            void* stream);
+int incin_philox_normal_bf16(void* out, long long n, uint64_t seed, uint64_t offset, float mean, float std,
+                             void* stream);
+/* y = x * mask / (1-p), mask regenerated from (seed, offset) in the backward pass, never stored */
+int incin_dropout_bf16(const void* x, void* y, long long n, float p, uint64_t seed, uint64_t offset, void* stream);
+
+/* ---- library info ------------------------------------------------------------------------------ */
+const char* incin_sm100_version(void);
+int incin_sm100_num_sms(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INCIN_B200_H */

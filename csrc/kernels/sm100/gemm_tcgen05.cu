@@ -1,0 +1,536 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a.
+//
+//   C[b][m][n] = epilogue( alpha * sum_k A[b][m][k] * B[b][n][k] )
+//
+// Data path: TMA (cp.async.bulk.tensor, this GPU's memory only, no cluster
+// multicast) -> 128B-swizzled shared memory ring -> tcgen05.mma issued by one
+// thread -> fp32 accumulators in tensor memory (double buffered, so the
+// epilogue of tile i overlaps the main loop of tile i+1) -> tcgen05.ld ->
+// fused epilogue (bias, GELU / SiLU, GELU-gradient mask, residual, bf16 or fp32
+// store, fp32 atomic accumulate for split-K and gradient accumulation).
+//
+// Both operands may be K-major ("row = m, contiguous along k") or MN-major
+// ("row = k, contiguous along m"), which covers the forward Linear
+// (x @ W^T), the data gradient (dY @ W) and the weight gradient (dY^T @ X)
+// without any transpose kernel.  Operands are addressed through 4-D tensor
+// maps {inner, rows, batch_lo, batch_hi} so strided batches (attention heads
+// inside a fused QKV buffer) need no copies either.
+//
+// Replaces the reference's f32 SIMT 128x128x8 SGEMM
+// (crates/incin-backends/src/cuda/ops/kernels/matmul.cu:1-94), which is 2-D
+// only and has no fused epilogue.
+#include "ptx.cuh"
+#include "../../include/incin_b200.h"
+
+#include <mutex>
+#include <unordered_map>
+#include <string>
+#include <cstring>
+#include <cstdio>
+
+namespace incin {
+
+constexpr int BM = 128;
+constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;  // warp0: TMA, warp1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int ACC_STRIDE = (BN <= 64) ? 64 : (BN <= 128 ? 128 : 256);
+  static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct GemmKernelParams {
+  int M, N, K;
+  int batch_lo, batch_hi;
+  int tiles_m, tiles_n, splits, total_units;
+  void* C;
+  long long ldc, c_stride_lo, c_stride_hi;
+  int out_fp32, accumulate;
+  float alpha;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  int act;
+  __nv_bfloat16* aux;
+  int* status;
+};
+
+struct Unit {
+  int m_blk, n_blk, b_lo, b_hi, kb0, kb1;
+};
+
+__device__ __forceinline__ Unit decode_unit(const GemmKernelParams& p, int u) {
+  Unit w;
+  const int split = u % p.splits;
+  int t = u / p.splits;
+  w.m_blk = t % p.tiles_m;
+  t /= p.tiles_m;
+  w.n_blk = t % p.tiles_n;
+  const int b = t / p.tiles_n;
+  w.b_lo = b % p.batch_lo;
+  w.b_hi = b / p.batch_lo;
+  const int kb_total = (p.K + BK - 1) / BK;
+  w.kb0 = static_cast<int>((static_cast<long long>(split) * kb_total) / p.splits);
+  w.kb1 = static_cast<int>((static_cast<long long>(split + 1) * kb_total) / p.splits);
+  return w;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmKernelParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full_bar = bars;                      // [STAGES]
+  uint64_t* empty_bar = bars + Cfg::STAGES;       // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * Cfg::STAGES;   // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;           // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_init_fence();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+        const Unit w = decode_unit(p, u);
+        const int m0 = w.m_blk * BM, n0 = w.n_blk * BN;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_4d(sa, &tmA, &full_bar[stage], k0, m0, w.b_lo, w.b_hi);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_4d(sa + c * 8192, &tmA, &full_bar[stage], m0 + c * 64, k0, w.b_lo, w.b_hi);
+          }
+          if (!B_MN) {
+            tma_load_4d(sb, &tmB, &full_bar[stage], k0, n0, w.b_lo, w.b_hi);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_4d(sb + c * 8192, &tmB, &full_bar[stage], n0 + c * 64, k0, w.b_lo, w.b_hi);
+          }
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x, ++iter) {
+        const Unit w = decode_unit(p, u);
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (iter >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kStatusTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+          const uint64_t adesc = A_MN ? make_smem_desc(sa, 8192, 1024) : make_smem_desc(sa, 16, 1024);
+          const uint64_t bdesc = B_MN ? make_smem_desc(sb, 8192, 1024) : make_smem_desc(sb, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: 16 bf16 = 32 B further along the swizzle row.
+            // MN-major: 16 K-rows of 128 B further.
+            const uint64_t a_adv = A_MN ? (uint64_t)(k * 2048 >> 4) : (uint64_t)(k * 32 >> 4);
+            const uint64_t b_adv = B_MN ? (uint64_t)(k * 2048 >> 4) : (uint64_t)(k * 32 >> 4);
+            umma_f16_ss(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue (4 warps = 128 TMEM lanes)
+    const int quarter = warp & 3;  // TMEM lanes a warp may touch: 32 * (warp % 4)
+    const int row_in_tile = quarter * 32 + lane;
+    int iter = 0;
+    for (int u = blockIdx.x; u < p.total_units; u += gridDim.x, ++iter) {
+      const Unit w = decode_unit(p, u);
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (iter >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, kStatusTimeoutTmemFull)) break;
+      tc_fence_after();
+      const int m = w.m_blk * BM + row_in_tile;
+      const int n0 = w.n_blk * BN;
+      const bool row_ok = m < p.M;
+      const long long cbase = (long long)w.b_lo * p.c_stride_lo + (long long)w.b_hi * p.c_stride_hi +
+                              (long long)m * p.ldc;
+      const bool vec_ok = (p.ldc % 8 == 0) && (p.c_stride_lo % 8 == 0) && (p.c_stride_hi % 8 == 0);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * Cfg::ACC_STRIDE + c * 32, r);
+        tmem_ld_wait();
+        const int nc = n0 + c * 32;
+        if (row_ok && nc < p.N) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        const bool full = (nc + 32 <= p.N) && vec_ok;
+        if (p.bias) {
+          if (full) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 bb = *reinterpret_cast<const uint4*>(p.bias + nc + q * 8);
+              const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = unpack_bf16x2(bw[e]);
+                v[q * 8 + e * 2] += f.x;
+                v[q * 8 + e * 2 + 1] += f.y;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nc + j < p.N) v[j] += __bfloat162float(p.bias[nc + j]);
+          }
+        }
+        if (p.act == INCIN_ACT_GELU || p.act == INCIN_ACT_SILU) {
+          if (p.aux) {  // keep the pre-activation for the backward pass
+            __nv_bfloat16* ax = p.aux + cbase + nc;
+            if (full) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+                o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+                o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+                o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+                *reinterpret_cast<uint4*>(ax + q * 8) = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nc + j < p.N) ax[j] = __float2bfloat16(v[j]);
+            }
+          }
+          if (p.act == INCIN_ACT_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = silu(v[j]);
+          }
+        } else if (p.act == INCIN_ACT_DGELU || p.act == INCIN_ACT_DSILU) {
+          // multiply by act'(pre-activation): fuses the activation backward into the data-gradient GEMM
+          const __nv_bfloat16* ax = p.aux + cbase + nc;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (nc + j < p.N) {
+              const float x = __bfloat162float(ax[j]);
+              v[j] *= (p.act == INCIN_ACT_DGELU) ? gelu_erf_grad(x) : silu_grad(x);
+            }
+          }
+        }
+        if (p.residual) {
+          const __nv_bfloat16* rs = p.residual + cbase + nc;
+          if (full) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 bb = *reinterpret_cast<const uint4*>(rs + q * 8);
+              const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = unpack_bf16x2(bw[e]);
+                v[q * 8 + e * 2] += f.x;
+                v[q * 8 + e * 2 + 1] += f.y;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nc + j < p.N) v[j] += __bfloat162float(rs[j]);
+          }
+        }
+        if (p.out_fp32) {
+          float* out = reinterpret_cast<float*>(p.C) + cbase + nc;
+          if (p.accumulate) {
+            if (full) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + q * 4), "f"(v[q * 4]),
+                             "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
+                             : "memory");
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nc + j < p.N) atomicAdd(out + j, v[j]);
+            }
+          } else {
+            if (full) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(out + q * 4) =
+                    make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nc + j < p.N) out[j] = v[j];
+            }
+          }
+        } else {
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + cbase + nc;
+          if (full) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              *reinterpret_cast<uint4*>(out + q * 8) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nc + j < p.N) out[j] = __float2bfloat16(v[j]);
+          }
+        }
+        }  // row_ok
+        __syncwarp();  // tcgen05.ld is warp-collective: reconverge before the next chunk
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  // common exit: every thread arrives here, also after a timed-out wait
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before the CTA retires
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// Tensor map over a bf16 operand: dims {inner, rows, batch_lo, batch_hi}, strides in elements.
+int make_operand_map(CUtensorMap* out, const void* ptr, long long inner, long long rows, long long ld,
+                     long long batch_lo, long long stride_lo, long long batch_hi, long long stride_hi, int box_inner,
+                     int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return INCIN_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ld % 8) || (batch_lo > 1 && stride_lo % 8) ||
+      (batch_hi > 1 && stride_hi % 8))
+    return INCIN_ERR_ALIGNMENT;
+  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)batch_lo, (cuuint64_t)batch_hi};
+  // strides of dims 1..3 in bytes; a unit batch dimension still needs a legal (multiple of 16) stride
+  cuuint64_t strides[3] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch_lo > 1 ? stride_lo : ld * rows) * 2,
+                           (cuuint64_t)(batch_hi > 1 ? stride_hi : ld * rows) * 2};
+  cuuint32_t box[4] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? INCIN_OK : INCIN_ERR_TENSOR_MAP;
+}
+
+static int g_num_sms = 0;
+int device_sm_count() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmKernelParams& p, int max_ctas,
+                      cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+      return INCIN_ERR_LAUNCH;
+    attr_set = true;
+  }
+  int grid = p.total_units < max_ctas ? p.total_units : max_ctas;
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
+}
+
+template <int BN>
+static int launch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb,
+                        const GemmKernelParams& p, int max_ctas, cudaStream_t s) {
+  if (!a_mn && !b_mn) return launch_cfg<BN, false, false>(ta, tb, p, max_ctas, s);
+  if (!a_mn && b_mn) return launch_cfg<BN, false, true>(ta, tb, p, max_ctas, s);
+  if (a_mn && !b_mn) return launch_cfg<BN, true, false>(ta, tb, p, max_ctas, s);
+  return launch_cfg<BN, true, true>(ta, tb, p, max_ctas, s);
+}
+
+// Pick the N tile that minimises (waves x per-tile cost) on this GPU.
+static int choose_bn(long long M, long long N, long long batch, int splits, int sms) {
+  const int cands[4] = {256, 192, 128, 64};
+  int best = 128;
+  double best_cost = 1e30;
+  for (int bn : cands) {
+    const long long tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * batch * splits;
+    const long long waves = (tiles + sms - 1) / sms;
+    // per-tile cost ~ MMA time (proportional to bn) + fixed pipeline fill/drain
+    const double cost = static_cast<double>(waves) * (bn + 24.0);
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+}  // namespace incin
+
+using namespace incin;
+
+extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!d || !d->A || !d->B || !d->C || d->M <= 0 || d->N <= 0 || d->K <= 0) return INCIN_ERR_ARGUMENT;
+  const int blo = d->batch_lo > 0 ? d->batch_lo : 1;
+  const int bhi = d->batch_hi > 0 ? d->batch_hi : 1;
+  const int sms = d->max_ctas > 0 ? d->max_ctas : device_sm_count();
+  int splits = d->splits > 0 ? d->splits : 1;
+  const int kb_total = (d->K + BK - 1) / BK;
+  if (splits > kb_total) splits = kb_total;
+  if (splits > 1 && !(d->out_fp32 && d->accumulate)) return INCIN_ERR_ARGUMENT;
+  if (splits > 1 && (d->bias || d->residual || d->act != INCIN_ACT_NONE)) return INCIN_ERR_ARGUMENT;
+  if ((d->act == INCIN_ACT_DGELU || d->act == INCIN_ACT_DSILU) && !d->aux) return INCIN_ERR_ARGUMENT;
+  int bn = d->tile_n;
+  if (bn != 64 && bn != 128 && bn != 192 && bn != 256) bn = choose_bn(d->M, d->N, (long long)blo * bhi, splits, sms);
+
+  CUtensorMap ta, tb;
+  int rc;
+  if (!d->a_mn_major)
+    rc = make_operand_map(&ta, d->A, d->K, d->M, d->lda, blo, d->a_stride_lo, bhi, d->a_stride_hi, BK, BM);
+  else
+    rc = make_operand_map(&ta, d->A, d->M, d->K, d->lda, blo, d->a_stride_lo, bhi, d->a_stride_hi, 64, BK);
+  if (rc != INCIN_OK) return rc;
+  if (!d->b_mn_major)
+    rc = make_operand_map(&tb, d->B, d->K, d->N, d->ldb, blo, d->b_stride_lo, bhi, d->b_stride_hi, BK, bn);
+  else
+    rc = make_operand_map(&tb, d->B, d->N, d->K, d->ldb, blo, d->b_stride_lo, bhi, d->b_stride_hi, 64, BK);
+  if (rc != INCIN_OK) return rc;
+
+  GemmKernelParams p;
+  p.M = d->M;
+  p.N = d->N;
+  p.K = d->K;
+  p.batch_lo = blo;
+  p.batch_hi = bhi;
+  p.tiles_m = (d->M + BM - 1) / BM;
+  p.tiles_n = (d->N + bn - 1) / bn;
+  p.splits = splits;
+  const long long units = (long long)p.tiles_m * p.tiles_n * blo * bhi * splits;
+  if (units > 0x7fffffffLL) return INCIN_ERR_ARGUMENT;
+  p.total_units = (int)units;
+  p.C = d->C;
+  p.ldc = d->ldc;
+  p.c_stride_lo = d->c_stride_lo;
+  p.c_stride_hi = d->c_stride_hi;
+  p.out_fp32 = d->out_fp32;
+  p.accumulate = d->accumulate;
+  p.alpha = d->alpha;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(d->bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(d->residual);
+  p.act = d->act;
+  p.aux = reinterpret_cast<__nv_bfloat16*>(d->aux);
+  p.status = reinterpret_cast<int*>(d->status);
+
+  const bool amn = d->a_mn_major != 0, bmn = d->b_mn_major != 0;
+  int rc2;
+  if (bn == 64) rc2 = incin::launch_major<64>(amn, bmn, ta, tb, p, sms, stream);
+  else if (bn == 128) rc2 = incin::launch_major<128>(amn, bmn, ta, tb, p, sms, stream);
+  else if (bn == 192) rc2 = incin::launch_major<192>(amn, bmn, ta, tb, p, sms, stream);
+  else rc2 = incin::launch_major<256>(amn, bmn, ta, tb, p, sms, stream);
+  return rc2;
+}

@@ -1,0 +1,86 @@
+"""The training-step engine: zero-grad -> forward -> backward -> (gradient reduction) -> optimiser,
+eager for the first calls, then one CUDA-graph replay per step.
+
+Everything in a step is enqueued on CUDA streams by hand-written kernels that
+take no host-side decisions, so after two eager steps the whole step is
+captured once and replayed; hyper-parameters that change per step (lr, step
+count) live in device memory the kernels read.  On the CPU backend the same
+object runs the PyTorch-CPU twins of the ops eagerly.
+
+The reference's single-device loop is ``Trainer::fit``
+(crates/incin/src/train.rs:576-617): per batch ``loss -> backward ->
+optimizer.step -> loss.to_scalar()``.
+"""
+from __future__ import annotations
+
+from typing import Callable, Sequence
+
+import torch
+
+from .optim.flat import ParamStore, _FlatOptimizer
+
+
+class TrainStep:
+    def __init__(self, model: torch.nn.Module, optimizer: _FlatOptimizer, *,
+                 loss_fn: Callable[..., torch.Tensor] | None = None, use_graph: bool = True,
+                 eager_steps: int = 2, reducer=None):
+        self.model = model
+        self.opt = optimizer
+        self.store: ParamStore = optimizer.store
+        self.loss_fn = loss_fn or (lambda m, *a: m(*a))
+        self.device = self.store.device
+        self.use_graph = bool(use_graph) and self.device.type == "cuda"
+        self.eager_steps = eager_steps
+        self.reducer = reducer  # data-parallel gradient reducer (fused reduce + optimiser), or None
+        self.calls = 0
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.static_inputs: list[torch.Tensor] | None = None
+        self.static_loss: torch.Tensor | None = None
+        self.launches_per_step: int | None = None
+
+    # one full step, enqueued on the current stream
+    def _enqueue(self, inputs: Sequence[torch.Tensor]) -> torch.Tensor:
+        self.store.zero_grad()
+        if self.reducer is not None:
+            self.reducer.begin_step()
+        loss = self.loss_fn(self.model, *inputs)
+        loss.backward()
+        if self.device.type != "cuda":
+            self.store.collect_autograd_grads()
+        if self.reducer is not None:
+            self.reducer.finish_step(self.opt)  # reduce-scatter + optimiser + all-gather, fused
+        else:
+            self.opt.launch()
+        return loss.detach()
+
+    def _capture(self, inputs: Sequence[torch.Tensor]) -> None:
+        self.static_inputs = [t.clone() for t in inputs]
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                self.static_loss = self._enqueue(self.static_inputs)
+        torch.cuda.current_stream().wait_stream(side)
+        self.graph = g
+
+    def __call__(self, *inputs: torch.Tensor) -> torch.Tensor:
+        """Run one optimisation step; returns the (device-resident) loss of this step."""
+        self.calls += 1
+        self.opt.prepare_step()
+        if not self.use_graph or self.calls <= self.eager_steps:
+            return self._enqueue(inputs)
+        if self.graph is None:
+            try:
+                self._capture(inputs)
+            except Exception:
+                # capture is an optimisation; any failure leaves the eager path in charge
+                self.use_graph = False
+                self.graph = None
+                torch.cuda.synchronize()
+                return self._enqueue(inputs)
+        for dst, src in zip(self.static_inputs, inputs):
+            if dst.data_ptr() != src.data_ptr():
+                dst.copy_(src, non_blocking=True)
+        self.graph.replay()
+        return self.static_loss

@@ -1,0 +1,150 @@
+"""Tensor-level front end of the tcgen05 GEMM (``incin_gemm_bf16``).
+
+The kernel computes ``C[b] = epi(alpha * A[b] @ B[b]^T)`` with A logically
+``[M, K]`` and B logically ``[N, K]``; either operand may instead be stored
+transposed ("MN-major"), which is how the three GEMMs of a Linear layer map
+onto one kernel without transposes:
+
+=========  =====================  ==========  ==========
+product    math                   A           B
+=========  =====================  ==========  ==========
+forward    y  = x  @ W^T          x  K-major  W  K-major
+dgrad      dx = dy @ W            dy K-major  W  MN-major
+wgrad      dW = dy^T @ x          dy MN-major x  MN-major
+=========  =====================  ==========  ==========
+
+Counterpart of ``Tensor::matmul`` / ``MatMulSpec`` in the reference
+(crates/incin-core/src/tensor/matmul.rs:349-444, exec/spec.rs:226).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native as nat
+
+_status: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word that kernels set when a bounded wait gave up."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronising check of the device status word; raises if any kernel timed out."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    code = int(status_word(device).item())
+    if code != 0:
+        status_word(device).zero_()
+        raise nat.NativeError(f"a device-side wait timed out (status {code}); results of this step are invalid")
+
+
+def auto_splits(M: int, N: int, K: int, batch: int = 1, sms: int = 148) -> int:
+    """Split-K factor for skinny outputs (weight gradients): fill the SMs, keep >= 4 k-blocks per split."""
+    tiles = ((M + 127) // 128) * ((N + 127) // 128) * batch
+    if tiles >= (sms * 3) // 4:
+        return 1
+    kb = (K + 63) // 64
+    want = (sms + tiles - 1) // tiles
+    return max(1, min(want, kb // 4 if kb >= 8 else 1))
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int, K: int, lda: int, ldb: int,
+         ldc: int, a_mn: bool = False, b_mn: bool = False, batch: tuple[int, int] = (1, 1),
+         a_strides: tuple[int, int] = (0, 0), b_strides: tuple[int, int] = (0, 0),
+         c_strides: tuple[int, int] = (0, 0), accumulate: bool = False, alpha: float = 1.0,
+         bias: torch.Tensor | None = None, residual: torch.Tensor | None = None, act: int = nat.ACT_NONE,
+         aux: torch.Tensor | None = None, splits: int = 1, tile_n: int = 0, max_ctas: int = 0,
+         a_offset: int = 0, b_offset: int = 0, c_offset: int = 0) -> torch.Tensor:
+    """Launch one (batched) GEMM on the current stream.  Offsets/strides are in elements."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "operands must be bf16"
+    assert out.dtype in (torch.bfloat16, torch.float32)
+    d = nat.GemmDesc()
+    d.A = a.data_ptr() + 2 * a_offset
+    d.B = b.data_ptr() + 2 * b_offset
+    d.C = out.data_ptr() + out.element_size() * c_offset
+    d.M, d.N, d.K = M, N, K
+    d.lda, d.ldb, d.ldc = lda, ldb, ldc
+    d.a_mn_major, d.b_mn_major = int(a_mn), int(b_mn)
+    d.batch_lo, d.batch_hi = batch
+    d.a_stride_lo, d.a_stride_hi = a_strides
+    d.b_stride_lo, d.b_stride_hi = b_strides
+    d.c_stride_lo, d.c_stride_hi = c_strides
+    d.out_fp32 = int(out.dtype == torch.float32)
+    d.accumulate = int(accumulate)
+    d.alpha = alpha
+    d.bias = nat.ptr(bias)
+    d.residual = nat.ptr(residual)
+    d.act = act
+    d.aux = nat.ptr(aux)
+    d.splits = splits
+    d.tile_n = tile_n
+    d.max_ctas = max_ctas
+    d.status = status_word(a.device).data_ptr()
+    nat.check(nat.cuda().incin_gemm_bf16(ctypes.byref(d), nat.stream_ptr()), "gemm")
+    return out
+
+
+def _rows(x: torch.Tensor) -> int:
+    return x.numel() // x.shape[-1]
+
+
+def mm_nt(x: torch.Tensor, w: torch.Tensor, *, bias=None, residual=None, act=nat.ACT_NONE, aux=None,
+          out: torch.Tensor | None = None, alpha: float = 1.0, max_ctas: int = 0) -> torch.Tensor:
+    """y[..., N] = x[..., K] @ w[N, K]^T with the fused epilogue (forward of Linear)."""
+    assert x.is_contiguous() and w.is_contiguous()
+    M, K = _rows(x), x.shape[-1]
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(*x.shape[:-1], N, dtype=torch.bfloat16, device=x.device)
+    return gemm(x, w, out, M=M, N=N, K=K, lda=K, ldb=K, ldc=N, bias=bias, residual=residual, act=act, aux=aux,
+                alpha=alpha, max_ctas=max_ctas)
+
+
+def mm_nn(dy: torch.Tensor, w: torch.Tensor, *, act=nat.ACT_NONE, aux=None, out: torch.Tensor | None = None,
+          max_ctas: int = 0) -> torch.Tensor:
+    """dx[..., K] = dy[..., N] @ w[N, K] (data gradient of Linear); optional act'(aux) mask."""
+    assert dy.is_contiguous() and w.is_contiguous()
+    M, N = _rows(dy), dy.shape[-1]
+    K = w.shape[1]
+    if out is None:
+        out = torch.empty(*dy.shape[:-1], K, dtype=torch.bfloat16, device=dy.device)
+    # reduction runs over N: A = dy (k-contiguous), B[K, N] is w stored [N(k)][K(n)] -> MN-major
+    return gemm(dy, w, out, M=M, N=K, K=N, lda=N, ldb=K, ldc=K, b_mn=True, act=act, aux=aux, max_ctas=max_ctas)
+
+
+def mm_tn_accum(dy: torch.Tensor, x: torch.Tensor, grad: torch.Tensor, *, splits: int | None = None,
+                max_ctas: int = 0) -> torch.Tensor:
+    """grad[N, K] (fp32) += dy[M, N]^T @ x[M, K] (weight gradient, split-K with fp32 atomics)."""
+    assert dy.is_contiguous() and x.is_contiguous() and grad.dtype == torch.float32
+    M, N = _rows(dy), dy.shape[-1]
+    K = x.shape[-1]
+    if splits is None:
+        splits = auto_splits(N, K, M)
+    return gemm(dy, x, grad, M=N, N=K, K=M, lda=N, ldb=K, ldc=K, a_mn=True, b_mn=True, accumulate=True,
+                splits=splits, max_ctas=max_ctas)
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """General ``a @ b`` for 2-D / batched 3-D bf16 tensors (b is [.., K, N], read MN-major)."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    a = a.contiguous()
+    b = b.contiguous()
+    if a.dim() == 2 and b.dim() == 2:
+        M, K = a.shape
+        N = b.shape[1]
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+        return gemm(a, b, out, M=M, N=N, K=K, lda=K, ldb=N, ldc=N, b_mn=True)
+    assert a.dim() == 3 and b.dim() == 3 and a.shape[0] == b.shape[0]
+    Bt, M, K = a.shape
+    N = b.shape[2]
+    out = torch.empty(Bt, M, N, dtype=torch.bfloat16, device=a.device)
+    return gemm(a, b, out, M=M, N=N, K=K, lda=K, ldb=N, ldc=N, b_mn=True, batch=(Bt, 1),
+                a_strides=(M * K, 0), b_strides=(K * N, 0), c_strides=(M * N, 0))
