@@ -148,6 +148,35 @@ int incin_philox_normal_bf16(void* out, long long n, uint64_t seed, uint64_t off
 /* y = x * mask / (1-p), mask regenerated from (seed, offset) in the backward pass, never stored */
 int incin_dropout_bf16(const void* x, void* y, long long n, float p, uint64_t seed, uint64_t offset, void* stream);
 
+/* ---- flash attention (causal, online softmax, GQA) ------------------------------------------------ */
+/* q/o/do/dq: [B, T, Hq, D]; k/v/dk/dv: [B, T, Hkv, D]; every tensor has its own (b, t, h) strides in elements
+ * so packed QKV buffers need no copies.  D is 64 or 128.  lse: fp32 [B, Hq, T] in the log2 domain
+ * (max*scale*log2e + log2(sum)).  The backward needs delta (fp32 [B, Hq, T]) and dq_accum (fp32 [B, T, Hq, D])
+ * as caller-provided scratch; it zeroes dq_accum itself. */
+typedef struct incin_attn_desc {
+  const void *q, *k, *v;
+  void* o;
+  float* lse;
+  int B, T, Hq, Hkv, D;
+  float scale;
+  long long q_stride_b, q_stride_t, q_stride_h;
+  long long k_stride_b, k_stride_t, k_stride_h;
+  long long v_stride_b, v_stride_t, v_stride_h;
+  long long o_stride_b, o_stride_t, o_stride_h;
+  /* backward only */
+  const void* d_o;
+  long long do_stride_b, do_stride_t, do_stride_h;
+  void *dq, *dk, *dv;
+  long long dq_stride_b, dq_stride_t, dq_stride_h;
+  long long dk_stride_b, dk_stride_t, dk_stride_h;
+  long long dv_stride_b, dv_stride_t, dv_stride_h;
+  float* delta;
+  float* dq_accum;
+  void* status;
+} incin_attn_desc;
+int incin_flash_attn_fwd(const incin_attn_desc* desc, void* stream);
+int incin_flash_attn_bwd(const incin_attn_desc* desc, void* stream);
+
 /* ---- library info ------------------------------------------------------------------------------ */
 const char* incin_sm100_version(void);
 int incin_sm100_num_sms(void);

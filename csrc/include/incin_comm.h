@@ -1,0 +1,47 @@
+/* C ABI of the communication layer: peer-mapped ("symmetric") buffers and the fused
+ * compute+collective kernels that run over them.  One process per GPU; buffers are exchanged as
+ * CUDA IPC handles over any side channel (torch.distributed object collectives or the incin
+ * rendezvous all-gather).  Kernels address peers with plain loads and stores. */
+#ifndef INCIN_COMM_H
+#define INCIN_COMM_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define INCIN_MAX_PEERS 8
+#define INCIN_DP_MAX_SLOTS 64
+#define INCIN_IPC_HANDLE_BYTES 64
+
+/* cudaMalloc'ed, zero-filled buffer plus its IPC handle (these two allocate; call them at set-up). */
+int incin_symm_alloc(long long bytes, void** ptr_out, uint8_t handle_out[INCIN_IPC_HANDLE_BYTES]);
+int incin_symm_open(const uint8_t handle[INCIN_IPC_HANDLE_BYTES], void** ptr_out);
+int incin_symm_close(void* peer_ptr);
+int incin_symm_free(void* ptr);
+/* 1 if `dev` can map `peer`'s memory (NVLink/NVSwitch or PCIe P2P) */
+int incin_can_access_peer(int dev, int peer);
+
+typedef struct incin_dp_desc {
+  void* grads[INCIN_MAX_PEERS];   /* fp32 flat gradient buffer of every rank (own entry = local pointer) */
+  void* shadows[INCIN_MAX_PEERS]; /* bf16 flat parameter buffer of every rank */
+  void* pads[INCIN_MAX_PEERS];    /* signal pad of every rank, incin_dp_pad_bytes() each, zero-initialised */
+  void *master, *m, *v;           /* local fp32 master weights and Adam moments (full length) */
+  const void* hyper;              /* device, 8 floats: lr, beta1, beta2, eps, weight_decay, step, grad_scale, - */
+  long long lo, hi, n_decay;      /* bucket [lo, hi) in elements, both multiples of 8 */
+  int world, rank;
+  int slot;                       /* signal slot of this bucket (< INCIN_DP_MAX_SLOTS), one per bucket */
+  int ctas;                       /* grid size; small grids leave the SMs to overlapping compute */
+  void* status;                   /* optional int32 device word set when a peer wait timed out */
+} incin_dp_desc;
+
+/* reduce-scatter(mean) of the bucket over peer memory + AdamW on the owned slice + all-gather of the new
+ * bf16 weights, in one kernel.  Every rank must launch it for the same buckets in the same order. */
+int incin_dp_reduce_adamw(const incin_dp_desc* desc, void* stream);
+int incin_dp_pad_bytes(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,427 @@
+// Causal flash attention backward for sm_100a (dQ, dK, dV), GQA-aware.
+//
+// One CTA owns a 128-row K/V tile of one KV head and walks the query tiles at or below the diagonal
+// (for every query head of the group).  Per query tile five tcgen05 GEMMs run, all with M = 128 and
+// accumulators in tensor memory:
+//     S^T  = K Q^T          dP^T = V dO^T                      (scores and their gradient, transposed)
+//     dV  += P^T dO         dK  += dS^T Q                      (accumulate over query tiles in TMEM)
+//     dQ_i = dS K                                             (per-tile partial, reduced with fp32 atomics)
+// Computing the transposed scores puts the KV index in the TMEM lanes, so the 128 softmax threads
+// (one KV row each) produce P^T and dS^T directly in the K-major layout the dV/dK GEMMs consume,
+// and the same shared-memory tiles are re-read MN-major for dQ: no transposes anywhere.
+// P is recomputed from the forward pass's log-sum-exp (log2 domain); delta = rowsum(O * dO) comes
+// from a small preprocess kernel.  dQ partials are added into an fp32 scratch buffer the caller
+// provides and converted to bf16 by a final strided cast.
+//
+// No counterpart in the reference (no attention backward exists there).
+#include "ptx.cuh"
+#include "../../include/incin_b200.h"
+#include <math_constants.h>
+
+namespace incin {
+
+int make_operand_map(CUtensorMap* out, const void* ptr, long long inner, long long rows, long long ld,
+                     long long batch_lo, long long stride_lo, long long batch_hi, long long stride_hi, int box_inner,
+                     int box_rows);
+
+constexpr int FB_T = 128;  // tile edge for both the KV tile (TMEM lanes) and the query tile
+constexpr int FB_THREADS = 192;
+
+template <int D>
+struct FbCfg {
+  static constexpr int STAGES = (D == 64) ? 2 : 1;
+  static constexpr int TILE_BYTES = FB_T * D * 2;      // K, V, Q, dO tiles
+  static constexpr int PT_BYTES = FB_T * FB_T * 2;     // P^T, dS^T tiles
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = TILE_BYTES;
+  static constexpr int OFF_Q = 2 * TILE_BYTES;
+  static constexpr int OFF_DO = OFF_Q + STAGES * TILE_BYTES;
+  static constexpr int OFF_P = OFF_DO + STAGES * TILE_BYTES;
+  static constexpr int OFF_DS = OFF_P + PT_BYTES;
+  static constexpr int OFF_STAT = OFF_DS + PT_BYTES;   // lse[128], delta[128] per stage
+  static constexpr int OFF_BAR = OFF_STAT + STAGES * 2 * FB_T * 4;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  // TMEM columns: S^T / dQ partial [0,128), dP^T [128,256), dV [256,256+D), dK [256+D, 256+2D)
+  static constexpr int COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 256 + D, TMEM_COLS = 512;
+};
+
+struct FbParams {
+  int T, Hq, Hkv, n_tiles;
+  float scale, scale_log2;
+  const float* lse;    // [B, Hq, T] log2 domain
+  const float* delta;  // [B, Hq, T]
+  float* dq_accum;     // [B, T, Hq, D] fp32, zero-initialised by the caller
+  __nv_bfloat16 *dk, *dv;
+  long long dk_stride_b, dk_stride_t, dk_stride_h, dv_stride_b, dv_stride_t, dv_stride_h;
+  int* status;
+};
+
+template <int D>
+__global__ void __launch_bounds__(FB_THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                 const FbParams p) {
+  using Cfg = FbCfg<D>;
+  constexpr int ST = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + Cfg::OFF_K;
+  uint8_t* sV = smem + Cfg::OFF_V;
+  uint8_t* sQ = smem + Cfg::OFF_Q;
+  uint8_t* sDO = smem + Cfg::OFF_DO;
+  uint8_t* sP = smem + Cfg::OFF_P;
+  uint8_t* sDS = smem + Cfg::OFF_DS;
+  float* sStat = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* kv_full = bars;            // 1
+  uint64_t* q_full = bars + 1;         // [ST]  Q_i and dO_i landed
+  uint64_t* q_empty = bars + 1 + ST;   // [ST]  the three consuming MMAs of that stage finished
+  uint64_t* sdp_full = bars + 1 + 2 * ST;  // S^T and dP^T in TMEM
+  uint64_t* pds_full = sdp_full + 1;       // 128 arrivals: P^T and dS^T in shared memory
+  uint64_t* dq_full = sdp_full + 2;        // dQ partial in TMEM (and dV/dK updated)
+  uint64_t* dq_drained = sdp_full + 3;     // 128 arrivals: dQ partial read out, S^T columns reusable
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sdp_full + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_tile = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int group = p.Hq / p.Hkv;
+  const int kv0 = kv_tile * FB_T;
+  const int first_q_tile = kv_tile;  // causal: query tiles at or below the diagonal
+  const int tiles_per_head = p.n_tiles - first_q_tile;
+  const int n_iters = tiles_per_head * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_drained, 128);
+    *abort_flag = 0;
+    mbar_init_fence();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDO);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_4d(sK + c * (FB_T * 128), &tmK, kv_full, c * 64, kv0, hkv, b);
+        tma_load_4d(sV + c * (FB_T * 128), &tmV, kv_full, c * 64, kv0, hkv, b);
+      }
+      for (int it = 0; it < n_iters; ++it) {
+        const int s = it % ST;
+        const int hq = hkv * group + it / tiles_per_head;
+        const int q0 = (first_q_tile + it % tiles_per_head) * FB_T;
+        if (!mbar_wait(&q_empty[s], ((it / ST) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
+        mbar_expect_tx(&q_full[s], 2 * Cfg::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_4d(sQ + s * Cfg::TILE_BYTES + c * (FB_T * 128), &tmQ, &q_full[s], c * 64, q0, hq, b);
+          tma_load_4d(sDO + s * Cfg::TILE_BYTES + c * (FB_T * 128), &tmDO, &q_full[s], c * 64, q0, hq, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t id_kk = make_idesc_bf16(FB_T, FB_T, false, false);  // S^T, dP^T
+      constexpr uint32_t id_kmn = make_idesc_bf16(FB_T, D, false, true);     // dV, dK
+      constexpr uint32_t id_mnmn = make_idesc_bf16(FB_T, D, true, true);     // dQ
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kStatusTimeoutFull);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), aDS = smem_u32(sDS);
+      for (int it = 0; it < n_iters && ok; ++it) {
+        const int s = it % ST;
+        const uint32_t aQ = smem_u32(sQ + s * Cfg::TILE_BYTES), aDO = smem_u32(sDO + s * Cfg::TILE_BYTES);
+        if (!mbar_wait(&q_full[s], (it / ST) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+        // the S^T columns double as the dQ partial of the previous iteration: wait until it was read out
+        if (!mbar_wait(dq_drained, (it & 1) ^ 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
+          umma_f16_ss(tmem_base + Cfg::COL_ST, make_smem_desc(aK + off, 16, 1024), make_smem_desc(aQ + off, 16, 1024),
+                      id_kk, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
+          umma_f16_ss(tmem_base + Cfg::COL_DPT, make_smem_desc(aV + off, 16, 1024),
+                      make_smem_desc(aDO + off, 16, 1024), id_kk, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_full, it & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < FB_T / 16; ++kk) {  // reduction over the 128 query rows of this tile
+          const uint32_t a_off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;  // P^T / dS^T: K-major, K = q
+          const uint32_t b_off = kk * 2048;                                  // dO / Q: MN-major, 16 q rows per step
+          umma_f16_ss(tmem_base + Cfg::COL_DV, make_smem_desc(aP + a_off, 16, 1024),
+                      make_smem_desc(aDO + b_off, FB_T * 128, 1024), id_kmn, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < FB_T / 16; ++kk) {
+          const uint32_t a_off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
+          const uint32_t b_off = kk * 2048;
+          umma_f16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(aDS + a_off, 16, 1024),
+                      make_smem_desc(aQ + b_off, FB_T * 128, 1024), id_kmn, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < FB_T / 16; ++kk) {  // dQ = dS K: reduction over the 128 kv rows
+          const uint32_t off = kk * 2048;          // both operands MN-major: 16 kv rows per step
+          umma_f16_ss(tmem_base + Cfg::COL_ST, make_smem_desc(aDS + off, FB_T * 128, 1024),
+                      make_smem_desc(aK + off, FB_T * 128, 1024), id_mnmn, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&q_empty[s]);
+        umma_commit(dq_full);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax-gradient threads (one KV row each)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int tid128 = threadIdx.x - 64;
+    const int kv_idx = kv0 + row;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < n_iters; ++it) {
+      const int s = it % ST;
+      const int hq = hkv * group + it / tiles_per_head;
+      const int q0 = (first_q_tile + it % tiles_per_head) * FB_T;
+      float* s_lse = sStat + s * 2 * FB_T;
+      float* s_delta = s_lse + FB_T;
+      {  // stage the per-query statistics of this tile (overlaps the S^T / dP^T MMAs)
+        const int q = q0 + tid128;
+        const long long idx = ((long long)b * p.Hq + hq) * p.T + q;
+        s_lse[tid128] = q < p.T ? p.lse[idx] : CUDART_INF_F;  // +inf -> P = 0 for rows past the end
+        s_delta[tid128] = q < p.T ? p.delta[idx] : 0.f;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      if (!mbar_wait(sdp_full, it & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = (q0 < kv0 + FB_T);  // only the diagonal tile needs the causal test
+      const bool kv_live = kv_idx < p.T;
+#pragma unroll 1
+      for (int c = 0; c < FB_T / 32; ++c) {
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32(tmem_base + Cfg::COL_ST + lane_addr + c * 32, rs);
+        tmem_ld_32x32(tmem_base + Cfg::COL_DPT + lane_addr + c * 32, rd);
+        tmem_ld_wait();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int qi = c * 32 + i + e;
+            const bool live = kv_live && (!diag || (q0 + qi >= kv_idx));
+            const float pr = live ? exp2f(fmaf(__uint_as_float(rs[i + e]), p.scale_log2, -s_lse[qi])) : 0.f;
+            pv[e] = pr;
+            dv[e] = pr * (__uint_as_float(rd[i + e]) - s_delta[qi]) * p.scale;
+          }
+          pp[i >> 1] = pack_bf16x2(pv[0], pv[1]);
+          dd[i >> 1] = pack_bf16x2(dv[0], dv[1]);
+        }
+        uint8_t* prow = sP + (c >> 1) * (FB_T * 128) + row * 128;
+        uint8_t* drow = sDS + (c >> 1) * (FB_T * 128) + row * 128;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int unit = ((c & 1) * 4 + u) ^ (row & 7);
+          *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pp[u * 4], pp[u * 4 + 1], pp[u * 4 + 2], pp[u * 4 + 3]);
+          *reinterpret_cast<uint4*>(drow + unit * 16) = make_uint4(dd[u * 4], dd[u * 4 + 1], dd[u * 4 + 2], dd[u * 4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+      // dQ partial: lanes are query rows of this tile
+      if (!mbar_wait(dq_full, it & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+      tc_fence_after();
+      const int q = q0 + row;
+      float* dq_row = p.dq_accum + (((long long)b * p.T + q) * p.Hq + hq) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + Cfg::COL_ST + lane_addr + c * 32, r);
+        tmem_ld_wait();
+        if (q < p.T) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + u * 4),
+                         "f"(__uint_as_float(r[u * 4])), "f"(__uint_as_float(r[u * 4 + 1])),
+                         "f"(__uint_as_float(r[u * 4 + 2])), "f"(__uint_as_float(r[u * 4 + 3]))
+                         : "memory");
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      mbar_arrive(dq_drained);
+    }
+    // final: dK and dV of this KV tile (dq_full of the last iteration implies both are complete)
+    if (ok && n_iters > 0) {
+      tc_fence_after();
+      __nv_bfloat16* dk_row = p.dk + (long long)b * p.dk_stride_b + (long long)kv_idx * p.dk_stride_t +
+                              (long long)hkv * p.dk_stride_h;
+      __nv_bfloat16* dv_row = p.dv + (long long)b * p.dv_stride_b + (long long)kv_idx * p.dv_stride_t +
+                              (long long)hkv * p.dv_stride_h;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t rk[32], rv[32];
+        tmem_ld_32x32(tmem_base + Cfg::COL_DK + lane_addr + c * 32, rk);
+        tmem_ld_32x32(tmem_base + Cfg::COL_DV + lane_addr + c * 32, rv);
+        tmem_ld_wait();
+        if (kv_idx < p.T) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 a, bb;
+            a.x = pack_bf16x2(__uint_as_float(rk[u * 8 + 0]), __uint_as_float(rk[u * 8 + 1]));
+            a.y = pack_bf16x2(__uint_as_float(rk[u * 8 + 2]), __uint_as_float(rk[u * 8 + 3]));
+            a.z = pack_bf16x2(__uint_as_float(rk[u * 8 + 4]), __uint_as_float(rk[u * 8 + 5]));
+            a.w = pack_bf16x2(__uint_as_float(rk[u * 8 + 6]), __uint_as_float(rk[u * 8 + 7]));
+            bb.x = pack_bf16x2(__uint_as_float(rv[u * 8 + 0]), __uint_as_float(rv[u * 8 + 1]));
+            bb.y = pack_bf16x2(__uint_as_float(rv[u * 8 + 2]), __uint_as_float(rv[u * 8 + 3]));
+            bb.z = pack_bf16x2(__uint_as_float(rv[u * 8 + 4]), __uint_as_float(rv[u * 8 + 5]));
+            bb.w = pack_bf16x2(__uint_as_float(rv[u * 8 + 6]), __uint_as_float(rv[u * 8 + 7]));
+            *reinterpret_cast<uint4*>(dk_row + c * 32 + u * 8) = a;
+            *reinterpret_cast<uint4*>(dv_row + c * 32 + u * 8) = bb;
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// delta[b, h, t] = sum_d O[b,t,h,d] * dO[b,t,h,d]; one warp per (b, t, h)
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                  long long B, int T, int H, int D, long long o_sb, long long o_st, long long o_sh, long long do_sb,
+                  long long do_st, long long do_sh) {
+  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= B * T * H) return;
+  const int h = (int)(w % H);
+  const int t = (int)((w / H) % T);
+  const long long b = w / ((long long)H * T);
+  const __nv_bfloat16* po = o + b * o_sb + (long long)t * o_st + (long long)h * o_sh;
+  const __nv_bfloat16* pd = d_o + b * do_sb + (long long)t * do_st + (long long)h * do_sh;
+  float s = 0.f;
+  for (int d = lane * 2; d < D; d += 64) {
+    const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(po + d));
+    const float2 c = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pd + d));
+    s += a.x * c.x + a.y * c.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) delta[(b * H + h) * T + t] = s;
+}
+
+// dq (bf16, strided) = dq_accum (fp32 [B,T,H,D] contiguous)
+__global__ void attn_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long B, int T,
+                                    int H, int D, long long sb, long long st, long long sh) {
+  const long long n4 = B * T * H * D / 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 v = reinterpret_cast<const float4*>(acc)[i];
+    const long long e = i * 4;
+    const int d = (int)(e % D);
+    const int h = (int)((e / D) % H);
+    const int t = (int)((e / ((long long)D * H)) % T);
+    const long long b = e / ((long long)D * H * T);
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(dq + b * sb + (long long)t * st + (long long)h * sh + d) = o;
+  }
+}
+
+template <int D>
+static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
+  using Cfg = FbCfg<D>;
+  CUtensorMap tq, tk, tv, tdo;
+  int rc = make_operand_map(&tq, d->q, D, d->T, d->q_stride_t, d->Hq, d->q_stride_h, d->B, d->q_stride_b, 64, FB_T);
+  if (rc) return rc;
+  rc = make_operand_map(&tk, d->k, D, d->T, d->k_stride_t, d->Hkv, d->k_stride_h, d->B, d->k_stride_b, 64, FB_T);
+  if (rc) return rc;
+  rc = make_operand_map(&tv, d->v, D, d->T, d->v_stride_t, d->Hkv, d->v_stride_h, d->B, d->v_stride_b, 64, FB_T);
+  if (rc) return rc;
+  rc = make_operand_map(&tdo, d->d_o, D, d->T, d->do_stride_t, d->Hq, d->do_stride_h, d->B, d->do_stride_b, 64, FB_T);
+  if (rc) return rc;
+  auto kern = flash_bwd_kernel<D>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+      return INCIN_ERR_LAUNCH;
+    attr = true;
+  }
+  const long long rows = (long long)d->B * d->T * d->Hq;
+  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
+      (const __nv_bfloat16*)d->o, (const __nv_bfloat16*)d->d_o, d->delta, d->B, d->T, d->Hq, D, d->o_stride_b,
+      d->o_stride_t, d->o_stride_h, d->do_stride_b, d->do_stride_t, d->do_stride_h);
+  if (cudaMemsetAsync(d->dq_accum, 0, sizeof(float) * rows * D, stream) != cudaSuccess) return INCIN_ERR_LAUNCH;
+  FbParams p;
+  p.T = d->T;
+  p.Hq = d->Hq;
+  p.Hkv = d->Hkv;
+  p.n_tiles = (d->T + FB_T - 1) / FB_T;
+  p.scale = d->scale;
+  p.scale_log2 = d->scale * 1.4426950408889634f;
+  p.lse = d->lse;
+  p.delta = d->delta;
+  p.dq_accum = d->dq_accum;
+  p.dk = (__nv_bfloat16*)d->dk;
+  p.dv = (__nv_bfloat16*)d->dv;
+  p.dk_stride_b = d->dk_stride_b;
+  p.dk_stride_t = d->dk_stride_t;
+  p.dk_stride_h = d->dk_stride_h;
+  p.dv_stride_b = d->dv_stride_b;
+  p.dv_stride_t = d->dv_stride_t;
+  p.dv_stride_h = d->dv_stride_h;
+  p.status = (int*)d->status;
+  dim3 grid(p.n_tiles, d->Hkv, d->B);
+  kern<<<grid, FB_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  long long n4 = rows * D / 4;
+  long long blocks = (n4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  attn_dq_cast_kernel<<<(unsigned)blocks, 256, 0, stream>>>(d->dq_accum, (__nv_bfloat16*)d->dq, d->B, d->T, d->Hq, D,
+                                                           d->dq_stride_b, d->dq_stride_t, d->dq_stride_h);
+  return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
+}
+
+}  // namespace incin
+
+extern "C" int incin_flash_attn_bwd(const incin_attn_desc* d, void* stream) {
+  if (!d || !d->q || !d->k || !d->v || !d->o || !d->d_o || !d->lse || !d->delta || !d->dq_accum || !d->dq ||
+      !d->dk || !d->dv || d->B <= 0 || d->T <= 0 || d->Hq <= 0 || d->Hkv <= 0 || d->Hq % d->Hkv != 0)
+    return INCIN_ERR_ARGUMENT;
+  if (d->D == 64) return incin::launch_bwd<64>(d, (cudaStream_t)stream);
+  if (d->D == 128) return incin::launch_bwd<128>(d, (cudaStream_t)stream);
+  return INCIN_ERR_UNSUPPORTED;
+}

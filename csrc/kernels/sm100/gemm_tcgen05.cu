@@ -33,7 +33,7 @@ namespace incin {
 constexpr int BM = 128;
 constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;  // warp0: TMA, warp1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int GEMM_THREADS = 320;  // warp0: TMA, warp1: MMA + TMEM owner, warps 2-9: epilogue (two per TMEM lane quarter)
 constexpr int SMEM_BUDGET = 200 * 1024;
 
 template <int BN>
@@ -107,7 +107,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], 8);
     }
     *abort_flag = 0;
     mbar_init_fence();
@@ -205,8 +205,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else {
-    // ------------------------------------------------------------- epilogue (4 warps = 128 TMEM lanes)
+    // ------------------------------------------------------------- epilogue (8 warps: 4 lane quarters x 2 column halves)
     const int quarter = warp & 3;  // TMEM lanes a warp may touch: 32 * (warp % 4)
+    const int half = (warp - 2) >> 2;
+    constexpr int CHUNKS_PER_HALF = BN / 64;
     const int row_in_tile = quarter * 32 + lane;
     int iter = 0;
     for (int u = blockIdx.x; u < p.total_units; u += gridDim.x, ++iter) {
@@ -222,7 +224,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                               (long long)m * p.ldc;
       const bool vec_ok = (p.ldc % 8 == 0) && (p.c_stride_lo % 8 == 0) && (p.c_stride_hi % 8 == 0);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * CHUNKS_PER_HALF; c < (half + 1) * CHUNKS_PER_HALF; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * Cfg::ACC_STRIDE + c * 32, r);
         tmem_ld_wait();
@@ -280,11 +282,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         } else if (p.act == INCIN_ACT_DGELU || p.act == INCIN_ACT_DSILU) {
           // multiply by act'(pre-activation): fuses the activation backward into the data-gradient GEMM
           const __nv_bfloat16* ax = p.aux + cbase + nc;
+          if (full) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (nc + j < p.N) {
-              const float x = __bfloat162float(ax[j]);
-              v[j] *= (p.act == INCIN_ACT_DGELU) ? gelu_erf_grad(x) : silu_grad(x);
+            for (int q = 0; q < 4; ++q) {
+              const uint4 bb = *reinterpret_cast<const uint4*>(ax + q * 8);
+              const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = unpack_bf16x2(bw[e]);
+                if (p.act == INCIN_ACT_DGELU) {
+                  v[q * 8 + e * 2] *= gelu_erf_grad(f.x);
+                  v[q * 8 + e * 2 + 1] *= gelu_erf_grad(f.y);
+                } else {
+                  v[q * 8 + e * 2] *= silu_grad(f.x);
+                  v[q * 8 + e * 2 + 1] *= silu_grad(f.y);
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (nc + j < p.N) {
+                const float x = __bfloat162float(ax[j]);
+                v[j] *= (p.act == INCIN_ACT_DGELU) ? gelu_erf_grad(x) : silu_grad(x);
+              }
             }
           }
         }
@@ -400,6 +421,13 @@ int make_operand_map(CUtensorMap* out, const void* ptr, long long inner, long lo
                      int box_rows) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return INCIN_ERR_DRIVER;
+  // cuTensorMapEncodeTiled is a driver call and needs a current context on the calling thread.  Autograd
+  // worker threads can reach this point before any runtime call has bound the primary context.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ld % 8) || (batch_lo > 1 && stride_lo % 8) ||
       (batch_hi > 1 && stride_hi % 8))
     return INCIN_ERR_ALIGNMENT;
@@ -459,8 +487,10 @@ static int choose_bn(long long M, long long N, long long batch, int splits, int 
   for (int bn : cands) {
     const long long tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * batch * splits;
     const long long waves = (tiles + sms - 1) / sms;
-    // per-tile cost ~ MMA time (proportional to bn) + fixed pipeline fill/drain
-    const double cost = static_cast<double>(waves) * (bn + 24.0);
+    // per-tile cost: MMA time grows with bn, but narrow tiles re-read the A operand from shared memory
+    // more often per FLOP (128x128 tiles are shared-memory-bandwidth bound near half rate)
+    const double per_tile = bn == 256 ? 256.0 : (bn == 192 ? 205.0 : (bn == 128 ? 160.0 : 110.0));
+    const double cost = static_cast<double>(waves) * (per_tile + 24.0);
     if (cost < best_cost) {
       best_cost = cost;
       best = bn;

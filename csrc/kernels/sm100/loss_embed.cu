@@ -285,6 +285,41 @@ colsum_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ dbias, l
   }
 }
 
+// 16-byte variant: 32 lanes x 8 columns = 256 columns per block, 8 row lanes, needs N % 8 == 0 and ld % 8 == 0
+__global__ void __launch_bounds__(256)
+colsum_vec_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ dbias, long long rows, int N,
+                  long long ld, int chunks) {
+  __shared__ float sh[8][256];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * 256 + tx * 8;
+  const long long rows_per = (rows + chunks - 1) / chunks;
+  const long long r0 = (long long)blockIdx.y * rows_per;
+  const long long r1 = r0 + rows_per < rows ? r0 + rows_per : rows;
+  float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (c0 < N) {
+    for (long long r = r0 + ty; r < r1; r += 8) {
+      const uint4 u = *reinterpret_cast<const uint4*>(dy + r * ld + c0);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack_bf16x2(w[i]);
+        a[2 * i] += f.x;
+        a[2 * i + 1] += f.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sh[ty][tx * 8 + i] = a[i];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sh[k][threadIdx.x];
+    atomicAdd(dbias + c, t);
+  }
+}
+
 }  // namespace incin
 
 using namespace incin;
@@ -349,6 +384,15 @@ extern "C" int incin_causal_softmax_bwd(void* dp, const void* p, long long batch
 
 extern "C" int incin_colsum_accum(const void* dy, float* dbias, long long rows, int N, long long ld, void* stream) {
   if (rows <= 0 || N <= 0) return INCIN_ERR_ARGUMENT;
+  if ((N % 8) == 0 && (ld % 8) == 0 && (reinterpret_cast<uintptr_t>(dy) & 15) == 0) {
+    const int colblocks = (N + 255) / 256;
+    long long chunks = (148 * 4 + colblocks - 1) / colblocks;
+    if (chunks > (rows + 31) / 32) chunks = (rows + 31) / 32;
+    if (chunks < 1) chunks = 1;
+    dim3 grid(colblocks, (unsigned)chunks);
+    colsum_vec_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, dbias, rows, N, ld, (int)chunks);
+    return CHECK_LAUNCH();
+  }
   long long chunks = (rows + 255) / 256;
   if (chunks > 128) chunks = 128;
   dim3 grid((N + 63) / 64, (unsigned)chunks);
