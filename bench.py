@@ -43,7 +43,7 @@ def parse_args():
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--attention", default="auto", choices=["auto", "flash", "composed"])
-    ap.add_argument("--dp", default="auto", choices=["auto", "fused", "nccl"])
+    ap.add_argument("--dp", default="auto", choices=["auto", "fused", "fused-tail", "nccl"])
     return ap.parse_args()
 
 
@@ -159,7 +159,8 @@ def main() -> None:
         opt = AdamW(store, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
         if reducer is not None:
             reducer.attach(store, opt)
-        step = TrainStep(model, opt, use_graph=not args.no_graph, reducer=reducer)
+        use_graph = not args.no_graph and args.dp != "nccl"  # NCCL collectives stay outside graph capture
+        step = TrainStep(model, opt, use_graph=use_graph, reducer=reducer)
 
     # synthetic data: a ring of distinct pinned host batches (token ids uniform in [0, vocab))
     gen = torch.Generator().manual_seed(1234 + rank)

@@ -32,25 +32,44 @@ def flush_l2() -> None:
     global _flush
     if _flush is None:
         _flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
-    _flush.zero_()
+    _flush.zero_()  # writes 256 MB, twice the 126 MB L2
+
+
+def _graph_ms(body, reps: int) -> float:
+    """Device milliseconds of `reps` back-to-back executions of body(), replayed from a CUDA graph so
+    that no host latency (Python, ctypes, tensor-map encoding) sits between the launches."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(reps):
+                body()
+    torch.cuda.current_stream().wait_stream(side)
+    g.replay()
+    torch.cuda.synchronize()
+    best = None
+    for _ in range(3):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        t = a.elapsed_time(b)
+        best = t if best is None else min(best, t)
+    return best
 
 
 def timeit(fn, iters: int = 10, warmup: int = 3) -> float:
-    """Median milliseconds of one call, L2 flushed before each timed call."""
+    """Device milliseconds of one call with a cold L2: ([flush L2; fn] x iters) minus ([flush L2] x iters),
+    both replayed from CUDA graphs and timed with CUDA events."""
+    flush_l2()
     for _ in range(warmup):
         fn()
-    ts = []
-    for _ in range(iters):
-        flush_l2()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        a.record()
-        fn()
-        b.record()
-        torch.cuda.synchronize()
-        ts.append(a.elapsed_time(b))
-    ts.sort()
-    return ts[len(ts) // 2]
+    torch.cuda.synchronize()
+    both = _graph_ms(lambda: (flush_l2(), fn()), iters)
+    only_flush = _graph_ms(flush_l2, iters)
+    return max(both - only_flush, 1e-6) / iters
 
 
 def bench_gemm(args) -> None:

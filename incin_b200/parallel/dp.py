@@ -1,0 +1,184 @@
+"""Data-parallel gradient reduction.
+
+Product path (:class:`FusedReducer`): the flat fp32 gradient buffer and the flat bf16 parameter buffer
+of every rank live in peer-mapped memory; per gradient bucket ONE kernel (``incin_dp_reduce_adamw``)
+does reduce-scatter over P2P loads, AdamW on the owned shard, and all-gather of the new bf16 weights
+over P2P stores.  With ``overlap=True`` buckets are launched on a side stream as soon as the backward
+pass has finished every gradient they contain, with a small grid so the GEMMs keep the SMs.
+
+Baseline path (:class:`NcclReducer`, not the product): ``all_reduce`` of the flat buffer through NCCL,
+then the local flat AdamW kernel.
+
+The reference's DP (crates/incin-core/src/dist/data_parallel.rs:136-245,
+crates/incin-backends/src/dist/nccl.rs:606-632) reduces one parameter tensor per ncclAllReduce(Avg)
+after backward, chained by ``depends_on``, two ranks only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from .. import _native as nat
+from ..ops.gemm import status_word
+from .symm import SymmetricBuffer
+
+MAX_PEERS = 8
+MAX_SLOTS = 64
+
+
+class DpDesc(C.Structure):
+    _fields_ = [("grads", C.c_void_p * MAX_PEERS), ("shadows", C.c_void_p * MAX_PEERS),
+                ("pads", C.c_void_p * MAX_PEERS), ("master", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
+                ("hyper", C.c_void_p), ("lo", C.c_longlong), ("hi", C.c_longlong), ("n_decay", C.c_longlong),
+                ("world", C.c_int), ("rank", C.c_int), ("slot", C.c_int), ("ctas", C.c_int), ("status", C.c_void_p)]
+
+
+nat.register_cuda_signatures({
+    "incin_dp_reduce_adamw": (C.c_int, [C.POINTER(DpDesc), C.c_void_p]),
+    "incin_dp_pad_bytes": (C.c_int, []),
+})
+
+
+class NcclReducer:
+    """Baseline: NCCL all-reduce of the flat gradient buffer, then the local optimiser kernel."""
+
+    kind = "nccl-allreduce+local-adamw (baseline)"
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+
+    def allocator(self, n, dtype, device):
+        return torch.zeros(n, dtype=dtype, device=device)
+
+    def attach(self, store, opt) -> None:
+        self.store = store
+        opt.grad_scale = 1.0 / self.world
+
+    def begin_step(self) -> None:
+        pass
+
+    def finish_step(self, opt) -> None:
+        dist.all_reduce(self.store.grad, group=self.group)
+        opt.launch()
+
+
+class FusedReducer:
+    kind = "fused p2p reduce-scatter + adamw + all-gather (one kernel per bucket)"
+
+    def __init__(self, device: torch.device, group=None, *, overlap: bool = True, bucket_elems: int = 16 << 20,
+                 ctas_overlap: int = 24, ctas_tail: int = 64):
+        self.device, self.group = device, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > MAX_PEERS:
+            raise ValueError(f"fused reducer supports up to {MAX_PEERS} ranks per node")
+        self.overlap = overlap
+        self.bucket_elems = bucket_elems
+        self.ctas_overlap, self.ctas_tail = ctas_overlap, ctas_tail
+        self._bufs: list[SymmetricBuffer] = []
+        self.comm_stream = None
+
+    # ParamStore calls this for the bf16 shadow and the fp32 gradient buffer
+    def allocator(self, n: int, dtype: torch.dtype, device) -> torch.Tensor:
+        buf = SymmetricBuffer(n * torch.empty((), dtype=dtype).element_size(), torch.device(device))
+        self._bufs.append(buf)
+        return buf.typed(dtype, n)
+
+    def attach(self, store, opt) -> None:
+        from ..optim.flat import AdamW
+        if not isinstance(opt, AdamW):
+            raise TypeError("the fused reducer implements AdamW")
+        self.store, self.opt = store, opt
+        shadow_buf = next(b for b in self._bufs if b.ptr == store.shadow.data_ptr())
+        grad_buf = next(b for b in self._bufs if b.ptr == store.grad.data_ptr())
+        self.pad = SymmetricBuffer(nat.cuda().incin_dp_pad_bytes(), self.device)
+        for b in (shadow_buf, grad_buf, self.pad):
+            b.exchange(self.group)
+        self.shadow_buf, self.grad_buf = shadow_buf, grad_buf
+        # buckets: contiguous ranges of the flat buffer, cut at parameter boundaries
+        bounds = [0]
+        for name, p, off, numel in store.entries:
+            if off - bounds[-1] >= self.bucket_elems:
+                bounds.append(off)
+        bounds.append(store.numel)
+        self.buckets = [(bounds[i], bounds[i + 1]) for i in range(len(bounds) - 1) if bounds[i + 1] > bounds[i]]
+        if not self.overlap:
+            self.buckets = [(0, store.numel)]
+        if len(self.buckets) > MAX_SLOTS:
+            raise ValueError("too many gradient buckets")
+        self._descs = [self._make_desc(i, lo, hi) for i, (lo, hi) in enumerate(self.buckets)]
+        # readiness bookkeeping: a bucket is ready when every parameter overlapping it is complete
+        self._entry_buckets: dict[int, list[int]] = {}
+        self._bucket_need = [0] * len(self.buckets)
+        for name, p, off, numel in store.entries:
+            hit = [i for i, (lo, hi) in enumerate(self.buckets) if off < hi and off + numel > lo]
+            self._entry_buckets[id(p)] = hit
+            for i in hit:
+                self._bucket_need[i] += 1
+            if self.overlap:
+                p._grad_ready = self._on_ready
+        if self.overlap:
+            self.comm_stream = torch.cuda.Stream(device=self.device)
+        dist.barrier(group=self.group)
+
+    def _make_desc(self, slot: int, lo: int, hi: int) -> DpDesc:
+        d = DpDesc()
+        for r in range(self.world):
+            d.grads[r] = self.grad_buf.ptrs[r]
+            d.shadows[r] = self.shadow_buf.ptrs[r]
+            d.pads[r] = self.pad.ptrs[r]
+        d.master, d.m, d.v = self.store.master.data_ptr(), self.opt.m.data_ptr(), self.opt.v.data_ptr()
+        d.hyper = self.opt.hyper.data_ptr()
+        d.lo, d.hi, d.n_decay = lo, hi, self.store.n_decay
+        d.world, d.rank, d.slot = self.world, self.rank, slot
+        d.ctas = self.ctas_overlap if self.overlap else self.ctas_tail
+        d.status = status_word(self.device).data_ptr()
+        return d
+
+    def begin_step(self) -> None:
+        self._uses_left = {id(p): getattr(p, "_grad_uses", 1) for _, p, _, _ in self.store.entries}
+        self._need_left = list(self._bucket_need)
+        self._launched = [False] * len(self.buckets)
+
+    def _launch(self, i: int, stream: torch.cuda.Stream) -> None:
+        nat.check(nat.cuda().incin_dp_reduce_adamw(C.byref(self._descs[i]), stream.cuda_stream), "dp_reduce_adamw")
+        self._launched[i] = True
+
+    def _on_ready(self, p) -> None:
+        key = id(p)
+        self._uses_left[key] -= 1
+        if self._uses_left[key] != 0:
+            return
+        for i in self._entry_buckets[key]:
+            self._need_left[i] -= 1
+            if self._need_left[i] == 0 and not self._launched[i]:
+                cur = torch.cuda.current_stream()
+                self.comm_stream.wait_stream(cur)
+                self._launch(i, self.comm_stream)
+
+    def finish_step(self, opt) -> None:
+        cur = torch.cuda.current_stream()
+        if self.overlap:
+            rest = [i for i, done in enumerate(self._launched) if not done]
+            if rest:
+                self.comm_stream.wait_stream(cur)
+                for i in rest:
+                    self._launch(i, self.comm_stream)
+            cur.wait_stream(self.comm_stream)
+        else:
+            self._launch(0, cur)
+
+
+def make_reducer(kind: str, device: torch.device, group=None):
+    """Returns ``(reducer, allocator, description)`` for ``bench.py`` / the Trainer."""
+    if kind in ("fused", "fused-overlap"):
+        r = FusedReducer(device, group, overlap=True)
+        return r, r.allocator, r.kind + " overlapped with backward"
+    if kind in ("auto", "fused-tail"):
+        r = FusedReducer(device, group, overlap=False)
+        return r, r.allocator, r.kind + " after backward"
+    r = NcclReducer(group)
+    return r, r.allocator, r.kind
