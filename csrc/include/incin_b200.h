@@ -150,8 +150,9 @@ int incin_dropout_bf16(const void* x, void* y, long long n, float p, uint64_t se
 
 /* ---- flash attention (causal, online softmax, GQA) ------------------------------------------------ */
 /* q/o/do/dq: [B, T, Hq, D]; k/v/dk/dv: [B, T, Hkv, D]; every tensor has its own (b, t, h) strides in elements
- * so packed QKV buffers need no copies.  D is 64 or 128.  lse: fp32 [B, Hq, T] in the log2 domain
- * (max*scale*log2e + log2(sum)).  The backward needs delta (fp32 [B, Hq, T]) and dq_accum (fp32 [B, T, Hq, D])
+ * so packed QKV buffers need no copies.  D is 64 or 128.  lse: fp32 [B, Hq, Tpad] in the log2 domain
+ * (max*scale*log2e + log2(sum)) with Tpad = T rounded up to 128 (padding rows hold +inf).  The backward needs
+ * delta (fp32 [B, Hq, Tpad]) and dq_accum (fp32 [B, T, Hq, D])
  * as caller-provided scratch; it zeroes dq_accum itself. */
 typedef struct incin_attn_desc {
   const void *q, *k, *v;

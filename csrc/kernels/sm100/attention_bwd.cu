@@ -25,7 +25,9 @@ int make_operand_map(CUtensorMap* out, const void* ptr, long long inner, long lo
                      int box_rows);
 
 constexpr int FB_T = 128;  // tile edge for both the KV tile (TMEM lanes) and the query tile
-constexpr int FB_THREADS = 192;
+constexpr int FB_CWARPS = 16;                       // compute warps: 4 TMEM lane quarters x 4 column blocks
+constexpr int FB_CTHREADS = FB_CWARPS * 32;
+constexpr int FB_THREADS = 64 + FB_CTHREADS;        // + TMA warp + MMA warp
 
 template <int D>
 struct FbCfg {
@@ -48,8 +50,9 @@ struct FbCfg {
 struct FbParams {
   int T, Hq, Hkv, n_tiles;
   float scale, scale_log2;
-  const float* lse;    // [B, Hq, T] log2 domain
-  const float* delta;  // [B, Hq, T]
+  int Tpad;            // T rounded up to the tile edge: row stride of lse / delta
+  const float* lse;    // [B, Hq, Tpad] log2 domain, +inf beyond T
+  const float* delta;  // [B, Hq, Tpad], 0 beyond T
   float* dq_accum;     // [B, T, Hq, D] fp32, zero-initialised by the caller
   __nv_bfloat16 *dk, *dv;
   long long dk_stride_b, dk_stride_t, dk_stride_h, dv_stride_b, dv_stride_t, dv_stride_h;
@@ -77,9 +80,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* q_full = bars + 1;         // [ST]  Q_i and dO_i landed
   uint64_t* q_empty = bars + 1 + ST;   // [ST]  the three consuming MMAs of that stage finished
   uint64_t* sdp_full = bars + 1 + 2 * ST;  // S^T and dP^T in TMEM
-  uint64_t* pds_full = sdp_full + 1;       // 128 arrivals: P^T and dS^T in shared memory
+  uint64_t* pds_full = sdp_full + 1;       // all compute threads: P^T and dS^T in shared memory
   uint64_t* dq_full = sdp_full + 2;        // dQ partial in TMEM (and dV/dK updated)
-  uint64_t* dq_drained = sdp_full + 3;     // 128 arrivals: dQ partial read out, S^T columns reusable
+  uint64_t* dq_drained = sdp_full + 3;     // all compute threads: dQ partial read out, S^T columns reusable
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sdp_full + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -98,9 +101,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&q_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, FB_CTHREADS);
     mbar_init(dq_full, 1);
-    mbar_init(dq_drained, 128);
+    mbar_init(dq_drained, FB_CTHREADS);
     *abort_flag = 0;
     mbar_init_fence();
     tma_prefetch_desc(&tmQ);
@@ -131,12 +134,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int hq = hkv * group + it / tiles_per_head;
         const int q0 = (first_q_tile + it % tiles_per_head) * FB_T;
         if (!mbar_wait(&q_empty[s], ((it / ST) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
-        mbar_expect_tx(&q_full[s], 2 * Cfg::TILE_BYTES);
+        mbar_expect_tx(&q_full[s], 2 * Cfg::TILE_BYTES + 2 * FB_T * 4);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
           tma_load_4d(sQ + s * Cfg::TILE_BYTES + c * (FB_T * 128), &tmQ, &q_full[s], c * 64, q0, hq, b);
           tma_load_4d(sDO + s * Cfg::TILE_BYTES + c * (FB_T * 128), &tmDO, &q_full[s], c * 64, q0, hq, b);
         }
+        // per-query statistics of this tile: two 512-byte bulk copies (rows are padded to the tile edge)
+        const long long stat = ((long long)b * p.Hq + hq) * p.Tpad + q0;
+        bulk_load_1d(sStat + s * 2 * FB_T, p.lse + stat, FB_T * 4, &q_full[s]);
+        bulk_load_1d(sStat + s * 2 * FB_T + FB_T, p.delta + stat, FB_T * 4, &q_full[s]);
       }
     }
   } else if (warp == 1) {
@@ -194,56 +201,59 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax-gradient threads (one KV row each)
+    // ---------------------------------------------------------------- softmax-gradient threads
+    // warp -> (TMEM lane quarter = KV rows, column block = 32 query columns of the tile)
+    const int cw = warp - 2;
     const int quarter = warp & 3;
+    const int cb = cw >> 2;
     const int row = quarter * 32 + lane;
-    const int tid128 = threadIdx.x - 64;
     const int kv_idx = kv0 + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const bool kv_live = kv_idx < p.T;
     bool ok = true;
     for (int it = 0; it < n_iters; ++it) {
       const int s = it % ST;
       const int hq = hkv * group + it / tiles_per_head;
       const int q0 = (first_q_tile + it % tiles_per_head) * FB_T;
-      float* s_lse = sStat + s * 2 * FB_T;
-      float* s_delta = s_lse + FB_T;
-      {  // stage the per-query statistics of this tile (overlaps the S^T / dP^T MMAs)
-        const int q = q0 + tid128;
-        const long long idx = ((long long)b * p.Hq + hq) * p.T + q;
-        s_lse[tid128] = q < p.T ? p.lse[idx] : CUDART_INF_F;  // +inf -> P = 0 for rows past the end
-        s_delta[tid128] = q < p.T ? p.delta[idx] : 0.f;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
+      const float* s_lse = sStat + s * 2 * FB_T + cb * 32;
+      const float* s_delta = s_lse + FB_T;
+      // q_full also covers the statistics; the MMA thread waited on it before sdp_full can complete
       if (!mbar_wait(sdp_full, it & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
       const bool diag = (q0 < kv0 + FB_T);  // only the diagonal tile needs the causal test
-      const bool kv_live = kv_idx < p.T;
-#pragma unroll 1
-      for (int c = 0; c < FB_T / 32; ++c) {
-        uint32_t rs[32], rd[32];
-        tmem_ld_32x32(tmem_base + Cfg::COL_ST + lane_addr + c * 32, rs);
-        tmem_ld_32x32(tmem_base + Cfg::COL_DPT + lane_addr + c * 32, rd);
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {  // two halves of 16 query columns keep the register footprint small
+        uint32_t rs[16], rd[16];
+        tmem_ld_32x16(tmem_base + Cfg::COL_ST + lane_addr + cb * 32 + hf * 16, rs);
+        tmem_ld_32x16(tmem_base + Cfg::COL_DPT + lane_addr + cb * 32 + hf * 16, rd);
         tmem_ld_wait();
-        uint32_t pp[16], dd[16];
+        uint32_t pp[8], dd[8];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float pv[2], dv[2];
+        for (int g = 0; g < 4; ++g) {
+          const float4 l4 = *reinterpret_cast<const float4*>(s_lse + hf * 16 + g * 4);
+          const float4 d4 = *reinterpret_cast<const float4*>(s_delta + hf * 16 + g * 4);
+          const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], dv[4];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int qi = c * 32 + i + e;
+          for (int e = 0; e < 4; ++e) {
+            const int i = g * 4 + e;
+            const int qi = cb * 32 + hf * 16 + i;
             const bool live = kv_live && (!diag || (q0 + qi >= kv_idx));
-            const float pr = live ? exp2f(fmaf(__uint_as_float(rs[i + e]), p.scale_log2, -s_lse[qi])) : 0.f;
+            const float pr = live ? exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse[e])) : 0.f;
             pv[e] = pr;
-            dv[e] = pr * (__uint_as_float(rd[i + e]) - s_delta[qi]) * p.scale;
+            dv[e] = pr * (__uint_as_float(rd[i]) - dl[e]) * p.scale;
           }
-          pp[i >> 1] = pack_bf16x2(pv[0], pv[1]);
-          dd[i >> 1] = pack_bf16x2(dv[0], dv[1]);
+          pp[g * 2] = pack_bf16x2(pv[0], pv[1]);
+          pp[g * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
+          dd[g * 2] = pack_bf16x2(dv[0], dv[1]);
+          dd[g * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
         }
-        uint8_t* prow = sP + (c >> 1) * (FB_T * 128) + row * 128;
-        uint8_t* drow = sDS + (c >> 1) * (FB_T * 128) + row * 128;
+        uint8_t* prow = sP + (cb >> 1) * (FB_T * 128) + row * 128;
+        uint8_t* drow = sDS + (cb >> 1) * (FB_T * 128) + row * 128;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int unit = ((c & 1) * 4 + u) ^ (row & 7);
+        for (int u = 0; u < 2; ++u) {
+          const int unit = ((cb & 1) * 4 + hf * 2 + u) ^ (row & 7);
           *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pp[u * 4], pp[u * 4 + 1], pp[u * 4 + 2], pp[u * 4 + 3]);
           *reinterpret_cast<uint4*>(drow + unit * 16) = make_uint4(dd[u * 4], dd[u * 4 + 1], dd[u * 4 + 2], dd[u * 4 + 3]);
         }
@@ -251,45 +261,58 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(pds_full);
-      // dQ partial: lanes are query rows of this tile
+      // dQ partial: lanes are query rows of this tile; this warp drains D/4 of the columns
       if (!mbar_wait(dq_full, it & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
       const int q = q0 + row;
-      float* dq_row = p.dq_accum + (((long long)b * p.T + q) * p.Hq + hq) * D;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + Cfg::COL_ST + lane_addr + c * 32, r);
+      constexpr int DC = D / 4;  // columns per warp: 16 (D = 64) or 32 (D = 128)
+      float* dq_row = p.dq_accum + (((long long)b * p.T + q) * p.Hq + hq) * D + cb * DC;
+      if constexpr (DC == 16) {
+        uint32_t r[16];
+        tmem_ld_32x16(tmem_base + Cfg::COL_ST + lane_addr + cb * DC, r);
         tmem_ld_wait();
         if (q < p.T) {
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + u * 4),
+          for (int u = 0; u < 4; ++u)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + u * 4),
                          "f"(__uint_as_float(r[u * 4])), "f"(__uint_as_float(r[u * 4 + 1])),
                          "f"(__uint_as_float(r[u * 4 + 2])), "f"(__uint_as_float(r[u * 4 + 3]))
                          : "memory");
         }
-        __syncwarp();
+      } else {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + Cfg::COL_ST + lane_addr + cb * DC, r);
+        tmem_ld_wait();
+        if (q < p.T) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + u * 4),
+                         "f"(__uint_as_float(r[u * 4])), "f"(__uint_as_float(r[u * 4 + 1])),
+                         "f"(__uint_as_float(r[u * 4 + 2])), "f"(__uint_as_float(r[u * 4 + 3]))
+                         : "memory");
+        }
       }
+      __syncwarp();
       tc_fence_before();
       mbar_arrive(dq_drained);
     }
     // final: dK and dV of this KV tile (dq_full of the last iteration implies both are complete)
     if (ok && n_iters > 0) {
       tc_fence_after();
+      constexpr int DC = D / 4;
       __nv_bfloat16* dk_row = p.dk + (long long)b * p.dk_stride_b + (long long)kv_idx * p.dk_stride_t +
-                              (long long)hkv * p.dk_stride_h;
+                              (long long)hkv * p.dk_stride_h + cb * DC;
       __nv_bfloat16* dv_row = p.dv + (long long)b * p.dv_stride_b + (long long)kv_idx * p.dv_stride_t +
-                              (long long)hkv * p.dv_stride_h;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t rk[32], rv[32];
-        tmem_ld_32x32(tmem_base + Cfg::COL_DK + lane_addr + c * 32, rk);
-        tmem_ld_32x32(tmem_base + Cfg::COL_DV + lane_addr + c * 32, rv);
-        tmem_ld_wait();
-        if (kv_idx < p.T) {
+                              (long long)hkv * p.dv_stride_h + cb * DC;
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+      for (int c = 0; c < DC / 16; ++c) {
+        uint32_t rk[16], rv[16];
+        tmem_ld_32x16(tmem_base + Cfg::COL_DK + lane_addr + cb * DC + c * 16, rk);
+        tmem_ld_32x16(tmem_base + Cfg::COL_DV + lane_addr + cb * DC + c * 16, rv);
+        tmem_ld_wait();
+        if (kv_live) {
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
             uint4 a, bb;
             a.x = pack_bf16x2(__uint_as_float(rk[u * 8 + 0]), __uint_as_float(rk[u * 8 + 1]));
             a.y = pack_bf16x2(__uint_as_float(rk[u * 8 + 2]), __uint_as_float(rk[u * 8 + 3]));
@@ -299,8 +322,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             bb.y = pack_bf16x2(__uint_as_float(rv[u * 8 + 2]), __uint_as_float(rv[u * 8 + 3]));
             bb.z = pack_bf16x2(__uint_as_float(rv[u * 8 + 4]), __uint_as_float(rv[u * 8 + 5]));
             bb.w = pack_bf16x2(__uint_as_float(rv[u * 8 + 6]), __uint_as_float(rv[u * 8 + 7]));
-            *reinterpret_cast<uint4*>(dk_row + c * 32 + u * 8) = a;
-            *reinterpret_cast<uint4*>(dv_row + c * 32 + u * 8) = bb;
+            *reinterpret_cast<uint4*>(dk_row + c * 16 + u * 8) = a;
+            *reinterpret_cast<uint4*>(dv_row + c * 16 + u * 8) = bb;
           }
         }
         __syncwarp();
@@ -319,28 +342,30 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-// delta[b, h, t] = sum_d O[b,t,h,d] * dO[b,t,h,d]; one warp per (b, t, h)
+// delta[b, h, t] = sum_d O[b,t,h,d] * dO[b,t,h,d] (0 for the padding rows t >= T); one warp per (b, t, h)
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
-                  long long B, int T, int H, int D, long long o_sb, long long o_st, long long o_sh, long long do_sb,
-                  long long do_st, long long do_sh) {
+                  long long B, int T, int Tpad, int H, int D, long long o_sb, long long o_st, long long o_sh,
+                  long long do_sb, long long do_st, long long do_sh) {
   const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (w >= B * T * H) return;
+  if (w >= B * Tpad * H) return;
   const int h = (int)(w % H);
-  const int t = (int)((w / H) % T);
-  const long long b = w / ((long long)H * T);
-  const __nv_bfloat16* po = o + b * o_sb + (long long)t * o_st + (long long)h * o_sh;
-  const __nv_bfloat16* pd = d_o + b * do_sb + (long long)t * do_st + (long long)h * do_sh;
+  const int t = (int)((w / H) % Tpad);
+  const long long b = w / ((long long)H * Tpad);
   float s = 0.f;
-  for (int d = lane * 2; d < D; d += 64) {
-    const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(po + d));
-    const float2 c = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pd + d));
-    s += a.x * c.x + a.y * c.y;
-  }
+  if (t < T) {
+    const __nv_bfloat16* po = o + b * o_sb + (long long)t * o_st + (long long)h * o_sh;
+    const __nv_bfloat16* pd = d_o + b * do_sb + (long long)t * do_st + (long long)h * do_sh;
+    for (int d = lane * 2; d < D; d += 64) {
+      const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(po + d));
+      const float2 c = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pd + d));
+      s += a.x * c.x + a.y * c.y;
+    }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) delta[(b * H + h) * T + t] = s;
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  }
+  if (lane == 0) delta[(b * H + h) * Tpad + t] = s;
 }
 
 // dq (bf16, strided) = dq_accum (fp32 [B,T,H,D] contiguous)
@@ -382,8 +407,10 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
     attr = true;
   }
   const long long rows = (long long)d->B * d->T * d->Hq;
-  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
-      (const __nv_bfloat16*)d->o, (const __nv_bfloat16*)d->d_o, d->delta, d->B, d->T, d->Hq, D, d->o_stride_b,
+  const int Tpad = (d->T + FB_T - 1) / FB_T * FB_T;
+  const long long prow = (long long)d->B * Tpad * d->Hq;
+  attn_delta_kernel<<<(unsigned)((prow + 7) / 8), 256, 0, stream>>>(
+      (const __nv_bfloat16*)d->o, (const __nv_bfloat16*)d->d_o, d->delta, d->B, d->T, Tpad, d->Hq, D, d->o_stride_b,
       d->o_stride_t, d->o_stride_h, d->do_stride_b, d->do_stride_t, d->do_stride_h);
   if (cudaMemsetAsync(d->dq_accum, 0, sizeof(float) * rows * D, stream) != cudaSuccess) return INCIN_ERR_LAUNCH;
   FbParams p;
@@ -391,6 +418,7 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.Hq = d->Hq;
   p.Hkv = d->Hkv;
   p.n_tiles = (d->T + FB_T - 1) / FB_T;
+  p.Tpad = Tpad;
   p.scale = d->scale;
   p.scale_log2 = d->scale * 1.4426950408889634f;
   p.lse = d->lse;

@@ -45,7 +45,8 @@ struct FaParams {
   float scale_log2;  // softmax scale * log2(e)
   __nv_bfloat16* O;
   long long o_stride_b, o_stride_t, o_stride_h;
-  float* lse;  // [B, Hq, T], log2 domain
+  float* lse;  // [B, Hq, Tpad], log2 domain; rows in [T, Tpad) are written as +inf
+  int Tpad;
   int* status;
 };
 
@@ -169,25 +170,29 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after();
       const int kv0 = j * BN;
       const bool need_mask = (kv0 + BN - 1 > q0) || (kv0 + BN > p.T);
-      // pass 1: row maximum
-      float mx = -CUDART_INF_F;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_S + lane_addr + c * 32, r);
-        tmem_ld_wait();
-        if (need_mask) {
+      // whole S row into registers with back-to-back TMEM loads and a single wait
+      uint32_t r[BN];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kv = kv0 + c * 32 + i;
-            if (kv <= q_idx && kv < p.T) mx = fmaxf(mx, __uint_as_float(r[i]));
-          }
-        } else {
+      for (int c = 0; c < BN / 32; ++c)
+        tmem_ld_32x32(tmem_S + lane_addr + c * 32, reinterpret_cast<uint32_t(&)[32]>(r[c * 32]));
+      tmem_ld_wait();
+      if (need_mask) {  // masked scores become -inf, so the code below needs no further tests
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < BN; ++i) {
+          const int kv = kv0 + i;
+          if (!(kv <= q_idx && kv < p.T)) r[i] = __float_as_uint(-CUDART_INF_F);
         }
       }
-      mx *= p.scale_log2;
+      // row maximum with four independent chains
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int i = 0; i < BN; i += 4) {
+        mx4[0] = fmaxf(mx4[0], __uint_as_float(r[i]));
+        mx4[1] = fmaxf(mx4[1], __uint_as_float(r[i + 1]));
+        mx4[2] = fmaxf(mx4[2], __uint_as_float(r[i + 2]));
+        mx4[3] = fmaxf(mx4[3], __uint_as_float(r[i + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       // lazy rescale: only move the reference when the maximum grew by more than 2^8
       const bool need = mx > m_ref + 8.0f;
       float alpha = 1.0f;
@@ -198,43 +203,40 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       if (j > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
-        for (int c = 0; c < D / 16; ++c) {
-          uint32_t r[16];
-          tmem_ld_32x16(tmem_O + lane_addr + c * 16, r);
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_O + lane_addr + c * 32, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st_32x16(tmem_O + lane_addr + c * 16, r);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32(tmem_O + lane_addr + c * 32, o);
         }
         tmem_st_wait();
       }
-      // pass 2: P = exp2(s * scale - m_ref), bf16, into swizzled shared memory
+      // P = exp2(s * scale - m_ref) as bf16 into 128B-swizzled shared memory; four independent sum chains
       const float neg_m = -m_ref;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_S + lane_addr + c * 32, r);
-        tmem_ld_wait();
-        float pv[32];
+      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv = kv0 + c * 32 + i;
-          const bool live = !need_mask || (kv <= q_idx && kv < p.T);
-          pv[i] = live ? exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m)) : 0.f;
-          l_sum += pv[i];
-        }
+      for (int c = 0; c < BN / 32; ++c) {
         uint8_t* prow = sP + (c >> 1) * (FA_BM * 128) + row * 128;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
+          float e[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            e[k] = exp2f(fmaf(__uint_as_float(r[c * 32 + u * 8 + k]), p.scale_log2, neg_m));
+            ls4[k & 3] += e[k];
+          }
           uint4 o;
-          o.x = pack_bf16x2(pv[u * 8 + 0], pv[u * 8 + 1]);
-          o.y = pack_bf16x2(pv[u * 8 + 2], pv[u * 8 + 3]);
-          o.z = pack_bf16x2(pv[u * 8 + 4], pv[u * 8 + 5]);
-          o.w = pack_bf16x2(pv[u * 8 + 6], pv[u * 8 + 7]);
+          o.x = pack_bf16x2(e[0], e[1]);
+          o.y = pack_bf16x2(e[2], e[3]);
+          o.z = pack_bf16x2(e[4], e[5]);
+          o.w = pack_bf16x2(e[6], e[7]);
           const int unit = ((c & 1) * 4 + u) ^ (row & 7);  // 128B swizzle: 16-byte unit ^ (row % 8)
           *reinterpret_cast<uint4*>(prow + unit * 16) = o;
         }
       }
+      l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
@@ -263,7 +265,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         __syncwarp();
       }
-      if (live_row) p.lse[((long long)b * p.Hq + hq) * p.T + q_idx] = m_ref + log2f(l_sum);
+      p.lse[((long long)b * p.Hq + hq) * p.Tpad + q_idx] = live_row ? m_ref + log2f(l_sum) : CUDART_INF_F;
     }
   }
 
@@ -306,6 +308,7 @@ static int launch_fwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.o_stride_t = d->o_stride_t;
   p.o_stride_h = d->o_stride_h;
   p.lse = d->lse;
+  p.Tpad = p.n_q_tiles * FA_BM;
   p.status = (int*)d->status;
   dim3 grid(p.n_q_tiles, d->Hq, d->B);
   kern<<<grid, FA_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);

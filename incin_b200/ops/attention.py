@@ -59,7 +59,7 @@ class _Flash(torch.autograd.Function):
         B, T, Hq, D = q.shape
         Hkv = k.shape[2]
         o = torch.empty(B, T, Hq, D, dtype=torch.bfloat16, device=q.device)
-        lse = torch.empty(B, Hq, T, dtype=torch.float32, device=q.device)
+        lse = torch.empty(B, Hq, (T + 127) // 128 * 128, dtype=torch.float32, device=q.device)
         d = AttnDesc()
         d.B, d.T, d.Hq, d.Hkv, d.D, d.scale = B, T, Hq, Hkv, D, scale
         _set(d, "q", q), _set(d, "k", k), _set(d, "v", v), _set(d, "o", o)
@@ -81,7 +81,7 @@ class _Flash(torch.autograd.Function):
         # gets a single contiguous gradient back through autograd's view backward with no concatenation
         packed = torch.empty(B, T, Hq + 2 * Hkv, D, dtype=torch.bfloat16, device=q.device)
         dq, dk, dv = packed[:, :, :Hq], packed[:, :, Hq:Hq + Hkv], packed[:, :, Hq + Hkv:]
-        delta = torch.empty(B, Hq, T, dtype=torch.float32, device=q.device)
+        delta = torch.empty_like(lse)
         acc = torch.empty(B, T, Hq, D, dtype=torch.float32, device=q.device)
         d = AttnDesc()
         d.B, d.T, d.Hq, d.Hkv, d.D, d.scale = B, T, Hq, Hkv, D, ctx.scale
@@ -109,7 +109,7 @@ class _FlashPacked(torch.autograd.Function):
         x = qkv.view(B, T, Hq + 2 * Hkv, D)
         q, k, v = x[:, :, :Hq], x[:, :, Hq:Hq + Hkv], x[:, :, Hq + Hkv:]
         o = torch.empty(B, T, Hq, D, dtype=torch.bfloat16, device=qkv.device)
-        lse = torch.empty(B, Hq, T, dtype=torch.float32, device=qkv.device)
+        lse = torch.empty(B, Hq, (T + 127) // 128 * 128, dtype=torch.float32, device=qkv.device)
         d = AttnDesc()
         d.B, d.T, d.Hq, d.Hkv, d.D, d.scale = B, T, Hq, Hkv, D, scale
         _set(d, "q", q), _set(d, "k", k), _set(d, "v", v), _set(d, "o", o)
@@ -130,7 +130,7 @@ class _FlashPacked(torch.autograd.Function):
         q, k, v = x[:, :, :Hq], x[:, :, Hq:Hq + Hkv], x[:, :, Hq + Hkv:]
         dqkv = torch.empty_like(x)
         dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
-        delta = torch.empty(B, Hq, T, dtype=torch.float32, device=qkv.device)
+        delta = torch.empty_like(lse)
         acc = torch.empty(B, T, Hq, D, dtype=torch.float32, device=qkv.device)
         d = AttnDesc()
         d.B, d.T, d.Hq, d.Hkv, d.D, d.scale = B, T, Hq, Hkv, D, scale
