@@ -77,13 +77,21 @@ void push(Node n) {
 TP linear(const TP& x, const TP& w, const TP& b) {
   const int64_t M = x->rows, K = x->cols, N = w->rows;
   TP y = make(M, N, true);
-  for (int64_t i = 0; i < M; ++i)
-    for (int64_t j = 0; j < N; ++j) {
-      float acc = b ? b->v[(size_t)j] : 0.f;
-      const float *xr = &x->v[(size_t)(i * K)], *wr = &w->v[(size_t)(j * K)];
-      for (int64_t k = 0; k < K; ++k) acc += xr[k] * wr[k];
-      y->v[(size_t)(i * N + j)] = acc;
+  // y[i, :] = b + sum_k x[i, k] * wt[k, :]: the inner loop runs over independent outputs, so it vectorises
+  // without reassociating the reduction (bit-stable across compilers, unlike a dot-product inner loop)
+  std::vector<float> wt((size_t)(K * N));
+  for (int64_t j = 0; j < N; ++j)
+    for (int64_t k = 0; k < K; ++k) wt[(size_t)(k * N + j)] = w->v[(size_t)(j * K + k)];
+  for (int64_t i = 0; i < M; ++i) {
+    float* yr = &y->v[(size_t)(i * N)];
+    for (int64_t j = 0; j < N; ++j) yr[j] = b ? b->v[(size_t)j] : 0.f;
+    const float* xr = &x->v[(size_t)(i * K)];
+    for (int64_t k = 0; k < K; ++k) {
+      const float xv = xr[k];
+      const float* wr = &wt[(size_t)(k * N)];
+      for (int64_t j = 0; j < N; ++j) yr[j] += xv * wr[j];
     }
+  }
   std::vector<uint64_t> ins = {x->id, w->id};
   if (b) ins.push_back(b->id);
   push({y->id, ins, [x, w, b, M, N, K](const std::vector<float>& g) {

@@ -53,6 +53,12 @@ def _ready(p: torch.Tensor) -> None:
         cb(p)
 
 
+def _nat(t: torch.Tensor) -> bool:
+    """True when the hand-written sm_100a kernels take this tensor (CUDA + bf16); other dtypes and the CPU
+    use the PyTorch twin of the op."""
+    return t.is_cuda and t.dtype == torch.bfloat16
+
+
 def _c(t: torch.Tensor) -> torch.Tensor:
     return t if t.is_contiguous() else t.contiguous()
 
@@ -91,7 +97,7 @@ class _Linear(torch.autograd.Function):
 
 def linear(x, w, b=None, *, act=None, residual=None):
     """``act(x @ w^T + b) + residual`` with everything fused into the GEMM epilogue on CUDA."""
-    if x.is_cuda:
+    if _nat(x):
         return _Linear.apply(x, w, b, residual, ACT[act])
     y = TF.linear(x, w, b)
     if act == "gelu":
@@ -134,7 +140,7 @@ class _MLP(torch.autograd.Function):
 
 
 def mlp(x, w1, b1, w2, b2, *, act="gelu", residual=None):
-    if x.is_cuda:
+    if _nat(x):
         return _MLP.apply(x, w1, b1, w2, b2, residual, ACT[act])
     h = TF.linear(x, w1, b1)
     h = TF.gelu(h) if act == "gelu" else TF.silu(h)
@@ -174,14 +180,14 @@ class _LayerNorm(torch.autograd.Function):
 
 
 def layer_norm(x, g, b=None, eps: float = 1e-5):
-    if x.is_cuda:
+    if _nat(x):
         return _LayerNorm.apply(x, g, b, eps, False)
     return TF.layer_norm(x, (x.shape[-1],), g, b, eps)
 
 
 def layernorm_fork(x, g, b=None, eps: float = 1e-5):
     """Returns ``(x, layer_norm(x))``; the backward adds both incoming gradients in the LN kernel."""
-    if x.is_cuda:
+    if _nat(x):
         return _LayerNorm.apply(x, g, b, eps, True)
     return x, TF.layer_norm(x, (x.shape[-1],), g, b, eps)
 
@@ -220,13 +226,13 @@ def _rms_cpu(x, g, eps):
 
 
 def rms_norm(x, g, eps: float = 1e-5):
-    if x.is_cuda:
+    if _nat(x):
         return _RMSNorm.apply(x, g, eps, False)
     return _rms_cpu(x, g, eps)
 
 
 def rmsnorm_fork(x, g, eps: float = 1e-5):
-    if x.is_cuda:
+    if _nat(x):
         return _RMSNorm.apply(x, g, eps, True)
     return x, _rms_cpu(x, g, eps)
 
@@ -253,7 +259,7 @@ class _Embedding(torch.autograd.Function):
 
 def embedding(tokens, wte, wpe=None):
     """``wte[tokens] + wpe[arange(T)]`` (learned positions optional)."""
-    if wte.is_cuda:
+    if _nat(wte):
         return _Embedding.apply(tokens, wte, wpe)
     out = TF.embedding(tokens, wte)
     if wpe is not None:
@@ -284,7 +290,7 @@ class _CrossEntropy(torch.autograd.Function):
 def cross_entropy(logits, targets, num_classes: int | None = None):
     """Mean CE of ``logits[..., :num_classes]`` (extra padded columns are ignored)."""
     V = num_classes or logits.shape[-1]
-    if logits.is_cuda:
+    if _nat(logits):
         return _CrossEntropy.apply(logits, targets, V)
     return TF.cross_entropy(logits[..., :V].reshape(-1, V).float(), targets.reshape(-1))
 
@@ -357,7 +363,7 @@ def set_attention_impl(name: str) -> None:
 def causal_attention(qkv, n_heads: int, head_dim: int, scale: float | None = None):
     """Causal self-attention over a packed ``[B, T, 3*H*D]`` QKV tensor -> ``[B, T, H*D]``."""
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
-    if not qkv.is_cuda:
+    if not _nat(qkv):
         return _attention_cpu(qkv, n_heads, head_dim, scale)
     impl = _attention_impl
     if impl in ("auto", "flash"):
@@ -385,7 +391,7 @@ class _SwiGLU(torch.autograd.Function):
 
 def swiglu(gate_up):
     """``silu(gate) * up`` for a fused ``[..., 2F]`` gate/up projection output."""
-    if gate_up.is_cuda:
+    if _nat(gate_up):
         return _SwiGLU.apply(gate_up)
     g, u = gate_up.chunk(2, dim=-1)
     return TF.silu(g) * u
@@ -413,8 +419,8 @@ class _Rope(torch.autograd.Function):
 def _rope_cpu(x, n, D, theta):
     B, T, Ht, _ = x.shape
     half = D // 2
-    freq = theta ** (-2.0 * torch.arange(half, dtype=torch.float32) / D)
-    ang = torch.arange(T, dtype=torch.float32)[:, None] * freq[None]
+    freq = theta ** (-2.0 * torch.arange(half, dtype=torch.float32, device=x.device) / D)
+    ang = torch.arange(T, dtype=torch.float32, device=x.device)[:, None] * freq[None]
     cs, sn = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
     r = x[:, :, :n].float()
     a, c = r[..., :half], r[..., half:]
@@ -424,6 +430,69 @@ def _rope_cpu(x, n, D, theta):
 
 def rope(x, n_rot_heads: int, head_dim: int, theta: float = 10000.0):
     """Rotary position embedding (rotate-half pairing) on the first ``n_rot_heads`` heads of [B,T,H,D]."""
-    if x.is_cuda:
+    if _nat(x):
         return _Rope.apply(x, n_rot_heads, head_dim, theta)
     return _rope_cpu(x, n_rot_heads, head_dim, theta)
+
+
+# --------------------------------------------------------------------------------------------- activations / dropout / conv
+class _Activation(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, act):
+        x = _c(x)
+        ctx.save_for_backward(x)
+        ctx.act = act
+        return K.act_fwd(x, act)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        return K.act_bwd(_c(dy), x, ctx.act), None
+
+
+def activation(x, name: str):
+    """Stand-alone GELU (exact erf) / SiLU for modules that do not fuse the activation into a GEMM epilogue."""
+    if _nat(x):
+        return _Activation.apply(x, ACT[name])
+    return TF.gelu(x) if name == "gelu" else TF.silu(x)
+
+
+class _Dropout(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, p, seed, offset):
+        ctx.args = (p, seed, offset)
+        return K.dropout(_c(x), p, seed, offset)
+
+    @staticmethod
+    def backward(ctx, dy):
+        p, seed, offset = ctx.args
+        return K.dropout(_c(dy), p, seed, offset), None, None, None   # same (seed, offset) -> same mask
+
+
+def dropout(x, p: float, seed: int = 0, offset: int = 0):
+    """Inverted dropout.  The mask is a pure function of (seed, offset, element index): it is regenerated in
+    the backward pass instead of being stored."""
+    if _nat(x):
+        return _Dropout.apply(x, p, seed, offset)
+    g = torch.Generator(device=x.device).manual_seed(seed * 1000003 + offset)
+    mask = (torch.rand(x.shape, generator=g, device=x.device) >= p).to(x.dtype)
+    return x * mask / (1.0 - p)
+
+
+def conv2d_im2col(x, w, b, stride, padding, dilation):
+    """bf16 CUDA convolution lowered to unfold + the tcgen05 GEMM (the reference lowers conv to im2col +
+    its SGEMM per batch and group: crates/incin-backends/src/cuda/backend.rs:1638-1645)."""
+    N, Cin, H, W = x.shape
+    O, _, KH, KW = w.shape
+    cols = TF.unfold(x, (KH, KW), dilation=dilation, padding=padding, stride=stride)   # [N, Cin*KH*KW, L]
+    L = cols.shape[-1]
+    a = cols.transpose(1, 2).reshape(N * L, Cin * KH * KW).contiguous()
+    kdim = a.shape[1]
+    wk = w.reshape(O, kdim)
+    if kdim % 8:   # TMA needs 16-byte row strides: pad the reduction dimension with zeros
+        pad = 8 - kdim % 8
+        a = TF.pad(a, (0, pad))
+        wk = TF.pad(wk, (0, pad))
+    y = linear(a, wk.contiguous(), b)
+    oh = (H + 2 * padding[0] - dilation[0] * (KH - 1) - 1) // stride[0] + 1
+    return y.reshape(N, L, O).transpose(1, 2).reshape(N, O, oh, L // oh)

@@ -217,3 +217,20 @@ class SGD(_FlatOptimizer):
             for n, p, o, k in self.store.entries:
                 out[f"momentum.{n}"] = self.mom[o:o + k].view(p.shape).clone()
         return out
+
+
+class Adam(AdamW):
+    """Adam = AdamW without decoupled weight decay (crates/incin-core/src/optim/mod.rs:93-124)."""
+
+    def __init__(self, store: ParamStore, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8):
+        super().__init__(store, lr, betas, eps, weight_decay=0.0)
+
+
+def make_store(module, device=None, compute_dtype=None, **kw) -> ParamStore:
+    """Flat store for a module: bf16 shadow on CUDA, fp32 on the CPU backend."""
+    import torch
+    params = list(module.named_parameters())
+    dev = torch.device(device) if device is not None else params[0][1].device
+    if compute_dtype is None:
+        compute_dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    return ParamStore(params, device=dev, compute_dtype=compute_dtype, **kw)

@@ -56,6 +56,7 @@ class NcclReducer:
     def attach(self, store, opt) -> None:
         self.store = store
         opt.grad_scale = 1.0 / self.world
+        opt.reducer = self
 
     def begin_step(self) -> None:
         pass
@@ -92,6 +93,7 @@ class FusedReducer:
         if not isinstance(opt, AdamW):
             raise TypeError("the fused reducer implements AdamW")
         self.store, self.opt = store, opt
+        opt.reducer = self
         shadow_buf = next(b for b in self._bufs if b.ptr == store.shadow.data_ptr())
         grad_buf = next(b for b in self._bufs if b.ptr == store.grad.data_ptr())
         self.pad = SymmetricBuffer(nat.cuda().incin_dp_pad_bytes(), self.device)

@@ -1,0 +1,340 @@
+"""CPU tests of the front end: shapes, policies, descriptors, nn layers, optimisers and schedulers, checkpoints,
+exporters, metrics, distributions, telemetry, data loader, Trainer and the native MLP benchmark."""
+import json
+import os
+
+import pytest
+import torch
+
+from incin_b200 import core, distributions as D, io, metrics as MT, nn, telemetry as T
+from incin_b200.core import policy as P, spec as S
+from incin_b200.core.shapes import matmul_shape
+
+
+def test_shapes_named_axes_and_errors():
+    B, Sq = core.dim("Batch", "Seq")
+    env = {}
+    core.s(B, Sq, 768).check(torch.zeros(4, 16, 768), env)
+    assert env == {"Batch": 4, "Seq": 16}
+    with pytest.raises(core.ShapeError) as e:
+        core.s(B, 10).check(torch.zeros(5, 10), env)
+    assert e.value.op is core.OperationKind.BIND
+    with pytest.raises(core.ShapeError):
+        core.broadcast_shapes(core.s(B, 4), core.s(Sq, 4))      # distinct named axes never unify
+    assert core.broadcast_shapes((8, 1, 6, 1), (7, 1, 5)).dims == core.s(8, 7, 6, 5).dims
+    with pytest.raises(core.ShapeError):
+        core.broadcast_shapes((3, 4), (5, 4))
+    assert matmul_shape(core.s(B, 16, 32), core.s(32, 8)) == core.s(B, 16, 8)
+    with pytest.raises(core.ShapeError):
+        matmul_shape((4, 5), (6, 7))
+    assert core.reshape_infer(24, (2, -1, 3)) == (2, 4, 3)
+    with pytest.raises(core.ShapeError):
+        core.reshape_infer(24, (5, -1))
+    with pytest.raises(core.ShapeError):
+        core.Shape(range(9))                                     # MAX_RANK
+
+
+def test_broadcast_fuzz_against_torch():
+    g = torch.Generator().manual_seed(0)
+    for _ in range(200):
+        ra, rb = int(torch.randint(0, 5, (1,), generator=g)), int(torch.randint(0, 5, (1,), generator=g))
+        a = [int(torch.randint(1, 4, (1,), generator=g)) for _ in range(ra)]
+        b = [int(torch.randint(1, 4, (1,), generator=g)) for _ in range(rb)]
+        try:
+            ref = tuple(torch.broadcast_shapes(tuple(a), tuple(b)))
+        except RuntimeError:
+            with pytest.raises(core.ShapeError):
+                core.broadcast_shapes(a, b)
+            continue
+        assert tuple(d.size for d in core.broadcast_shapes(a, b).dims) == ref
+
+
+def test_idx_slicing_is_bounds_checked():
+    x = torch.arange(8 * 4 * 40).reshape(8, 4, 40)
+    assert core.idx[0:5, ..., 15:30].apply(x).shape == (5, 4, 15)
+    assert torch.equal(core.idx[2].apply(x), x[2])
+    with pytest.raises(core.ShapeError):
+        core.idx[0:9].apply(x)
+    with pytest.raises(core.ShapeError):
+        core.idx[..., ...]
+
+
+def test_dtype_and_device():
+    assert core.size_bytes(core.DTypeId.Q8_0, 32) == 34 and core.size_bytes(core.DTypeId.Q8_0, 33) == 68
+    assert core.size_bytes(core.DTypeId.BF16, 10) == 20
+    assert core.from_torch(torch.bfloat16) is core.DTypeId.BF16
+    with pytest.raises(TypeError):
+        core.to_torch(core.DTypeId.Q8_0)
+    assert core.detect_device(core.DevicePreference.DEFAULT) == core.Cpu    # the default backend is always the CPU
+    assert len(core.DeviceSet.cuda(range(4))) == 4
+    with pytest.raises(ValueError):
+        core.DeviceSet([core.Cpu, core.Cuda(0)])
+    with pytest.raises(ValueError):
+        core.DeviceSet([core.Cuda(1), core.Cuda(1)])
+
+
+def test_policy_scopes_and_loss_scaling():
+    assert P.current_policy().determinism is P.Determinism.PERMITTED
+    with P.policy_scope(determinism=P.Determinism.REQUIRED) as outer:
+        with P.policy_scope(math=P.MathMode.FAST):
+            assert P.current_policy().determinism is P.Determinism.REQUIRED and P.current_policy().math is P.MathMode.FAST
+        assert P.current_policy() == outer
+    assert P.current_policy() == P.ExecutionPolicy()
+    assert P.ExecutionPolicy().cache_key() != P.ExecutionPolicy(math=P.MathMode.FAST).cache_key()
+    with P.no_grad():
+        assert P.grad_mode() is P.GradMode.DISABLED
+    ls = P.LossScaling.dynamic(1024.0, 2.0, 0.5, 3)
+    ls.update(True)
+    assert ls.scale() == 512.0
+    for _ in range(3):
+        ls.update(False)
+    assert ls.scale() == 1024.0
+    tiny = P.LossScaling.dynamic(1.5, 2.0, 0.5, 10)
+    tiny.update(True)
+    assert tiny.scale() == 1.0                                    # never below 1
+    assert P.PrecisionPolicy.mixed_bf16().compute is core.DTypeId.BF16
+    assert P.PrecisionPolicy.mixed_f16().loss_scaling.kind == "dynamic"
+
+
+def test_descriptors_and_capabilities():
+    a, b = S.TensorMeta.of(torch.zeros(4, 3, 5)), S.TensorMeta.of(torch.zeros(5, 7))
+    v = S.validate(S.MatMulSpec(a, b))
+    assert v.output_shape == (4, 3, 7)
+    v.audit()
+    with pytest.raises(core.ShapeError):
+        S.validate(S.MatMulSpec(a, a))
+    assert S.validate(S.ReductionSpec(a, S.ReduceOp.MEAN, (0, 2))).output_shape == (3,)
+    with pytest.raises(core.ShapeError):
+        S.validate(S.ReductionSpec(a, S.ReduceOp.SUM, (1, 1)))
+    assert S.TensorMeta.of(torch.zeros(3, 4).t()).layout is S.LayoutClass.STRIDED
+    assert S.TensorMeta.of(torch.zeros(3, 4).t()).max_physical_index() == 11
+    cuda = S.REGISTRIES[core.DeviceKind.CUDA]
+    assert cuda.query(S.CapabilityQuery("matmul", core.DTypeId.BF16, core.DeviceKind.CUDA)).level is S.SupportLevel.NATIVE
+    assert not cuda.supports("topk", core.DTypeId.BF16)
+    assert "gemm_tcgen05" in S.capability_table_markdown() or "matmul" in S.capability_table_markdown()
+    assert S.ProofLevel.STATIC.meet(S.ProofLevel.RANKED) is S.ProofLevel.RANKED
+
+
+def test_layers_match_torch_and_state_dict_layout():
+    nn.manual_seed(0)
+    m = nn.seq(nn.Flatten(), nn.Linear(12, 8), nn.GELU(), nn.LayerNorm(8), nn.Linear(8, 3))
+    assert [n for n, _ in m.named_parameters()] == ["1.weight", "1.bias", "3.weight", "3.bias", "4.weight", "4.bias"]
+    assert sorted(io.state_dict(m))[0] == "1.bias."               # trailing dot, as in incin checkpoints
+    assert m[1].weight.shape == (8, 12) and m[1].weight.abs().max() <= 1 / 12 ** 0.5 + 1e-6
+    x = torch.randn(5, 3, 4)
+    ref = torch.nn.functional.linear(x.flatten(1), m[1].weight, m[1].bias)
+    ref = torch.nn.functional.layer_norm(torch.nn.functional.gelu(ref), (8,), m[3].weight, m[3].bias)
+    assert torch.allclose(m(x), torch.nn.functional.linear(ref, m[4].weight, m[4].bias), atol=1e-6)
+    r = nn.RMSNorm(8)
+    z = torch.randn(2, 8)
+    assert torch.allclose(r(z), z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + 1e-5), atol=1e-6)
+    d = nn.Dropout(0.5, seed=3).train()
+    y = d(torch.ones(10000))
+    assert abs(float((y == 0).float().mean()) - 0.5) < 0.03 and abs(float(y.mean()) - 1.0) < 0.05
+    assert torch.equal(d.eval()(z), z)
+    st = nn.ComputeStats.of(m)
+    assert st.parameters == 12 * 8 + 8 + 16 + 8 * 3 + 3
+    out, (h, c) = nn.LSTM(4, 6)(torch.randn(2, 5, 4))
+    assert out.shape == (2, 5, 6) and torch.equal(out[:, -1], h)
+
+
+def test_flat_optimizers_match_torch_and_schedulers():
+    from incin_b200.optim import SGD, AdamW, CosineAnnealingLR, LinearLR, StepLR, make_store
+    torch.manual_seed(0)
+    m1 = torch.nn.Linear(6, 4)
+    m2 = torch.nn.Linear(6, 4)
+    m2.load_state_dict(m1.state_dict())
+    ref = torch.optim.AdamW(m1.parameters(), lr=1e-2, weight_decay=0.1)
+    store = make_store(m2, decay_filter=lambda n, p: True)
+    opt = AdamW(store, lr=1e-2, weight_decay=0.1)
+    x, y = torch.randn(16, 6), torch.randn(16, 4)
+    for _ in range(5):
+        ref.zero_grad()
+        ((m1(x) - y) ** 2).mean().backward()
+        ref.step()
+        store.zero_grad()
+        ((m2(x) - y) ** 2).mean().backward()
+        store.collect_autograd_grads()
+        opt.step()
+    assert torch.allclose(m1.weight, m2.weight, atol=1e-6) and torch.allclose(m1.bias, m2.bias, atol=1e-6)
+    sd = opt.state_dict()
+    assert sd["step_count"] == 5 and "m.weight" in sd and "v.bias" in sd
+    s2 = SGD(make_store(torch.nn.Linear(2, 2)), lr=0.1)
+    lin = LinearLR(s2, 0.0, 1.0, 10)
+    assert [round(lin.step(), 3) for _ in range(3)] == [0.01, 0.02, 0.03]
+    cos = CosineAnnealingLR(s2, 100, base_lr=1.0)
+    assert abs(cos.lr_at(50) - 0.5) < 1e-9 and cos.lr_at(100) == 0.0
+    assert StepLR(s2, 10, 0.5, base_lr=1.0).lr_at(25) == 0.25
+    st = lin.state_dict()
+    lin2 = LinearLR(s2, 0.0, 1.0, 10)
+    lin2.load_state_dict(st)
+    assert lin2.last_step == 3
+
+
+def test_checkpoint_roundtrip_resharding_and_limits(tmp_path):
+    from incin_b200.optim import AdamW, make_store
+    nn.manual_seed(1)
+    m = nn.seq(nn.Linear(16, 8), nn.ReLU(), nn.Linear(8, 4))
+    opt = AdamW(make_store(m), lr=1e-3)
+    m(torch.randn(3, 16)).sum().backward()
+    opt.store.collect_autograd_grads()
+    opt.step()
+    io.save_checkpoint(tmp_path, m, world_size=2, placements={"0.weight": "sharded:0", "2.weight": "sharded:1"},
+                       optimizer=opt, trainer_state={"scheduler": {"last_step": 7}})
+    man = json.loads((tmp_path / "manifest.json").read_text())
+    assert man["world_size"] == 2 and man["tensors"]["0.weight."]["placement_kind"] == "sharded:0"
+    m2 = nn.seq(nn.Linear(16, 8), nn.ReLU(), nn.Linear(8, 4))
+    opt2 = AdamW(make_store(m2), lr=1e-3)
+    extra = io.load_checkpoint(tmp_path, m2, opt2)
+    assert torch.equal(m[0].weight, m2[0].weight) and torch.equal(opt.m, opt2.m) and opt2.step_count == 1
+    assert extra["scheduler"]["last_step"] == 7
+    for world in (2, 4):
+        parts = [io.load_resharded_checkpoint(tmp_path, r, world) for r in range(world)]
+        assert torch.equal(torch.cat([p["0.weight."] for p in parts], 0), m[0].weight.detach())
+        assert torch.equal(torch.cat([p["2.weight."] for p in parts], 1), m[2].weight.detach())
+        assert torch.equal(parts[1]["0.bias."], m[0].bias.detach())
+    with pytest.raises(ValueError):
+        io.slice_bytes_for_rank(b"\0" * 24, [2, 3], core.DTypeId.F32, 1, 0, 2)
+    with pytest.raises(io.LimitError):
+        io.load_safetensors(tmp_path / "model.safetensors", io.ResourceLimits(max_tensor_count=1))
+    bad = tmp_path / "bad.safetensors"
+    bad.write_bytes((10 ** 12).to_bytes(8, "little") + b"{}")
+    with pytest.raises(io.LimitError):
+        io.load_safetensors(bad)
+
+
+def test_exporters_and_quantisation(tmp_path):
+    from incin_b200.ops.quant import dequantize_q8_0, quantize_q8_0, quantized_matmul
+    w = torch.randn(8, 64)
+    q = quantize_q8_0(w)
+    assert q.numel() == 8 * 64 // 32 * 34
+    assert (dequantize_q8_0(q, w.numel()).reshape(8, 64) - w).abs().max() <= w.abs().max() / 127 + 1e-6
+    x = torch.randn(3, 64)
+    assert torch.allclose(quantized_matmul(x, q, 8, 64), x @ w.t(), atol=0.6)
+    io.export_gguf({"w": w, "b": torch.zeros(8)}, tmp_path / "m.gguf", quantize="q8_0")
+    idx = io.read_gguf_index(tmp_path / "m.gguf")
+    assert idx["tensors"]["w"] == {"shape": [8, 64], "type": 8, "offset": idx["tensors"]["w"]["offset"]}
+    assert idx["tensors"]["b"]["type"] == 0
+    rep = io.inspect_file(tmp_path / "m.gguf")
+    assert rep.format == "gguf" and rep.parameters == 8 * 64 + 8
+    io.export_mlx({"w": w}, tmp_path / "mlx", {"hidden": 64})
+    assert io.inspect_file(tmp_path / "mlx" / "weights.safetensors").metadata == {"format": "mlx"}
+
+
+def test_metrics_and_distributions():
+    p, t = torch.tensor([0, 1, 2, 2, 1]), torch.tensor([0, 1, 1, 2, 1])
+    acc, f1, cm = MT.Accuracy(), MT.F1Score(3), MT.ConfusionMatrix(3)
+    for m in (acc, f1, cm):
+        m.update(p, t)
+    assert acc.compute() == 0.8 and cm.compute()[1].tolist() == [0, 2, 1]
+    assert abs(f1.compute() - (1.0 + 0.8 + 2 / 3) / 3) < 1e-9
+    assert MT.Precision(3, "micro").compute() == 0.0
+    mse = MT.MSE()
+    mse.update(torch.tensor([1.0, 3.0]), torch.tensor([0.0, 1.0]))
+    assert mse.compute() == 2.5
+    u = D.Uniform(-1, 1).sample((20000,), seed=0)
+    assert -1 < float(u.min()) and float(u.max()) < 1 and abs(float(u.mean())) < 0.02
+    n = D.Normal(2, 3).sample((100000,), seed=1, offset=5)
+    assert abs(float(n.mean()) - 2) < 0.05 and abs(float(n.std()) - 3) < 0.05
+    assert torch.equal(n, D.Normal(2, 3).sample((100000,), seed=1, offset=5))      # (seed, offset) names a stream
+    assert not torch.equal(n, D.Normal(2, 3).sample((100000,), seed=1, offset=6))
+    assert abs(float(D.Bernoulli(0.3).sample((20000,), 2).mean()) - 0.3) < 0.02
+    assert abs(float(D.Exponential(2).sample((20000,), 3).mean()) - 0.5) < 0.02
+    assert abs(float(D.Gumbel().sample((50000,), 4).mean()) - 0.5772) < 0.03
+
+
+def test_telemetry_emitter_bounds_and_viewer(tmp_path):
+    class Slow:
+        def __init__(self):
+            self.lines = []
+        def send(self, line):
+            import time
+            time.sleep(0.0005)
+            self.lines.append(line)
+        def close(self):
+            pass
+    tr = Slow()
+    e = T.Emitter(tr)
+    e.emit(T.Event("epoch", "epoch", 1.0), priority=True)
+    for i in range(T.BULK_CAP + 2000):
+        e.emit(T.Event("scalar", "loss", float(i), i))
+    e.close()
+    assert e.dropped > 0 and len(tr.lines) + e.dropped == T.BULK_CAP + 2001
+    assert any('"epoch"' in ln for ln in tr.lines)                 # priority events survive a bulk flood
+    p = tmp_path / "run.jsonl"
+    e2 = T.Emitter(T.FileTransport(p))
+    T.set_emitter(e2)
+    for i in range(20):
+        T.emit_scalar("loss", 1.0 / (i + 1), i)
+    T.emit_hyperparam("lr", 3e-4)
+    e2.close()
+    T.set_emitter(None)
+    evs = T.read_run(p)
+    assert len(evs) == 21 and evs[0].v == T.SCHEMA_VERSION
+    fut = T.Event.from_json('{"kind":"new_kind","name":"x","future_field":3}')
+    assert fut.kind == "new_kind" and fut.payload["future_field"] == 3
+    from incin_b200.telemetry.viz import render
+    assert "loss" in render(p) and "lr=0.0003" in render(p)
+    a, b = T.uuid7(), T.uuid7()
+    assert a[14] == "7" and a[:8] <= b[:8]
+
+
+def test_dataloader_order_workers_and_transforms():
+    from incin_b200.data import CenterCrop, Compose, DataLoader, Normalize, Scale, SyntheticTokens, TensorDataset
+    ds = TensorDataset(torch.arange(23).float().unsqueeze(1), torch.arange(23))
+    a = [b[1].tolist() for b in DataLoader(ds, 5, shuffle=True, workers=3, seed=1)]
+    b = [x[1].tolist() for x in DataLoader(ds, 5, shuffle=True, workers=0, seed=1)]
+    assert a == b and sorted(sum(a, [])) == list(range(23)) and len(a) == 5
+    assert len(list(DataLoader(ds, 5, drop_last=True))) == 4
+    dl = DataLoader(ds, 5, shuffle=True, seed=1)
+    e1 = [x[1].tolist() for x in dl]
+    e2 = [x[1].tolist() for x in dl]
+    assert e1 != e2                                                # reshuffled every epoch
+    class Bad(TensorDataset):
+        def __getitem__(self, i):
+            raise RuntimeError("boom")
+    with pytest.raises(RuntimeError, match="boom"):
+        list(DataLoader(Bad(torch.zeros(4, 1)), 2, workers=2))
+    x = Compose(Scale(2.0), Normalize([1.0], [2.0]), CenterCrop(2, 2))(torch.ones(1, 4, 4))
+    assert x.shape == (1, 2, 2) and float(x[0, 0, 0]) == 0.5
+    tok, tgt = SyntheticTokens(4, 16, 100)[0]
+    assert tok.shape == (16,) and torch.equal(tok[1:], tgt[:-1])
+
+
+def test_trainer_plan_explain_and_fit():
+    from incin_b200.data import DataLoader, TensorDataset
+    from incin_b200.optim import SGD, make_store
+    from incin_b200.train import CollectivesUnavailable, DeviceUnavailable, NotCompiledIn, Trainer
+    class NoGpu:
+        def compiled_in(self, k): return k is not core.DeviceKind.WGPU
+        def has_device(self, d): return d.kind is core.DeviceKind.CPU
+        def collectives_available(self, n): return False
+    plan = Trainer.plan().epochs(3).build_on(NoGpu())
+    assert [d.code for d in plan.decisions] == ["devices-requested", "devices-resolved", "epochs"]
+    assert json.loads(plan.explain_json())["devices"] == ["cpu"] and "[epochs] 3" in plan.explain()
+    with pytest.raises(DeviceUnavailable):
+        Trainer.plan().devices(core.DeviceSet.cuda(range(2))).build_on(NoGpu())
+    with pytest.raises(NotCompiledIn):
+        Trainer.plan().devices(core.DeviceSet([core.DeviceId(core.DeviceKind.WGPU)])).build_on(NoGpu())
+    class TwoGpus(NoGpu):
+        def has_device(self, d): return True
+    p2 = Trainer.plan().devices(core.DeviceSet.cuda(range(2))).build_on(TwoGpus())
+    assert "collectives-required" in [d.code for d in p2.decisions] and p2.is_multi_device
+    nn.manual_seed(0)
+    m = nn.seq(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 2))
+    opt = SGD(make_store(m), lr=0.1)
+    with pytest.raises(CollectivesUnavailable):
+        Trainer(p2, TwoGpus()).fit(m, opt, [], None)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(64, 8, generator=g)
+    y = (x[:, 0] > 0).long()
+    hist = Trainer(plan).fit(m, opt, DataLoader(TensorDataset(x, y), 16), lambda mod, a, b: nn.cross_entropy_loss(mod(a), b))
+    assert len(hist) == 12 and hist[-1] < hist[0]
+
+
+def test_native_mlp_benchmark_matches_pytorch_cpu():
+    from incin_b200.models.mlp import train_native, train_torch
+    a, _ = train_native(steps=100)
+    b, _ = train_torch(steps=100)
+    assert abs(a[0] - 2.3025) < 1e-3 and a[-1] < 0.7
+    assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5

@@ -65,7 +65,6 @@ def test_bind_minimum_link_and_stable_ids():
                           minimum_link=M.LinkClass.HIGH_BANDWIDTH)
     assert e.value.kind is M.BindErrorKind.INSUFFICIENT_LINK
     assert _mesh(2, 4).mesh_id == _mesh(2, 4).mesh_id != _mesh(4, 2).mesh_id
-    assert M.Digest().text("a").finish() == 0x0F29A94F0E6C8D0B or True  # value pinned below
     assert M.Digest().bytes(b"hello").finish() == 0xA430D84680AABD0B  # FNV-1a 64 test vector
 
 
