@@ -66,6 +66,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
     """Launch one (batched) GEMM on the current stream.  Offsets/strides are in elements."""
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "operands must be bf16"
     assert out.dtype in (torch.bfloat16, torch.float32)
+    if tile_n == 0 and not accumulate:
+        tile_n = _tuned_tile_n(locals())
     d = nat.GemmDesc()
     d.A = a.data_ptr() + 2 * a_offset
     d.B = b.data_ptr() + 2 * b_offset
@@ -90,6 +92,27 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
     d.status = status_word(a.device).data_ptr()
     nat.check(nat.cuda().incin_gemm_bf16(ctypes.byref(d), nat.stream_ptr()), "gemm")
     return out
+
+
+def _tuned_tile_n(kw: dict) -> int:
+    """Ask the autotune service for the N tile of this problem.  With the default policy this is a dictionary
+    lookup that falls through to the kernel's own heuristic (0); under ``coordinated_warmup`` /
+    ``profile_guided`` the four tile widths are timed once per (shape, layout) and the winner is cached."""
+    from ..tuning import TuningPolicy, candidates, service, time_cuda
+    svc = service()
+    if svc.policy in (TuningPolicy.DISABLED, TuningPolicy.HEURISTIC) and not svc.lru:
+        return 0
+    if torch.cuda.is_current_stream_capturing():
+        return 0
+    key = (f"gemm/{kw['M']}x{kw['N']}x{kw['K']}/{int(kw['a_mn'])}{int(kw['b_mn'])}/b{kw['batch'][0] * kw['batch'][1]}"
+           f"/e{kw['act']}{int(kw['bias'] is not None)}{int(kw['residual'] is not None)}")
+
+    def measure(params):
+        args = {k: kw[k] for k in ("M", "N", "K", "lda", "ldb", "ldc", "a_mn", "b_mn", "batch", "a_strides", "b_strides",
+                                   "c_strides", "alpha", "bias", "residual", "act", "aux", "splits", "max_ctas",
+                                   "a_offset", "b_offset", "c_offset")}
+        return time_cuda(lambda: gemm(kw["a"], kw["b"], kw["out"], tile_n=params["tile_n"], **args))
+    return svc.choose(key, candidates(tile_n=[64, 128, 192, 256]), lambda: {"tile_n": 0}, measure)["tile_n"]
 
 
 def _rows(x: torch.Tensor) -> int:
