@@ -65,6 +65,22 @@ typedef struct incin_gemm_desc {
   int tile_n;    /* 0 = heuristic, else 64/128/192/256 */
   int max_ctas;  /* 0 = all SMs; smaller leaves SMs to a concurrent communication kernel */
   void* status;  /* optional int32 device word: receives a KernelStatus code if a wait timed out */
+  /* --- fused all-gather -> GEMM (tensor-parallel column layer).  ag_world > 1 switches it on: A must then be
+   * the LOCAL gathered buffer [ag_world * ag_rows_per_rank][lda] with lda == K, and ag_src[r] is rank r's
+   * shard [ag_rows_per_rank][K] (a peer-mapped pointer for r != ag_rank).  ag_copy_ctas CTAs of the same launch
+   * pull the shards into the gathered buffer with bulk copies (each remote byte crosses NVLink once) and
+   * publish one flag per 128-row tile in ag_flags (uint32[tiles_m], zeroed by the caller before the launch);
+   * the GEMM CTAs consume tiles in the order they arrive, own shard first.  ag_rows_per_rank % 128 == 0. */
+  int ag_world, ag_rank, ag_rows_per_rank, ag_copy_ctas;
+  const void* ag_src[8];
+  void* ag_flags;
+  /* --- fused GEMM -> reduce-scatter (row layer).  rs_world > 1: the epilogue stores each 128-row tile of the
+   * partial product as bf16 into the slot of this rank inside the OWNER rank's slot buffer
+   * rs_dst[owner] = [rs_world][rs_rows_per_rank][ldc] over peer stores; C is ignored.  The owner sums the
+   * slots afterwards (incin_slot_reduce) once a peer barrier has passed. */
+  int rs_world, rs_rank, rs_rows_per_rank, rs_pad_;
+  void* rs_dst[8];
+  long long rs_slot_stride;
 } incin_gemm_desc;
 
 int incin_gemm_bf16(const incin_gemm_desc* desc, void* stream);
@@ -177,6 +193,11 @@ typedef struct incin_attn_desc {
 } incin_attn_desc;
 int incin_flash_attn_fwd(const incin_attn_desc* desc, void* stream);
 int incin_flash_attn_bwd(const incin_attn_desc* desc, void* stream);
+
+/* ---- tensor-parallel helpers -------------------------------------------------------------------- */
+/* out[r][n] = sum_s slots[s][r][n] (+ residual[r][n]) in fp32, written as bf16; slots: bf16 [world][rows][ld] */
+int incin_slot_reduce(const void* slots, long long slot_stride, int world, const void* residual, void* out,
+                      long long rows, int N, long long ld, void* stream);
 
 /* ---- library info ------------------------------------------------------------------------------ */
 const char* incin_sm100_version(void);

@@ -41,6 +41,20 @@ typedef struct incin_dp_desc {
 int incin_dp_reduce_adamw(const incin_dp_desc* desc, void* stream);
 int incin_dp_pad_bytes(void);
 
+/* Barrier across the GPUs of a group, as one tiny kernel per GPU: every rank signals every peer's pad and waits
+ * (bounded) for theirs.  When it has completed on a GPU, every peer has reached the same point of its stream, i.e.
+ * every kernel the peers enqueued before their barrier has finished.  pads[r] = rank r's pad (incin_barrier_pad_bytes()
+ * bytes, zero-initialised, one pad per group); `slot` picks one of 64 independent barriers in the pad. */
+int incin_peer_barrier(void* const* pads, int world, int rank, int slot, void* status, void* stream);
+int incin_barrier_pad_bytes(void);
+
+/* In-place all-reduce(sum) of fp32 ranges over a peer group, for the few tensors a tensor-parallel job keeps
+ * replicated inside a sub-group.  Two launches around a barrier: stage 0 sums the peers' ranges into `scratch`
+ * (local, fp32, at least total length), stage 1 copies scratch back.  ranges = int64 [n_ranges][2] (offset, length)
+ * in device memory, offsets relative to each rank's base pointer. */
+int incin_peer_sum_ranges(void* const* bases, int world, const void* ranges, int n_ranges, void* scratch, int stage,
+                          void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -60,6 +60,15 @@ struct GemmKernelParams {
   int act;
   __nv_bfloat16* aux;
   int* status;
+  // all-gather -> GEMM
+  int ag_world, ag_rank, ag_rows_per_rank, gemm_ctas;  // gemm_ctas: CTAs [0, gemm_ctas) compute, the rest copy
+  const __nv_bfloat16* ag_src[8];
+  uint32_t* ag_flags;
+  __nv_bfloat16* ag_gathered;
+  // GEMM -> reduce-scatter
+  int rs_world, rs_rank, rs_rows_per_rank;
+  __nv_bfloat16* rs_dst[8];
+  long long rs_slot_stride;
 };
 
 struct Unit {
@@ -70,10 +79,21 @@ __device__ __forceinline__ Unit decode_unit(const GemmKernelParams& p, int u) {
   Unit w;
   const int split = u % p.splits;
   int t = u / p.splits;
-  w.m_blk = t % p.tiles_m;
-  t /= p.tiles_m;
-  w.n_blk = t % p.tiles_n;
-  const int b = t / p.tiles_n;
+  int b;
+  if (p.ag_world > 1) {
+    // tiles of one 128-row block are consecutive (one flag wait serves them all) and the row blocks are visited
+    // in arrival order: own shard first, then the peers' shards in the order the copy CTAs fetch them
+    w.n_blk = t % p.tiles_n;
+    t /= p.tiles_n;
+    const int mi = t % p.tiles_m;
+    w.m_blk = (mi + p.ag_rank * (p.ag_rows_per_rank / BM)) % p.tiles_m;
+    b = t / p.tiles_m;
+  } else {
+    w.m_blk = t % p.tiles_m;
+    t /= p.tiles_m;
+    w.n_blk = t % p.tiles_n;
+    b = t / p.tiles_n;
+  }
   w.b_lo = b % p.batch_lo;
   w.b_hi = b / p.batch_lo;
   const int kb_total = (p.K + BK - 1) / BK;
@@ -96,9 +116,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* tempty_bar = tfull_bar + 2;           // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* copy_bar = bars;   // copy CTAs reuse the (otherwise idle) full/empty barriers, 2*STAGES >= NBUF of them
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // all-gather mode: the first CTAs of the grid (dispatched first) copy, the remaining gemm_ctas compute
+  const int n_compute = p.ag_world > 1 ? p.gemm_ctas : (int)gridDim.x;
+  const int n_copy = (int)gridDim.x - n_compute;
+  const bool is_copier = (int)blockIdx.x < n_copy;
+  const int cta = (int)blockIdx.x - n_copy;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) {
@@ -123,15 +149,79 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (is_copier) {
+    // ------------------------------------------------------------- all-gather copy CTA (one thread drives TMA)
+    // Pulls 128-row tiles of the peers' shards (and the own shard) into the local gathered buffer through shared
+    // memory with bulk copies, so each remote byte crosses NVLink exactly once, and publishes one flag per tile.
+    if (threadIdx.x == 0) {
+      constexpr int CHUNK = 32 * 1024;
+      constexpr int NBUF = Cfg::STAGES * Cfg::STAGE_BYTES / CHUNK;   // the whole operand ring is staging space here
+      const int copier = (int)blockIdx.x, n_copiers = n_copy;
+      const long long tile_bytes = (long long)BM * p.K * 2;
+      const int chunks_per_tile = (int)((tile_bytes + CHUNK - 1) / CHUNK);
+      const int tiles_per_rank = p.ag_rows_per_rank / BM;
+      uint32_t issued = 0, landed = 0;   // chunk counters; buffer = counter % NBUF, full_bar doubles as its barrier
+      bool ok = true;
+      // this CTA's tiles, in consumption order
+      for (int mi = copier; mi < p.tiles_m && ok; mi += n_copiers) {
+        const int m_blk = (mi + p.ag_rank * tiles_per_rank) % p.tiles_m;
+        const int owner = m_blk / tiles_per_rank;
+        const char* src = reinterpret_cast<const char*>(p.ag_src[owner]) + (long long)(m_blk % tiles_per_rank) * tile_bytes;
+        char* dst = reinterpret_cast<char*>(p.ag_gathered) + (long long)m_blk * tile_bytes;
+        int next_load = 0, next_store = 0;
+        while (next_store < chunks_per_tile && ok) {
+          while (next_load < chunks_per_tile && issued - landed < (uint32_t)NBUF) {
+            const int buf = issued % NBUF;
+            const long long off = (long long)next_load * CHUNK;
+            const uint32_t bytes = (uint32_t)((tile_bytes - off) < CHUNK ? (tile_bytes - off) : CHUNK);
+            mbar_expect_tx(&copy_bar[buf], bytes);
+            bulk_load_1d(smem + buf * CHUNK, src + off, bytes, &copy_bar[buf]);
+            ++issued;
+            ++next_load;
+          }
+          const int buf = landed % NBUF;
+          if (!mbar_wait(&copy_bar[buf], (landed / NBUF) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+          const long long off = (long long)next_store * CHUNK;
+          const uint32_t bytes = (uint32_t)((tile_bytes - off) < CHUNK ? (tile_bytes - off) : CHUNK);
+          bulk_store_1d(dst + off, smem + buf * CHUNK, bytes);
+          bulk_commit_wait_all();   // the chunk is in local memory and the staging buffer is free again
+          ++landed;
+          ++next_store;
+        }
+        if (ok) {
+          fence_proxy_async_global();
+          __threadfence();
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ag_flags + m_blk), "r"(1u) : "memory");
+        }
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+      for (int u = cta; u < p.total_units && ok; u += n_compute) {
         const Unit w = decode_unit(p, u);
         const int m0 = w.m_blk * BM, n0 = w.n_blk * BN;
+        if (p.ag_world > 1) {
+          // the row block must have been gathered: bounded spin on its flag, then order the async proxy after it
+          const long long t0 = clock64();
+          uint32_t f = 0;
+          for (;;) {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(p.ag_flags + w.m_blk) : "memory");
+            if (f != 0) break;
+            if (*abort_flag || clock64() - t0 > INCIN_WAIT_CLOCKS) {
+              *abort_flag = 1;
+              if (p.status) atomicCAS(p.status, 0, kStatusTimeoutPeer);
+              ok = false;
+              break;
+            }
+            __nanosleep(100);
+          }
+          if (!ok) break;
+          fence_proxy_async_global();
+        }
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) {
             ok = false;
@@ -170,7 +260,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t phase = 0;
       int iter = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x, ++iter) {
+      for (int u = cta; u < p.total_units && ok; u += n_compute, ++iter) {
         const Unit w = decode_unit(p, u);
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1;
@@ -211,7 +301,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     constexpr int CHUNKS_PER_HALF = BN / 64;
     const int row_in_tile = quarter * 32 + lane;
     int iter = 0;
-    for (int u = blockIdx.x; u < p.total_units; u += gridDim.x, ++iter) {
+    for (int u = cta; u < p.total_units; u += n_compute, ++iter) {
       const Unit w = decode_unit(p, u);
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
@@ -220,8 +310,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int m = w.m_blk * BM + row_in_tile;
       const int n0 = w.n_blk * BN;
       const bool row_ok = m < p.M;
-      const long long cbase = (long long)w.b_lo * p.c_stride_lo + (long long)w.b_hi * p.c_stride_hi +
-                              (long long)m * p.ldc;
+      long long cbase = (long long)w.b_lo * p.c_stride_lo + (long long)w.b_hi * p.c_stride_hi +
+                        (long long)m * p.ldc;
+      void* c_ptr = p.C;
+      if (p.rs_world > 1) {
+        // reduce-scatter: this tile belongs to `owner`; write it into this rank's slot of the owner's buffer
+        const int owner = (w.m_blk * BM) / p.rs_rows_per_rank;
+        c_ptr = p.rs_dst[owner];
+        cbase = (long long)p.rs_rank * p.rs_slot_stride + (long long)(m - owner * p.rs_rows_per_rank) * p.ldc;
+      }
       const bool vec_ok = (p.ldc % 8 == 0) && (p.c_stride_lo % 8 == 0) && (p.c_stride_hi % 8 == 0);
 #pragma unroll 1
       for (int c = half * CHUNKS_PER_HALF; c < (half + 1) * CHUNKS_PER_HALF; ++c) {
@@ -330,7 +427,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         if (p.out_fp32) {
-          float* out = reinterpret_cast<float*>(p.C) + cbase + nc;
+          float* out = reinterpret_cast<float*>(c_ptr) + cbase + nc;
           if (p.accumulate) {
             if (full) {
 #pragma unroll
@@ -356,7 +453,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
         } else {
-          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + cbase + nc;
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(c_ptr) + cbase + nc;
           if (full) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -466,7 +563,17 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmKe
     attr_set = true;
   }
   int grid = p.total_units < max_ctas ? p.total_units : max_ctas;
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  GemmKernelParams q = p;
+  if (p.ag_world > 1) {
+    int copy = p.gemm_ctas;   // the caller's request for copy CTAs travels in gemm_ctas until here
+    if (copy < 1) copy = 8;
+    if (copy > max_ctas / 2) copy = max_ctas / 2;
+    int compute = max_ctas - copy;
+    if (compute > p.total_units) compute = p.total_units;
+    q.gemm_ctas = compute;
+    grid = compute + copy;
+  }
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, q);
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
 
@@ -505,7 +612,7 @@ using namespace incin;
 
 extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  if (!d || !d->A || !d->B || !d->C || d->M <= 0 || d->N <= 0 || d->K <= 0) return INCIN_ERR_ARGUMENT;
+  if (!d || !d->A || !d->B || (!d->C && d->rs_world <= 1) || d->M <= 0 || d->N <= 0 || d->K <= 0) return INCIN_ERR_ARGUMENT;
   const int blo = d->batch_lo > 0 ? d->batch_lo : 1;
   const int bhi = d->batch_hi > 0 ? d->batch_hi : 1;
   const int sms = d->max_ctas > 0 ? d->max_ctas : device_sm_count();
@@ -555,6 +662,34 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   p.act = d->act;
   p.aux = reinterpret_cast<__nv_bfloat16*>(d->aux);
   p.status = reinterpret_cast<int*>(d->status);
+  p.ag_world = d->ag_world > 1 ? d->ag_world : 0;
+  p.ag_rank = d->ag_rank;
+  p.ag_rows_per_rank = d->ag_rows_per_rank;
+  p.gemm_ctas = d->ag_copy_ctas;
+  p.ag_flags = reinterpret_cast<uint32_t*>(d->ag_flags);
+  p.ag_gathered = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(d->A));
+  p.rs_world = d->rs_world > 1 ? d->rs_world : 0;
+  p.rs_rank = d->rs_rank;
+  p.rs_rows_per_rank = d->rs_rows_per_rank;
+  p.rs_slot_stride = d->rs_slot_stride;
+  for (int r = 0; r < 8; ++r) {
+    p.ag_src[r] = reinterpret_cast<const __nv_bfloat16*>(d->ag_src[r]);
+    p.rs_dst[r] = reinterpret_cast<__nv_bfloat16*>(d->rs_dst[r]);
+  }
+  if (p.ag_world) {
+    if (p.ag_world > 8 || d->a_mn_major || d->lda != d->K || (d->K % 8) || p.ag_rows_per_rank % BM ||
+        d->M != p.ag_world * p.ag_rows_per_rank || !p.ag_flags || splits != 1 || blo * bhi != 1)
+      return INCIN_ERR_ARGUMENT;
+    for (int r = 0; r < p.ag_world; ++r)
+      if (!p.ag_src[r]) return INCIN_ERR_ARGUMENT;
+  }
+  if (p.rs_world) {
+    if (p.rs_world > 8 || d->out_fp32 || p.rs_rows_per_rank % BM || d->M != p.rs_world * p.rs_rows_per_rank ||
+        splits != 1 || blo * bhi != 1 || d->residual || d->aux)
+      return INCIN_ERR_ARGUMENT;
+    for (int r = 0; r < p.rs_world; ++r)
+      if (!p.rs_dst[r]) return INCIN_ERR_ARGUMENT;
+  }
 
   const bool amn = d->a_mn_major != 0, bmn = d->b_mn_major != 0;
   int rc2;

@@ -56,6 +56,10 @@ class GemmDesc(C.Structure):
         ("out_fp32", c_int), ("accumulate", c_int), ("alpha", c_float),
         ("bias", c_void_p), ("residual", c_void_p), ("act", c_int), ("aux", c_void_p),
         ("splits", c_int), ("tile_n", c_int), ("max_ctas", c_int), ("status", c_void_p),
+        ("ag_world", c_int), ("ag_rank", c_int), ("ag_rows_per_rank", c_int), ("ag_copy_ctas", c_int),
+        ("ag_src", c_void_p * 8), ("ag_flags", c_void_p),
+        ("rs_world", c_int), ("rs_rank", c_int), ("rs_rows_per_rank", c_int), ("rs_pad_", c_int),
+        ("rs_dst", c_void_p * 8), ("rs_slot_stride", c_ll),
     ]
 
 
@@ -89,6 +93,7 @@ _CUDA_SIGS = {
     "incin_philox_normal_f32": (c_int, [c_void_p, c_ll, c_u64, c_u64, c_float, c_float, c_void_p]),
     "incin_philox_normal_bf16": (c_int, [c_void_p, c_ll, c_u64, c_u64, c_float, c_float, c_void_p]),
     "incin_dropout_bf16": (c_int, [c_void_p, c_void_p, c_ll, c_float, c_u64, c_u64, c_void_p]),
+    "incin_slot_reduce": (c_int, [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_ll, c_void_p]),
     "incin_sm100_version": (C.c_char_p, []),
     "incin_sm100_num_sms": (c_int, []),
 }

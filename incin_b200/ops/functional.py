@@ -496,3 +496,25 @@ def conv2d_im2col(x, w, b, stride, padding, dilation):
     y = linear(a, wk.contiguous(), b)
     oh = (H + 2 * padding[0] - dilation[0] * (KH - 1) - 1) // stride[0] + 1
     return y.reshape(N, L, O).transpose(1, 2).reshape(N, O, oh, L // oh)
+
+
+def _gqa_cpu(qkv, Hq, Hkv, D, scale):
+    B, T, _ = qkv.shape
+    x = qkv.view(B, T, Hq + 2 * Hkv, D)
+    q = x[:, :, :Hq].transpose(1, 2)
+    k = x[:, :, Hq:Hq + Hkv].transpose(1, 2).repeat_interleave(Hq // Hkv, dim=1)
+    v = x[:, :, Hq + Hkv:].transpose(1, 2).repeat_interleave(Hq // Hkv, dim=1)
+    o = TF.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale)
+    return o.transpose(1, 2).reshape(B, T, Hq * D)
+
+
+def gqa_attention(qkv, n_heads: int, n_kv_heads: int, head_dim: int, scale: float | None = None):
+    """Causal grouped-query attention over a packed ``[B, T, (Hq + 2 Hkv) * D]`` projection (query heads first,
+    then key heads, then value heads) -> ``[B, T, Hq * D]``."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    if _nat(qkv):
+        from . import attention as A
+        if A.flash_supported(qkv, n_heads, head_dim, n_kv_heads):
+            return A.flash_attention_packed(qkv, n_heads, head_dim, scale, n_kv_heads)
+        raise nat.NativeError("no attention kernel for this head configuration (head_dim must be 64 or 128)")
+    return _gqa_cpu(qkv, n_heads, n_kv_heads, head_dim, scale)

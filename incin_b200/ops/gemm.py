@@ -62,11 +62,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
          c_strides: tuple[int, int] = (0, 0), accumulate: bool = False, alpha: float = 1.0,
          bias: torch.Tensor | None = None, residual: torch.Tensor | None = None, act: int = nat.ACT_NONE,
          aux: torch.Tensor | None = None, splits: int = 1, tile_n: int = 0, max_ctas: int = 0,
-         a_offset: int = 0, b_offset: int = 0, c_offset: int = 0) -> torch.Tensor:
-    """Launch one (batched) GEMM on the current stream.  Offsets/strides are in elements."""
+         a_offset: int = 0, b_offset: int = 0, c_offset: int = 0, gather: dict | None = None,
+         scatter: dict | None = None) -> torch.Tensor:
+    """Launch one (batched) GEMM on the current stream.  Offsets/strides are in elements.
+    ``gather`` = {world, rank, rows_per_rank, src: [ptr]*world, flags: tensor, copy_ctas} turns the launch into the
+    fused all-gather -> GEMM (``a`` is then the local gathered buffer); ``scatter`` = {world, rank, rows_per_rank,
+    dst: [ptr]*world, slot_stride} makes the epilogue store partial tiles into the owners' slot buffers."""
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "operands must be bf16"
     assert out.dtype in (torch.bfloat16, torch.float32)
-    if tile_n == 0 and not accumulate:
+    if tile_n == 0 and not accumulate and gather is None and scatter is None:
         tile_n = _tuned_tile_n(locals())
     d = nat.GemmDesc()
     d.A = a.data_ptr() + 2 * a_offset
@@ -90,6 +94,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
     d.tile_n = tile_n
     d.max_ctas = max_ctas
     d.status = status_word(a.device).data_ptr()
+    if gather is not None:
+        d.ag_world, d.ag_rank, d.ag_rows_per_rank = gather["world"], gather["rank"], gather["rows_per_rank"]
+        d.ag_copy_ctas = gather.get("copy_ctas", 8)
+        for r, ptr in enumerate(gather["src"]):
+            d.ag_src[r] = ptr
+        d.ag_flags = gather["flags"].data_ptr()
+    if scatter is not None:
+        d.rs_world, d.rs_rank, d.rs_rows_per_rank = scatter["world"], scatter["rank"], scatter["rows_per_rank"]
+        for r, ptr in enumerate(scatter["dst"]):
+            d.rs_dst[r] = ptr
+        d.rs_slot_stride = scatter["slot_stride"]
     nat.check(nat.cuda().incin_gemm_bf16(ctypes.byref(d), nat.stream_ptr()), "gemm")
     return out
 

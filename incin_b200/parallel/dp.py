@@ -177,7 +177,9 @@ class FusedReducer:
 def make_reducer(kind: str, device: torch.device, group=None):
     """Returns ``(reducer, allocator, description)`` for ``bench.py`` / the Trainer."""
     if kind in ("fused", "fused-overlap"):
-        r = FusedReducer(device, group, overlap=True)
+        import os
+        r = FusedReducer(device, group, overlap=True, ctas_overlap=int(os.environ.get("INCIN_DP_OVERLAP_CTAS", "8")),
+                         bucket_elems=int(os.environ.get("INCIN_DP_BUCKET_ELEMS", str(16 << 20))))
         return r, r.allocator, r.kind + " overlapped with backward"
     if kind in ("auto", "fused-tail"):
         r = FusedReducer(device, group, overlap=False)

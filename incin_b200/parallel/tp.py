@@ -1,0 +1,203 @@
+"""Tensor parallelism with sequence-sharded activations, lowered onto two fused kernels.
+
+Between layers an activation ``[M, C]`` (M = all tokens of the step) is ``Sharded(0)`` over the tensor-parallel
+group: every rank holds ``M / tp`` rows.
+
+* column-parallel linear (QKV, gate/up; weight ``Sharded(0)`` over outputs):  ``Sharded(0) -> Replicated`` input
+  transition fused into the GEMM — copy CTAs of the same launch pull the peers' row shards into local memory by
+  bulk copies while the remaining CTAs run tcgen05 tiles on the rows that have arrived
+  (``incin_gemm_bf16`` with ``gather``);
+* row-parallel linear (attention output, FFN down; weight ``Sharded(1)`` over inputs): the product is
+  ``Partial(Sum)`` and goes ``-> Sharded(0)``: the GEMM epilogue stores each 128-row tile as bf16 into this rank's
+  slot of the OWNER's buffer over NVLink peer stores (``scatter``), then the owner sums the slots (+ residual).
+
+The backward of each is the other one (all-gather <-> reduce-scatter are adjoint), so the same two kernels serve
+both passes.  Buffers that peers read or write live in peer-mapped memory and alternate between two parities;
+one barrier kernel (``incin_peer_barrier``) per fused op orders "my shard is written" / "your slots are complete"
+against the peers' streams.  No NCCL call is on this path.
+
+Reference: crates/incin-core/src/dist/tensor_parallel.rs (ColumnOutputGather / RowOutputSum) executed as
+ncclAllGather / ncclAllReduce plus separate SGEMMs and reshapes (crates/incin-backends/src/dist/nccl.rs:642-791,
+1187-1229), two ranks only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from .. import _native as nat
+from ..ops import gemm as G
+from ..ops import kernels as K
+from ..ops.functional import _ready, main_grad
+from ..ops.gemm import status_word
+from .symm import SymmetricBuffer
+
+nat.register_cuda_signatures({
+    "incin_peer_barrier": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "incin_barrier_pad_bytes": (C.c_int, []),
+    "incin_peer_sum_ranges": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+})
+
+
+class TensorParallel:
+    """Per-process context of one tensor-parallel group (all ranks of ``group`` on one NVSwitch node)."""
+
+    def __init__(self, device: torch.device, group=None, *, max_rows_per_rank: int, max_cols: int, copy_ctas: int = 8):
+        self.device, self.group = device, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("a tensor-parallel group spans at most the 8 GPUs of one node")
+        if max_rows_per_rank % 128:
+            raise ValueError("rows per rank must be a multiple of 128 (one GEMM tile never straddles two owners)")
+        self.rows, self.cols, self.copy_ctas = max_rows_per_rank, max_cols, copy_ctas
+        shard_bytes = max_rows_per_rank * max_cols * 2
+        self.shard = [SymmetricBuffer(shard_bytes, device).exchange(group) for _ in range(2)]
+        self.slots = [SymmetricBuffer(self.world * shard_bytes, device).exchange(group) for _ in range(2)]
+        self.pad = SymmetricBuffer(nat.cuda().incin_barrier_pad_bytes(), device).exchange(group)
+        self._pad_ptrs = torch.tensor(self.pad.ptrs, dtype=torch.int64, device=device)
+        self._shard_parity = self._slot_parity = 0
+        self._barrier_slot = 0
+        dist.barrier(group=group)
+
+    # ------------------------------------------------------------------------------------------------ primitives
+    def barrier(self) -> None:
+        """Cross-GPU barrier as one tiny kernel on the current stream (bounded waits, status word on timeout)."""
+        nat.check(nat.cuda().incin_peer_barrier(self._pad_ptrs.data_ptr(), self.world, self.rank, 0,
+                                               status_word(self.device).data_ptr(), nat.stream_ptr()), "peer_barrier")
+
+    def gather_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, out: torch.Tensor | None = None,
+                    ldc: int | None = None, c_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+        """``(all_gather(x_shard) @ W^T, gathered)``: x_shard ``[Ml, Kd]`` bf16, W ``[N, Kd]`` (or ``[Kd, N]`` with
+        ``b_mn``).  Returns the product ``[tp*Ml, N]`` and the gathered input (kept for the weight gradient)."""
+        Ml, Kd = x_shard.shape
+        if Ml % 128 or Ml > self.rows or Kd > self.cols or Kd % 8:
+            raise ValueError(f"shard [{Ml}, {Kd}] does not fit the tensor-parallel buffers [{self.rows}, {self.cols}]")
+        p = self._shard_parity
+        self._shard_parity ^= 1
+        buf = self.shard[p]
+        buf.typed(torch.bfloat16, Ml * Kd).view(Ml, Kd).copy_(x_shard)
+        self.barrier()   # every peer's shard of this parity is written; every peer is done with this parity's last use
+        M = Ml * self.world
+        N = w.shape[1] if b_mn else w.shape[0]
+        gathered = torch.empty(M, Kd, dtype=torch.bfloat16, device=self.device)
+        flags = torch.zeros(M // 128, dtype=torch.int32, device=self.device)
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=self.device)
+            ldc = N
+        G.gemm(gathered, w, out, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=ldc, b_mn=b_mn, c_offset=c_offset,
+               gather={"world": self.world, "rank": self.rank, "rows_per_rank": Ml, "src": buf.ptrs, "flags": flags,
+                       "copy_ctas": self.copy_ctas})
+        return out, gathered
+
+    def gemm_scatter(self, a: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False,
+                     residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``reduce_scatter(a @ W^T) (+ residual)``: a ``[M, Kd]`` (full rows, local K shard), W ``[N, Kd]`` (or
+        ``[Kd, N]`` with ``b_mn``) -> ``[M / tp, N]`` rows owned by this rank."""
+        M, Kd = a.shape
+        N = w.shape[1] if b_mn else w.shape[0]
+        Ml = M // self.world
+        if M % self.world or Ml % 128 or Ml > self.rows or N > self.cols or N % 8:
+            raise ValueError(f"product [{M}, {N}] does not fit the tensor-parallel buffers")
+        p = self._slot_parity
+        self._slot_parity ^= 1
+        buf = self.slots[p]
+        G.gemm(a, w, a, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=N, b_mn=b_mn,
+               scatter={"world": self.world, "rank": self.rank, "rows_per_rank": Ml, "dst": buf.ptrs,
+                        "slot_stride": Ml * N})
+        self.barrier()   # every peer's tiles for my rows have landed in my slot buffer
+        out = torch.empty(Ml, N, dtype=torch.bfloat16, device=self.device)
+        nat.check(nat.cuda().incin_slot_reduce(buf.ptr, Ml * N, self.world, nat.ptr(residual), out.data_ptr(), Ml, N, N,
+                                              nat.stream_ptr()), "slot_reduce")
+        return out
+
+
+# ---------------------------------------------------------------------------------------------------- autograd
+class _ColumnParallel(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_shard, tp: TensorParallel, *weights):
+        x_shard = x_shard.contiguous()
+        n_total = sum(w.shape[0] for w in weights)
+        M = x_shard.shape[0] * tp.world
+        out = torch.empty(M, n_total, dtype=torch.bfloat16, device=x_shard.device)
+        _, gathered = tp.gather_gemm(x_shard, weights[0], out=out, ldc=n_total, c_offset=0)
+        off = weights[0].shape[0]
+        for w in weights[1:]:      # further weights reuse the gathered rows: plain local GEMMs
+            G.gemm(gathered, w, out, M=M, N=w.shape[0], K=w.shape[1], lda=w.shape[1], ldb=w.shape[1], ldc=n_total,
+                   c_offset=off)
+            off += w.shape[0]
+        ctx.save_for_backward(gathered, *weights)
+        ctx.tp = tp
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        gathered, *weights = ctx.saved_tensors
+        tp, dy = ctx.tp, dy.contiguous()
+        M, n_total = dy.shape
+        Kd = gathered.shape[1]
+        # weight gradients from the gathered input
+        off = 0
+        for w in weights:
+            n = w.shape[0]
+            if w.requires_grad:
+                G.gemm(dy, gathered, main_grad(w), M=n, N=Kd, K=M, lda=n_total, ldb=Kd, ldc=Kd, a_mn=True, b_mn=True,
+                       accumulate=True, splits=G.auto_splits(n, Kd, M), a_offset=off)
+                _ready(w)
+            off += n
+        # dx = dy @ [W0; W1; ...]: partial over the output shards -> reduce-scatter over rows
+        if len(weights) == 1:
+            dx = tp.gemm_scatter(dy, weights[0], b_mn=True)
+        else:
+            wcat = torch.cat(list(weights), dim=0)
+            dx = tp.gemm_scatter(dy, wcat, b_mn=True)
+        return (dx, None) + (None,) * len(weights)
+
+
+class _RowParallel(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, tp: TensorParallel, w, residual_shard):
+        a = a.contiguous()
+        ctx.save_for_backward(a, w)
+        ctx.tp, ctx.has_res = tp, residual_shard is not None
+        return tp.gemm_scatter(a, w, residual=residual_shard.contiguous() if residual_shard is not None else None)
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        a, w = ctx.saved_tensors
+        tp, dy_shard = ctx.tp, dy_shard.contiguous()
+        # da = all_gather(dy) @ W   (W is [N, Kd]: read MN-major);  dW += all_gather(dy)^T @ a
+        da, dy_full = tp.gather_gemm(dy_shard, w, b_mn=True)
+        if w.requires_grad:
+            M, N = dy_full.shape
+            Kd = a.shape[1]
+            G.gemm(dy_full, a, main_grad(w), M=N, N=Kd, K=M, lda=N, ldb=Kd, ldc=Kd, a_mn=True, b_mn=True,
+                   accumulate=True, splits=G.auto_splits(N, Kd, M))
+            _ready(w)
+        return da, None, None, (dy_shard if ctx.has_res else None)
+
+
+def column_parallel_linear(x_shard, tp: TensorParallel, *weights):
+    """``all_gather(x_shard) @ cat(weights)^T`` -> ``[M, sum(out_i)]`` (columns of this rank's weight shards)."""
+    return _ColumnParallel.apply(x_shard, tp, *weights)
+
+
+def row_parallel_linear(a, tp: TensorParallel, w, residual_shard=None):
+    """``reduce_scatter(a @ w^T) + residual_shard`` -> ``[M / tp, N]``."""
+    return _RowParallel.apply(a, tp, w, residual_shard)
+
+
+def peer_sum_ranges(bufs: SymmetricBuffer, ranges: list[tuple[int, int]], group_ranks: list[int], my_rank: int,
+                    tp: TensorParallel, scratch: torch.Tensor, device) -> None:
+    """In-place all-reduce(sum) of fp32 element ranges of a peer-mapped buffer over a sub-group of ranks."""
+    order = sorted(group_ranks)
+    bases0 = torch.tensor([bufs.ptrs[r] for r in order], dtype=torch.int64, device=device)
+    bases1 = torch.tensor([bufs.ptrs[my_rank]], dtype=torch.int64, device=device)
+    rt = torch.tensor(ranges, dtype=torch.int64, device=device).reshape(-1)
+    tp.barrier()
+    nat.check(nat.cuda().incin_peer_sum_ranges(bases0.data_ptr(), len(order), rt.data_ptr(), len(ranges),
+                                              scratch.data_ptr(), 0, nat.stream_ptr()), "peer_sum_ranges")
+    tp.barrier()
+    nat.check(nat.cuda().incin_peer_sum_ranges(bases1.data_ptr(), 1, rt.data_ptr(), len(ranges), scratch.data_ptr(), 1,
+                                              nat.stream_ptr()), "peer_sum_ranges")

@@ -1,0 +1,93 @@
+"""Worker for the multi-GPU tensor-parallel test (torch.distributed.run, one rank per GPU).
+
+Checks the two fused kernels against plain math (all-gather -> GEMM, GEMM -> reduce-scatter), then trains a tiny
+Llama tensor-parallel and compares loss and parameters with the same model trained on one GPU."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def rel(a, b):
+    return (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-6)
+
+
+def main():
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    from incin_b200.engine import TrainStep
+    from incin_b200.models.llama import Llama, LlamaConfig
+    from incin_b200.models.llama_tp import LlamaTP, TPOptimizer
+    from incin_b200.ops import gemm as G
+    from incin_b200.optim import AdamW, make_store
+    from incin_b200.parallel.tp import TensorParallel
+    out = {"world": world}
+
+    # ---- kernel level
+    Ml, Kd, N = 256, 320, 448
+    tp = TensorParallel(dev, max_rows_per_rank=Ml, max_cols=max(Kd, N, 512))
+    g = torch.Generator().manual_seed(7)
+    x_full = (torch.randn(world * Ml, Kd, generator=g)).to(torch.bfloat16).to(dev)
+    w = (torch.randn(N, Kd, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+    for it in range(3):   # repeated: exercises buffer parities and barrier epochs
+        y, gathered = tp.gather_gemm(x_full[rank * Ml:(rank + 1) * Ml].contiguous(), w)
+        G.check_status()
+        out[f"ag_gemm_{it}"] = max(rel(y, x_full.float() @ w.float().t()), rel(gathered, x_full))
+    a = (torch.randn(world * Ml, Kd, generator=torch.Generator().manual_seed(100 + rank))).to(torch.bfloat16).to(dev)
+    res = torch.randn(Ml, N, generator=g).to(torch.bfloat16).to(dev)
+    for it in range(3):
+        ys = tp.gemm_scatter(a, w, residual=res)
+        G.check_status()
+        part = (a.float() @ w.float().t())
+        dist.all_reduce(part)
+        out[f"gemm_rs_{it}"] = rel(ys, part[rank * Ml:(rank + 1) * Ml] + res.float())
+
+    # ---- model level
+    for name, kvh in (("sharded_kv", 2), ("shared_kv", 1)):
+        cfg = LlamaConfig(vocab_size=512, n_layer=2, d_model=256, n_head=4, n_kv_head=kvh, head_dim=64, d_ffn=512)
+        B, T = 4, 128
+        tpm = TensorParallel(dev, max_rows_per_rank=B * T // world, max_cols=cfg.d_model)
+        gg = torch.Generator().manual_seed(3)
+        tok = torch.randint(0, cfg.vocab_size, (B, T), generator=gg).to(dev)
+        tgt = torch.randint(0, cfg.vocab_size, (B, T), generator=gg).to(dev)
+        ref = Llama(cfg, seed=0).to(dev)
+        ref_opt = AdamW(make_store(ref), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+        ref_step = TrainStep(ref, ref_opt, use_graph=False)
+        m = LlamaTP.from_seed(cfg, world, rank, seed=0).to(dev)
+        m.tp = tpm
+        opt = TPOptimizer(m, tpm, dev, lr=1e-3)
+        step = TrainStep(m, opt, use_graph=False)
+        lr_, lt_ = [], []
+        for _ in range(4):
+            lr_.append(float(ref_step(tok, tgt)))
+            l = step(tok, tgt).clone()
+            dist.all_reduce(l)
+            lt_.append(float(l))
+        G.check_status()
+        full_q = dict(ref.named_parameters())["blocks.1.qkv_w"][: cfg.n_head * 64]
+        mine = dict(m.named_parameters())["blocks.1.q_w"]
+        hq = cfg.n_head // world * 64
+        out[name] = {"loss_ref": lr_, "loss_tp": lt_, "q_w_diff": rel(mine, full_q[rank * hq:(rank + 1) * hq]),
+                     "embed_diff": rel(m.embed, ref.embed)}
+    ok = all(v < 2e-2 for k, v in out.items() if k.startswith(("ag_", "gemm_")))
+    for name in ("sharded_kv", "shared_kv"):
+        r = out[name]
+        ok = ok and all(abs(a - b) < 5e-2 for a, b in zip(r["loss_ref"], r["loss_tp"])) and r["loss_tp"][-1] < r["loss_tp"][0]
+        ok = ok and r["q_w_diff"] < 5e-2 and r["embed_diff"] < 5e-2
+    out["ok"] = ok
+    if rank == 0:
+        print("TP_RESULT " + json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()
