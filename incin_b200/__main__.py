@@ -1,0 +1,89 @@
+"""Command line (the role of ``cargo incin``: doctor | plan | tune | inspect | new | watch | capabilities | build).
+
+    python -m incin_b200 doctor [--json]
+    python -m incin_b200 plan --world 8 --params 1.1e9 --layers 22 --hidden 2048 --batch 16 --seq 2048 --shard 32
+    python -m incin_b200 inspect model.safetensors
+    python -m incin_b200 watch run.jsonl
+    python -m incin_b200 new my_project
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+from pathlib import Path
+
+TEMPLATE = '''"""{name}: a minimal incin_b200 training script."""
+import torch
+from incin_b200 import nn
+from incin_b200.data import DataLoader, TensorDataset
+from incin_b200.optim import SGD, make_store
+from incin_b200.train import Trainer
+
+nn.manual_seed(0)
+model = nn.seq(nn.Linear(784, 256), nn.ReLU(), nn.Linear(256, 10))
+opt = SGD(make_store(model), lr=0.01)
+x, y = torch.randn(640, 784), torch.randint(0, 10, (640,))
+plan = Trainer.plan().epochs(2).build()
+print(plan.explain())
+losses = Trainer(plan).fit(model, opt, DataLoader(TensorDataset(x, y), 64),
+                           lambda m, a, b: nn.cross_entropy_loss(m(a), b))
+print("final loss", losses[-1])
+'''
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="incin_b200")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    d = sub.add_parser("doctor"); d.add_argument("--json", action="store_true")
+    sub.add_parser("capabilities")
+    sub.add_parser("build")
+    sub.add_parser("tune")
+    p = sub.add_parser("plan")
+    p.add_argument("--world", type=int, default=8); p.add_argument("--params", type=float, default=1.1e9)
+    p.add_argument("--layers", type=int, default=22); p.add_argument("--hidden", type=int, default=2048)
+    p.add_argument("--batch", type=int, default=16); p.add_argument("--seq", type=int, default=2048)
+    p.add_argument("--shard", type=int, default=32); p.add_argument("--objective", default="step_time")
+    i = sub.add_parser("inspect"); i.add_argument("path")
+    w = sub.add_parser("watch"); w.add_argument("path"); w.add_argument("--once", action="store_true")
+    n = sub.add_parser("new"); n.add_argument("name")
+    a = ap.parse_args(argv)
+    if a.cmd == "doctor":
+        from .doctor import doctor
+        rep = doctor()
+        print(rep.to_json() if a.json else rep.to_text())
+        return 0 if rep.healthy else 1
+    if a.cmd == "capabilities":
+        from .doctor import capability_report
+        print(capability_report())
+    elif a.cmd == "build":
+        from . import build
+        print(build())
+    elif a.cmd == "tune":
+        from .doctor import tune_report
+        print(tune_report())
+    elif a.cmd == "plan":
+        from .doctor import plan_report
+        print(plan_report(a.world, params=int(a.params), layers=a.layers, hidden=a.hidden, batch=a.batch, seq=a.seq,
+                          shard_extent=a.shard, objective=a.objective))
+    elif a.cmd == "inspect":
+        from .io import inspect_file
+        print(inspect_file(a.path))
+    elif a.cmd == "watch":
+        from .telemetry.viz import render, watch
+        if a.once:
+            print(render(a.path))
+        else:
+            watch(a.path)
+    elif a.cmd == "new":
+        d = Path(a.name)
+        if d.exists():
+            print(f"{d} already exists", file=sys.stderr)
+            return 1
+        d.mkdir(parents=True)
+        (d / "train.py").write_text(TEMPLATE.format(name=a.name))
+        print(f"created {d}/train.py")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

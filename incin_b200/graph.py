@@ -1,0 +1,257 @@
+"""Graph IR, op tracing and the compiled-graph layer.
+
+Counterparts: crates/incin-core/src/graph.rs (``Graph`` / ``OpType``), tensor/tracing.rs (``TracingBackend``
+records every op into a process-wide graph; ``extract_graph`` / ``tracing_graph_snapshot``) and
+crates/incin-core/src/compiled (``CapturedGraph::capture``, ``FusionPass``, ``ShapeBucket``, ``CompiledPlan`` +
+``ShapeGuard``, ``AllocationPlanner`` / ``LivenessMap`` / ``MemoryPlan``, ``CompiledArtifact`` with an Adler-32
+header, ``ReproducibilityManifest``).
+
+Tracing here hooks PyTorch's dispatcher (``TorchDispatchMode``) instead of wrapping a backend type, so any model
+code is traceable unchanged.  The fusion pass groups maximal chains of pointwise ops (the reference fuses adjacent
+pairs) and lowers each chain to one kernel of :mod:`incin_b200.codegen`.  The execution-side counterpart of a
+compiled plan is the CUDA-graph capture in :class:`incin_b200.engine.TrainStep`; ``CompiledPlan`` carries the shape
+guard that decides whether a captured graph may be replayed for a new input.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import struct
+import zlib
+from dataclasses import asdict, dataclass, field
+
+import torch
+from torch.utils._python_dispatch import TorchDispatchMode
+
+POINTWISE = {"add", "sub", "mul", "div", "relu", "gelu", "silu", "sigmoid", "tanh", "exp", "log", "sqrt", "neg", "abs",
+             "rsqrt", "clamp", "pow", "maximum", "minimum", "where", "mish", "elu", "softplus", "sign", "reciprocal"}
+
+
+@dataclass
+class Node:
+    id: int
+    op: str
+    inputs: list[int]
+    shape: tuple[int, ...]
+    dtype: str
+    attrs: dict = field(default_factory=dict)
+
+
+class Graph:
+    def __init__(self):
+        self.nodes: list[Node] = []
+        self.inputs: list[int] = []
+        self.outputs: list[int] = []
+
+    def add(self, op: str, inputs, shape, dtype: str, **attrs) -> int:
+        nid = len(self.nodes)
+        self.nodes.append(Node(nid, op, list(inputs), tuple(shape), dtype, attrs))
+        return nid
+
+    def to_list(self) -> list[dict]:
+        return [asdict(n) for n in self.nodes]
+
+    def digest(self) -> str:
+        return hashlib.sha256(json.dumps(self.to_list(), sort_keys=True, default=str).encode()).hexdigest()
+
+    def consumers(self) -> dict[int, list[int]]:
+        out: dict[int, list[int]] = {n.id: [] for n in self.nodes}
+        for n in self.nodes:
+            for i in n.inputs:
+                out[i].append(n.id)
+        return out
+
+
+class _Tracer(TorchDispatchMode):
+    def __init__(self, graph: Graph):
+        super().__init__()
+        self.g = graph
+        self.ids: dict[int, int] = {}
+
+    def _id(self, t: torch.Tensor) -> int:
+        key = id(t)
+        if key not in self.ids:
+            self.ids[key] = self.g.add("input", [], t.shape, str(t.dtype).replace("torch.", ""))
+            self.g.inputs.append(self.ids[key])
+        return self.ids[key]
+
+    def __torch_dispatch__(self, func, types, args=(), kwargs=None):
+        out = func(*args, **(kwargs or {}))
+        name = func.__name__.split(".")[0].rstrip("_")
+        ins = [self._id(a) for a in args if isinstance(a, torch.Tensor)]
+        for a in args:
+            if isinstance(a, (list, tuple)):
+                ins += [self._id(x) for x in a if isinstance(x, torch.Tensor)]
+        outs = out if isinstance(out, (list, tuple)) else [out]
+        for o in outs:
+            if isinstance(o, torch.Tensor):
+                self.ids[id(o)] = self.g.add(name, ins, o.shape, str(o.dtype).replace("torch.", ""))
+        self._keep = getattr(self, "_keep", []) + [o for o in outs if isinstance(o, torch.Tensor)]  # ids stay unique
+        return out
+
+
+_TRACING_GRAPH: Graph | None = None
+
+
+def trace(fn, *args) -> Graph:
+    """Run ``fn(*args)`` once and record every dispatched op (``CapturedGraph::capture``)."""
+    global _TRACING_GRAPH
+    g = Graph()
+    tr = _Tracer(g)
+    for a in args:
+        if isinstance(a, torch.Tensor):
+            tr._id(a)
+    with tr:
+        out = fn(*args)
+    outs = out if isinstance(out, (list, tuple)) else [out]
+    g.outputs = [tr.ids[id(o)] for o in outs if isinstance(o, torch.Tensor) and id(o) in tr.ids]
+    _TRACING_GRAPH = g
+    return g
+
+
+def tracing_graph_snapshot() -> Graph | None:
+    return _TRACING_GRAPH
+
+
+# ------------------------------------------------------------------------------------------------ fusion
+@dataclass
+class FusionGroup:
+    nodes: list[int]
+
+
+def fusion_pass(g: Graph) -> list[FusionGroup]:
+    """Maximal chains of pointwise nodes where each intermediate has exactly one consumer and the same shape."""
+    cons = g.consumers()
+    grouped: set[int] = set()
+    groups = []
+    for n in g.nodes:
+        if n.op not in POINTWISE or n.id in grouped:
+            continue
+        chain = [n.id]
+        cur = n
+        while True:
+            nxt = cons[cur.id]
+            if len(nxt) != 1:
+                break
+            c = g.nodes[nxt[0]]
+            if c.op not in POINTWISE or c.shape != cur.shape or c.id in grouped:
+                break
+            chain.append(c.id)
+            cur = c
+        if len(chain) > 1:
+            groups.append(FusionGroup(chain))
+            grouped.update(chain)
+    return groups
+
+
+# ------------------------------------------------------------------------------------------------ memory planning
+@dataclass
+class MemoryPlan:
+    offsets: dict[int, int]
+    peak_bytes: int
+    naive_bytes: int
+
+
+_ESZ = {"float32": 4, "bfloat16": 2, "float16": 2, "int64": 8, "int32": 4, "uint8": 1, "bool": 1, "float64": 8}
+
+
+def liveness(g: Graph) -> dict[int, tuple[int, int]]:
+    """node id -> (first, last) position it is alive; graph outputs live to the end."""
+    last = {n.id: n.id for n in g.nodes}
+    for n in g.nodes:
+        for i in n.inputs:
+            last[i] = max(last[i], n.id)
+    for o in g.outputs:
+        last[o] = len(g.nodes)
+    return {n.id: (n.id, last[n.id]) for n in g.nodes}
+
+
+def plan_memory(g: Graph, align: int = 256) -> MemoryPlan:
+    """Greedy first-fit reuse of a single arena by liveness (``AllocationPlanner``)."""
+    live = liveness(g)
+    size = {}
+    for n in g.nodes:
+        numel = 1
+        for d in n.shape:
+            numel *= d
+        size[n.id] = (numel * _ESZ.get(n.dtype, 4) + align - 1) // align * align
+    placed: list[tuple[int, int, int, int]] = []   # (offset, size, first, last)
+    offsets, peak = {}, 0
+    for n in g.nodes:
+        if n.op == "input":
+            continue
+        f, l = live[n.id]
+        busy = sorted((o, s) for o, s, pf, pl in placed if not (pl < f or pf > l))
+        off = 0
+        for o, s in busy:
+            if off + size[n.id] <= o:
+                break
+            off = max(off, o + s)
+        offsets[n.id] = off
+        placed.append((off, size[n.id], f, l))
+        peak = max(peak, off + size[n.id])
+    return MemoryPlan(offsets, peak, sum(size[n.id] for n in g.nodes if n.op != "input"))
+
+
+# ------------------------------------------------------------------------------------------------ plans / artifacts
+def shape_bucket(n: int, base: int = 64) -> int:
+    """Round a dynamic extent up to its bucket (powers of two times ``base``) so nearby shapes share a plan."""
+    b = base
+    while b < n:
+        b *= 2
+    return b
+
+
+@dataclass
+class ShapeGuard:
+    shapes: tuple[tuple[int, ...], ...]
+    dtypes: tuple[str, ...]
+
+    def admits(self, *tensors: torch.Tensor) -> bool:
+        return (tuple(tuple(t.shape) for t in tensors) == self.shapes and
+                tuple(str(t.dtype).replace("torch.", "") for t in tensors) == self.dtypes)
+
+
+@dataclass
+class CompiledPlan:
+    graph_digest: str
+    guard: ShapeGuard
+    fusion_groups: list[list[int]]
+    memory: MemoryPlan
+
+    @staticmethod
+    def build(fn, *args) -> "CompiledPlan":
+        g = trace(fn, *args)
+        ts = [a for a in args if isinstance(a, torch.Tensor)]
+        guard = ShapeGuard(tuple(tuple(t.shape) for t in ts), tuple(str(t.dtype).replace("torch.", "") for t in ts))
+        return CompiledPlan(g.digest(), guard, [fg.nodes for fg in fusion_pass(g)], plan_memory(g))
+
+
+MAGIC = b"INCINCG1"
+
+
+def write_artifact(path, plan: CompiledPlan, manifest: dict | None = None) -> None:
+    """``magic | adler32(payload) | length | payload(json)``: a torn or edited file fails the checksum on load."""
+    payload = json.dumps({"plan": {"graph_digest": plan.graph_digest, "guard": asdict(plan.guard),
+                                   "fusion_groups": plan.fusion_groups, "memory": asdict(plan.memory)},
+                          "manifest": manifest or reproducibility_manifest()}).encode()
+    with open(path, "wb") as f:
+        f.write(MAGIC + struct.pack("<IQ", zlib.adler32(payload), len(payload)) + payload)
+
+
+def read_artifact(path) -> dict:
+    raw = open(path, "rb").read()
+    if raw[:8] != MAGIC:
+        raise ValueError("not a compiled-graph artifact")
+    chk, n = struct.unpack_from("<IQ", raw, 8)
+    payload = raw[20:20 + n]
+    if len(payload) != n or zlib.adler32(payload) != chk:
+        raise ValueError("compiled-graph artifact failed its checksum")
+    return json.loads(payload)
+
+
+def reproducibility_manifest() -> dict:
+    from . import __version__
+    from .core.policy import current_policy
+    return {"incin_b200": __version__, "torch": torch.__version__, "cuda": str(torch.version.cuda),
+            "policy": current_policy().cache_key(), "arch": "sm_100a"}

@@ -18,7 +18,7 @@ import torch
 from torch import nn
 
 from ..ops import functional as F
-from ..parallel.tp import TensorParallel, column_parallel_linear, peer_sum_ranges, row_parallel_linear
+from ..parallel.tp import PeerRangeSum, TensorParallel, column_parallel_linear, row_parallel_linear
 from .llama import Llama, LlamaConfig
 
 
@@ -169,10 +169,10 @@ class TPOptimizer:
         if self.kv_share > 1:
             if self.dp_reducer is not None:
                 raise NotImplementedError("shared K/V heads together with a data axis: use n_kv_head >= tp")
-            self._kv_ranges = [(o, k) for n, p, o, k in self.sh_store.entries if n.endswith("kv_w")]
+            ranges = [(o, k) for n, p, o, k in self.sh_store.entries if n.endswith("kv_w")]
             base = (tp.rank // self.kv_share) * self.kv_share
-            self._kv_group = list(range(base, base + self.kv_share))
-            self._kv_scratch = torch.empty(sum(k for _, k in self._kv_ranges), dtype=torch.float32, device=device)
+            self._kv_sum = PeerRangeSum(self._grad_buf, ranges, list(range(base, base + self.kv_share)), tp.rank, tp,
+                                        device)
         self.store = self
         self.lr, self.step_count = lr, 0
 
@@ -204,8 +204,7 @@ class TPOptimizer:
 
     def launch(self) -> None:
         if self.kv_share > 1:
-            peer_sum_ranges(self._grad_buf, self._kv_ranges, self._kv_group, self.tp.rank, self.tp, self._kv_scratch,
-                            self._device)
+            self._kv_sum.run()
         self.rep_reducer.begin_step()
         self.rep_reducer.finish_step(self.rep_opt)
         if self.dp_reducer is not None:

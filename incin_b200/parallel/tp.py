@@ -44,14 +44,21 @@ nat.register_cuda_signatures({
 class TensorParallel:
     """Per-process context of one tensor-parallel group (all ranks of ``group`` on one NVSwitch node)."""
 
-    def __init__(self, device: torch.device, group=None, *, max_rows_per_rank: int, max_cols: int, copy_ctas: int = 8):
+    def __init__(self, device: torch.device, group=None, *, max_rows_per_rank: int, max_cols: int, copy_ctas: int = 0,
+                 mode: str = "fused"):
+        """``mode="nccl"`` is the baseline arm (not the product): the same layers with NCCL all-gather /
+        reduce-scatter as separate launches around the local GEMM."""
+        assert mode in ("fused", "nccl")
+        self.mode = mode
         self.device, self.group = device, group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if self.world > 8:
             raise ValueError("a tensor-parallel group spans at most the 8 GPUs of one node")
         if max_rows_per_rank % 128:
             raise ValueError("rows per rank must be a multiple of 128 (one GEMM tile never straddles two owners)")
-        self.rows, self.cols, self.copy_ctas = max_rows_per_rank, max_cols, copy_ctas
+        self.rows, self.cols = max_rows_per_rank, max_cols
+        # copy CTAs: enough outstanding bulk copies to keep NVLink busy, no more SMs than that taken from the GEMM
+        self.copy_ctas = copy_ctas or min(12, 2 * self.world)
         shard_bytes = max_rows_per_rank * max_cols * 2
         self.shard = [SymmetricBuffer(shard_bytes, device).exchange(group) for _ in range(2)]
         self.slots = [SymmetricBuffer(self.world * shard_bytes, device).exchange(group) for _ in range(2)]
@@ -72,6 +79,16 @@ class TensorParallel:
         """``(all_gather(x_shard) @ W^T, gathered)``: x_shard ``[Ml, Kd]`` bf16, W ``[N, Kd]`` (or ``[Kd, N]`` with
         ``b_mn``).  Returns the product ``[tp*Ml, N]`` and the gathered input (kept for the weight gradient)."""
         Ml, Kd = x_shard.shape
+        if self.mode == "nccl":
+            M = Ml * self.world
+            N = w.shape[1] if b_mn else w.shape[0]
+            gathered = torch.empty(M, Kd, dtype=torch.bfloat16, device=self.device)
+            dist.all_gather_into_tensor(gathered, x_shard.contiguous(), group=self.group)
+            if out is None:
+                out, ldc = torch.empty(M, N, dtype=torch.bfloat16, device=self.device), N
+            G.gemm(gathered, w, out, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=ldc, b_mn=b_mn,
+                   c_offset=c_offset)
+            return out, gathered
         if Ml % 128 or Ml > self.rows or Kd > self.cols or Kd % 8:
             raise ValueError(f"shard [{Ml}, {Kd}] does not fit the tensor-parallel buffers [{self.rows}, {self.cols}]")
         p = self._shard_parity
@@ -98,6 +115,12 @@ class TensorParallel:
         M, Kd = a.shape
         N = w.shape[1] if b_mn else w.shape[0]
         Ml = M // self.world
+        if self.mode == "nccl":
+            full = torch.empty(M, N, dtype=torch.bfloat16, device=self.device)
+            G.gemm(a, w, full, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=N, b_mn=b_mn)
+            out = torch.empty(Ml, N, dtype=torch.bfloat16, device=self.device)
+            dist.reduce_scatter_tensor(out, full, group=self.group)
+            return out if residual is None else out + residual
         if M % self.world or Ml % 128 or Ml > self.rows or N > self.cols or N % 8:
             raise ValueError(f"product [{M}, {N}] does not fit the tensor-parallel buffers")
         p = self._slot_parity
@@ -188,16 +211,24 @@ def row_parallel_linear(a, tp: TensorParallel, w, residual_shard=None):
     return _RowParallel.apply(a, tp, w, residual_shard)
 
 
-def peer_sum_ranges(bufs: SymmetricBuffer, ranges: list[tuple[int, int]], group_ranks: list[int], my_rank: int,
-                    tp: TensorParallel, scratch: torch.Tensor, device) -> None:
-    """In-place all-reduce(sum) of fp32 element ranges of a peer-mapped buffer over a sub-group of ranks."""
-    order = sorted(group_ranks)
-    bases0 = torch.tensor([bufs.ptrs[r] for r in order], dtype=torch.int64, device=device)
-    bases1 = torch.tensor([bufs.ptrs[my_rank]], dtype=torch.int64, device=device)
-    rt = torch.tensor(ranges, dtype=torch.int64, device=device).reshape(-1)
-    tp.barrier()
-    nat.check(nat.cuda().incin_peer_sum_ranges(bases0.data_ptr(), len(order), rt.data_ptr(), len(ranges),
-                                              scratch.data_ptr(), 0, nat.stream_ptr()), "peer_sum_ranges")
-    tp.barrier()
-    nat.check(nat.cuda().incin_peer_sum_ranges(bases1.data_ptr(), 1, rt.data_ptr(), len(ranges), scratch.data_ptr(), 1,
-                                              nat.stream_ptr()), "peer_sum_ranges")
+class PeerRangeSum:
+    """In-place all-reduce(sum) of fp32 element ranges of a peer-mapped buffer over a sub-group of ranks.  All
+    device-side tables are built once, so ``run()`` only enqueues kernels (capturable in a CUDA graph)."""
+
+    def __init__(self, bufs: SymmetricBuffer, ranges: list[tuple[int, int]], group_ranks: list[int], my_rank: int,
+                 tp: TensorParallel, device):
+        order = sorted(group_ranks)
+        self.tp, self.n_peers, self.n_ranges = tp, len(order), len(ranges)
+        self.bases_all = torch.tensor([bufs.ptrs[r] for r in order], dtype=torch.int64, device=device)
+        self.base_self = torch.tensor([bufs.ptrs[my_rank]], dtype=torch.int64, device=device)
+        self.ranges = torch.tensor(ranges, dtype=torch.int64, device=device).reshape(-1)
+        self.scratch = torch.empty(sum(k for _, k in ranges), dtype=torch.float32, device=device)
+
+    def run(self) -> None:
+        lib = nat.cuda()
+        self.tp.barrier()    # every peer's gradients are final
+        nat.check(lib.incin_peer_sum_ranges(self.bases_all.data_ptr(), self.n_peers, self.ranges.data_ptr(),
+                                            self.n_ranges, self.scratch.data_ptr(), 0, nat.stream_ptr()), "peer_sum")
+        self.tp.barrier()    # every peer has finished reading before anyone overwrites
+        nat.check(lib.incin_peer_sum_ranges(self.base_self.data_ptr(), 1, self.ranges.data_ptr(), self.n_ranges,
+                                            self.scratch.data_ptr(), 1, nat.stream_ptr()), "peer_sum")
