@@ -77,10 +77,15 @@ typedef struct incin_gemm_desc {
   /* --- fused GEMM -> reduce-scatter (row layer).  rs_world > 1: the epilogue stores each 128-row tile of the
    * partial product as bf16 into the slot of this rank inside the OWNER rank's slot buffer
    * rs_dst[owner] = [rs_world][rs_rows_per_rank][ldc] over peer stores; C is ignored.  The owner sums the
-   * slots afterwards (incin_slot_reduce) once a peer barrier has passed. */
-  int rs_world, rs_rank, rs_rows_per_rank, rs_pad_;
+   * slots afterwards (incin_slot_reduce) once a peer barrier has passed.
+   * With rs_copy_ctas > 0 and rs_ready != NULL the transfer is done by copy CTAs instead: the epilogue writes
+   * tiles owned by other ranks into the local staging buffer C ([M][ldc], ldc == N), counts finished epilogue
+   * warps per 128-row block in rs_ready (uint32[tiles_m], zeroed by the caller), and rs_copy_ctas CTAs of the
+   * same launch push each completed block to its owner in 32 KB bulk copies while later blocks are computed. */
+  int rs_world, rs_rank, rs_rows_per_rank, rs_copy_ctas;
   void* rs_dst[8];
   long long rs_slot_stride;
+  void* rs_ready;
 } incin_gemm_desc;
 
 int incin_gemm_bf16(const incin_gemm_desc* desc, void* stream);

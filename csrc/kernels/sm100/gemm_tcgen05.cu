@@ -67,8 +67,10 @@ struct GemmKernelParams {
   __nv_bfloat16* ag_gathered;
   // GEMM -> reduce-scatter
   int rs_world, rs_rank, rs_rows_per_rank;
+  int rs_push;            // 1: remote tiles go to the local staging buffer C and copy CTAs push them to their owners
   __nv_bfloat16* rs_dst[8];
   long long rs_slot_stride;
+  uint32_t* rs_ready;     // push mode: per 128-row block, epilogue warps that have finished writing it
 };
 
 struct Unit {
@@ -87,6 +89,14 @@ __device__ __forceinline__ Unit decode_unit(const GemmKernelParams& p, int u) {
     t /= p.tiles_n;
     const int mi = t % p.tiles_m;
     w.m_blk = (mi + p.ag_rank * (p.ag_rows_per_rank / BM)) % p.tiles_m;
+    b = t / p.tiles_m;
+  } else if (p.rs_push) {
+    // row blocks owned by the next rank first, own rows last: the copy CTAs push finished blocks while the
+    // remaining ones are still being computed, and nothing has to leave this GPU after the last tile
+    w.n_blk = t % p.tiles_n;
+    t /= p.tiles_n;
+    const int mi = t % p.tiles_m;
+    w.m_blk = (mi + (p.rs_rank + 1) * (p.rs_rows_per_rank / BM)) % p.tiles_m;
     b = t / p.tiles_m;
   } else {
     w.m_blk = t % p.tiles_m;
@@ -121,7 +131,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   // all-gather mode: the first CTAs of the grid (dispatched first) copy, the remaining gemm_ctas compute
-  const int n_compute = p.ag_world > 1 ? p.gemm_ctas : (int)gridDim.x;
+  const int n_compute = (p.ag_world > 1 || p.rs_push) ? p.gemm_ctas : (int)gridDim.x;
   const int n_copy = (int)gridDim.x - n_compute;
   const bool is_copier = (int)blockIdx.x < n_copy;
   const int cta = (int)blockIdx.x - n_copy;
@@ -150,49 +160,104 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
 
   if (is_copier) {
-    // ------------------------------------------------------------- all-gather copy CTA (one thread drives TMA)
-    // Pulls 128-row tiles of the peers' shards (and the own shard) into the local gathered buffer through shared
-    // memory with bulk copies, so each remote byte crosses NVLink exactly once, and publishes one flag per tile.
+    // ------------------------------------------------------------- copy CTA (one thread drives the bulk copies)
+    // all-gather:     pulls 128-row tiles of the peers' shards (and the own shard) into the local gathered buffer
+    //                 and publishes one flag per tile;
+    // reduce-scatter: waits until a 128-row block of the partial product is complete in the local staging buffer
+    //                 and pushes it into this rank's slot of the owner's buffer.
+    // Either way the data moves global -> shared -> global in 32 KB bulk copies, so every byte crosses NVLink
+    // exactly once and in large transfers.
     if (threadIdx.x == 0) {
       constexpr int CHUNK = 32 * 1024;
       constexpr int NBUF = Cfg::STAGES * Cfg::STAGE_BYTES / CHUNK;   // the whole operand ring is staging space here
+      constexpr int PENDING = 2;   // bulk stores whose shared-memory reads may still be outstanding
+      static_assert(NBUF > PENDING + 1, "staging ring too small");
+      const bool pull = p.ag_world > 1;
       const int copier = (int)blockIdx.x, n_copiers = n_copy;
-      const long long tile_bytes = (long long)BM * p.K * 2;
+      const long long row_bytes = pull ? (long long)p.K * 2 : (long long)p.N * 2;
+      const long long tile_bytes = (long long)BM * row_bytes;
       const int chunks_per_tile = (int)((tile_bytes + CHUNK - 1) / CHUNK);
-      const int tiles_per_rank = p.ag_rows_per_rank / BM;
-      uint32_t issued = 0, landed = 0;   // chunk counters; buffer = counter % NBUF, full_bar doubles as its barrier
+      const int tiles_per_rank = (pull ? p.ag_rows_per_rank : p.rs_rows_per_rank) / BM;
+      const int list_len = pull ? p.tiles_m : p.tiles_m - tiles_per_rank;   // push: remote row blocks only
+      const int first = pull ? p.ag_rank * tiles_per_rank : (p.rs_rank + 1) * tiles_per_rank;
+      const int my_tiles = copier < list_len ? (list_len - copier + n_copiers - 1) / n_copiers : 0;
+      const long long my_chunks = (long long)my_tiles * chunks_per_tile;
+      const uint32_t ready_target = (uint32_t)p.tiles_n * 8u;   // 8 epilogue warps per output tile
+      // chunk g of this CTA: tile g / chunks_per_tile of its list (consumption order), piece g % chunks_per_tile
+      auto locate = [&](long long g, int& m_blk, long long& off, uint32_t& bytes) {
+        const int mi = copier + (int)(g / chunks_per_tile) * n_copiers;
+        m_blk = (mi + first) % p.tiles_m;
+        off = (g % chunks_per_tile) * (long long)CHUNK;
+        bytes = (uint32_t)((tile_bytes - off) < CHUNK ? (tile_bytes - off) : CHUNK);
+      };
+      auto block_ready = [&](int m_blk) {
+        uint32_t f;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(p.rs_ready + m_blk) : "memory");
+        return f >= ready_target;
+      };
+      // Loads run ahead of the stores, across tile boundaries.  A staging buffer is free for the next load once
+      // the bulk store that drained it has READ it (wait_group.read), not once its writes have landed.
+      long long loaded = 0, stored = 0;
+      long long ready_upto = pull ? my_chunks : 0;   // chunks below this index belong to blocks known to be complete
       bool ok = true;
-      // this CTA's tiles, in consumption order
-      for (int mi = copier; mi < p.tiles_m && ok; mi += n_copiers) {
-        const int m_blk = (mi + p.ag_rank * tiles_per_rank) % p.tiles_m;
-        const int owner = m_blk / tiles_per_rank;
-        const char* src = reinterpret_cast<const char*>(p.ag_src[owner]) + (long long)(m_blk % tiles_per_rank) * tile_bytes;
-        char* dst = reinterpret_cast<char*>(p.ag_gathered) + (long long)m_blk * tile_bytes;
-        int next_load = 0, next_store = 0;
-        while (next_store < chunks_per_tile && ok) {
-          while (next_load < chunks_per_tile && issued - landed < (uint32_t)NBUF) {
-            const int buf = issued % NBUF;
-            const long long off = (long long)next_load * CHUNK;
-            const uint32_t bytes = (uint32_t)((tile_bytes - off) < CHUNK ? (tile_bytes - off) : CHUNK);
-            mbar_expect_tx(&copy_bar[buf], bytes);
-            bulk_load_1d(smem + buf * CHUNK, src + off, bytes, &copy_bar[buf]);
-            ++issued;
-            ++next_load;
+      while (stored < my_chunks && ok) {
+        const long long reusable = stored > PENDING ? stored - PENDING : 0;
+        while (loaded < my_chunks && loaded < reusable + NBUF) {
+          int m_blk; long long off; uint32_t bytes;
+          locate(loaded, m_blk, off, bytes);
+          if (loaded >= ready_upto) {
+            // push mode, first chunk of a new block: go on only if the block is complete; if stores are still
+            // owed, do those first and look again, else wait here (bounded)
+            bool rdy = block_ready(m_blk);
+            if (!rdy && stored == loaded) {
+              const long long t0 = clock64();
+              while (!(rdy = block_ready(m_blk))) {
+                if (*abort_flag || clock64() - t0 > INCIN_WAIT_CLOCKS) {
+                  *abort_flag = 1;
+                  if (p.status) atomicCAS(p.status, 0, kStatusTimeoutPeer);
+                  ok = false;
+                  break;
+                }
+                __nanosleep(200);
+              }
+            }
+            if (!rdy) break;
+            fence_proxy_async_global();   // the block was written with ordinary stores; the bulk loads come after
+            ready_upto = loaded + chunks_per_tile;
           }
-          const int buf = landed % NBUF;
-          if (!mbar_wait(&copy_bar[buf], (landed / NBUF) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
-          const long long off = (long long)next_store * CHUNK;
-          const uint32_t bytes = (uint32_t)((tile_bytes - off) < CHUNK ? (tile_bytes - off) : CHUNK);
-          bulk_store_1d(dst + off, smem + buf * CHUNK, bytes);
-          bulk_commit_wait_all();   // the chunk is in local memory and the staging buffer is free again
-          ++landed;
-          ++next_store;
+          const int buf = (int)(loaded % NBUF);
+          const char* src =
+              pull ? reinterpret_cast<const char*>(p.ag_src[m_blk / tiles_per_rank]) + (long long)(m_blk % tiles_per_rank) * tile_bytes + off
+                   : reinterpret_cast<const char*>(p.C) + (long long)m_blk * tile_bytes + off;
+          mbar_expect_tx(&copy_bar[buf], bytes);
+          bulk_load_1d(smem + buf * CHUNK, src, bytes, &copy_bar[buf]);
+          ++loaded;
         }
-        if (ok) {
+        if (!ok || stored == loaded) continue;
+        int m_blk; long long off; uint32_t bytes;
+        locate(stored, m_blk, off, bytes);
+        const int buf = (int)(stored % NBUF);
+        if (!mbar_wait(&copy_bar[buf], (uint32_t)((stored / NBUF) & 1), abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+        char* dst = pull ? reinterpret_cast<char*>(p.ag_gathered) + (long long)m_blk * tile_bytes + off
+                         : reinterpret_cast<char*>(p.rs_dst[m_blk / tiles_per_rank]) + p.rs_rank * p.rs_slot_stride * 2 +
+                               (long long)(m_blk % tiles_per_rank) * tile_bytes + off;
+        bulk_store_1d(dst, smem + buf * CHUNK, bytes);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        ++stored;
+        if (pull && stored % chunks_per_tile == 0) {
+          // tile complete: its writes must have landed before the flag is published (loads stay in flight meanwhile)
+          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
           fence_proxy_async_global();
           __threadfence();
           asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ag_flags + m_blk), "r"(1u) : "memory");
+        } else {
+          asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
         }
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      if (!pull) {
+        fence_proxy_async_global();
+        __threadfence_system();   // pushed blocks are visible to their owners before the cross-GPU barrier that follows
       }
     }
   } else if (warp == 0) {
@@ -315,9 +380,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       void* c_ptr = p.C;
       if (p.rs_world > 1) {
         // reduce-scatter: this tile belongs to `owner`; write it into this rank's slot of the owner's buffer
+        // (push mode: only when this rank owns it; other tiles stay in the local staging buffer C for the copy CTAs)
         const int owner = (w.m_blk * BM) / p.rs_rows_per_rank;
-        c_ptr = p.rs_dst[owner];
-        cbase = (long long)p.rs_rank * p.rs_slot_stride + (long long)(m - owner * p.rs_rows_per_rank) * p.ldc;
+        if (!p.rs_push || owner == p.rs_rank) {
+          c_ptr = p.rs_dst[owner];
+          cbase = (long long)p.rs_rank * p.rs_slot_stride + (long long)(m - owner * p.rs_rows_per_rank) * p.ldc;
+        }
       }
       const bool vec_ok = (p.ldc % 8 == 0) && (p.c_stride_lo % 8 == 0) && (p.c_stride_hi % 8 == 0);
 #pragma unroll 1
@@ -475,7 +543,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (lane == 0) {
+        mbar_arrive(&tempty_bar[acc]);
+        if (p.rs_push) {   // this warp's part of the tile is in the staging buffer: count it for the copy CTAs
+          __threadfence();
+          asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.rs_ready + w.m_blk), "r"(1u) : "memory");
+        }
+      }
     }
   }
 
@@ -564,7 +638,7 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmKe
   }
   int grid = p.total_units < max_ctas ? p.total_units : max_ctas;
   GemmKernelParams q = p;
-  if (p.ag_world > 1) {
+  if (p.ag_world > 1 || p.rs_push) {
     int copy = p.gemm_ctas;   // the caller's request for copy CTAs travels in gemm_ctas until here
     if (copy < 1) copy = 8;
     if (copy > max_ctas / 2) copy = max_ctas / 2;
@@ -665,13 +739,15 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   p.ag_world = d->ag_world > 1 ? d->ag_world : 0;
   p.ag_rank = d->ag_rank;
   p.ag_rows_per_rank = d->ag_rows_per_rank;
-  p.gemm_ctas = d->ag_copy_ctas;
+  p.gemm_ctas = d->ag_world > 1 ? d->ag_copy_ctas : d->rs_copy_ctas;
   p.ag_flags = reinterpret_cast<uint32_t*>(d->ag_flags);
   p.ag_gathered = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(d->A));
   p.rs_world = d->rs_world > 1 ? d->rs_world : 0;
   p.rs_rank = d->rs_rank;
   p.rs_rows_per_rank = d->rs_rows_per_rank;
   p.rs_slot_stride = d->rs_slot_stride;
+  p.rs_ready = reinterpret_cast<uint32_t*>(d->rs_ready);
+  p.rs_push = (p.rs_world && d->rs_copy_ctas > 0 && d->rs_ready) ? 1 : 0;
   for (int r = 0; r < 8; ++r) {
     p.ag_src[r] = reinterpret_cast<const __nv_bfloat16*>(d->ag_src[r]);
     p.rs_dst[r] = reinterpret_cast<__nv_bfloat16*>(d->rs_dst[r]);
@@ -685,8 +761,10 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   }
   if (p.rs_world) {
     if (p.rs_world > 8 || d->out_fp32 || p.rs_rows_per_rank % BM || d->M != p.rs_world * p.rs_rows_per_rank ||
-        splits != 1 || blo * bhi != 1 || d->residual || d->aux)
+        splits != 1 || blo * bhi != 1 || d->residual || d->aux || p.ag_world)
       return INCIN_ERR_ARGUMENT;
+    // push mode moves whole 128-row blocks of the staging buffer with bulk copies: rows must be dense and 16-byte sized
+    if (p.rs_push && (!d->C || d->ldc != d->N || (d->N % 8))) return INCIN_ERR_ARGUMENT;
     for (int r = 0; r < p.rs_world; ++r)
       if (!p.rs_dst[r]) return INCIN_ERR_ARGUMENT;
   }

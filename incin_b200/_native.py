@@ -58,8 +58,8 @@ class GemmDesc(C.Structure):
         ("splits", c_int), ("tile_n", c_int), ("max_ctas", c_int), ("status", c_void_p),
         ("ag_world", c_int), ("ag_rank", c_int), ("ag_rows_per_rank", c_int), ("ag_copy_ctas", c_int),
         ("ag_src", c_void_p * 8), ("ag_flags", c_void_p),
-        ("rs_world", c_int), ("rs_rank", c_int), ("rs_rows_per_rank", c_int), ("rs_pad_", c_int),
-        ("rs_dst", c_void_p * 8), ("rs_slot_stride", c_ll),
+        ("rs_world", c_int), ("rs_rank", c_int), ("rs_rows_per_rank", c_int), ("rs_copy_ctas", c_int),
+        ("rs_dst", c_void_p * 8), ("rs_slot_stride", c_ll), ("rs_ready", c_void_p),
     ]
 
 

@@ -85,7 +85,8 @@ class _Tracer(TorchDispatchMode):
         outs = out if isinstance(out, (list, tuple)) else [out]
         for o in outs:
             if isinstance(o, torch.Tensor):
-                self.ids[id(o)] = self.g.add(name, ins, o.shape, str(o.dtype).replace("torch.", ""))
+                self.ids[id(o)] = self.g.add(name, ins, o.shape, str(o.dtype).replace("torch.", ""),
+                                             scalars=[a for a in args if isinstance(a, (int, float)) and not isinstance(a, bool)])
         self._keep = getattr(self, "_keep", []) + [o for o in outs if isinstance(o, torch.Tensor)]  # ids stay unique
         return out
 
@@ -142,6 +143,41 @@ def fusion_pass(g: Graph) -> list[FusionGroup]:
             groups.append(FusionGroup(chain))
             grouped.update(chain)
     return groups
+
+
+_UNARY = {"relu": "relu", "gelu": "gelu", "silu": "swish", "sigmoid": "sigmoid", "tanh": "tanh", "exp": "exp", "log": "log",
+          "sqrt": "sqrt", "rsqrt": "rsqrt", "neg": "neg", "abs": "abs", "mish": "mish", "elu": "elu",
+          "softplus": "softplus", "sign": "sign", "reciprocal": "recip"}
+_BINARY = {"add": "add", "sub": "sub", "mul": "mul", "div": "div", "maximum": "max", "minimum": "min", "pow": "pow"}
+
+
+def lower_group(g: Graph, group: FusionGroup):
+    """One fusion group -> ``(PointwiseExpr, external input node ids)``: the expression of the group's last node
+    over the tensors that enter the group from outside.  ``codegen.compile_pointwise`` turns it into one kernel."""
+    from .codegen.pointwise import Arg, Binary, Const, Unary
+    inside = set(group.nodes)
+    ext: list[int] = []
+    memo: dict[int, object] = {}
+
+    def expr(nid: int):
+        if nid not in inside:
+            if nid not in ext:
+                ext.append(nid)
+            return Arg(ext.index(nid))
+        if nid in memo:
+            return memo[nid]
+        n = g.nodes[nid]
+        ops = [expr(i) for i in n.inputs] + [Const(float(s)) for s in n.attrs.get("scalars", [])]
+        if n.op in _UNARY and len(ops) == 1:
+            e = Unary(_UNARY[n.op], ops[0])
+        elif n.op in _BINARY and len(ops) == 2:
+            e = Binary(_BINARY[n.op], ops[0], ops[1])
+        else:
+            raise ValueError(f"cannot lower {n.op} with {len(ops)} operands")
+        memo[nid] = e
+        return e
+
+    return expr(group.nodes[-1]), ext
 
 
 # ------------------------------------------------------------------------------------------------ memory planning

@@ -105,6 +105,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
         for r, ptr in enumerate(scatter["dst"]):
             d.rs_dst[r] = ptr
         d.rs_slot_stride = scatter["slot_stride"]
+        if scatter.get("copy_ctas", 0) > 0:
+            d.rs_copy_ctas, d.rs_ready = scatter["copy_ctas"], scatter["ready"].data_ptr()
     nat.check(nat.cuda().incin_gemm_bf16(ctypes.byref(d), nat.stream_ptr()), "gemm")
     return out
 

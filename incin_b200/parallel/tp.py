@@ -57,8 +57,7 @@ class TensorParallel:
         if max_rows_per_rank % 128:
             raise ValueError("rows per rank must be a multiple of 128 (one GEMM tile never straddles two owners)")
         self.rows, self.cols = max_rows_per_rank, max_cols
-        # copy CTAs: enough outstanding bulk copies to keep NVLink busy, no more SMs than that taken from the GEMM
-        self.copy_ctas = copy_ctas or min(12, 2 * self.world)
+        self.copy_ctas = copy_ctas          # 0 = choose per call from the copy volume and the GEMM size
         shard_bytes = max_rows_per_rank * max_cols * 2
         self.shard = [SymmetricBuffer(shard_bytes, device).exchange(group) for _ in range(2)]
         self.slots = [SymmetricBuffer(self.world * shard_bytes, device).exchange(group) for _ in range(2)]
@@ -69,6 +68,23 @@ class TensorParallel:
         dist.barrier(group=group)
 
     # ------------------------------------------------------------------------------------------------ primitives
+    COPY_CTA_GBS = 26.0      # measured: bytes one copy CTA moves through its shared-memory staging ring per second
+    LINK_GBS = 650.0
+    GEMM_TFLOPS = 1200.0
+
+    def _copy_ctas(self, copy_bytes: float, link_bytes: float, flops: float) -> int:
+        """Number of CTAs of the fused launch that copy instead of computing: the count that minimises
+        ``max(copy time, link time, GEMM time on the remaining SMs)``."""
+        if self.copy_ctas:
+            return self.copy_ctas
+        best, best_t = 8, float("inf")
+        for c in range(4, 73, 4):
+            t = max(copy_bytes / (c * self.COPY_CTA_GBS * 1e9), link_bytes / (self.LINK_GBS * 1e9),
+                    flops / (self.GEMM_TFLOPS * 1e12 * (148 - c) / 148))
+            if t < best_t * 0.97:      # prefer fewer copy CTAs unless more of them buy at least 3 %
+                best, best_t = c, t
+        return best
+
     def barrier(self) -> None:
         """Cross-GPU barrier as one tiny kernel on the current stream (bounded waits, status word on timeout)."""
         nat.check(nat.cuda().incin_peer_barrier(self._pad_ptrs.data_ptr(), self.world, self.rank, 0,
@@ -105,7 +121,7 @@ class TensorParallel:
             ldc = N
         G.gemm(gathered, w, out, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=ldc, b_mn=b_mn, c_offset=c_offset,
                gather={"world": self.world, "rank": self.rank, "rows_per_rank": Ml, "src": buf.ptrs, "flags": flags,
-                       "copy_ctas": self.copy_ctas})
+                       "copy_ctas": self._copy_ctas(M * Kd * 2, (self.world - 1) * Ml * Kd * 2, 2.0 * M * N * Kd)})
         return out, gathered
 
     def gemm_scatter(self, a: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False,
@@ -126,9 +142,15 @@ class TensorParallel:
         p = self._slot_parity
         self._slot_parity ^= 1
         buf = self.slots[p]
-        G.gemm(a, w, a, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=N, b_mn=b_mn,
+        # tiles owned by peers are staged locally and pushed by copy CTAs of the same launch (large bulk transfers
+        # over NVLink instead of one small store per thread); this rank's own tiles go straight into its slot
+        stage = torch.empty(M, N, dtype=torch.bfloat16, device=self.device)
+        ready = torch.zeros(M // 128, dtype=torch.int32, device=self.device)
+        remote = (self.world - 1) * Ml * N * 2
+        G.gemm(a, w, stage, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=N, b_mn=b_mn,
                scatter={"world": self.world, "rank": self.rank, "rows_per_rank": Ml, "dst": buf.ptrs,
-                        "slot_stride": Ml * N})
+                        "slot_stride": Ml * N, "ready": ready,
+                        "copy_ctas": self._copy_ctas(remote, remote, 2.0 * M * N * Kd)})
         self.barrier()   # every peer's tiles for my rows have landed in my slot buffer
         out = torch.empty(Ml, N, dtype=torch.bfloat16, device=self.device)
         nat.check(nat.cuda().incin_slot_reduce(buf.ptr, Ml * N, self.world, nat.ptr(residual), out.data_ptr(), Ml, N, N,

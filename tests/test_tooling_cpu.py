@@ -1,0 +1,229 @@
+"""CPU tests: graph tracing / fusion / memory plan / artifacts, the pointwise code generator (render + NVRTC
+compile for sm_100a, no GPU needed), the tuning service and its cache, collective tuning votes, doctor + CLI."""
+import json
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from incin_b200 import graph as G
+from incin_b200.codegen.pointwise import Arg, Binary, Const, Layout, Scalar, Ternary, Unary, count_args, kernel_key, render_cuda
+from incin_b200.tuning import (Candidate, Identity, PersistentCache, TuningPolicy, TuningRecord, TuningService,
+                               candidates, prune)
+from incin_b200.tuning import collective as C
+
+
+def _fn(x, w, b):
+    h = torch.relu(x @ w + b)
+    h = torch.tanh(h * 2.0)
+    return h.sum()
+
+
+def test_trace_records_ops_and_io():
+    x, w, b = torch.randn(8, 16), torch.randn(16, 32), torch.randn(8, 32)
+    g = G.trace(_fn, x, w, b)
+    ops = [n.op for n in g.nodes]
+    assert ops[:3] == ["input"] * 3 and "mm" in ops and ops[-1] == "sum"
+    assert len(g.inputs) == 3 and g.outputs == [g.nodes[-1].id]
+    assert G.tracing_graph_snapshot() is g
+    assert g.digest() == G.trace(_fn, x, w, b).digest()
+    assert g.digest() != G.trace(_fn, x[:4], w, b[:4]).digest()
+
+
+def test_fusion_groups_pointwise_chain_and_lowers_to_one_kernel():
+    x, w, b = torch.randn(8, 16), torch.randn(16, 32), torch.randn(8, 32)
+    g = G.trace(_fn, x, w, b)
+    groups = G.fusion_pass(g)
+    assert len(groups) == 1 and [g.nodes[i].op for i in groups[0].nodes] == ["add", "relu", "mul", "tanh"]
+    expr, ext = G.lower_group(g, groups[0])
+    assert len(ext) == 2 and count_args(expr) == (2, 0)
+    src, key = render_cuda(expr, "f32")
+    assert "tanhf" in src and "fmaxf" in src and key.entry in src
+
+
+def test_fusion_stops_at_fanout():
+    def f(x):
+        a = torch.relu(x)
+        return a * 2.0 + torch.exp(a)   # relu has two consumers: it ends its group
+    g = G.trace(f, torch.randn(4, 4))
+    for grp in G.fusion_pass(g):
+        assert all(g.nodes[i].op != "relu" or i == grp.nodes[-1] for i in grp.nodes)
+
+
+def test_memory_plan_reuses_dead_buffers_without_overlap():
+    x, w, b = torch.randn(64, 64), torch.randn(64, 64), torch.randn(64, 64)
+    g = G.trace(_fn, x, w, b)
+    mp = G.plan_memory(g)
+    assert mp.peak_bytes < mp.naive_bytes
+    live = G.liveness(g)
+    ids = list(mp.offsets)
+    size = {n.id: max(256, (torch.Size(n.shape).numel() * 4 + 255) // 256 * 256) for n in g.nodes}
+    for i in ids:
+        for j in ids:
+            if i < j and not (live[i][1] < live[j][0] or live[j][1] < live[i][0]):
+                a0, b0 = mp.offsets[i], mp.offsets[j]
+                assert a0 + size[i] <= b0 or b0 + size[j] <= a0, (i, j)
+
+
+def test_compiled_plan_guard_and_artifact_roundtrip(tmp_path):
+    x, w, b = torch.randn(8, 16), torch.randn(16, 32), torch.randn(8, 32)
+    plan = G.CompiledPlan.build(_fn, x, w, b)
+    assert plan.guard.admits(x, w, b) and not plan.guard.admits(x[:4], w, b[:4])
+    assert not plan.guard.admits(x.double(), w, b)
+    p = tmp_path / "plan.bin"
+    G.write_artifact(p, plan)
+    back = G.read_artifact(p)
+    assert back["plan"]["graph_digest"] == plan.graph_digest and back["manifest"]["arch"] == "sm_100a"
+    raw = bytearray(p.read_bytes())
+    raw[-3] ^= 0x40
+    p.write_bytes(bytes(raw))
+    with pytest.raises(ValueError, match="checksum"):
+        G.read_artifact(p)
+    p.write_bytes(b"garbage!" + bytes(raw[8:]))
+    with pytest.raises(ValueError, match="not a compiled"):
+        G.read_artifact(p)
+
+
+def test_shape_buckets():
+    assert [G.shape_bucket(n) for n in (1, 64, 65, 128, 1000)] == [64, 64, 128, 128, 1024]
+
+
+# ------------------------------------------------------------------------------------------------ codegen
+def test_render_every_op_and_reject_bad_trees():
+    e = Ternary("fma", Unary("gelu_tanh", Arg(0)), Scalar(0), Binary("max", Arg(1), Const(0.5)))
+    assert count_args(e) == (2, 1)
+    for dt in ("f32", "bf16", "f16"):
+        for lay in (Layout.CONTIGUOUS, Layout.STRIDED):
+            src, key = render_cuda(e, dt, lay)
+            assert key.entry in src and "fmaf" in src
+    assert kernel_key(e, "bf16", Layout.CONTIGUOUS) == kernel_key(e, "bf16", Layout.CONTIGUOUS)
+    assert kernel_key(e, "bf16", Layout.CONTIGUOUS) != kernel_key(e, "f16", Layout.CONTIGUOUS)
+    with pytest.raises(ValueError):
+        Unary("nope", Arg(0))
+    assert count_args(Binary("add", Arg(0), Arg(2))) == (3, 0)   # an unused input still takes a slot
+
+
+def test_nvrtc_compiles_generated_kernel_for_sm100a():
+    rt = pytest.importorskip("incin_b200.codegen.runtime")
+    e = Binary("mul", Unary("swish", Arg(0)), Arg(1))
+    for dt in ("bf16", "f32"):
+        for lay in (Layout.CONTIGUOUS, Layout.STRIDED):
+            src, key = render_cuda(e, dt, lay)
+            cubin = rt.nvrtc_compile(src, key.entry + ".cu")
+            assert cubin[:4] == b"\x7fELF" and len(cubin) > 1000
+    with pytest.raises(rt.CompileError):
+        rt.nvrtc_compile("__global__ void k() { this is not C++; }")
+
+
+# ------------------------------------------------------------------------------------------------ tuning
+def test_candidates_and_pruning():
+    cs = candidates(block=[128, 256], vec=[1, 4])
+    assert len(cs) == 4 and cs[0].as_dict() == {"block": 128, "vec": 1}
+    kept = prune(cs, {"n": 130}, [lambda c, s: s["n"] % c["vec"] == 0 or c["vec"] == 1])
+    assert [c.as_dict()["vec"] for c in kept] == [1, 1]
+
+
+def test_service_policies_measure_cache_and_persist(tmp_path):
+    ident = Identity("B200", "sm_100a", "12.9", "0.1.0")
+    cache = PersistentCache(tmp_path / "tune.json")
+    cs = candidates(tile=[64, 128, 256])
+    calls = []
+
+    def measure(p):
+        calls.append(p["tile"])
+        return {64: 3.0, 128: 1.0, 256: 2.0}[p["tile"]]
+    heur = lambda: {"tile": 64}
+    assert TuningService(TuningPolicy.DISABLED, cache, ident).choose("k", cs, heur, measure) == {"tile": 64}
+    assert TuningService(TuningPolicy.HEURISTIC, cache, ident).choose("k", cs, heur, measure) == {"tile": 64}
+    assert calls == []
+    svc = TuningService(TuningPolicy.PROFILE_GUIDED, cache, ident)
+    assert svc.choose("k", cs, heur, measure) == {"tile": 128} and calls == [64, 128, 256]
+    assert svc.choose("k", cs, heur, measure) == {"tile": 128} and len(calls) == 3      # LRU hit
+    assert "tile=128" in svc.explain() or "128" in svc.explain()
+    # a new process with the same identity reads the record from disk; another identity ignores it
+    assert TuningService(TuningPolicy.HEURISTIC, PersistentCache(tmp_path / "tune.json"), ident).choose("k", cs, heur) == {"tile": 128}
+    other = Identity("H100", "sm_90a", "12.9", "0.1.0")
+    assert TuningService(TuningPolicy.HEURISTIC, PersistentCache(tmp_path / "tune.json"), other).choose("k", cs, heur) == {"tile": 64}
+    # warm-up policy measures only until end_warmup()
+    w = TuningService(TuningPolicy.COORDINATED_WARMUP, None, ident)
+    w.end_warmup()
+    assert w.choose("k2", cs, heur, measure) == {"tile": 64}
+
+
+def test_corrupt_cache_file_is_ignored(tmp_path):
+    p = tmp_path / "tune.json"
+    ident = Identity("B200", "sm_100a", "12.9", "0.1.0")
+    c = PersistentCache(p)
+    c.store(TuningRecord("k", ident.token(), {"tile": 128}, 1.0))
+    assert [r.key for r in PersistentCache(p).load().values()] == ["k"]
+    p.write_text(p.read_text().replace("128", "256", 1))
+    assert PersistentCache(p).load() == {}
+
+
+def test_failing_candidate_is_skipped():
+    svc = TuningService(TuningPolicy.PROFILE_GUIDED, None, Identity("B200", "sm_100a", "12.9", "0.1.0"))
+
+    def measure(p):
+        if p["tile"] == 128:
+            raise RuntimeError("cannot launch")
+        return float(p["tile"])
+    assert svc.choose("k", candidates(tile=[128, 64, 256]), lambda: {"tile": 1}, measure) == {"tile": 64}
+
+
+def test_collective_tuning_commit_needs_agreement():
+    reports = [C.SampleReport(r, c, s) for r in range(2) for c, s in (("a", (10, 12, 11)), ("b", (7 + 10 * r, 8, 9)))]
+    sc = C.score(reports)
+    assert sc["a"] == 11 and sc["b"] == 9    # max over ranks per sample, then median
+    votes = [C.local_vote(r, reports) for r in range(2)]
+    out = C.commit(2, reports, votes)
+    assert out.candidate == "b" and out.world == 2
+    with pytest.raises(C.TuningDisagreement):
+        C.commit(2, reports, [C.CommitVote(0, "a"), C.CommitVote(1, "b")])
+    with pytest.raises(C.TuningDisagreement):
+        C.commit(3, reports, votes)
+    with pytest.raises(C.TuningDisagreement):
+        C.commit(2, reports, [C.CommitVote(0, "zz"), C.CommitVote(1, "zz")])
+
+
+# ------------------------------------------------------------------------------------------------ doctor / CLI
+class _FakeHost:
+    def __init__(self, devices, tools=None, libs=None):
+        self._d, self._t, self._l = devices, tools or {"nvcc": "/usr/local/cuda/bin/nvcc"}, libs or {}
+
+    def python(self): return "3.12.3"
+    def torch_version(self): return "2.11.0"
+    def cuda_devices(self): return self._d
+    def tools(self): return self._t
+    def libraries(self): return self._l
+
+
+def _dev(i, arch="sm_100", peers=()):
+    return {"index": i, "name": "NVIDIA B200" if arch == "sm_100" else "NVIDIA H100", "arch": arch, "sms": 148,
+            "memory_gib": 178.4, "peers": list(peers)}
+
+
+def test_doctor_reports_against_fake_hosts():
+    from incin_b200.doctor import doctor
+    libs = {"libincin_sm100.so": True, "libincin_host.so": True}
+    good = doctor(_FakeHost([_dev(0, peers=[1]), _dev(1, peers=[0])], libs=libs))
+    assert good.healthy and "B200" in good.to_text() and good.findings[0].code == "all-good"
+    none = doctor(_FakeHost([], libs=libs))
+    assert none.healthy and "no CUDA device" in none.to_text() and json.loads(none.to_json())["healthy"]
+    old = doctor(_FakeHost([_dev(0, "sm_90")], libs=libs))
+    assert not old.healthy and old.findings[0].code == "arch-unsupported"
+    unbuilt = doctor(_FakeHost([_dev(0)], libs={}))
+    assert {f.code for f in unbuilt.findings} >= {"native-missing", "host-missing"}
+    lonely = doctor(_FakeHost([_dev(0), _dev(1, peers=[0])], tools={"nvcc": None}, libs=libs))
+    assert {f.code for f in lonely.findings} == {"peer-access", "nvcc-missing"} and lonely.healthy
+
+
+def test_cli_subcommands_run():
+    def run(*a):
+        r = subprocess.run([sys.executable, "-m", "incin_b200", *a], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-800:]
+        return r.stdout
+    assert "sm_100a" in run("capabilities") or "tcgen05" in run("capabilities")
+    out = run("plan", "--world", "8")
+    assert "chosen" in out and "dp=8" in out
+    assert run("doctor", "--json").lstrip().startswith("{")
