@@ -206,6 +206,65 @@ int incin_slot_reduce(const void* slots, long long slot_stride, int world, const
 
 /* ---- library info ------------------------------------------------------------------------------ */
 const char* incin_sm100_version(void);
+/* ---- reductions (reduce.cu) ------------------------------------------------------------------ */
+/* op: 0 sum, 1 mean, 2 max, 3 min, 4 prod, 5 argmax, 6 argmin.  x is dense, viewed as [outer][reduce][inner];
+ * values keep the input dtype (bf16 or fp32, fp32 accumulation), arg* write int64 indices into idx_out. */
+int incin_reduce_axis(const void* x, void* out, long long* idx_out, long long outer, long long reduce, long long inner,
+                      int op, int is_bf16, void* stream);
+/* Whole-tensor reduction in ONE launch with a fixed combine order (bitwise reproducible); result is fp32 (or int64).
+ * Uses one file-scope partial buffer per device: launches must be ordered on one stream. */
+int incin_reduce_all(const void* x, float* out, long long* idx_out, long long n, int op, int is_bf16, void* stream);
+int incin_cumsum(const void* x, void* out, long long outer, long long n, long long inner, int is_bf16, void* stream);
+
+/* ---- data movement (shape.cu) ---------------------------------------------------------------- */
+/* dst[sum i_d * dst_strides[d]] = src[sum i_d * src_strides[d]] over shape[0..rank), rank <= 6, strides in elements
+ * (0 = broadcast): transpose, narrow, paste, broadcast, concat and pad are all this one copy. */
+int incin_strided_copy(const void* src, void* dst, int rank, const long long* shape, const long long* src_strides,
+                       const long long* dst_strides, int elem_bytes, void* stream);
+/* Indexed ops check every index: an out-of-range one is skipped and *err_flag (device int, may be NULL) is set. */
+int incin_gather_rows(const void* src, const long long* index, void* out, long long n_idx, long long row_elems,
+                      long long src_rows, int elem_bytes, int* err_flag, void* stream);
+int incin_scatter_add_rows(const void* src, const long long* index, float* dst, long long n_idx, long long row_elems,
+                           long long dst_rows, int src_is_bf16, int* err_flag, void* stream);
+int incin_gather_last(const void* src, const long long* index, void* out, long long rows, long long n_src, long long n_idx,
+                      int elem_bytes, int* err_flag, void* stream);
+int incin_scatter_last(const void* src, const long long* index, void* dst, long long rows, long long n_dst, long long n_idx,
+                       int elem_bytes, int* err_flag, void* stream);
+int incin_masked_fill(const void* x, const uint8_t* mask, void* out, float value, long long n, int is_bf16, void* stream);
+int incin_where(const uint8_t* cond, const void* a, const void* b, void* out, long long n, int elem_bytes, void* stream);
+int incin_tri(const void* x, void* out, long long batch, long long rows, long long cols, long long diagonal, int upper,
+              int elem_bytes, void* stream);
+
+/* ---- convolution helpers, pooling, batch norm (spatial.cu); NCHW ------------------------------ */
+typedef struct incin_conv_geom {
+  int N, C, H, W, KH, KW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+} incin_conv_geom;
+int incin_conv_out_hw(const incin_conv_geom* g, int* oh, int* ow);
+/* cols = [N*OH*OW][C*KH*KW]: the K-major A operand of the convolution GEMM */
+int incin_im2col(const void* x, void* cols, const incin_conv_geom* g, int is_bf16, void* stream);
+/* dx = fold(cols): a gather per input pixel (no atomics, deterministic) */
+int incin_col2im(const void* cols, void* dx, const incin_conv_geom* g, int is_bf16, void* stream);
+int incin_maxpool2d_fwd(const void* x, void* y, int* argmax, const incin_conv_geom* g, int is_bf16, void* stream);
+int incin_maxpool2d_bwd(const void* dy, const int* argmax, void* dx, const incin_conv_geom* g, int is_bf16, void* stream);
+int incin_avgpool2d(const void* in, void* out, const incin_conv_geom* g, int backward, int is_bf16, void* stream);
+int incin_batchnorm_train_fwd(const void* x, const float* gamma, const float* beta, void* y, float* save_mean, float* save_rstd,
+                              float* running_mean, float* running_var, int N, int C, long long HW, float eps, float momentum,
+                              int is_bf16, void* stream);
+int incin_batchnorm_eval(const void* x, const float* gamma, const float* beta, const float* mean, const float* var, void* y,
+                         int N, int C, long long HW, float eps, int is_bf16, void* stream);
+/* dgamma / dbeta are ACCUMULATED into (fp32) */
+int incin_batchnorm_bwd(const void* dy, const void* x, const float* gamma, const float* save_mean, const float* save_rstd,
+                        void* dx, float* dgamma, float* dbeta, int N, int C, long long HW, int is_bf16, void* stream);
+
+/* ---- Q8_0 and deterministic embedding backward (quant_embed.cu) ------------------------------- */
+int incin_quantize_q8_0(const void* x, void* packed, long long n, int is_bf16, void* stream);
+int incin_dequantize_q8_0(const void* packed, void* out, long long n, int out_bf16, void* stream);
+/* order: positions sorted by token id; segment s = sorted positions [seg_start[s], seg_start[s+1]) of token
+ * seg_token[s] (seg_start has n_segments + 1 entries).  dwte / dwpe (may be NULL) are accumulated into. */
+int incin_embedding_bwd_sorted(const void* dout, const long long* order, const long long* seg_start, const long long* seg_token,
+                               long long n_segments, float* dwte, float* dwpe, long long B, int T, int C, long long vocab,
+                               void* stream);
+
 int incin_sm100_num_sms(void);
 
 #ifdef __cplusplus

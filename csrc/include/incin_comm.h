@@ -55,6 +55,25 @@ int incin_barrier_pad_bytes(void);
 int incin_peer_sum_ranges(void* const* bases, int world, const void* ranges, int n_ranges, void* scratch, int stage,
                           void* stream);
 
+/* ---- stand-alone collectives over peer-mapped buffers (collectives.cu) -------------------------------------
+ * bufs[r] = rank r's symmetric buffer as mapped here (HOST array of `world` pointers).  Sizes and offsets are
+ * multiples of 16 bytes.  Bracket each call with incin_peer_barrier on the same stream. */
+/* out[r * bytes ..] = bufs[r][offset .. offset + bytes) */
+int incin_coll_all_gather(void* const* bufs, int world, int rank, long long offset_bytes, long long bytes, void* out,
+                          void* stream);
+/* out[r * chunk ..] = bufs[r][offset + rank * chunk .. + chunk) */
+int incin_coll_all_to_all(void* const* bufs, int world, int rank, long long offset_bytes, long long chunk_bytes, void* out,
+                          void* stream);
+/* out[i] = reduce_r bufs[r][offset + first_elem + i], i < n; op 0 sum, 1 mean, 2 max, 3 min; fp32 or bf16 elements.
+ * reduce-scatter: first_elem = rank * n; all-reduce: first_elem = 0 and n = whole length.  Rank order is fixed,
+ * so every rank gets bitwise the same sums. */
+int incin_coll_reduce(void* const* bufs, int world, long long offset_bytes, long long first_elem, long long n, int op,
+                      int is_bf16, void* out, void* stream);
+/* Pipeline transfers: copy `bytes` into the receiver's buffer, then release `seq` into the receiver's flag word.
+ * The receiver's wait spins on its own flag for at most timeout_ms (<= 10 s) and records status 5 when it gives up. */
+int incin_p2p_send(void* peer_dst, const void* src, long long bytes, void* peer_flag, unsigned seq, void* stream);
+int incin_p2p_wait(const void* local_flag, unsigned seq, void* status, long long timeout_ms, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -19,8 +19,8 @@
 // Replaces the reference's f32 SIMT 128x128x8 SGEMM
 // (crates/incin-backends/src/cuda/ops/kernels/matmul.cu:1-94), which is 2-D
 // only and has no fused epilogue.
-#include "ptx.cuh"
-#include "../../include/incin_b200.h"
+#include "gemm_common.cuh"
+#include "gemm_pair.cuh"
 
 #include <mutex>
 #include <unordered_map>
@@ -29,88 +29,6 @@
 #include <cstdio>
 
 namespace incin {
-
-constexpr int BM = 128;
-constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
-constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 320;  // warp0: TMA, warp1: MMA + TMEM owner, warps 2-9: epilogue (two per TMEM lane quarter)
-constexpr int SMEM_BUDGET = 200 * 1024;
-
-template <int BN>
-struct GemmCfg {
-  static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES;
-  static constexpr int ACC_STRIDE = (BN <= 64) ? 64 : (BN <= 128 ? 128 : 256);
-  static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-};
-
-struct GemmKernelParams {
-  int M, N, K;
-  int batch_lo, batch_hi;
-  int tiles_m, tiles_n, splits, total_units;
-  void* C;
-  long long ldc, c_stride_lo, c_stride_hi;
-  int out_fp32, accumulate;
-  float alpha;
-  const __nv_bfloat16* bias;
-  const __nv_bfloat16* residual;
-  int act;
-  __nv_bfloat16* aux;
-  int* status;
-  // all-gather -> GEMM
-  int ag_world, ag_rank, ag_rows_per_rank, gemm_ctas;  // gemm_ctas: CTAs [0, gemm_ctas) compute, the rest copy
-  const __nv_bfloat16* ag_src[8];
-  uint32_t* ag_flags;
-  __nv_bfloat16* ag_gathered;
-  // GEMM -> reduce-scatter
-  int rs_world, rs_rank, rs_rows_per_rank;
-  int rs_push;            // 1: remote tiles go to the local staging buffer C and copy CTAs push them to their owners
-  __nv_bfloat16* rs_dst[8];
-  long long rs_slot_stride;
-  uint32_t* rs_ready;     // push mode: per 128-row block, epilogue warps that have finished writing it
-};
-
-struct Unit {
-  int m_blk, n_blk, b_lo, b_hi, kb0, kb1;
-};
-
-__device__ __forceinline__ Unit decode_unit(const GemmKernelParams& p, int u) {
-  Unit w;
-  const int split = u % p.splits;
-  int t = u / p.splits;
-  int b;
-  if (p.ag_world > 1) {
-    // tiles of one 128-row block are consecutive (one flag wait serves them all) and the row blocks are visited
-    // in arrival order: own shard first, then the peers' shards in the order the copy CTAs fetch them
-    w.n_blk = t % p.tiles_n;
-    t /= p.tiles_n;
-    const int mi = t % p.tiles_m;
-    w.m_blk = (mi + p.ag_rank * (p.ag_rows_per_rank / BM)) % p.tiles_m;
-    b = t / p.tiles_m;
-  } else if (p.rs_push) {
-    // row blocks owned by the next rank first, own rows last: the copy CTAs push finished blocks while the
-    // remaining ones are still being computed, and nothing has to leave this GPU after the last tile
-    w.n_blk = t % p.tiles_n;
-    t /= p.tiles_n;
-    const int mi = t % p.tiles_m;
-    w.m_blk = (mi + (p.rs_rank + 1) * (p.rs_rows_per_rank / BM)) % p.tiles_m;
-    b = t / p.tiles_m;
-  } else {
-    w.m_blk = t % p.tiles_m;
-    t /= p.tiles_m;
-    w.n_blk = t % p.tiles_n;
-    b = t / p.tiles_n;
-  }
-  w.b_lo = b % p.batch_lo;
-  w.b_hi = b / p.batch_lo;
-  const int kb_total = (p.K + BK - 1) / BK;
-  w.kb0 = static_cast<int>((static_cast<long long>(split) * kb_total) / p.splits);
-  w.kb1 = static_cast<int>((static_cast<long long>(split + 1) * kb_total) / p.splits);
-  return w;
-}
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -394,151 +312,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * Cfg::ACC_STRIDE + c * 32, r);
         tmem_ld_wait();
         const int nc = n0 + c * 32;
-        if (row_ok && nc < p.N) {
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        const bool full = (nc + 32 <= p.N) && vec_ok;
-        if (p.bias) {
-          if (full) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 bb = *reinterpret_cast<const uint4*>(p.bias + nc + q * 8);
-              const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = unpack_bf16x2(bw[e]);
-                v[q * 8 + e * 2] += f.x;
-                v[q * 8 + e * 2 + 1] += f.y;
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nc + j < p.N) v[j] += __bfloat162float(p.bias[nc + j]);
-          }
-        }
-        if (p.act == INCIN_ACT_GELU || p.act == INCIN_ACT_SILU) {
-          if (p.aux) {  // keep the pre-activation for the backward pass
-            __nv_bfloat16* ax = p.aux + cbase + nc;
-            if (full) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 o;
-                o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-                o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-                o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-                o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-                *reinterpret_cast<uint4*>(ax + q * 8) = o;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nc + j < p.N) ax[j] = __float2bfloat16(v[j]);
-            }
-          }
-          if (p.act == INCIN_ACT_GELU) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = silu(v[j]);
-          }
-        } else if (p.act == INCIN_ACT_DGELU || p.act == INCIN_ACT_DSILU) {
-          // multiply by act'(pre-activation): fuses the activation backward into the data-gradient GEMM
-          const __nv_bfloat16* ax = p.aux + cbase + nc;
-          if (full) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 bb = *reinterpret_cast<const uint4*>(ax + q * 8);
-              const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = unpack_bf16x2(bw[e]);
-                if (p.act == INCIN_ACT_DGELU) {
-                  v[q * 8 + e * 2] *= gelu_erf_grad(f.x);
-                  v[q * 8 + e * 2 + 1] *= gelu_erf_grad(f.y);
-                } else {
-                  v[q * 8 + e * 2] *= silu_grad(f.x);
-                  v[q * 8 + e * 2 + 1] *= silu_grad(f.y);
-                }
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (nc + j < p.N) {
-                const float x = __bfloat162float(ax[j]);
-                v[j] *= (p.act == INCIN_ACT_DGELU) ? gelu_erf_grad(x) : silu_grad(x);
-              }
-            }
-          }
-        }
-        if (p.residual) {
-          const __nv_bfloat16* rs = p.residual + cbase + nc;
-          if (full) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 bb = *reinterpret_cast<const uint4*>(rs + q * 8);
-              const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = unpack_bf16x2(bw[e]);
-                v[q * 8 + e * 2] += f.x;
-                v[q * 8 + e * 2 + 1] += f.y;
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nc + j < p.N) v[j] += __bfloat162float(rs[j]);
-          }
-        }
-        if (p.out_fp32) {
-          float* out = reinterpret_cast<float*>(c_ptr) + cbase + nc;
-          if (p.accumulate) {
-            if (full) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + q * 4), "f"(v[q * 4]),
-                             "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
-                             : "memory");
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nc + j < p.N) atomicAdd(out + j, v[j]);
-            }
-          } else {
-            if (full) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<float4*>(out + q * 4) =
-                    make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nc + j < p.N) out[j] = v[j];
-            }
-          }
-        } else {
-          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(c_ptr) + cbase + nc;
-          if (full) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 o;
-              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-              *reinterpret_cast<uint4*>(out + q * 8) = o;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nc + j < p.N) out[j] = __float2bfloat16(v[j]);
-          }
-        }
-        }  // row_ok
+        if (row_ok && nc < p.N) epilogue_chunk(p, r, c_ptr, cbase, nc, vec_ok);
         __syncwarp();  // tcgen05.ld is warp-collective: reconverge before the next chunk
       }
       tc_fence_before();
@@ -660,6 +434,48 @@ static int launch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUten
   return launch_cfg<BN, true, true>(ta, tb, p, max_ctas, s);
 }
 
+// CTA-pair kernel launch: as many clusters as the device can hold at once (at most one CTA per SM).
+template <bool A_MN, bool B_MN>
+static int launch_pair_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmKernelParams& p, int tiles_m2, int max_ctas,
+                           cudaStream_t stream) {
+  auto kern = gemm_tcgen05_pair_kernel<A_MN, B_MN>;
+  static int max_clusters = 0;
+  if (max_clusters == 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES) != cudaSuccess)
+      return INCIN_ERR_LAUNCH;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 74, 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      return INCIN_ERR_LAUNCH;
+    }
+    max_clusters = n;
+  }
+  int pairs = max_clusters < max_ctas / 2 ? max_clusters : max_ctas / 2;
+  if (pairs > p.total_units) pairs = p.total_units;
+  if (pairs < 1) return INCIN_ERR_ARGUMENT;
+  kern<<<2 * pairs, GEMM_THREADS, PairCfg::SMEM_BYTES, stream>>>(ta, tb, p, tiles_m2);
+  return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
+}
+
+static int launch_pair(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmKernelParams& p,
+                       int tiles_m2, int max_ctas, cudaStream_t s) {
+  if (!a_mn && !b_mn) return launch_pair_cfg<false, false>(ta, tb, p, tiles_m2, max_ctas, s);
+  if (!a_mn && b_mn) return launch_pair_cfg<false, true>(ta, tb, p, tiles_m2, max_ctas, s);
+  if (a_mn && !b_mn) return launch_pair_cfg<true, false>(ta, tb, p, tiles_m2, max_ctas, s);
+  return launch_pair_cfg<true, true>(ta, tb, p, tiles_m2, max_ctas, s);
+}
+
 // Pick the N tile that minimises (waves x per-tile cost) on this GPU.
 static int choose_bn(long long M, long long N, long long batch, int splits, int sms) {
   const int cands[4] = {256, 192, 128, 64};
@@ -697,7 +513,14 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   if (splits > 1 && (d->bias || d->residual || d->act != INCIN_ACT_NONE)) return INCIN_ERR_ARGUMENT;
   if ((d->act == INCIN_ACT_DGELU || d->act == INCIN_ACT_DSILU) && !d->aux) return INCIN_ERR_ARGUMENT;
   int bn = d->tile_n;
+  const bool fused_collective = d->ag_world > 1 || d->rs_world > 1;
+  // 512 = the 256 x 256 tile of a CTA pair.  Chosen automatically for long reductions on tiles that fill the
+  // pairs: there the single-CTA tile is bound by shared-memory and L2 operand traffic, which the pair cuts by a
+  // third (measured +9 % at 8192^3, +24 % at 8192 x 768 x 3072); short reductions stay with the single-CTA tiles.
+  if (bn == 0 && !fused_collective && d->K >= 2048 && d->M >= 512 && d->N >= 512 && sms >= 148) bn = 512;
+  const bool pair = bn == 512 && !fused_collective;
   if (bn != 64 && bn != 128 && bn != 192 && bn != 256) bn = choose_bn(d->M, d->N, (long long)blo * bhi, splits, sms);
+  const int b_box = pair ? 128 : bn;                      // B rows one CTA loads per k-block
 
   CUtensorMap ta, tb;
   int rc;
@@ -707,7 +530,7 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
     rc = make_operand_map(&ta, d->A, d->M, d->K, d->lda, blo, d->a_stride_lo, bhi, d->a_stride_hi, 64, BK);
   if (rc != INCIN_OK) return rc;
   if (!d->b_mn_major)
-    rc = make_operand_map(&tb, d->B, d->K, d->N, d->ldb, blo, d->b_stride_lo, bhi, d->b_stride_hi, BK, bn);
+    rc = make_operand_map(&tb, d->B, d->K, d->N, d->ldb, blo, d->b_stride_lo, bhi, d->b_stride_hi, BK, b_box);
   else
     rc = make_operand_map(&tb, d->B, d->N, d->K, d->ldb, blo, d->b_stride_lo, bhi, d->b_stride_hi, 64, BK);
   if (rc != INCIN_OK) return rc;
@@ -719,9 +542,10 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   p.batch_lo = blo;
   p.batch_hi = bhi;
   p.tiles_m = (d->M + BM - 1) / BM;
-  p.tiles_n = (d->N + bn - 1) / bn;
+  p.tiles_n = pair ? (d->N + 255) / 256 : (d->N + bn - 1) / bn;
   p.splits = splits;
-  const long long units = (long long)p.tiles_m * p.tiles_n * blo * bhi * splits;
+  const int tiles_m2 = (d->M + 255) / 256;
+  const long long units = (long long)(pair ? tiles_m2 : p.tiles_m) * p.tiles_n * blo * bhi * splits;
   if (units > 0x7fffffffLL) return INCIN_ERR_ARGUMENT;
   p.total_units = (int)units;
   p.C = d->C;
@@ -770,6 +594,7 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   }
 
   const bool amn = d->a_mn_major != 0, bmn = d->b_mn_major != 0;
+  if (pair) return incin::launch_pair(amn, bmn, ta, tb, p, tiles_m2, sms, stream);
   int rc2;
   if (bn == 64) rc2 = incin::launch_major<64>(amn, bmn, ta, tb, p, sms, stream);
   else if (bn == 128) rc2 = incin::launch_major<128>(amn, bmn, ta, tb, p, sms, stream);

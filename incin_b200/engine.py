@@ -34,6 +34,7 @@ class TrainStep:
         self.reducer = reducer  # data-parallel gradient reducer (fused reduce + optimiser), or None
         self.calls = 0
         self.graph: torch.cuda.CUDAGraph | None = None
+        self.capture_error: str | None = None
         self.static_inputs: list[torch.Tensor] | None = None
         self.static_loss: torch.Tensor | None = None
         self.launches_per_step: int | None = None
@@ -53,13 +54,13 @@ class TrainStep:
             self.opt.launch()
         return loss.detach()
 
-    def _capture(self, inputs: Sequence[torch.Tensor]) -> None:
+    def _capture(self, inputs: Sequence[torch.Tensor], mode: str = "global") -> None:
         self.static_inputs = [t.clone() for t in inputs]
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
         g = torch.cuda.CUDAGraph()
         with torch.cuda.stream(side):
-            with torch.cuda.graph(g, stream=side):
+            with torch.cuda.graph(g, stream=side, capture_error_mode=mode):
                 self.static_loss = self._enqueue(self.static_inputs)
         torch.cuda.current_stream().wait_stream(side)
         self.graph = g
@@ -73,8 +74,16 @@ class TrainStep:
         if self.graph is None:
             try:
                 self._capture(inputs)
-            except Exception:
-                # capture is an optimisation; any failure leaves the eager path in charge
+            except Exception as e:
+                # capture is an optimisation; any failure leaves the eager path in charge (and says why)
+                import traceback
+                import warnings
+                self.capture_error = f"{type(e).__name__}: {e}\n" + "".join(traceback.format_tb(e.__traceback__)[-6:])
+                warnings.warn("CUDA-graph capture of the training step failed, running eagerly.  A common cause: a loss "
+                              "tensor from a forward pass made BEFORE this step is still referenced, which keeps the "
+                              "parameters' gradient-accumulator nodes of the default stream alive; autograd then records "
+                              "an event on the default stream during capture, which CUDA forbids.  Drop that reference "
+                              f"(del loss) or detach it.  Error: {self.capture_error}")
                 self.use_graph = False
                 self.graph = None
                 torch.cuda.synchronize()

@@ -173,9 +173,44 @@ class Conv2d(nn.Conv2d):
 
 
 Conv1d = nn.Conv1d
-BatchNorm2d = nn.BatchNorm2d
-MaxPool2d = nn.MaxPool2d
-AvgPool2d = nn.AvgPool2d
+class BatchNorm2d(nn.Module):
+    """Per-channel batch normalisation over ``[N, C, H, W]`` (crates/incin-core/src/nn/batch_norm.rs): fp32 affine
+    parameters and running statistics, training forward + backward and the inference form on the native kernels."""
+
+    def __init__(self, num_features: int, eps: float = 1e-5, momentum: float = 0.1, affine: bool = True):
+        super().__init__()
+        self.num_features, self.eps, self.momentum = num_features, eps, momentum
+        self.weight = nn.Parameter(torch.ones(num_features)) if affine else None
+        self.bias = nn.Parameter(torch.zeros(num_features)) if affine else None
+        self.register_buffer("running_mean", torch.zeros(num_features))
+        self.register_buffer("running_var", torch.ones(num_features))
+
+    def forward(self, x):
+        from ..ops.tensor_ops import batch_norm
+        return batch_norm(x, self.weight, self.bias, self.running_mean, self.running_var, self.training, self.momentum,
+                          self.eps)
+
+
+class MaxPool2d(nn.Module):
+    def __init__(self, kernel_size, stride=None, padding=0):
+        super().__init__()
+        self.kernel_size, self.stride, self.padding = kernel_size, stride, padding
+
+    def forward(self, x):
+        from ..ops.tensor_ops import max_pool2d
+        return max_pool2d(x, self.kernel_size, self.stride, self.padding)
+
+
+class AvgPool2d(nn.Module):
+    def __init__(self, kernel_size, stride=None, padding=0):
+        super().__init__()
+        self.kernel_size, self.stride, self.padding = kernel_size, stride, padding
+
+    def forward(self, x):
+        from ..ops.tensor_ops import avg_pool2d
+        return avg_pool2d(x, self.kernel_size, self.stride, self.padding)
+
+
 AdaptiveAvgPool2d = nn.AdaptiveAvgPool2d
 
 

@@ -250,7 +250,15 @@ class _Embedding(torch.autograd.Function):
     def backward(ctx, dout):
         (tokens,) = ctx.saved_tensors
         wte, wpe = ctx.wte, ctx.wpe
-        K.embedding_bwd(_c(dout), tokens, main_grad(wte), main_grad(wpe) if wpe is not None else None)
+        from ..core.policy import Determinism, current_policy
+        if current_policy().determinism is Determinism.REQUIRED and not torch.cuda.is_current_stream_capturing():
+            # fixed summation order: sort by token, one block per distinct token (not capturable: the number of
+            # distinct tokens is read back to size the launch)
+            from .tensor_ops import embedding_bwd_deterministic
+            embedding_bwd_deterministic(_c(dout), tokens, main_grad(wte), main_grad(wpe) if wpe is not None else None,
+                                        tokens.shape[-1])
+        else:
+            K.embedding_bwd(_c(dout), tokens, main_grad(wte), main_grad(wpe) if wpe is not None else None)
         _ready(wte)
         if wpe is not None:
             _ready(wpe)
@@ -484,9 +492,14 @@ def conv2d_im2col(x, w, b, stride, padding, dilation):
     its SGEMM per batch and group: crates/incin-backends/src/cuda/backend.rs:1638-1645)."""
     N, Cin, H, W = x.shape
     O, _, KH, KW = w.shape
-    cols = TF.unfold(x, (KH, KW), dilation=dilation, padding=padding, stride=stride)   # [N, Cin*KH*KW, L]
-    L = cols.shape[-1]
-    a = cols.transpose(1, 2).reshape(N * L, Cin * KH * KW).contiguous()
+    if x.requires_grad or not x.is_cuda:
+        cols = TF.unfold(x, (KH, KW), dilation=dilation, padding=padding, stride=stride)   # [N, Cin*KH*KW, L]
+        L = cols.shape[-1]
+        a = cols.transpose(1, 2).reshape(N * L, Cin * KH * KW).contiguous()
+    else:   # no gradient flows into the input (first layer, inference): the native unfold writes the GEMM operand directly
+        from .tensor_ops import im2col
+        a = im2col(x, (KH, KW), tuple(stride), tuple(padding), tuple(dilation))
+        L = a.shape[0] // N
     kdim = a.shape[1]
     wk = w.reshape(O, kdim)
     if kdim % 8:   # TMA needs 16-byte row strides: pad the reduction dimension with zeros
