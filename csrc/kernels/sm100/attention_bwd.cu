@@ -15,6 +15,7 @@
 //
 // No counterpart in the reference (no attention backward exists there).
 #include "ptx.cuh"
+#include "launch.cuh"
 #include "../../include/incin_b200.h"
 #include <math_constants.h>
 
@@ -119,6 +120,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();   // tensor memory is held
+  pdl_wait();
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -347,6 +350,8 @@ __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
                   long long B, int T, int Tpad, int H, int D, long long o_sb, long long o_st, long long o_sh,
                   long long do_sb, long long do_st, long long do_sh) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (w >= B * Tpad * H) return;
@@ -371,6 +376,8 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
 // dq (bf16, strided) = dq_accum (fp32 [B,T,H,D] contiguous)
 __global__ void attn_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long B, int T,
                                     int H, int D, long long sb, long long st, long long sh) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long n4 = B * T * H * D / 4;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
@@ -409,9 +416,11 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   const long long rows = (long long)d->B * d->T * d->Hq;
   const int Tpad = (d->T + FB_T - 1) / FB_T * FB_T;
   const long long prow = (long long)d->B * Tpad * d->Hq;
-  attn_delta_kernel<<<(unsigned)((prow + 7) / 8), 256, 0, stream>>>(
-      (const __nv_bfloat16*)d->o, (const __nv_bfloat16*)d->d_o, d->delta, d->B, d->T, Tpad, d->Hq, D, d->o_stride_b,
-      d->o_stride_t, d->o_stride_h, d->do_stride_b, d->do_stride_t, d->do_stride_h);
+  if (launch_pdl(attn_delta_kernel, dim3((unsigned)((prow + 7) / 8)), dim3(256), 0, stream, (const __nv_bfloat16*)d->o,
+                 (const __nv_bfloat16*)d->d_o, d->delta, (long long)d->B, (int)d->T, Tpad, (int)d->Hq, D, (long long)d->o_stride_b,
+                 (long long)d->o_stride_t, (long long)d->o_stride_h, (long long)d->do_stride_b, (long long)d->do_stride_t,
+                 (long long)d->do_stride_h) != cudaSuccess)
+    return INCIN_ERR_LAUNCH;
   if (cudaMemsetAsync(d->dq_accum, 0, sizeof(float) * rows * D, stream) != cudaSuccess) return INCIN_ERR_LAUNCH;
   FbParams p;
   p.T = d->T;
@@ -434,12 +443,14 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.dv_stride_h = d->dv_stride_h;
   p.status = (int*)d->status;
   dim3 grid(p.n_tiles, d->Hkv, d->B);
-  kern<<<grid, FB_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  if (launch_pdl(kern, grid, dim3(FB_THREADS), Cfg::SMEM_BYTES, stream, tq, tk, tv, tdo, p) != cudaSuccess) return INCIN_ERR_LAUNCH;
   long long n4 = rows * D / 4;
   long long blocks = (n4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  attn_dq_cast_kernel<<<(unsigned)blocks, 256, 0, stream>>>(d->dq_accum, (__nv_bfloat16*)d->dq, d->B, d->T, d->Hq, D,
-                                                           d->dq_stride_b, d->dq_stride_t, d->dq_stride_h);
+  if (launch_pdl(attn_dq_cast_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)d->dq_accum,
+                 (__nv_bfloat16*)d->dq, (long long)d->B, (int)d->T, (int)d->Hq, D, (long long)d->dq_stride_b,
+                 (long long)d->dq_stride_t, (long long)d->dq_stride_h) != cudaSuccess)
+    return INCIN_ERR_LAUNCH;
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
 

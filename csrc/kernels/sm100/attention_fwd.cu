@@ -13,6 +13,7 @@
 // (crates/incin-backends/src/cpu/ops/shape_ops.rs:1245-1269) and CUDA reports SDPA as unsupported;
 // flash_attention_lite.cu there is dead code with one thread per query row.
 #include "ptx.cuh"
+#include "launch.cuh"
 #include "../../include/incin_b200.h"
 #include <math_constants.h>
 
@@ -106,6 +107,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + BN;
+  pdl_launch_dependents();   // tensor memory is held; a successor may be scheduled as CTAs retire
+  pdl_wait();                // no global memory was touched above
 
   if (warp == 0) {
     if (lane == 0) {
@@ -311,7 +314,7 @@ static int launch_fwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.Tpad = p.n_q_tiles * FA_BM;
   p.status = (int*)d->status;
   dim3 grid(p.n_q_tiles, d->Hq, d->B);
-  kern<<<grid, FA_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  if (launch_pdl(kern, grid, dim3(FA_THREADS), Cfg::SMEM_BYTES, stream, tq, tk, tv, p) != cudaSuccess) return INCIN_ERR_LAUNCH;
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
 

@@ -2,6 +2,7 @@
 // the persistent tile order, and the fused epilogue of one 32-column accumulator chunk.
 #pragma once
 #include "ptx.cuh"
+#include "launch.cuh"
 #include "../../include/incin_b200.h"
 
 namespace incin {
@@ -10,7 +11,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 320;  // warp0: TMA, warp1: MMA + TMEM owner, warps 2-9: epilogue (two per TMEM lane quarter)
-constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr int SMEM_BUDGET = 224 * 1024;   // of the 227 KB a CTA may use; the rest holds barriers and alignment slack
 
 template <int BN>
 struct GemmCfg {

@@ -1,6 +1,6 @@
 // CTA-pair variant of the tcgen05 GEMM (cta_group::2): two CTAs of a 2-CTA cluster, on neighbouring SMs, compute
 // one 256 x 256 output tile.  Each CTA loads 128 rows of A and 128 of the tile's 256 B rows per k-block (32 KB per
-// stage, six stages), the leader CTA issues M=256, N=256 MMAs for the pair, and each CTA's tensor memory receives
+// stage, seven stages), the leader CTA issues M=256, N=256 MMAs for the pair, and each CTA's tensor memory receives
 // the accumulator of its own 128 rows.  Per FLOP a CTA reads one third less shared memory than the single-CTA
 // 128 x 256 tile, which is the bound of that kernel; the operand traffic from L2 halves for B.
 //
@@ -22,7 +22,7 @@ struct PairCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN_CTA * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = 6;
+  static constexpr int STAGES = 7;
   static constexpr int ACC_STRIDE = 256;
   static constexpr int TMEM_COLS = 512;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
@@ -90,6 +90,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   cluster_sync_all();   // both CTAs' barriers are initialised and both allocations are done before anyone signals
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();   // both CTAs hold their tensor memory
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer (one per CTA)

@@ -76,6 +76,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();   // tensor memory is held: a successor may be scheduled as SMs drain
+  pdl_wait();                // nothing above touched global memory; everything below may depend on earlier kernels
 
   if (is_copier) {
     // ------------------------------------------------------------- copy CTA (one thread drives the bulk copies)
@@ -421,8 +423,12 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmKe
     q.gemm_ctas = compute;
     grid = compute + copy;
   }
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, q);
-  return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
+  // fused-collective launches wait on other GPUs: those stay ordinary launches
+  if (q.ag_world > 1 || q.rs_world > 1) {
+    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, q);
+    return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
+  }
+  return launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), Cfg::SMEM_BYTES, stream, ta, tb, q) == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
 
 template <int BN>
@@ -464,8 +470,9 @@ static int launch_pair_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const G
   int pairs = max_clusters < max_ctas / 2 ? max_clusters : max_ctas / 2;
   if (pairs > p.total_units) pairs = p.total_units;
   if (pairs < 1) return INCIN_ERR_ARGUMENT;
-  kern<<<2 * pairs, GEMM_THREADS, PairCfg::SMEM_BYTES, stream>>>(ta, tb, p, tiles_m2);
-  return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
+  return launch_pdl(kern, dim3(2 * pairs), dim3(GEMM_THREADS), PairCfg::SMEM_BYTES, stream, ta, tb, p, tiles_m2) == cudaSuccess
+             ? INCIN_OK
+             : INCIN_ERR_LAUNCH;
 }
 
 static int launch_pair(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmKernelParams& p,
@@ -476,23 +483,55 @@ static int launch_pair(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtens
   return launch_pair_cfg<true, true>(ta, tb, p, tiles_m2, max_ctas, s);
 }
 
-// Pick the N tile that minimises (waves x per-tile cost) on this GPU.
-static int choose_bn(long long M, long long N, long long batch, int splits, int sms) {
-  const int cands[4] = {256, 192, 128, 64};
-  int best = 128;
+// Pick the tile and the split-K factor that minimise a cost model fitted to per-launch CUDA-event timings on a B200
+// (L2 flushed before every launch; 18 shapes x 5 tiles x up to 4 split factors, candidates interleaved):
+//     time = fixed(tile) + waves x k_blocks_per_split x step(tile) + split penalty
+// step(tile) is the microseconds one 64-deep k-block costs a CTA when every SM is busy.  It is set by the operand
+// traffic from L2 (all tiles sustain about 14 TB/s in aggregate, the CTA pair about 10.5 TB/s), so it grows more
+// slowly than the tile: wider tiles do more work per byte.  fixed(tile) is prologue plus the tail epilogue, which
+// grows with the tile; the pair pays for its cluster launch and two cluster-wide syncs.  A last wave that fills only
+// part of the machine is cheaper than a full one because its CTAs contend less for L2.
+struct TileChoice {
+  int bn;       // 64 / 128 / 192 / 256, or 512 for the 256 x 256 tile of a CTA pair
+  int splits;
+};
+
+static double waves_cost(long long units, int slots) {
+  const long long full = units / slots;
+  const double part = static_cast<double>(units % slots) / slots;
+  return static_cast<double>(full) + (part > 0.0 ? 0.55 + 0.45 * part : 0.0);
+}
+
+static TileChoice choose_tile(long long M, long long N, long long K, long long batch, int fixed_bn, int fixed_splits,
+                              bool may_split, bool may_pair, int sms) {
+  static const int kBn[5] = {64, 128, 192, 256, 512};
+  static const double kStep[5] = {0.370, 0.395, 0.420, 0.498, 0.452};
+  static const double kFixed[5] = {10.0, 11.4, 13.6, 16.0, 21.0};
+  static const int kSplits[7] = {1, 2, 3, 4, 5, 6, 8};
+  const long long kb = (K + BK - 1) / BK;
+  TileChoice best = {128, 1};
   double best_cost = 1e30;
-  for (int bn : cands) {
-    const long long tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * batch * splits;
-    const long long waves = (tiles + sms - 1) / sms;
-    // per-tile cost: MMA time grows with bn, but narrow tiles re-read the A operand from shared memory
-    // more often per FLOP (128x128 tiles are shared-memory-bandwidth bound near half rate)
-    const double per_tile = bn == 256 ? 256.0 : (bn == 192 ? 205.0 : (bn == 128 ? 160.0 : 110.0));
-    const double cost = static_cast<double>(waves) * (per_tile + 24.0);
-    if (cost < best_cost) {
-      best_cost = cost;
-      best = bn;
+  for (int t = 0; t < 5; ++t) {
+    const int bn = kBn[t];
+    if (fixed_bn > 0 && bn != fixed_bn) continue;
+    const bool pair = bn == 512;
+    if (pair && (!may_pair || sms < 148 || (fixed_bn != 512 && (M < 512 || N < 512)))) continue;
+    const long long tiles = pair ? ((M + 255) / 256) * ((N + 255) / 256) * batch
+                                 : ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * batch;
+    const int slots = pair ? sms / 2 : sms;
+    for (int si = 0; si < 7; ++si) {
+      const int sp = kSplits[si];
+      if (fixed_splits > 0 ? sp != fixed_splits : (sp > 1 && (!may_split || kb / sp < 4))) continue;
+      const long long kbs = (kb + sp - 1) / sp;
+      const double cost = kFixed[t] + waves_cost(tiles * sp, slots) * static_cast<double>(kbs) * kStep[t] + 1.5 * (sp - 1);
+      if (cost < best_cost) {
+        best_cost = cost;
+        best.bn = bn;
+        best.splits = sp;
+      }
     }
   }
+  if (fixed_splits > 0) best.splits = fixed_splits;
   return best;
 }
 
@@ -506,20 +545,24 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   const int blo = d->batch_lo > 0 ? d->batch_lo : 1;
   const int bhi = d->batch_hi > 0 ? d->batch_hi : 1;
   const int sms = d->max_ctas > 0 ? d->max_ctas : device_sm_count();
-  int splits = d->splits > 0 ? d->splits : 1;
+  // splits == 0 asks for the split-K factor to be chosen together with the tile (fp32 accumulating outputs only)
+  const bool can_split = d->out_fp32 && d->accumulate && !d->bias && !d->residual && d->act == INCIN_ACT_NONE &&
+                         d->ag_world <= 1 && d->rs_world <= 1;
   const int kb_total = (d->K + BK - 1) / BK;
+  int splits = d->splits > 0 ? d->splits : (can_split ? 0 : 1);
   if (splits > kb_total) splits = kb_total;
   if (splits > 1 && !(d->out_fp32 && d->accumulate)) return INCIN_ERR_ARGUMENT;
   if (splits > 1 && (d->bias || d->residual || d->act != INCIN_ACT_NONE)) return INCIN_ERR_ARGUMENT;
   if ((d->act == INCIN_ACT_DGELU || d->act == INCIN_ACT_DSILU) && !d->aux) return INCIN_ERR_ARGUMENT;
-  int bn = d->tile_n;
   const bool fused_collective = d->ag_world > 1 || d->rs_world > 1;
-  // 512 = the 256 x 256 tile of a CTA pair.  Chosen automatically for long reductions on tiles that fill the
-  // pairs: there the single-CTA tile is bound by shared-memory and L2 operand traffic, which the pair cuts by a
-  // third (measured +9 % at 8192^3, +24 % at 8192 x 768 x 3072); short reductions stay with the single-CTA tiles.
-  if (bn == 0 && !fused_collective && d->K >= 2048 && d->M >= 512 && d->N >= 512 && sms >= 148) bn = 512;
-  const bool pair = bn == 512 && !fused_collective;
-  if (bn != 64 && bn != 128 && bn != 192 && bn != 256) bn = choose_bn(d->M, d->N, (long long)blo * bhi, splits, sms);
+  int bn = d->tile_n;
+  if (bn != 64 && bn != 128 && bn != 192 && bn != 256 && bn != 512) bn = 0;
+  if (bn == 512 && fused_collective) bn = 0;
+  const incin::TileChoice pick = incin::choose_tile(d->M, d->N, d->K, (long long)blo * bhi, bn, splits, can_split,
+                                                    !fused_collective, sms);
+  bn = pick.bn;
+  splits = pick.splits;
+  const bool pair = bn == 512;
   const int b_box = pair ? 128 : bn;                      // B rows one CTA loads per k-block
 
   CUtensorMap ta, tb;

@@ -6,6 +6,7 @@
 // nll_loss kernel reads int64 targets through an int* (loss.cu:6); here targets
 // are int64 end to end and the whole loss is two passes over the logits.
 #include "ptx.cuh"
+#include "launch.cuh"
 #include "../../include/incin_b200.h"
 #include <math_constants.h>
 
@@ -53,6 +54,8 @@ __device__ __forceinline__ float block_max(float v, float* sh) {
 __global__ void embedding_fwd_kernel(const int64_t* __restrict__ tok, const __nv_bfloat16* __restrict__ wte,
                                      const __nv_bfloat16* __restrict__ wpe, __nv_bfloat16* __restrict__ out,
                                      long long BT, int T, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long row = blockIdx.x;
   if (row >= BT) return;
   const int t = (int)(row % T);
@@ -85,6 +88,8 @@ __global__ void embedding_fwd_kernel(const int64_t* __restrict__ tok, const __nv
 
 __global__ void embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const int64_t* __restrict__ tok,
                                      float* __restrict__ dwte, float* __restrict__ dwpe, long long BT, int T, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long row = blockIdx.x;
   if (row >= BT) return;
   const int t = (int)(row % T);
@@ -104,6 +109,8 @@ constexpr int XENT_THREADS = 512;
 __global__ void __launch_bounds__(XENT_THREADS)
 xent_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
                 float* __restrict__ loss, float* __restrict__ lse_out, int V, long long ld) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sh[32];
   const long long row = blockIdx.x;
   const __nv_bfloat16* lr = logits + row * ld;
@@ -164,6 +171,8 @@ xent_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __restr
 __global__ void __launch_bounds__(XENT_THREADS)
 xent_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
                 const float* __restrict__ lse_in, const float* __restrict__ dloss, float scale, int V, long long ld) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long row = blockIdx.x;
   __nv_bfloat16* lr = logits + row * ld;
   const float lse = lse_in[row];
@@ -195,6 +204,8 @@ xent_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ 
 }
 
 __global__ void __launch_bounds__(1024) mean_kernel(const float* __restrict__ x, float* __restrict__ out, long long n) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sh[32];
   float s = 0.f;
   for (long long i = threadIdx.x; i < n; i += 1024) s += x[i];
@@ -249,6 +260,8 @@ causal_softmax_bwd_kernel(__nv_bfloat16* __restrict__ dp, const __nv_bfloat16* _
 __global__ void __launch_bounds__(256)
 colsum_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ dbias, long long rows, int N, long long ld,
               int chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sh[8][64];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c0 = blockIdx.x * 64 + tx * 2;
@@ -289,6 +302,8 @@ colsum_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ dbias, l
 __global__ void __launch_bounds__(256)
 colsum_vec_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ dbias, long long rows, int N,
                   long long ld, int chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sh[8][256];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c0 = blockIdx.x * 256 + tx * 8;
@@ -330,7 +345,7 @@ extern "C" int incin_embedding_fwd(const int64_t* tokens, const void* wte, const
   const long long BT = B * T;
   if (BT <= 0 || C <= 0 || BT > 0x7fffffffLL) return INCIN_ERR_ARGUMENT;
   int threads = C / 8 >= 128 ? 128 : 64;
-  embedding_fwd_kernel<<<(unsigned)BT, threads, 0, (cudaStream_t)stream>>>(
+  launch_pdl(embedding_fwd_kernel, dim3((unsigned)BT), dim3(threads), 0, (cudaStream_t)stream, 
       tokens, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, (__nv_bfloat16*)out, BT, T, C);
   return CHECK_LAUNCH();
 }
@@ -339,7 +354,7 @@ extern "C" int incin_embedding_bwd(const void* dout, const int64_t* tokens, floa
                                    int T, int C, void* stream) {
   const long long BT = B * T;
   if (BT <= 0 || C <= 0 || BT > 0x7fffffffLL) return INCIN_ERR_ARGUMENT;
-  embedding_bwd_kernel<<<(unsigned)BT, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dout, tokens, dwte, dwpe,
+  launch_pdl(embedding_bwd_kernel, dim3((unsigned)BT), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)dout, tokens, dwte, dwpe,
                                                                         BT, T, C);
   return CHECK_LAUNCH();
 }
@@ -347,7 +362,7 @@ extern "C" int incin_embedding_bwd(const void* dout, const int64_t* tokens, floa
 extern "C" int incin_xent_fwd(const void* logits, const int64_t* targets, float* loss, float* lse, long long rows,
                               int V, long long ld, void* stream) {
   if (rows <= 0 || V <= 0 || ld < V || rows > 0x7fffffffLL) return INCIN_ERR_ARGUMENT;
-  xent_fwd_kernel<<<(unsigned)rows, XENT_THREADS, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, targets,
+  launch_pdl(xent_fwd_kernel, dim3((unsigned)rows), dim3(XENT_THREADS), 0, (cudaStream_t)stream, (const __nv_bfloat16*)logits, targets,
                                                                               loss, lse, V, ld);
   return CHECK_LAUNCH();
 }
@@ -355,14 +370,14 @@ extern "C" int incin_xent_fwd(const void* logits, const int64_t* targets, float*
 extern "C" int incin_xent_bwd(void* logits, const int64_t* targets, const float* lse, const float* dloss, float scale,
                               long long rows, int V, long long ld, void* stream) {
   if (rows <= 0 || V <= 0 || ld < V || rows > 0x7fffffffLL || ld > 0x7fffffffLL) return INCIN_ERR_ARGUMENT;
-  xent_bwd_kernel<<<(unsigned)rows, XENT_THREADS, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)logits, targets, lse,
+  launch_pdl(xent_bwd_kernel, dim3((unsigned)rows), dim3(XENT_THREADS), 0, (cudaStream_t)stream, (__nv_bfloat16*)logits, targets, lse,
                                                                               dloss, scale, V, ld);
   return CHECK_LAUNCH();
 }
 
 extern "C" int incin_mean_f32(const float* x, float* out, long long n, void* stream) {
   if (n <= 0) return INCIN_ERR_ARGUMENT;
-  mean_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(x, out, n);
+  launch_pdl(mean_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, x, out, n);
   return CHECK_LAUNCH();
 }
 
@@ -390,12 +405,12 @@ extern "C" int incin_colsum_accum(const void* dy, float* dbias, long long rows, 
     if (chunks > (rows + 31) / 32) chunks = (rows + 31) / 32;
     if (chunks < 1) chunks = 1;
     dim3 grid(colblocks, (unsigned)chunks);
-    colsum_vec_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, dbias, rows, N, ld, (int)chunks);
+    launch_pdl(colsum_vec_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)dy, dbias, rows, N, ld, (int)chunks);
     return CHECK_LAUNCH();
   }
   long long chunks = (rows + 255) / 256;
   if (chunks > 128) chunks = 128;
   dim3 grid((N + 63) / 64, (unsigned)chunks);
-  colsum_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, dbias, rows, N, ld, (int)chunks);
+  launch_pdl(colsum_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)dy, dbias, rows, N, ld, (int)chunks);
   return CHECK_LAUNCH();
 }

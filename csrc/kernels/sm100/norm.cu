@@ -10,6 +10,7 @@
 // (crates/incin-backends/src/kernel.rs:1233-1336) and composes RMSNorm from
 // six elementwise launches (crates/incin-core/src/nn/rms_norm.rs:88-126).
 #include "ptx.cuh"
+#include "launch.cuh"
 #include "../../include/incin_b200.h"
 
 namespace incin {
@@ -47,6 +48,8 @@ __global__ void __launch_bounds__(NORM_WARPS * 32)
 norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                 const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
                 float* __restrict__ rstd_out, long long rows, int C, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -125,6 +128,8 @@ norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
                    const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
                    const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dx_add,
                    __nv_bfloat16* __restrict__ dx, long long rows, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -195,6 +200,8 @@ __global__ void __launch_bounds__(32 * PG_TY)
 norm_bwd_param_partial(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                        const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                        float* __restrict__ scratch, long long rows, int C, int chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sg[PG_TY][PG_COLS];
   __shared__ float sb[PG_TY][PG_COLS];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -256,6 +263,8 @@ __global__ void __launch_bounds__(256)
 norm_bwd_param_partial_vec(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                            const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                            float* __restrict__ scratch, long long rows, int C, int chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sg[8][256];
   __shared__ float sb[8][256];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -299,6 +308,8 @@ norm_bwd_param_partial_vec(const __nv_bfloat16* __restrict__ dy, const __nv_bflo
 
 __global__ void norm_bwd_param_final(const float* __restrict__ scratch, float* __restrict__ dgamma,
                                      float* __restrict__ dbeta, int C, int chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
   float a = 0.f, b = 0.f;
@@ -323,7 +334,7 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, con
                            int C, cudaStream_t s) {
   if (rows <= 0 || C <= 0) return INCIN_ERR_ARGUMENT;
   const unsigned blocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
-  norm_bwd_dx_kernel<RMS><<<blocks, NORM_WARPS * 32, 0, s>>>(
+  launch_pdl(norm_bwd_dx_kernel<RMS>, dim3(blocks), dim3(NORM_WARPS * 32), 0, s, 
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd,
       (const __nv_bfloat16*)dx_add, (__nv_bfloat16*)dx, rows, C);
   if (dgamma) {
@@ -331,14 +342,14 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, con
     const int chunks = param_chunks(rows);
     if ((C % 8) == 0) {
       dim3 grid((C + 255) / 256, chunks);
-      norm_bwd_param_partial_vec<RMS><<<grid, 256, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, mean,
+      launch_pdl(norm_bwd_param_partial_vec<RMS>, dim3(grid), dim3(256), 0, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, mean,
                                                            rstd, scratch, rows, C, chunks);
     } else {
       dim3 grid((C + PG_COLS - 1) / PG_COLS, chunks);
-      norm_bwd_param_partial<RMS><<<grid, 32 * PG_TY, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+      launch_pdl(norm_bwd_param_partial<RMS>, dim3(grid), dim3(32 * PG_TY), 0, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                                mean, rstd, scratch, rows, C, chunks);
     }
-    norm_bwd_param_final<<<(C + 255) / 256, 256, 0, s>>>(scratch, dgamma, dbeta, C, chunks);
+    launch_pdl(norm_bwd_param_final, dim3((C + 255) / 256), dim3(256), 0, s, scratch, dgamma, dbeta, C, chunks);
   }
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
@@ -351,7 +362,7 @@ extern "C" int incin_layernorm_fwd(const void* x, const void* gamma, const void*
                                    float* rstd, long long rows, int C, float eps, void* stream) {
   if (rows <= 0 || C <= 0 || !x || !gamma || !y || !rstd) return INCIN_ERR_ARGUMENT;
   const unsigned blocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
-  norm_fwd_kernel<false><<<blocks, NORM_WARPS * 32, 0, (cudaStream_t)stream>>>(
+  launch_pdl(norm_fwd_kernel<false>, dim3(blocks), dim3(NORM_WARPS * 32), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, (const __nv_bfloat16*)beta, (__nv_bfloat16*)y, mean, rstd,
       rows, C, eps);
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
@@ -361,7 +372,7 @@ extern "C" int incin_rmsnorm_fwd(const void* x, const void* gamma, void* y, floa
                                  float eps, void* stream) {
   if (rows <= 0 || C <= 0 || !x || !gamma || !y || !rstd) return INCIN_ERR_ARGUMENT;
   const unsigned blocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
-  norm_fwd_kernel<true><<<blocks, NORM_WARPS * 32, 0, (cudaStream_t)stream>>>(
+  launch_pdl(norm_fwd_kernel<true>, dim3(blocks), dim3(NORM_WARPS * 32), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, nullptr, (__nv_bfloat16*)y, nullptr, rstd, rows, C, eps);
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }

@@ -11,6 +11,7 @@
 // follows the CPU contract: bias-corrected moments, decoupled weight decay
 // (crates/incin-backends/src/cpu/ops/optimizer.rs:43-59).
 #include "ptx.cuh"
+#include "launch.cuh"
 #include "../../include/incin_b200.h"
 
 namespace incin {
@@ -27,6 +28,8 @@ __global__ void __launch_bounds__(256)
 adamw_flat_kernel(float* __restrict__ w, float* __restrict__ m, float* __restrict__ v, const float* __restrict__ g,
                   __nv_bfloat16* __restrict__ shadow, long long n, long long n_decay,
                   const float* __restrict__ hyper) {
+  pdl_launch_dependents();
+  pdl_wait();
   const float lr = hyper[0], b1 = hyper[1], b2 = hyper[2], eps = hyper[3], wd = hyper[4], step = hyper[5];
   const float gs = hyper[6];
   const float bc1 = 1.f - powf(b1, step), bc2 = 1.f - powf(b2, step);
@@ -119,6 +122,8 @@ sumsq_nonfinite_kernel(const float* __restrict__ x, long long n, float* __restri
 
 // ----------------------------------------------------------------------------- fills / casts
 __global__ void fill_f32_kernel(float* __restrict__ x, float value, long long n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long n4 = n >> 2;
   const float4 v4 = make_float4(value, value, value, value);
@@ -146,12 +151,16 @@ __device__ __forceinline__ float act_grad(float x, int act) {
 }
 __global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n,
                                int act) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
     y[i] = __float2bfloat16(act_apply(__bfloat162float(x[i]), act));
 }
 __global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ pre,
                                __nv_bfloat16* __restrict__ dx, long long n, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
     dx[i] = __float2bfloat16(__bfloat162float(dy[i]) * act_grad(__bfloat162float(pre[i]), act));
@@ -160,6 +169,8 @@ __global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_
 // gate_up: [rows][2F] with gate = [:, :F], up = [:, F:]
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ y, long long rows,
                                   int F) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long total = rows * F;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -172,6 +183,8 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfl
 }
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ gu,
                                   __nv_bfloat16* __restrict__ dgu, long long rows, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long total = rows * F;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -188,6 +201,8 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __
 // Rotary embedding, "rotate-half" convention: pairs (i, i + D/2), angle = t * theta^(-2i/D).
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, long long B, int T, int H, int D, long long sb,
                             long long st, long long sh, float theta, int inverse) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int half = D / 2;
   const long long total = B * T * H * half;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -290,7 +305,7 @@ using namespace incin;
 extern "C" int incin_adamw_flat(float* master, float* m, float* v, const float* grad, void* shadow, long long n,
                                 long long n_decay, const float* hyper, void* stream) {
   if (n <= 0 || !master || !m || !v || !grad || !hyper) return INCIN_ERR_ARGUMENT;
-  adamw_flat_kernel<<<grid_for(n, 1024), 256, 0, ST(stream)>>>(master, m, v, grad, (__nv_bfloat16*)shadow, n, n_decay,
+  launch_pdl(adamw_flat_kernel, dim3(grid_for(n, 1024)), dim3(256), 0, ST(stream), master, m, v, grad, (__nv_bfloat16*)shadow, n, n_decay,
                                                                hyper);
   return CHECK_LAUNCH();
 }
@@ -308,7 +323,7 @@ extern "C" int incin_sumsq_nonfinite_f32(const float* x, long long n, float* out
 }
 extern "C" int incin_fill_f32(float* x, float value, long long n, void* stream) {
   if (n <= 0) return INCIN_ERR_ARGUMENT;
-  fill_f32_kernel<<<grid_for(n, 1024), 256, 0, ST(stream)>>>(x, value, n);
+  launch_pdl(fill_f32_kernel, dim3(grid_for(n, 1024)), dim3(256), 0, ST(stream), x, value, n);
   return CHECK_LAUNCH();
 }
 extern "C" int incin_cast_f32_to_bf16(const float* x, void* y, long long n, void* stream) {
@@ -323,32 +338,32 @@ extern "C" int incin_cast_bf16_to_f32(const void* x, float* y, long long n, void
 }
 extern "C" int incin_act_fwd(const void* x, void* y, long long n, int act, void* stream) {
   if (n <= 0) return INCIN_ERR_ARGUMENT;
-  act_fwd_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, act);
+  launch_pdl(act_fwd_kernel, dim3(grid_for(n, 256)), dim3(256), 0, ST(stream), (const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, act);
   return CHECK_LAUNCH();
 }
 extern "C" int incin_act_bwd(const void* dy, const void* pre, void* dx, long long n, int act, void* stream) {
   if (n <= 0) return INCIN_ERR_ARGUMENT;
-  act_bwd_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)pre,
+  launch_pdl(act_bwd_kernel, dim3(grid_for(n, 256)), dim3(256), 0, ST(stream), (const __nv_bfloat16*)dy, (const __nv_bfloat16*)pre,
                                                            (__nv_bfloat16*)dx, n, act);
   return CHECK_LAUNCH();
 }
 extern "C" int incin_swiglu_fwd(const void* gate_up, void* y, long long rows, int F, void* stream) {
   if (rows <= 0 || F <= 0) return INCIN_ERR_ARGUMENT;
-  swiglu_fwd_kernel<<<grid_for(rows * F, 256), 256, 0, ST(stream)>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)y,
+  launch_pdl(swiglu_fwd_kernel, dim3(grid_for(rows * F, 256)), dim3(256), 0, ST(stream), (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)y,
                                                                      rows, F);
   return CHECK_LAUNCH();
 }
 extern "C" int incin_swiglu_bwd(const void* dy, const void* gate_up, void* dgate_up, long long rows, int F,
                                 void* stream) {
   if (rows <= 0 || F <= 0) return INCIN_ERR_ARGUMENT;
-  swiglu_bwd_kernel<<<grid_for(rows * F, 256), 256, 0, ST(stream)>>>(
+  launch_pdl(swiglu_bwd_kernel, dim3(grid_for(rows * F, 256)), dim3(256), 0, ST(stream), 
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)dgate_up, rows, F);
   return CHECK_LAUNCH();
 }
 extern "C" int incin_rope(void* x, long long B, int T, int H, int D, long long stride_b, long long stride_t,
                           long long stride_h, float theta, int inverse, void* stream) {
   if (B <= 0 || T <= 0 || H <= 0 || D <= 0 || (D & 1)) return INCIN_ERR_ARGUMENT;
-  rope_kernel<<<grid_for(B * T * H * (D / 2), 256), 256, 0, ST(stream)>>>((__nv_bfloat16*)x, B, T, H, D, stride_b,
+  launch_pdl(rope_kernel, dim3(grid_for(B * T * H * (D / 2), 256)), dim3(256), 0, ST(stream), (__nv_bfloat16*)x, B, T, H, D, stride_b,
                                                                           stride_t, stride_h, theta, inverse);
   return CHECK_LAUNCH();
 }

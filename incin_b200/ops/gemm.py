@@ -47,13 +47,9 @@ def check_status(device: torch.device | None = None) -> None:
 
 
 def auto_splits(M: int, N: int, K: int, batch: int = 1, sms: int = 148) -> int:
-    """Split-K factor for skinny outputs (weight gradients): fill the SMs, keep >= 4 k-blocks per split."""
-    tiles = ((M + 127) // 128) * ((N + 127) // 128) * batch
-    if tiles >= (sms * 3) // 4:
-        return 1
-    kb = (K + 63) // 64
-    want = (sms + tiles - 1) // tiles
-    return max(1, min(want, kb // 4 if kb >= 8 else 1))
+    """Split-K factor for accumulating fp32 outputs (weight gradients).  0 = let the kernel library choose the
+    factor together with the tile from its measured cost model (the default for every shape)."""
+    return 0
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int, K: int, lda: int, ldb: int,
@@ -114,7 +110,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
 def _tuned_tile_n(kw: dict) -> int:
     """Ask the autotune service for the N tile of this problem.  With the default policy this is a dictionary
     lookup that falls through to the kernel's own heuristic (0); under ``coordinated_warmup`` /
-    ``profile_guided`` the four tile widths are timed once per (shape, layout) and the winner is cached."""
+    ``profile_guided`` the tile widths (512 = the CTA-pair tile) are timed once per (shape, layout) and the winner is cached."""
     from ..tuning import TuningPolicy, candidates, service, time_cuda
     svc = service()
     if svc.policy in (TuningPolicy.DISABLED, TuningPolicy.HEURISTIC) and not svc.lru:
@@ -129,7 +125,7 @@ def _tuned_tile_n(kw: dict) -> int:
                                    "c_strides", "alpha", "bias", "residual", "act", "aux", "splits", "max_ctas",
                                    "a_offset", "b_offset", "c_offset")}
         return time_cuda(lambda: gemm(kw["a"], kw["b"], kw["out"], tile_n=params["tile_n"], **args))
-    return svc.choose(key, candidates(tile_n=[64, 128, 192, 256]), lambda: {"tile_n": 0}, measure)["tile_n"]
+    return svc.choose(key, candidates(tile_n=[64, 128, 192, 256, 512]), lambda: {"tile_n": 0}, measure)["tile_n"]
 
 
 def _rows(x: torch.Tensor) -> int:
