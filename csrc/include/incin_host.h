@@ -1,0 +1,65 @@
+/* C ABI of libincin_host.so: CPU oracle kernels, tape autograd, N-rank TCP rendezvous and the reference
+ * (in-process, host-memory) collective transport.  Every function is plain C, thread-compatible, and allocates only
+ * what its result needs. */
+#ifndef INCIN_HOST_H
+#define INCIN_HOST_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+
+/* ---- CPU oracle (fp32 reference of every op; Philox identical to the device generator) ---- */
+void incin_cpu_gemm_f32(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t a_bs, int64_t a_rs, int64_t a_cs, int64_t b_bs, int64_t b_rs, int64_t b_cs, int64_t c_bs, int64_t c_rs, float alpha, float beta);
+void incin_cpu_unary_f32(const float* x, float* y, int64_t n, int op);
+void incin_cpu_softmax_f32(const float* x, float* y, int64_t rows, int64_t C, int log_softmax);
+void incin_cpu_layernorm_f32(const float* x, const float* g, const float* b, float* y, int64_t rows, int64_t C, float eps, int rms);
+float incin_cpu_cross_entropy_f32(const float* logits, const int64_t* targets, float* dlogits, int64_t rows, int64_t V);
+void incin_cpu_sgd_f32(float* w, const float* g, int64_t n, float lr);
+void incin_cpu_adamw_f32(float* w, float* m, float* v, const float* g, int64_t n, float lr, float b1, float b2, float eps, float wd, int step);
+void incin_cpu_attention_f32(const float* q, const float* k, const float* v, float* o, int64_t heads, int64_t T, int64_t D, float scale, int causal);
+int64_t incin_cpu_q8_0_bytes(int64_t n);
+void incin_cpu_quantize_q8_0(const float* x, uint8_t* out, int64_t n);
+void incin_cpu_dequantize_q8_0(const uint8_t* in, float* y, int64_t n);
+void incin_cpu_philox_uniform_f32(float* out, int64_t n, uint64_t seed, uint64_t offset);
+void incin_cpu_philox_normal_f32(float* out, int64_t n, uint64_t seed, uint64_t offset, float mean, float std_);
+
+/* ---- tape autograd and the native MLP training loop ---- */
+int64_t incin_tape_tensor(const float* data, int64_t rows, int64_t cols, int requires_grad);
+int64_t incin_tape_linear(int64_t x, int64_t w, int64_t b);
+int64_t incin_tape_relu(int64_t x);
+int64_t incin_tape_cross_entropy(int64_t logits, const int64_t* targets);
+int incin_tape_backward(int64_t root);
+int incin_tape_read(int64_t h, float* out);
+int incin_tape_grad(int64_t h, float* out);
+int64_t incin_tape_depth(void);
+void incin_tape_set_grad_mode(int on);
+void incin_tape_set_nan_policy(int p);
+void incin_tape_reset(void);
+uint64_t incin_tape_tensor_id(int64_t h);
+int incin_cpu_mlp_train(int steps, int batch, int n_in, int n_hidden, int n_out, float lr, uint64_t seed, float* losses_out, float* final_params_out);
+
+/* ---- rendezvous (TCP, 160-byte frames, plan-hash preflight) ---- */
+int incin_rdv_connect(int rank, int world, const char* addr, const char* run_id, int64_t local_device, int timeout_ms, int64_t* handle_out);
+int incin_rdv_state(int64_t h);
+int incin_rdv_failure_code(int64_t h);
+void incin_rdv_invalidate(int64_t h, int code);
+int incin_rdv_ensure_active(int64_t h);
+int incin_rdv_abort(int64_t h, int code, int timeout_ms);
+int incin_rdv_wait_for_peer(int64_t h, int timeout_ms, int* kind, int* code, int* from);
+int incin_rdv_shutdown(int64_t h, int timeout_ms);
+int incin_rdv_allgather(int64_t h, const void* mine, int bytes, void* all, int timeout_ms);
+int64_t incin_rdv_peer_device(int64_t h, int rank);
+void incin_rdv_destroy(int64_t h);
+
+/* ---- reference transport (collective semantics on host memory) ---- */
+int incin_ref_all_reduce(const void* const* in, void* const* out, int world, int64_t n, int dtype, int op);
+int incin_ref_all_gather(const void* const* in, void* const* out, int world, int64_t n, int dtype);
+int incin_ref_reduce_scatter(const void* const* in, void* const* out, int world, int64_t n, int dtype, int op);
+int incin_ref_all_to_all(const void* const* in, void* const* out, int world, int64_t n, int dtype);
+int incin_ref_send_recv(const void* const* in, void* const* out, int world, int64_t n, int dtype, int src, int dst);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -36,6 +36,8 @@ def main(argv=None) -> int:
     sub = ap.add_subparsers(dest="cmd", required=True)
     d = sub.add_parser("doctor"); d.add_argument("--json", action="store_true")
     sub.add_parser("capabilities")
+    f = sub.add_parser("ffi"); f.add_argument("--write", action="store_true", help="rewrite rust/incin-b200-sys/src/lib.rs")
+    c = sub.add_parser("check"); c.add_argument("bench_json"); c.add_argument("--budgets", default=None)
     sub.add_parser("build")
     sub.add_parser("tune")
     p = sub.add_parser("plan")
@@ -55,6 +57,20 @@ def main(argv=None) -> int:
     if a.cmd == "capabilities":
         from .doctor import capability_report
         print(capability_report())
+    elif a.cmd == "ffi":
+        from . import ffi
+        text = ffi.render_rust()
+        if a.write:
+            out = Path(__file__).resolve().parent.parent / "rust" / "incin-b200-sys" / "src" / "lib.rs"
+            out.write_text(text)
+            print(f"wrote {out}")
+        else:
+            print(text)
+    elif a.cmd == "check":
+        from .budgets import check_bench
+        ok, report = check_bench(a.bench_json, a.budgets)
+        print(report)
+        return 0 if ok else 1
     elif a.cmd == "build":
         from . import build
         print(build())

@@ -275,6 +275,15 @@ CUDA_CAPABILITIES: tuple[CapabilityRule, ...] = (
     CapabilityRule("dropout", _BF, SupportLevel.NATIVE, "philox dropout"),
     CapabilityRule("quantize_q8_0", (DTypeId.F32,), SupportLevel.NATIVE, "q8_0 quantize/dequantize"),
     CapabilityRule("conv2d", _BF, SupportLevel.COMPOSED, "im2col + gemm_tcgen05"),
+    CapabilityRule("argmax", _BF + (DTypeId.F32,), SupportLevel.NATIVE, "reduce kernels (index output)"),
+    CapabilityRule("cumsum", _BF + (DTypeId.F32,), SupportLevel.NATIVE, "block scan"),
+    CapabilityRule("max_pool2d", _BF + (DTypeId.F32,), SupportLevel.NATIVE, "maxpool2d fwd (argmax kept) / gather bwd"),
+    CapabilityRule("avg_pool2d", _BF + (DTypeId.F32,), SupportLevel.NATIVE, "avgpool2d fwd/bwd"),
+    CapabilityRule("batch_norm", _BF + (DTypeId.F32,), SupportLevel.NATIVE, "batchnorm train fwd/bwd + eval"),
+    CapabilityRule("concat", _ALL, SupportLevel.NATIVE, "strided copy"),
+    CapabilityRule("gather", _BF + (DTypeId.F32, DTypeId.U32), SupportLevel.NATIVE, "gather_last / scatter_last"),
+    CapabilityRule("index_select", _BF + (DTypeId.F32, DTypeId.U32), SupportLevel.NATIVE, "gather_rows / scatter_add_rows"),
+    CapabilityRule("quantized_matmul", (DTypeId.Q8_0,), SupportLevel.COMPOSED, "dequantize_q8_0 (bf16) + gemm_tcgen05"),
     CapabilityRule("reshape", _ALL, SupportLevel.NATIVE, "view"),
     CapabilityRule("transpose", _ALL, SupportLevel.NATIVE, "view (GEMM reads either major)"),
 )

@@ -145,6 +145,28 @@ def fusion_pass(g: Graph) -> list[FusionGroup]:
     return groups
 
 
+def constant_fold(g: Graph, constants: set[int] = frozenset()) -> list[int]:
+    """Nodes that depend only on ``constants`` (graph inputs that are weights): candidates for evaluation at
+    compile time.  (``ConstantFolder`` in the reference is a pass-through stub; this one does the analysis and leaves
+    the evaluation to the caller, which owns the tensors.)"""
+    dynamic = set(g.inputs) - set(constants)
+    for n in g.nodes:
+        if any(i in dynamic for i in n.inputs):
+            dynamic.add(n.id)
+    return [n.id for n in g.nodes if n.op != "input" and n.id not in dynamic]
+
+
+def weight_prepack_plan(g: Graph, weight_inputs: set[int]) -> dict[int, str]:
+    """Which weight operands a compiled plan would re-lay-out once ahead of time: the second operand of every matrix
+    product fed directly by a weight.  The tcgen05 GEMM reads K-major and MN-major operands alike, so the plan is
+    "none" for every weight; the pass exists so that a back end with a layout preference has a place to say so."""
+    plan = {}
+    for n in g.nodes:
+        if n.op in ("mm", "matmul", "addmm", "linear", "bmm") and n.inputs and n.inputs[-1] in weight_inputs:
+            plan[n.inputs[-1]] = "none (either major is read in place)"
+    return plan
+
+
 _UNARY = {"relu": "relu", "gelu": "gelu", "silu": "swish", "sigmoid": "sigmoid", "tanh": "tanh", "exp": "exp", "log": "log",
           "sqrt": "sqrt", "rsqrt": "rsqrt", "neg": "neg", "abs": "abs", "mish": "mish", "elu": "elu",
           "softplus": "softplus", "sign": "sign", "reciprocal": "recip"}

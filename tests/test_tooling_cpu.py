@@ -227,3 +227,110 @@ def test_cli_subcommands_run():
     out = run("plan", "--world", "8")
     assert "chosen" in out and "dp=8" in out
     assert run("doctor", "--json").lstrip().startswith("{")
+
+
+# ------------------------------------------------------------------------------------------------ ffi / budgets / misc
+def test_rust_bindings_match_the_c_headers():
+    from pathlib import Path
+    from incin_b200 import ffi
+    structs, funcs = ffi.parse_headers()
+    assert {s.name for s in structs} >= {"incin_gemm_desc", "incin_attn_desc", "incin_dp_desc", "incin_conv_geom"}
+    names = {f.name for f in funcs}
+    assert {"incin_gemm_bf16", "incin_flash_attn_fwd", "incin_dp_reduce_adamw", "incin_peer_barrier", "incin_coll_reduce",
+            "incin_layernorm_bwd_noalloc", "incin_rdv_connect", "incin_cpu_mlp_train"} <= names
+    committed = (Path(ffi.__file__).resolve().parent.parent / "rust" / "incin-b200-sys" / "src" / "lib.rs").read_text()
+    assert committed == ffi.render_rust(), "run `python -m incin_b200 ffi --write` after changing a header"
+    gemm = next(s for s in structs if s.name == "incin_gemm_desc")
+    from incin_b200._native import GemmDesc
+    assert [f[0] for f in gemm.fields] == [n for n, _ in GemmDesc._fields_]      # ctypes mirror has the same layout
+
+
+def test_budget_check(tmp_path):
+    from incin_b200.budgets import check_bench, feature_table
+    good = tmp_path / "b.json"
+    good.write_text('noise\n{"value": 640000.0, "unit": "tokens/s", "n_gpus": 1, "higher_is_better": true, "config": {"model": "gpt2-small"}}\n')
+    assert check_bench(good)[0]
+    bad = tmp_path / "c.json"
+    bad.write_text('{"value": 300000.0, "unit": "tokens/s", "n_gpus": 1, "higher_is_better": true, "config": {"model": "gpt2-small"}}')
+    ok, rep = check_bench(bad)
+    assert not ok and "REGRESSION" in rep
+    assert check_bench(tmp_path / "b.json", None)[1].startswith("gpt2-small/n1")
+    assert "| matmul |" in feature_table()
+
+
+def test_backends_dispatch_dummy_and_conformance():
+    from incin_b200.backends import BackendUnavailable, CpuBackend, DispatchBackend, DummyBackend, run_conformance
+    res = run_conformance(CpuBackend())
+    assert res and all(r.status == "passed" for r in res), [r for r in res if r.status != "passed"]
+    d = DummyBackend()
+    assert d.run("matmul", torch.empty(4, 8), torch.empty(8, 16)).shape == (4, 16)
+    assert d.run("matmul", torch.empty(4, 8), torch.empty(8, 16)).device.type == "meta"
+    disp = DispatchBackend()
+    assert float(disp.run("sum", torch.ones(3, 3))) == 9.0
+    with pytest.raises(BackendUnavailable):
+        disp.backend_for(torch.empty(2, device="meta"))
+
+    class Claimless(CpuBackend):       # a subject that claims nothing is skipped everywhere, not failed
+        def supports(self, op, dtype):
+            from incin_b200.core.spec import SupportLevel
+            return SupportLevel.UNSUPPORTED
+    assert all(r.status == "skipped" for r in run_conformance(Claimless()))
+
+
+def test_iteration_plans_collapse_broadcast_and_bounds():
+    from incin_b200.core.iteration import IterationError, check_bounds, plan, unary_plan
+    from incin_b200.core.spec import LayoutClass, TensorMeta
+    a, b, o = torch.empty(4, 1, 8), torch.empty(3, 8), torch.empty(4, 3, 8)
+    p = plan([TensorMeta.of(a), TensorMeta.of(b)], TensorMeta.of(o))
+    assert p.shape == (4, 3, 8) and p.operands[0].strides == (8, 0, 1) and p.operands[1].strides == (0, 8, 1)
+    assert p.layout is LayoutClass.BROADCAST
+    x = torch.empty(6, 10, 7)
+    assert unary_plan(TensorMeta.of(x), TensorMeta.of(torch.empty(6, 10, 7))).shape == (420,)     # fully collapsed
+    pt = plan([TensorMeta.of(x.transpose(0, 1))], TensorMeta.of(torch.empty(10, 6, 7)))
+    assert pt.layout is LayoutClass.STRIDED and pt.operands[0].strides == (7, 70, 1)
+    check_bounds(pt, [420, 420])
+    with pytest.raises(IterationError):
+        check_bounds(pt, [400, 420])
+    with pytest.raises(IterationError):
+        plan([TensorMeta.of(torch.empty(5, 8))], TensorMeta.of(torch.empty(4, 8)))
+    s = plan([TensorMeta.of(torch.empty(1)), TensorMeta.of(x)], TensorMeta.of(torch.empty(6, 10, 7)))
+    assert s.layout is LayoutClass.SCALAR
+
+
+def test_onnx_roundtrip_and_diagnostics(tmp_path):
+    from torch import nn
+    from incin_b200.diagnostics import explain, humanize
+    from incin_b200.io import onnx as O
+    m = nn.Sequential(nn.Flatten(), nn.Linear(784, 64), nn.ReLU(), nn.Dropout(0.1), nn.LayerNorm(64), nn.Linear(64, 10, bias=False),
+                      nn.Softmax(-1)).eval()
+    p = tmp_path / "m.onnx"
+    g = O.export_module(m, (4, 1, 28, 28), p)
+    assert [n.op_type for n in g.nodes] == ["Flatten", "Gemm", "Relu", "Identity", "LayerNormalization", "Gemm", "Softmax"]
+    back = O.import_model(p)
+    x = torch.randn(4, 1, 28, 28)
+    torch.testing.assert_close(back.run(x)[0], m(x))
+    torch.testing.assert_close(back.to_module().eval()(x), m(x))
+    assert back.inputs == [("input", (4, 1, 28, 28))] and back.outputs[0][1] == (4, 10)
+    p.write_bytes(p.read_bytes()[:1000])
+    with pytest.raises(ValueError):
+        O.import_model(p)
+    with pytest.raises(RuntimeError, match="looks transposed"):
+        with humanize():
+            torch.randn(3, 4) @ torch.randn(5, 4)
+    assert "not divisible" in str(explain("shape '[3, -1, 5]' is invalid for input of size 32"))
+    assert explain("something else entirely") is None
+
+
+def test_tensor_creation_is_seeded_and_graph_passes():
+    from incin_b200 import graph as G
+    from incin_b200 import tensor as Tn
+    Tn.manual_seed(7)
+    a = Tn.randn(4, 5)
+    Tn.manual_seed(7)
+    assert torch.equal(a, Tn.randn(4, 5)) and not torch.equal(a, Tn.randn(4, 5))
+    assert abs(float(Tn.rand(4000).mean()) - 0.5) < 0.03 and Tn.to_vec1(Tn.arange(4)) == [0, 1, 2, 3]
+    x = torch.randn(2, 8, 4, 4)
+    torch.testing.assert_close(Tn.group_norm(x, 4), torch.nn.functional.group_norm(x, 4), rtol=1e-4, atol=1e-5)
+    g = G.trace(lambda x, w: x @ w + (w * 2.0).sum(), torch.randn(3, 4), torch.randn(4, 5))
+    assert [g.nodes[i].op for i in G.constant_fold(g, {1})] == ["mul", "sum"]
+    assert list(G.weight_prepack_plan(g, {1})) == [1]
