@@ -443,7 +443,7 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.dv_stride_h = d->dv_stride_h;
   p.status = (int*)d->status;
   dim3 grid(p.n_tiles, d->Hkv, d->B);
-  if (launch_pdl(kern, grid, dim3(FB_THREADS), Cfg::SMEM_BYTES, stream, tq, tk, tv, tdo, p) != cudaSuccess) return INCIN_ERR_LAUNCH;
+  if (launch_pdl<true>(kern, grid, dim3(FB_THREADS), Cfg::SMEM_BYTES, stream, tq, tk, tv, tdo, p) != cudaSuccess) return INCIN_ERR_LAUNCH;
   long long n4 = rows * D / 4;
   long long blocks = (n4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;

@@ -314,7 +314,7 @@ static int launch_fwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.Tpad = p.n_q_tiles * FA_BM;
   p.status = (int*)d->status;
   dim3 grid(p.n_q_tiles, d->Hq, d->B);
-  if (launch_pdl(kern, grid, dim3(FA_THREADS), Cfg::SMEM_BYTES, stream, tq, tk, tv, p) != cudaSuccess) return INCIN_ERR_LAUNCH;
+  if (launch_pdl<true>(kern, grid, dim3(FA_THREADS), Cfg::SMEM_BYTES, stream, tq, tk, tv, p) != cudaSuccess) return INCIN_ERR_LAUNCH;
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
 

@@ -428,7 +428,7 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmKe
     kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, q);
     return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
   }
-  return launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), Cfg::SMEM_BYTES, stream, ta, tb, q) == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
+  return launch_pdl<true>(kern, dim3(grid), dim3(GEMM_THREADS), Cfg::SMEM_BYTES, stream, ta, tb, q) == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
 
 template <int BN>
@@ -470,7 +470,7 @@ static int launch_pair_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const G
   int pairs = max_clusters < max_ctas / 2 ? max_clusters : max_ctas / 2;
   if (pairs > p.total_units) pairs = p.total_units;
   if (pairs < 1) return INCIN_ERR_ARGUMENT;
-  return launch_pdl(kern, dim3(2 * pairs), dim3(GEMM_THREADS), PairCfg::SMEM_BYTES, stream, ta, tb, p, tiles_m2) == cudaSuccess
+  return launch_pdl<true>(kern, dim3(2 * pairs), dim3(GEMM_THREADS), PairCfg::SMEM_BYTES, stream, ta, tb, p, tiles_m2) == cudaSuccess
              ? INCIN_OK
              : INCIN_ERR_LAUNCH;
 }

@@ -11,9 +11,10 @@
 //     while this grid waits for the allocation).  Plain kernels call it first thing.
 // Both instructions are no-ops in a kernel that was launched the ordinary way, and a successor launched the ordinary
 // way simply waits for full completion, so instrumented and plain kernels mix freely.
-// The attribute is OFF by default and switched on with INCIN_PDL=1: measured on one B200 inside the captured graph
-// of a GPT-2-small training step it made the step 1.8 % SLOWER (12.99 ms against 12.76 ms, two runs each; the
-// early-scheduled successors raise the power draw until the power cap engages), so ordinary launches stay the default.
+// INCIN_PDL selects who gets the attribute: 2 (default) = only the tensor-core kernels (GEMM, attention), 1 = every
+// instrumented kernel, 0 = nobody.  Measured on one B200 inside the captured graph of a GPT-2-small training step
+// (20 steps, two runs each): off 12.70 / 12.73 ms, tensor-core kernels only 12.61 / 12.62 ms, everything 12.94 ms -
+// early-scheduled grids of the small bandwidth kernels cost more than their hidden launch gaps give back.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -25,15 +26,16 @@ namespace incin {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-inline bool pdl_enabled() {
-  static const bool on = [] {
+// 0: off.  1: every instrumented kernel.  2 (default): only the tensor-core kernels (GEMM, attention).
+inline int pdl_mode() {
+  static const int mode = [] {
     const char* e = std::getenv("INCIN_PDL");
-    return e && e[0] == '1';
+    return (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2;
   }();
-  return on;
+  return mode;
 }
 
-template <typename... KArgs, typename... Args>
+template <bool HEAVY = false, typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args&&... args) {
   cudaLaunchConfig_t cfg = {};
@@ -45,7 +47,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = (pdl_mode() == 1 || (HEAVY && pdl_mode() == 2)) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 

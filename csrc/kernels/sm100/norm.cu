@@ -306,19 +306,35 @@ norm_bwd_param_partial_vec(const __nv_bfloat16* __restrict__ dy, const __nv_bflo
   }
 }
 
-__global__ void norm_bwd_param_final(const float* __restrict__ scratch, float* __restrict__ dgamma,
-                                     float* __restrict__ dbeta, int C, int chunks) {
+// Stage 2: 32 columns x 8 chunk lanes per block.  Each thread adds every 8th partial (independent, coalesced loads),
+// then the 8 lanes of a column are combined in a fixed order, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256)
+norm_bwd_param_final(const float* __restrict__ scratch, float* __restrict__ dgamma, float* __restrict__ dbeta, int C,
+                     int chunks) {
   pdl_launch_dependents();
   pdl_wait();
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+  __shared__ float sa[8][33], sb[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float a = 0.f, b = 0.f;
-  for (int k = 0; k < chunks; ++k) {
-    a += scratch[((long long)k * 2 + 0) * C + c];
-    b += scratch[((long long)k * 2 + 1) * C + c];
+  if (c < C) {
+    for (int k = ty; k < chunks; k += 8) {
+      a += scratch[((long long)k * 2 + 0) * C + c];
+      b += scratch[((long long)k * 2 + 1) * C + c];
+    }
   }
-  dgamma[c] += a;
-  if (dbeta) dbeta[c] += b;
+  sa[ty][tx] = a;
+  sb[ty][tx] = b;
+  __syncthreads();
+  if (ty == 0 && c < C) {
+#pragma unroll
+    for (int t = 1; t < 8; ++t) {
+      a += sa[t][tx];
+      b += sb[t][tx];
+    }
+    dgamma[c] += a;
+    if (dbeta) dbeta[c] += b;
+  }
 }
 
 static int param_chunks(long long rows) {
@@ -349,7 +365,7 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, con
       launch_pdl(norm_bwd_param_partial<RMS>, dim3(grid), dim3(32 * PG_TY), 0, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                                mean, rstd, scratch, rows, C, chunks);
     }
-    launch_pdl(norm_bwd_param_final, dim3((C + 255) / 256), dim3(256), 0, s, scratch, dgamma, dbeta, C, chunks);
+    launch_pdl(norm_bwd_param_final, dim3((C + 31) / 32), dim3(256), 0, s, scratch, dgamma, dbeta, C, chunks);
   }
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
