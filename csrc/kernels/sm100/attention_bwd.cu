@@ -46,6 +46,11 @@ struct FbCfg {
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   // TMEM columns: S^T / dQ partial [0,128), dP^T [128,256), dV [256,256+D), dK [256+D, 256+2D)
   static constexpr int COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 256 + D, TMEM_COLS = 512;
+  // D = 64 leaves 128 columns free: two dQ partial buffers of their own, so the dQ drain of tile i-1 and the
+  // dV/dK/dQ MMAs of tile i-1 overlap the softmax-gradient math of tile i (PIPELINED).  With D = 128 tensor memory
+  // is full and the dQ partial has to reuse the S^T columns, which serialises the iteration.
+  static constexpr bool PIPELINED = (D == 64);
+  static constexpr int COL_DQ = 256 + 2 * D;
 };
 
 struct FbParams {
@@ -82,9 +87,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* q_empty = bars + 1 + ST;   // [ST]  the three consuming MMAs of that stage finished
   uint64_t* sdp_full = bars + 1 + 2 * ST;  // S^T and dP^T in TMEM
   uint64_t* pds_full = sdp_full + 1;       // all compute threads: P^T and dS^T in shared memory
-  uint64_t* dq_full = sdp_full + 2;        // dQ partial in TMEM (and dV/dK updated)
-  uint64_t* dq_drained = sdp_full + 3;     // all compute threads: dQ partial read out, S^T columns reusable
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sdp_full + 4);
+  uint64_t* dq_full = sdp_full + 2;        // [2] dQ partial in TMEM (and dV/dK updated); the serial flow uses [0]
+  uint64_t* dq_drained = sdp_full + 4;     // [2] all compute threads: dQ partial read out
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sdp_full + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -103,8 +108,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     mbar_init(sdp_full, 1);
     mbar_init(pds_full, FB_CTHREADS);
-    mbar_init(dq_full, 1);
-    mbar_init(dq_drained, FB_CTHREADS);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&dq_full[i], 1);
+      mbar_init(&dq_drained[i], FB_CTHREADS);
+    }
     *abort_flag = 0;
     mbar_init_fence();
     tma_prefetch_desc(&tmQ);
@@ -157,50 +164,111 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t id_mnmn = make_idesc_bf16(FB_T, D, true, true);     // dQ
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kStatusTimeoutFull);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), aDS = smem_u32(sDS);
-      for (int it = 0; it < n_iters && ok; ++it) {
-        const int s = it % ST;
-        const uint32_t aQ = smem_u32(sQ + s * Cfg::TILE_BYTES), aDO = smem_u32(sDO + s * Cfg::TILE_BYTES);
-        if (!mbar_wait(&q_full[s], (it / ST) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
-        // the S^T columns double as the dQ partial of the previous iteration: wait until it was read out
-        if (!mbar_wait(dq_drained, (it & 1) ^ 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
-        tc_fence_after();
+      if constexpr (Cfg::PIPELINED) {
+        // one extra pass: pass `it` issues the dV/dK/dQ MMAs of tile it-1 and then the score MMAs of tile it
+        for (int it = 0; it <= n_iters && ok; ++it) {
+          if (it < n_iters) {
+            if (!mbar_wait(&q_full[it % ST], (it / ST) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+          }
+          if (it > 0) {
+            const int j = it - 1, sj = j % ST, bq = j & 1;
+            const uint32_t aQ = smem_u32(sQ + sj * Cfg::TILE_BYTES), aDO = smem_u32(sDO + sj * Cfg::TILE_BYTES);
+            // tile j's P^T / dS^T are in shared memory, and its S^T / dP^T columns have been read
+            if (!mbar_wait(pds_full, j & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+            if (j >= 2 && !mbar_wait(&dq_drained[bq], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
-          umma_f16_ss(tmem_base + Cfg::COL_ST, make_smem_desc(aK + off, 16, 1024), make_smem_desc(aQ + off, 16, 1024),
-                      id_kk, kk > 0 ? 1u : 0u);
-        }
+            for (int kk = 0; kk < FB_T / 16; ++kk) {
+              const uint32_t a_off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
+              const uint32_t b_off = kk * 2048;
+              umma_f16_ss(tmem_base + Cfg::COL_DV, make_smem_desc(aP + a_off, 16, 1024),
+                          make_smem_desc(aDO + b_off, FB_T * 128, 1024), id_kmn, (j > 0 || kk > 0) ? 1u : 0u);
+            }
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
-          umma_f16_ss(tmem_base + Cfg::COL_DPT, make_smem_desc(aV + off, 16, 1024),
-                      make_smem_desc(aDO + off, 16, 1024), id_kk, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(sdp_full);
-        if (!mbar_wait(pds_full, it & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
-        tc_fence_after();
+            for (int kk = 0; kk < FB_T / 16; ++kk) {
+              const uint32_t a_off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
+              const uint32_t b_off = kk * 2048;
+              umma_f16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(aDS + a_off, 16, 1024),
+                          make_smem_desc(aQ + b_off, FB_T * 128, 1024), id_kmn, (j > 0 || kk > 0) ? 1u : 0u);
+            }
 #pragma unroll
-        for (int kk = 0; kk < FB_T / 16; ++kk) {  // reduction over the 128 query rows of this tile
-          const uint32_t a_off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;  // P^T / dS^T: K-major, K = q
-          const uint32_t b_off = kk * 2048;                                  // dO / Q: MN-major, 16 q rows per step
-          umma_f16_ss(tmem_base + Cfg::COL_DV, make_smem_desc(aP + a_off, 16, 1024),
-                      make_smem_desc(aDO + b_off, FB_T * 128, 1024), id_kmn, (it > 0 || kk > 0) ? 1u : 0u);
-        }
+            for (int kk = 0; kk < FB_T / 16; ++kk) {
+              const uint32_t off = kk * 2048;
+              umma_f16_ss(tmem_base + Cfg::COL_DQ + bq * D, make_smem_desc(aDS + off, FB_T * 128, 1024),
+                          make_smem_desc(aK + off, FB_T * 128, 1024), id_mnmn, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(&q_empty[sj]);
+            umma_commit(&dq_full[bq]);
+          }
+          if (it < n_iters) {
+            const int s = it % ST;
+            const uint32_t aQ = smem_u32(sQ + s * Cfg::TILE_BYTES), aDO = smem_u32(sDO + s * Cfg::TILE_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < FB_T / 16; ++kk) {
-          const uint32_t a_off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
-          const uint32_t b_off = kk * 2048;
-          umma_f16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(aDS + a_off, 16, 1024),
-                      make_smem_desc(aQ + b_off, FB_T * 128, 1024), id_kmn, (it > 0 || kk > 0) ? 1u : 0u);
-        }
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
+              umma_f16_ss(tmem_base + Cfg::COL_ST, make_smem_desc(aK + off, 16, 1024), make_smem_desc(aQ + off, 16, 1024),
+                          id_kk, kk > 0 ? 1u : 0u);
+            }
 #pragma unroll
-        for (int kk = 0; kk < FB_T / 16; ++kk) {  // dQ = dS K: reduction over the 128 kv rows
-          const uint32_t off = kk * 2048;          // both operands MN-major: 16 kv rows per step
-          umma_f16_ss(tmem_base + Cfg::COL_ST, make_smem_desc(aDS + off, FB_T * 128, 1024),
-                      make_smem_desc(aK + off, FB_T * 128, 1024), id_mnmn, kk > 0 ? 1u : 0u);
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
+              umma_f16_ss(tmem_base + Cfg::COL_DPT, make_smem_desc(aV + off, 16, 1024),
+                          make_smem_desc(aDO + off, 16, 1024), id_kk, kk > 0 ? 1u : 0u);
+            }
+            // arrives once everything issued so far has completed, the previous tile's dV/dK/dQ MMAs included: only
+            // then may the compute threads overwrite P^T / dS^T in shared memory
+            umma_commit(sdp_full);
+          }
         }
-        umma_commit(&q_empty[s]);
-        umma_commit(dq_full);
+      } else {
+        for (int it = 0; it < n_iters && ok; ++it) {
+          const int s = it % ST;
+          const uint32_t aQ = smem_u32(sQ + s * Cfg::TILE_BYTES), aDO = smem_u32(sDO + s * Cfg::TILE_BYTES);
+          if (!mbar_wait(&q_full[s], (it / ST) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+          // the S^T columns double as the dQ partial of the previous iteration: wait until it was read out
+          if (!mbar_wait(dq_drained, (it & 1) ^ 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) { ok = false; break; }
+          tc_fence_after();
+  #pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
+            umma_f16_ss(tmem_base + Cfg::COL_ST, make_smem_desc(aK + off, 16, 1024), make_smem_desc(aQ + off, 16, 1024),
+                        id_kk, kk > 0 ? 1u : 0u);
+          }
+  #pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
+            umma_f16_ss(tmem_base + Cfg::COL_DPT, make_smem_desc(aV + off, 16, 1024),
+                        make_smem_desc(aDO + off, 16, 1024), id_kk, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(sdp_full);
+          if (!mbar_wait(pds_full, it & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+          tc_fence_after();
+  #pragma unroll
+          for (int kk = 0; kk < FB_T / 16; ++kk) {  // reduction over the 128 query rows of this tile
+            const uint32_t a_off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;  // P^T / dS^T: K-major, K = q
+            const uint32_t b_off = kk * 2048;                                  // dO / Q: MN-major, 16 q rows per step
+            umma_f16_ss(tmem_base + Cfg::COL_DV, make_smem_desc(aP + a_off, 16, 1024),
+                        make_smem_desc(aDO + b_off, FB_T * 128, 1024), id_kmn, (it > 0 || kk > 0) ? 1u : 0u);
+          }
+  #pragma unroll
+          for (int kk = 0; kk < FB_T / 16; ++kk) {
+            const uint32_t a_off = (kk >> 2) * (FB_T * 128) + (kk & 3) * 32;
+            const uint32_t b_off = kk * 2048;
+            umma_f16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(aDS + a_off, 16, 1024),
+                        make_smem_desc(aQ + b_off, FB_T * 128, 1024), id_kmn, (it > 0 || kk > 0) ? 1u : 0u);
+          }
+  #pragma unroll
+          for (int kk = 0; kk < FB_T / 16; ++kk) {  // dQ = dS K: reduction over the 128 kv rows
+            const uint32_t off = kk * 2048;          // both operands MN-major: 16 kv rows per step
+            umma_f16_ss(tmem_base + Cfg::COL_ST, make_smem_desc(aDS + off, FB_T * 128, 1024),
+                        make_smem_desc(aK + off, FB_T * 128, 1024), id_mnmn, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(&q_empty[s]);
+          umma_commit(dq_full);
+        }
       }
     }
   } else {
@@ -213,10 +281,51 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int kv_idx = kv0 + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const bool kv_live = kv_idx < p.T;
+    // dQ partial of tile j: lanes are query rows of that tile; this warp adds D/4 of the columns into the fp32
+    // accumulator.  Pipelined flow: buffer j & 1 of the dedicated dQ columns; serial flow: the S^T columns.
+    auto drain_dq = [&](int j) -> bool {
+      const int bq = Cfg::PIPELINED ? (j & 1) : 0;
+      const uint32_t parity = Cfg::PIPELINED ? ((j >> 1) & 1) : (j & 1);
+      if (!mbar_wait(&dq_full[bq], parity, abort_flag, p.status, kStatusTimeoutTmemFull)) return false;
+      tc_fence_after();
+      const int hq_j = hkv * group + j / tiles_per_head;
+      const int q = (first_q_tile + j % tiles_per_head) * FB_T + row;
+      constexpr int DC = D / 4;  // columns per warp: 16 (D = 64) or 32 (D = 128)
+      const uint32_t col = Cfg::PIPELINED ? (Cfg::COL_DQ + bq * D) : Cfg::COL_ST;
+      float* dq_row = p.dq_accum + (((long long)b * p.T + q) * p.Hq + hq_j) * D + cb * DC;
+      if constexpr (DC == 16) {
+        uint32_t r[16];
+        tmem_ld_32x16(tmem_base + col + lane_addr + cb * DC, r);
+        tmem_ld_wait();
+        if (q < p.T) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + u * 4),
+                         "f"(__uint_as_float(r[u * 4])), "f"(__uint_as_float(r[u * 4 + 1])),
+                         "f"(__uint_as_float(r[u * 4 + 2])), "f"(__uint_as_float(r[u * 4 + 3]))
+                         : "memory");
+        }
+      } else {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + col + lane_addr + cb * DC, r);
+        tmem_ld_wait();
+        if (q < p.T) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + u * 4),
+                         "f"(__uint_as_float(r[u * 4])), "f"(__uint_as_float(r[u * 4 + 1])),
+                         "f"(__uint_as_float(r[u * 4 + 2])), "f"(__uint_as_float(r[u * 4 + 3]))
+                         : "memory");
+        }
+      }
+      __syncwarp();
+      tc_fence_before();
+      mbar_arrive(&dq_drained[bq]);
+      return true;
+    };
     bool ok = true;
     for (int it = 0; it < n_iters; ++it) {
       const int s = it % ST;
-      const int hq = hkv * group + it / tiles_per_head;
       const int q0 = (first_q_tile + it % tiles_per_head) * FB_T;
       const float* s_lse = sStat + s * 2 * FB_T + cb * 32;
       const float* s_delta = s_lse + FB_T;
@@ -264,40 +373,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(pds_full);
-      // dQ partial: lanes are query rows of this tile; this warp drains D/4 of the columns
-      if (!mbar_wait(dq_full, it & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
-      tc_fence_after();
-      const int q = q0 + row;
-      constexpr int DC = D / 4;  // columns per warp: 16 (D = 64) or 32 (D = 128)
-      float* dq_row = p.dq_accum + (((long long)b * p.T + q) * p.Hq + hq) * D + cb * DC;
-      if constexpr (DC == 16) {
-        uint32_t r[16];
-        tmem_ld_32x16(tmem_base + Cfg::COL_ST + lane_addr + cb * DC, r);
-        tmem_ld_wait();
-        if (q < p.T) {
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + u * 4),
-                         "f"(__uint_as_float(r[u * 4])), "f"(__uint_as_float(r[u * 4 + 1])),
-                         "f"(__uint_as_float(r[u * 4 + 2])), "f"(__uint_as_float(r[u * 4 + 3]))
-                         : "memory");
-        }
+      if constexpr (Cfg::PIPELINED) {
+        if (it > 0 && !drain_dq(it - 1)) { ok = false; break; }   // overlaps the MMAs the issuer has just launched
       } else {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + Cfg::COL_ST + lane_addr + cb * DC, r);
-        tmem_ld_wait();
-        if (q < p.T) {
-#pragma unroll
-          for (int u = 0; u < 8; ++u)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + u * 4),
-                         "f"(__uint_as_float(r[u * 4])), "f"(__uint_as_float(r[u * 4 + 1])),
-                         "f"(__uint_as_float(r[u * 4 + 2])), "f"(__uint_as_float(r[u * 4 + 3]))
-                         : "memory");
-        }
+        if (!drain_dq(it)) { ok = false; break; }
       }
-      __syncwarp();
-      tc_fence_before();
-      mbar_arrive(dq_drained);
+    }
+    if constexpr (Cfg::PIPELINED) {
+      if (ok && n_iters > 0) ok = drain_dq(n_iters - 1);
     }
     // final: dK and dV of this KV tile (dq_full of the last iteration implies both are complete)
     if (ok && n_iters > 0) {

@@ -25,7 +25,7 @@ def _err(a, b):
 
 @pytest.mark.parametrize("B,T,Hq,Hkv,D", [(1, 128, 1, 1, 64), (2, 256, 2, 2, 64), (1, 384, 4, 2, 64), (2, 200, 2, 1, 64),
                                           (1, 128, 1, 1, 128), (1, 512, 2, 2, 128), (1, 320, 4, 1, 128),
-                                          (1, 1024, 2, 2, 64)])
+                                          (1, 1024, 2, 2, 64), (2, 640, 6, 2, 64)])
 def test_flash_fwd_bwd(B, T, Hq, Hkv, D):
     from incin_b200.ops import attention as A
     from incin_b200.ops import gemm as G
