@@ -18,6 +18,7 @@
 #include "launch.cuh"
 #include "../../include/incin_b200.h"
 #include <math_constants.h>
+#include <type_traits>
 
 namespace incin {
 
@@ -107,10 +108,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&q_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, FB_CTHREADS);
+    mbar_init(pds_full, FB_CWARPS);   // one arrival per compute warp
     for (int i = 0; i < 2; ++i) {
       mbar_init(&dq_full[i], 1);
-      mbar_init(&dq_drained[i], FB_CTHREADS);
+      mbar_init(&dq_drained[i], FB_CWARPS);
     }
     *abort_flag = 0;
     mbar_init_fence();
@@ -301,8 +302,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int u = 0; u < 4; ++u)
             asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + u * 4),
-                         "f"(__uint_as_float(r[u * 4])), "f"(__uint_as_float(r[u * 4 + 1])),
-                         "f"(__uint_as_float(r[u * 4 + 2])), "f"(__uint_as_float(r[u * 4 + 3]))
+                         "f"(__uint_as_float(r[u * 4]) * p.scale), "f"(__uint_as_float(r[u * 4 + 1]) * p.scale),
+                         "f"(__uint_as_float(r[u * 4 + 2]) * p.scale), "f"(__uint_as_float(r[u * 4 + 3]) * p.scale)
                          : "memory");
         }
       } else {
@@ -313,14 +314,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int u = 0; u < 8; ++u)
             asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + u * 4),
-                         "f"(__uint_as_float(r[u * 4])), "f"(__uint_as_float(r[u * 4 + 1])),
-                         "f"(__uint_as_float(r[u * 4 + 2])), "f"(__uint_as_float(r[u * 4 + 3]))
+                         "f"(__uint_as_float(r[u * 4]) * p.scale), "f"(__uint_as_float(r[u * 4 + 1]) * p.scale),
+                         "f"(__uint_as_float(r[u * 4 + 2]) * p.scale), "f"(__uint_as_float(r[u * 4 + 3]) * p.scale)
                          : "memory");
         }
       }
-      __syncwarp();
       tc_fence_before();
-      mbar_arrive(&dq_drained[bq]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&dq_drained[bq]);
       return true;
     };
     bool ok = true;
@@ -332,47 +333,54 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // q_full also covers the statistics; the MMA thread waited on it before sdp_full can complete
       if (!mbar_wait(sdp_full, it & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
-      const bool diag = (q0 < kv0 + FB_T);  // only the diagonal tile needs the causal test
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {  // two halves of 16 query columns keep the register footprint small
-        uint32_t rs[16], rd[16];
-        tmem_ld_32x16(tmem_base + Cfg::COL_ST + lane_addr + cb * 32 + hf * 16, rs);
-        tmem_ld_32x16(tmem_base + Cfg::COL_DPT + lane_addr + cb * 32 + hf * 16, rd);
-        tmem_ld_wait();
-        uint32_t pp[8], dd[8];
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const float4 l4 = *reinterpret_cast<const float4*>(s_lse + hf * 16 + g * 4);
-          const float4 d4 = *reinterpret_cast<const float4*>(s_delta + hf * 16 + g * 4);
-          const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
-          const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pv[4], dv[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = g * 4 + e;
-            const int qi = cb * 32 + hf * 16 + i;
-            const bool live = kv_live && (!diag || (q0 + qi >= kv_idx));
-            const float pr = live ? exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse[e])) : 0.f;
-            pv[e] = pr;
-            dv[e] = pr * (__uint_as_float(rd[i]) - dl[e]) * p.scale;
+      // Only the diagonal tile needs the causal test and only the last KV tile can hold dead rows: every other tile
+      // takes the unmasked instantiation (three instructions fewer per element in an issue-bound loop).
+      auto softmax_grad = [&](auto masked_tag) {
+        constexpr bool MASKED = decltype(masked_tag)::value;
+  #pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {  // two halves of 16 query columns keep the register footprint small
+          uint32_t rs[16], rd[16];
+          tmem_ld_32x16(tmem_base + Cfg::COL_ST + lane_addr + cb * 32 + hf * 16, rs);
+          tmem_ld_32x16(tmem_base + Cfg::COL_DPT + lane_addr + cb * 32 + hf * 16, rd);
+          tmem_ld_wait();
+          uint32_t pp[8], dd[8];
+  #pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const float4 l4 = *reinterpret_cast<const float4*>(s_lse + hf * 16 + g * 4);
+            const float4 d4 = *reinterpret_cast<const float4*>(s_delta + hf * 16 + g * 4);
+            const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
+            const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pv[4], dv[4];
+  #pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = g * 4 + e;
+              const int qi = cb * 32 + hf * 16 + i;
+              float pr = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse[e]));
+              if constexpr (MASKED) pr = (kv_live && (q0 + qi >= kv_idx)) ? pr : 0.f;
+              pv[e] = pr;
+              dv[e] = pr * (__uint_as_float(rd[i]) - dl[e]);   // the softmax scale is applied when dQ / dK leave TMEM
+            }
+            pp[g * 2] = pack_bf16x2(pv[0], pv[1]);
+            pp[g * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
+            dd[g * 2] = pack_bf16x2(dv[0], dv[1]);
+            dd[g * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
           }
-          pp[g * 2] = pack_bf16x2(pv[0], pv[1]);
-          pp[g * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
-          dd[g * 2] = pack_bf16x2(dv[0], dv[1]);
-          dd[g * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
+          uint8_t* prow = sP + (cb >> 1) * (FB_T * 128) + row * 128;
+          uint8_t* drow = sDS + (cb >> 1) * (FB_T * 128) + row * 128;
+  #pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int unit = ((cb & 1) * 4 + hf * 2 + u) ^ (row & 7);
+            *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pp[u * 4], pp[u * 4 + 1], pp[u * 4 + 2], pp[u * 4 + 3]);
+            *reinterpret_cast<uint4*>(drow + unit * 16) = make_uint4(dd[u * 4], dd[u * 4 + 1], dd[u * 4 + 2], dd[u * 4 + 3]);
+          }
         }
-        uint8_t* prow = sP + (cb >> 1) * (FB_T * 128) + row * 128;
-        uint8_t* drow = sDS + (cb >> 1) * (FB_T * 128) + row * 128;
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int unit = ((cb & 1) * 4 + hf * 2 + u) ^ (row & 7);
-          *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pp[u * 4], pp[u * 4 + 1], pp[u * 4 + 2], pp[u * 4 + 3]);
-          *reinterpret_cast<uint4*>(drow + unit * 16) = make_uint4(dd[u * 4], dd[u * 4 + 1], dd[u * 4 + 2], dd[u * 4 + 3]);
-        }
-      }
+      };
+      if (q0 < kv0 + FB_T || kv0 + FB_T > p.T) softmax_grad(std::true_type{});
+      else softmax_grad(std::false_type{});
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(pds_full);
+      __syncwarp();                          // every lane's writes and fences precede the single arrival of its warp
+      if (lane == 0) mbar_arrive(pds_full);
       if constexpr (Cfg::PIPELINED) {
         if (it > 0 && !drain_dq(it - 1)) { ok = false; break; }   // overlaps the MMAs the issuer has just launched
       } else {
@@ -400,10 +408,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
             uint4 a, bb;
-            a.x = pack_bf16x2(__uint_as_float(rk[u * 8 + 0]), __uint_as_float(rk[u * 8 + 1]));
-            a.y = pack_bf16x2(__uint_as_float(rk[u * 8 + 2]), __uint_as_float(rk[u * 8 + 3]));
-            a.z = pack_bf16x2(__uint_as_float(rk[u * 8 + 4]), __uint_as_float(rk[u * 8 + 5]));
-            a.w = pack_bf16x2(__uint_as_float(rk[u * 8 + 6]), __uint_as_float(rk[u * 8 + 7]));
+            a.x = pack_bf16x2(__uint_as_float(rk[u * 8 + 0]) * p.scale, __uint_as_float(rk[u * 8 + 1]) * p.scale);
+            a.y = pack_bf16x2(__uint_as_float(rk[u * 8 + 2]) * p.scale, __uint_as_float(rk[u * 8 + 3]) * p.scale);
+            a.z = pack_bf16x2(__uint_as_float(rk[u * 8 + 4]) * p.scale, __uint_as_float(rk[u * 8 + 5]) * p.scale);
+            a.w = pack_bf16x2(__uint_as_float(rk[u * 8 + 6]) * p.scale, __uint_as_float(rk[u * 8 + 7]) * p.scale);
             bb.x = pack_bf16x2(__uint_as_float(rv[u * 8 + 0]), __uint_as_float(rv[u * 8 + 1]));
             bb.y = pack_bf16x2(__uint_as_float(rv[u * 8 + 2]), __uint_as_float(rv[u * 8 + 3]));
             bb.z = pack_bf16x2(__uint_as_float(rv[u * 8 + 4]), __uint_as_float(rv[u * 8 + 5]));

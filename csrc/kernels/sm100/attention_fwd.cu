@@ -91,7 +91,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(v_full, 1);
     mbar_init(v_empty, 1);
     mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 4);   // one arrival per softmax warp
     *abort_flag = 0;
     mbar_init_fence();
     tma_prefetch_desc(&tmQ);
@@ -242,7 +242,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_full);
+      __syncwarp();                        // every lane's writes and fences precede the single arrival of its warp
+      if (lane == 0) mbar_arrive(p_full);
     }
     if (ok && mbar_wait(s_full, n_tiles & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) {
       tc_fence_after();
