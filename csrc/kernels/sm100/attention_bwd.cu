@@ -18,6 +18,7 @@
 #include "launch.cuh"
 #include "../../include/incin_b200.h"
 #include <math_constants.h>
+#include <cstdlib>
 #include <type_traits>
 
 namespace incin {
@@ -485,6 +486,10 @@ __global__ void attn_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16
   }
 }
 
+}  // namespace incin
+#include "attention_bwd64.cuh"
+namespace incin {
+
 template <int D>
 static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   using Cfg = FbCfg<D>;
@@ -497,12 +502,20 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   if (rc) return rc;
   rc = make_operand_map(&tdo, d->d_o, D, d->T, d->do_stride_t, d->Hq, d->do_stride_h, d->B, d->do_stride_b, 64, FB_T);
   if (rc) return rc;
-  auto kern = flash_bwd_kernel<D>;
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+  // head_dim 64 runs the half-split kernel (tensor core and softmax-gradient threads overlap); INCIN_ATTN_BWD_SPLIT=0
+  // selects the one-tile-at-a-time kernel instead
+  static const bool split64 = [] {
+    const char* e = std::getenv("INCIN_ATTN_BWD_SPLIT");
+    return !(e && e[0] == '0');
+  }();
+  const bool use_split = (D == 64) && split64;
+  auto kern = use_split ? flash_bwd64_kernel : flash_bwd_kernel<D>;
+  const int smem_bytes = use_split ? Fb64::SMEM_BYTES : Cfg::SMEM_BYTES;
+  static bool attr[2] = {false, false};
+  if (!attr[use_split]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
       return INCIN_ERR_LAUNCH;
-    attr = true;
+    attr[use_split] = true;
   }
   const long long rows = (long long)d->B * d->T * d->Hq;
   const int Tpad = (d->T + FB_T - 1) / FB_T * FB_T;
@@ -534,7 +547,7 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.dv_stride_h = d->dv_stride_h;
   p.status = (int*)d->status;
   dim3 grid(p.n_tiles, d->Hkv, d->B);
-  if (launch_pdl<true>(kern, grid, dim3(FB_THREADS), Cfg::SMEM_BYTES, stream, tq, tk, tv, tdo, p) != cudaSuccess) return INCIN_ERR_LAUNCH;
+  if (launch_pdl<true>(kern, grid, dim3(FB_THREADS), smem_bytes, stream, tq, tk, tv, tdo, p) != cudaSuccess) return INCIN_ERR_LAUNCH;
   long long n4 = rows * D / 4;
   long long blocks = (n4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;

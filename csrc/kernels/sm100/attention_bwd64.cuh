@@ -1,0 +1,327 @@
+// Attention backward for head_dim 64 with the query tile split in two halves, so that the tensor core and the
+// softmax-gradient threads work at the same time.
+//
+// One CTA owns a 128-row KV tile and walks the query tiles at or below the diagonal, as in flash_bwd_kernel.  Each
+// 128-query tile is handled as halves a and b (64 queries each):
+//
+//   tensor core : S_a dP_a (i) | dV dK dQ (i-1) | S_b dP_b (i) | S_a dP_a (i+1) | ...
+//   compute     :      ...  half b (i-1) | half a (i)      | half b (i)   | half a (i+1) ...
+//
+// The score MMAs of half a of tile i only need the S_a / dP_a columns of tensor memory, which the compute threads
+// have finished reading once half a of tile i-1 is done; so while they work on half b, the next half a is already
+// being produced, and while they work on half a of tile i the tensor core runs the three gradient products of
+// tile i-1.  The shared-memory copy of P^T / dS^T that those products read is therefore still in use when half a of
+// the next tile is written: half a is double buffered, half b is not (it is rewritten only after the products that
+// read it have been committed).  Buffers sit in shared memory as [a0][b][a1], which lets the dQ product, whose A
+// operand is dS in MN-major form with a fixed positive stride between its two 64-query chunks, read (a0, b) for even
+// tiles and (b, a1) for odd tiles; for odd tiles the rows of the dQ partial are then the query rows rotated by 64,
+// which the drain undoes.
+//
+// Tensor memory (512 columns): S^T a|b [0,128), dP^T a|b [128,256), dV [256,320), dK [320,384), dQ partial x2
+// [384,512).  All waits are bounded; a timed-out wait unwinds through the common exit.
+#pragma once
+
+namespace incin {
+
+struct Fb64 {
+  static constexpr int D = 64;
+  static constexpr int H = 64;                          // queries per half
+  static constexpr int ST = 2;                          // Q / dO stages
+  static constexpr int TILE_BYTES = FB_T * D * 2;       // 16 KB: K, V, Q, dO tiles
+  static constexpr int CHUNK_BYTES = FB_T * H * 2;      // 16 KB: one half of P^T or dS^T ([128 kv][64 q])
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = TILE_BYTES;
+  static constexpr int OFF_Q = 2 * TILE_BYTES;
+  static constexpr int OFF_DO = OFF_Q + ST * TILE_BYTES;
+  static constexpr int OFF_P = OFF_DO + ST * TILE_BYTES;      // [a0][b][a1]
+  static constexpr int OFF_DS = OFF_P + 3 * CHUNK_BYTES;      // [a0][b][a1]
+  static constexpr int OFF_STAT = OFF_DS + 3 * CHUNK_BYTES;   // lse[128], delta[128] per stage
+  static constexpr int OFF_BAR = OFF_STAT + ST * 2 * FB_T * 4;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static constexpr int COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384, TMEM_COLS = 512;
+  // byte offset of half h of tile `it` inside a [a0][b][a1] triple
+  __device__ static constexpr int chunk_off(int h, int it) { return h ? CHUNK_BYTES : ((it & 1) ? 2 * CHUNK_BYTES : 0); }
+};
+
+__global__ void __launch_bounds__(FB_THREADS, 1)
+flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const FbParams p) {
+  using Cfg = Fb64;
+  constexpr int D = Cfg::D, ST = Cfg::ST, H = Cfg::H;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + Cfg::OFF_K;
+  uint8_t* sV = smem + Cfg::OFF_V;
+  uint8_t* sQ = smem + Cfg::OFF_Q;
+  uint8_t* sDO = smem + Cfg::OFF_DO;
+  uint8_t* sP = smem + Cfg::OFF_P;
+  uint8_t* sDS = smem + Cfg::OFF_DS;
+  float* sStat = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* kv_full = bars;          // 1
+  uint64_t* q_full = bars + 1;       // [2]  Q_i, dO_i and their statistics landed
+  uint64_t* q_empty = bars + 3;      // [2]  the MMAs that read that stage finished
+  uint64_t* sdp = bars + 5;          // [2]  half a / half b of S^T and dP^T are in tensor memory
+  uint64_t* pds = bars + 7;          // [2]  half a / half b of P^T and dS^T are in shared memory (one arrival per warp)
+  uint64_t* dq_full = bars + 9;      // [2]  dQ partial buffer written (and dV / dK updated)
+  uint64_t* dq_drained = bars + 11;  // [2]  dQ partial buffer read out (one arrival per warp)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_tile = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int group = p.Hq / p.Hkv;
+  const int kv0 = kv_tile * FB_T;
+  const int first_q_tile = kv_tile;
+  const int tiles_per_head = p.n_tiles - first_q_tile;
+  const int n_iters = tiles_per_head * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+      mbar_init(&sdp[s], 1);
+      mbar_init(&pds[s], FB_CWARPS);
+      mbar_init(&dq_full[s], 1);
+      mbar_init(&dq_drained[s], FB_CWARPS);
+    }
+    *abort_flag = 0;
+    mbar_init_fence();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDO);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();   // tensor memory is held
+  pdl_wait();
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
+      tma_load_4d(sK, &tmK, kv_full, 0, kv0, hkv, b);
+      tma_load_4d(sV, &tmV, kv_full, 0, kv0, hkv, b);
+      for (int it = 0; it < n_iters; ++it) {
+        const int s = it % ST;
+        const int hq = hkv * group + it / tiles_per_head;
+        const int q0 = (first_q_tile + it % tiles_per_head) * FB_T;
+        if (!mbar_wait(&q_empty[s], ((it / ST) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
+        mbar_expect_tx(&q_full[s], 2 * Cfg::TILE_BYTES + 2 * FB_T * 4);
+        tma_load_4d(sQ + s * Cfg::TILE_BYTES, &tmQ, &q_full[s], 0, q0, hq, b);
+        tma_load_4d(sDO + s * Cfg::TILE_BYTES, &tmDO, &q_full[s], 0, q0, hq, b);
+        const long long stat = ((long long)b * p.Hq + hq) * p.Tpad + q0;
+        bulk_load_1d(sStat + s * 2 * FB_T, p.lse + stat, FB_T * 4, &q_full[s]);
+        bulk_load_1d(sStat + s * 2 * FB_T + FB_T, p.delta + stat, FB_T * 4, &q_full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t id_half = make_idesc_bf16(FB_T, H, false, false);   // S^T / dP^T of one half: [128 kv] x [64 q]
+      constexpr uint32_t id_kmn = make_idesc_bf16(FB_T, D, false, true);     // dV, dK
+      constexpr uint32_t id_mnmn = make_idesc_bf16(FB_T, D, true, true);     // dQ
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kStatusTimeoutFull);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), aDS = smem_u32(sDS);
+      // score products of half h of the tile in stage s: rows h*64.. of Q / dO are 64 x 128 bytes further on
+      auto scores = [&](int h, int s) {
+        const uint32_t aQ = smem_u32(sQ + s * Cfg::TILE_BYTES) + h * (H * 128);
+        const uint32_t aDO = smem_u32(sDO + s * Cfg::TILE_BYTES) + h * (H * 128);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16_ss(tmem_base + Cfg::COL_ST + h * H, make_smem_desc(aK + kk * 32, 16, 1024),
+                      make_smem_desc(aQ + kk * 32, 16, 1024), id_half, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16_ss(tmem_base + Cfg::COL_DPT + h * H, make_smem_desc(aV + kk * 32, 16, 1024),
+                      make_smem_desc(aDO + kk * 32, 16, 1024), id_half, kk > 0 ? 1u : 0u);
+        umma_commit(&sdp[h]);
+      };
+      for (int it = 0; it <= n_iters && ok; ++it) {
+        if (it < n_iters) {
+          if (!mbar_wait(&q_full[it % ST], (it / ST) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+          // half a of the previous tile has been read out of tensor memory
+          if (it > 0 && !mbar_wait(&pds[0], (it - 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+          tc_fence_after();
+          scores(0, it % ST);
+        }
+        if (it > 0) {
+          const int j = it - 1, sj = j % ST, bq = j & 1;
+          const uint32_t aQ = smem_u32(sQ + sj * Cfg::TILE_BYTES), aDO = smem_u32(sDO + sj * Cfg::TILE_BYTES);
+          if (!mbar_wait(&pds[1], j & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+          if (j >= 2 && !mbar_wait(&dq_drained[bq], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t off_a = Cfg::chunk_off(0, j), off_b = Cfg::chunk_off(1, j);
+#pragma unroll
+          for (int kk = 0; kk < FB_T / 16; ++kk) {  // dV += P^T dO: reduction over the 128 queries, 16 per step
+            const uint32_t a_off = (kk < 4 ? off_a : off_b) + (kk & 3) * 32;
+            umma_f16_ss(tmem_base + Cfg::COL_DV, make_smem_desc(aP + a_off, 16, 1024),
+                        make_smem_desc(aDO + kk * 2048, FB_T * 128, 1024), id_kmn, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < FB_T / 16; ++kk) {  // dK += dS^T Q
+            const uint32_t a_off = (kk < 4 ? off_a : off_b) + (kk & 3) * 32;
+            umma_f16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(aDS + a_off, 16, 1024),
+                        make_smem_desc(aQ + kk * 2048, FB_T * 128, 1024), id_kmn, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          // dQ partial = dS K: A = dS in MN-major form, two 64-query chunks CHUNK_BYTES apart starting at the lower
+          // of the two addresses: (a0, b) for even tiles, (b, a1) for odd tiles (rows then come out rotated by 64)
+          const uint32_t ds_first = aDS + (bq ? Cfg::CHUNK_BYTES : 0);
+#pragma unroll
+          for (int kk = 0; kk < FB_T / 16; ++kk)
+            umma_f16_ss(tmem_base + Cfg::COL_DQ + bq * D, make_smem_desc(ds_first + kk * 2048, Cfg::CHUNK_BYTES, 1024),
+                        make_smem_desc(aK + kk * 2048, FB_T * 128, 1024), id_mnmn, kk > 0 ? 1u : 0u);
+          umma_commit(&q_empty[sj]);
+          umma_commit(&dq_full[bq]);
+        }
+        if (it < n_iters) scores(1, it % ST);   // half b: its columns were read out before pds[1] of the previous tile
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax-gradient threads
+    // warp -> (TMEM lane quarter = 32 KV rows, column block cb = 16 query columns of each half)
+    const int cw = warp - 2;
+    const int quarter = warp & 3;
+    const int cb = cw >> 2;
+    const int row = quarter * 32 + lane;
+    const int kv_idx = kv0 + row;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const bool kv_live = kv_idx < p.T;
+
+    auto drain_dq = [&](int j) -> bool {
+      const int bq = j & 1;
+      if (!mbar_wait(&dq_full[bq], (j >> 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) return false;
+      tc_fence_after();
+      const int hq_j = hkv * group + j / tiles_per_head;
+      const int q_local = bq ? ((row + H) & (FB_T - 1)) : row;   // odd tiles: rows are the queries rotated by 64
+      const int q = (first_q_tile + j % tiles_per_head) * FB_T + q_local;
+      constexpr int DC = D / 4;
+      float* dq_row = p.dq_accum + (((long long)b * p.T + q) * p.Hq + hq_j) * D + cb * DC;
+      uint32_t r[16];
+      tmem_ld_32x16(tmem_base + Cfg::COL_DQ + bq * D + lane_addr + cb * DC, r);
+      tmem_ld_wait();
+      if (q < p.T) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + u * 4),
+                       "f"(__uint_as_float(r[u * 4]) * p.scale), "f"(__uint_as_float(r[u * 4 + 1]) * p.scale),
+                       "f"(__uint_as_float(r[u * 4 + 2]) * p.scale), "f"(__uint_as_float(r[u * 4 + 3]) * p.scale)
+                       : "memory");
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&dq_drained[bq]);
+      return true;
+    };
+
+    bool ok = true;
+    for (int it = 0; it < n_iters && ok; ++it) {
+      const int s = it % ST;
+      const int q0 = (first_q_tile + it % tiles_per_head) * FB_T;
+      const bool masked = (q0 < kv0 + FB_T) || (kv0 + FB_T > p.T);   // diagonal tile, or a KV tile with dead rows
+      auto half = [&](int h, auto masked_tag) -> bool {
+        constexpr bool MASKED = decltype(masked_tag)::value;
+        if (!mbar_wait(&sdp[h], it & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) return false;
+        tc_fence_after();
+        const int c0 = h * H + cb * 16;                      // first of this thread's 16 query columns in the tile
+        const float* s_lse = sStat + s * 2 * FB_T + c0;      // q_full (waited by the issuer) covers the statistics
+        const float* s_delta = s_lse + FB_T;
+        uint32_t rs[16], rd[16];
+        tmem_ld_32x16(tmem_base + Cfg::COL_ST + lane_addr + c0, rs);
+        tmem_ld_32x16(tmem_base + Cfg::COL_DPT + lane_addr + c0, rd);
+        tmem_ld_wait();
+        uint32_t pp[8], dd[8];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const float4 l4 = *reinterpret_cast<const float4*>(s_lse + g * 4);
+          const float4 d4 = *reinterpret_cast<const float4*>(s_delta + g * 4);
+          const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], dv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = g * 4 + e;
+            float pr = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse[e]));
+            if constexpr (MASKED) pr = (kv_live && (q0 + c0 + i >= kv_idx)) ? pr : 0.f;
+            pv[e] = pr;
+            dv[e] = pr * (__uint_as_float(rd[i]) - dl[e]);   // the softmax scale is applied when dQ / dK leave TMEM
+          }
+          pp[g * 2] = pack_bf16x2(pv[0], pv[1]);
+          pp[g * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
+          dd[g * 2] = pack_bf16x2(dv[0], dv[1]);
+          dd[g * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
+        }
+        // [128 kv rows][64 q] bf16, 128 bytes per row, 16-byte units swizzled with the row (SWIZZLE_128B)
+        const int off = Cfg::chunk_off(h, it) + row * 128;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int unit = (cb * 2 + u) ^ (row & 7);
+          *reinterpret_cast<uint4*>(sP + off + unit * 16) = make_uint4(pp[u * 4], pp[u * 4 + 1], pp[u * 4 + 2], pp[u * 4 + 3]);
+          *reinterpret_cast<uint4*>(sDS + off + unit * 16) = make_uint4(dd[u * 4], dd[u * 4 + 1], dd[u * 4 + 2], dd[u * 4 + 3]);
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&pds[h]);
+        return true;
+      };
+      if (masked) ok = half(0, std::true_type{}) && half(1, std::true_type{});
+      else ok = half(0, std::false_type{}) && half(1, std::false_type{});
+      if (ok && it > 0) ok = drain_dq(it - 1);   // overlaps the gradient products the issuer has just launched
+    }
+    if (ok && n_iters > 0) ok = drain_dq(n_iters - 1);
+    // final: dK and dV of this KV tile (dq_full of the last tile implies both are complete)
+    if (ok && n_iters > 0) {
+      tc_fence_after();
+      constexpr int DC = D / 4;
+      __nv_bfloat16* dk_row = p.dk + (long long)b * p.dk_stride_b + (long long)kv_idx * p.dk_stride_t +
+                              (long long)hkv * p.dk_stride_h + cb * DC;
+      __nv_bfloat16* dv_row = p.dv + (long long)b * p.dv_stride_b + (long long)kv_idx * p.dv_stride_t +
+                              (long long)hkv * p.dv_stride_h + cb * DC;
+      uint32_t rk[16], rv[16];
+      tmem_ld_32x16(tmem_base + Cfg::COL_DK + lane_addr + cb * DC, rk);
+      tmem_ld_32x16(tmem_base + Cfg::COL_DV + lane_addr + cb * DC, rv);
+      tmem_ld_wait();
+      if (kv_live) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          uint4 a, bb;
+          a.x = pack_bf16x2(__uint_as_float(rk[u * 8 + 0]) * p.scale, __uint_as_float(rk[u * 8 + 1]) * p.scale);
+          a.y = pack_bf16x2(__uint_as_float(rk[u * 8 + 2]) * p.scale, __uint_as_float(rk[u * 8 + 3]) * p.scale);
+          a.z = pack_bf16x2(__uint_as_float(rk[u * 8 + 4]) * p.scale, __uint_as_float(rk[u * 8 + 5]) * p.scale);
+          a.w = pack_bf16x2(__uint_as_float(rk[u * 8 + 6]) * p.scale, __uint_as_float(rk[u * 8 + 7]) * p.scale);
+          bb.x = pack_bf16x2(__uint_as_float(rv[u * 8 + 0]), __uint_as_float(rv[u * 8 + 1]));
+          bb.y = pack_bf16x2(__uint_as_float(rv[u * 8 + 2]), __uint_as_float(rv[u * 8 + 3]));
+          bb.z = pack_bf16x2(__uint_as_float(rv[u * 8 + 4]), __uint_as_float(rv[u * 8 + 5]));
+          bb.w = pack_bf16x2(__uint_as_float(rv[u * 8 + 6]), __uint_as_float(rv[u * 8 + 7]));
+          *reinterpret_cast<uint4*>(dk_row + u * 8) = a;
+          *reinterpret_cast<uint4*>(dv_row + u * 8) = bb;
+        }
+      }
+      __syncwarp();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace incin
