@@ -57,6 +57,7 @@ struct FbCfg {
 
 struct FbParams {
   int T, Hq, Hkv, n_tiles;
+  int batch;           // B (the persistent kernel enumerates its work items itself)
   float scale, scale_log2;
   int Tpad;            // T rounded up to the tile edge: row stride of lse / delta
   const float* lse;    // [B, Hq, Tpad] log2 domain, +inf beyond T
@@ -531,6 +532,7 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.Hq = d->Hq;
   p.Hkv = d->Hkv;
   p.n_tiles = (d->T + FB_T - 1) / FB_T;
+  p.batch = d->B;
   p.Tpad = Tpad;
   p.scale = d->scale;
   p.scale_log2 = d->scale * 1.4426950408889634f;
@@ -547,6 +549,11 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.dv_stride_h = d->dv_stride_h;
   p.status = (int*)d->status;
   dim3 grid(p.n_tiles, d->Hkv, d->B);
+  if (use_split) {   // persistent: one CTA per SM (or per item when there are fewer items)
+    const long long items = (long long)p.n_tiles * d->Hkv * d->B;
+    static const int sms = [] { int dev = 0, n = 148; cudaGetDevice(&dev); cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev); return n; }();
+    grid = dim3((unsigned)(items < sms ? items : sms), 1, 1);
+  }
   if (launch_pdl<true>(kern, grid, dim3(FB_THREADS), smem_bytes, stream, tq, tk, tv, tdo, p) != cudaSuccess) return INCIN_ERR_LAUNCH;
   long long n4 = rows * D / 4;
   long long blocks = (n4 + 255) / 256;

@@ -17,6 +17,10 @@
 // tiles and (b, a1) for odd tiles; for odd tiles the rows of the dQ partial are then the query rows rotated by 64,
 // which the drain undoes.
 //
+// The kernel is persistent: one CTA per SM walks a list of (KV tile, KV head, batch) items, longest first and in
+// snake order over the CTAs, so barrier set-up and the tensor-memory allocation are paid once per SM instead of once
+// per item (measured at about 10 us per item before), and the causal imbalance between KV tiles evens out.
+//
 // Tensor memory (512 columns): S^T a|b [0,128), dP^T a|b [128,256), dV [256,320), dK [320,384), dQ partial x2
 // [384,512).  All waits are bounded; a timed-out wait unwinds through the common exit.
 #pragma once
@@ -65,16 +69,27 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* pds = bars + 7;          // [2]  half a / half b of P^T and dS^T are in shared memory (one arrival per warp)
   uint64_t* dq_full = bars + 9;      // [2]  dQ partial buffer written (and dV / dK updated)
   uint64_t* dq_drained = bars + 11;  // [2]  dQ partial buffer read out (one arrival per warp)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* kv_empty = bars + 13;    // every product of the current item has been committed: K / V may be replaced
+  uint64_t* dkv_drained = bars + 14; // dK / dV of the current item have been read out (one arrival per warp)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kv_tile = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int group = p.Hq / p.Hkv;
-  const int kv0 = kv_tile * FB_T;
-  const int first_q_tile = kv_tile;
-  const int tiles_per_head = p.n_tiles - first_q_tile;
-  const int n_iters = tiles_per_head * group;
+  const int heads_batches = p.Hkv * p.batch;
+  const int n_items = p.n_tiles * heads_batches;
+  // item list: KV tile 0 (most query tiles) first; round r of CTA c takes item r*G + c (even r) or (r+1)*G - 1 - c
+  // (odd r), which pairs long and short items on every CTA.  Returns false when this CTA has no item in round r.
+  auto item_of = [&](int r, int& kv_tile, int& hkv, int& b) -> bool {
+    const int G = (int)gridDim.x, c = (int)blockIdx.x;
+    const int idx = (r & 1) ? (r + 1) * G - 1 - c : r * G + c;
+    if (idx >= n_items) return false;
+    kv_tile = idx / heads_batches;
+    const int hb = idx % heads_batches;
+    hkv = hb % p.Hkv;
+    b = hb / p.Hkv;
+    return true;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -86,6 +101,8 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(&dq_full[s], 1);
       mbar_init(&dq_drained[s], FB_CWARPS);
     }
+    mbar_init(kv_empty, 1);
+    mbar_init(dkv_drained, FB_CWARPS);
     *abort_flag = 0;
     mbar_init_fence();
     tma_prefetch_desc(&tmQ);
@@ -107,20 +124,32 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
-      tma_load_4d(sK, &tmK, kv_full, 0, kv0, hkv, b);
-      tma_load_4d(sV, &tmV, kv_full, 0, kv0, hkv, b);
-      for (int it = 0; it < n_iters; ++it) {
-        const int s = it % ST;
-        const int hq = hkv * group + it / tiles_per_head;
-        const int q0 = (first_q_tile + it % tiles_per_head) * FB_T;
-        if (!mbar_wait(&q_empty[s], ((it / ST) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
-        mbar_expect_tx(&q_full[s], 2 * Cfg::TILE_BYTES + 2 * FB_T * 4);
-        tma_load_4d(sQ + s * Cfg::TILE_BYTES, &tmQ, &q_full[s], 0, q0, hq, b);
-        tma_load_4d(sDO + s * Cfg::TILE_BYTES, &tmDO, &q_full[s], 0, q0, hq, b);
-        const long long stat = ((long long)b * p.Hq + hq) * p.Tpad + q0;
-        bulk_load_1d(sStat + s * 2 * FB_T, p.lse + stat, FB_T * 4, &q_full[s]);
-        bulk_load_1d(sStat + s * 2 * FB_T + FB_T, p.delta + stat, FB_T * 4, &q_full[s]);
+      int base = 0;   // query tiles handed to the pipeline so far (all roles count the same way)
+      bool ok = true;
+      for (int r = 0; ok; ++r) {
+        int kv_tile, hkv, b;
+        if (!item_of(r, kv_tile, hkv, b)) break;
+        const int kv0 = kv_tile * FB_T;
+        const int tiles_per_head = p.n_tiles - kv_tile;
+        const int n_iters = tiles_per_head * group;
+        // K / V of the previous item are still operands until its last product has been committed
+        if (r > 0 && !mbar_wait(kv_empty, (r - 1) & 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
+        mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
+        tma_load_4d(sK, &tmK, kv_full, 0, kv0, hkv, b);
+        tma_load_4d(sV, &tmV, kv_full, 0, kv0, hkv, b);
+        for (int it = 0; it < n_iters; ++it) {
+          const int g = base + it, s = g % ST;
+          const int hq = hkv * group + it / tiles_per_head;
+          const int q0 = (kv_tile + it % tiles_per_head) * FB_T;
+          if (!mbar_wait(&q_empty[s], ((g / ST) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) { ok = false; break; }
+          mbar_expect_tx(&q_full[s], 2 * Cfg::TILE_BYTES + 2 * FB_T * 4);
+          tma_load_4d(sQ + s * Cfg::TILE_BYTES, &tmQ, &q_full[s], 0, q0, hq, b);
+          tma_load_4d(sDO + s * Cfg::TILE_BYTES, &tmDO, &q_full[s], 0, q0, hq, b);
+          const long long stat = ((long long)b * p.Hq + hq) * p.Tpad + q0;
+          bulk_load_1d(sStat + s * 2 * FB_T, p.lse + stat, FB_T * 4, &q_full[s]);
+          bulk_load_1d(sStat + s * 2 * FB_T + FB_T, p.delta + stat, FB_T * 4, &q_full[s]);
+        }
+        base += n_iters;
       }
     }
   } else if (warp == 1) {
@@ -129,7 +158,6 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       constexpr uint32_t id_half = make_idesc_bf16(FB_T, H, false, false);   // S^T / dP^T of one half: [128 kv] x [64 q]
       constexpr uint32_t id_kmn = make_idesc_bf16(FB_T, D, false, true);     // dV, dK
       constexpr uint32_t id_mnmn = make_idesc_bf16(FB_T, D, true, true);     // dQ
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kStatusTimeoutFull);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), aDS = smem_u32(sDS);
       // score products of half h of the tile in stage s: rows h*64.. of Q / dO are 64 x 128 bytes further on
       auto scores = [&](int h, int s) {
@@ -145,47 +173,64 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                       make_smem_desc(aDO + kk * 32, 16, 1024), id_half, kk > 0 ? 1u : 0u);
         umma_commit(&sdp[h]);
       };
-      for (int it = 0; it <= n_iters && ok; ++it) {
-        if (it < n_iters) {
-          if (!mbar_wait(&q_full[it % ST], (it / ST) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
-          // half a of the previous tile has been read out of tensor memory
-          if (it > 0 && !mbar_wait(&pds[0], (it - 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
-          tc_fence_after();
-          scores(0, it % ST);
+      int base = 0;
+      bool ok = true;
+      for (int r = 0; ok; ++r) {
+        int kv_tile, hkv, b;
+        if (!item_of(r, kv_tile, hkv, b)) break;
+        const int n_iters = (p.n_tiles - kv_tile) * group;
+        if (!mbar_wait(kv_full, r & 1, abort_flag, p.status, kStatusTimeoutFull)) break;
+        for (int it = 0; it <= n_iters && ok; ++it) {
+          const int g = base + it;
+          if (it < n_iters) {
+            if (!mbar_wait(&q_full[g % ST], (g / ST) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+            // half a of the previous tile has been read out of tensor memory (across items the previous item's last
+            // tile was waited for through pds[1])
+            if (it > 0 && !mbar_wait(&pds[0], (g - 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+            tc_fence_after();
+            scores(0, g % ST);
+          }
+          if (it > 0) {
+            const int j = it - 1, gj = g - 1, sj = gj % ST, bq = gj & 1;
+            const uint32_t aQ = smem_u32(sQ + sj * Cfg::TILE_BYTES), aDO = smem_u32(sDO + sj * Cfg::TILE_BYTES);
+            if (!mbar_wait(&pds[1], gj & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+            if (gj >= 2 && !mbar_wait(&dq_drained[bq], ((gj >> 1) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) {
+              ok = false;
+              break;
+            }
+            // the first products of an item overwrite dV / dK: the previous item's must have been read out
+            if (j == 0 && r > 0 && !mbar_wait(dkv_drained, (r - 1) & 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t off_a = Cfg::chunk_off(0, gj), off_b = Cfg::chunk_off(1, gj);
+#pragma unroll
+            for (int kk = 0; kk < FB_T / 16; ++kk) {  // dV += P^T dO: reduction over the 128 queries, 16 per step
+              const uint32_t a_off = (kk < 4 ? off_a : off_b) + (kk & 3) * 32;
+              umma_f16_ss(tmem_base + Cfg::COL_DV, make_smem_desc(aP + a_off, 16, 1024),
+                          make_smem_desc(aDO + kk * 2048, FB_T * 128, 1024), id_kmn, (j > 0 || kk > 0) ? 1u : 0u);
+            }
+#pragma unroll
+            for (int kk = 0; kk < FB_T / 16; ++kk) {  // dK += dS^T Q
+              const uint32_t a_off = (kk < 4 ? off_a : off_b) + (kk & 3) * 32;
+              umma_f16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(aDS + a_off, 16, 1024),
+                          make_smem_desc(aQ + kk * 2048, FB_T * 128, 1024), id_kmn, (j > 0 || kk > 0) ? 1u : 0u);
+            }
+            // dQ partial = dS K: A = dS in MN-major form, two 64-query chunks CHUNK_BYTES apart starting at the
+            // lower of the two addresses: (a0, b) for even tiles, (b, a1) for odd tiles (rows come out rotated by 64)
+            const uint32_t ds_first = aDS + (bq ? Cfg::CHUNK_BYTES : 0);
+#pragma unroll
+            for (int kk = 0; kk < FB_T / 16; ++kk)
+              umma_f16_ss(tmem_base + Cfg::COL_DQ + bq * D, make_smem_desc(ds_first + kk * 2048, Cfg::CHUNK_BYTES, 1024),
+                          make_smem_desc(aK + kk * 2048, FB_T * 128, 1024), id_mnmn, kk > 0 ? 1u : 0u);
+            umma_commit(&q_empty[sj]);
+            umma_commit(&dq_full[bq]);
+            if (it == n_iters) umma_commit(kv_empty);   // last product of the item: K / V may be replaced
+          }
+          if (it < n_iters) scores(1, g % ST);   // half b: its columns were read out before pds[1] of the previous tile
         }
-        if (it > 0) {
-          const int j = it - 1, sj = j % ST, bq = j & 1;
-          const uint32_t aQ = smem_u32(sQ + sj * Cfg::TILE_BYTES), aDO = smem_u32(sDO + sj * Cfg::TILE_BYTES);
-          if (!mbar_wait(&pds[1], j & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
-          if (j >= 2 && !mbar_wait(&dq_drained[bq], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t off_a = Cfg::chunk_off(0, j), off_b = Cfg::chunk_off(1, j);
-#pragma unroll
-          for (int kk = 0; kk < FB_T / 16; ++kk) {  // dV += P^T dO: reduction over the 128 queries, 16 per step
-            const uint32_t a_off = (kk < 4 ? off_a : off_b) + (kk & 3) * 32;
-            umma_f16_ss(tmem_base + Cfg::COL_DV, make_smem_desc(aP + a_off, 16, 1024),
-                        make_smem_desc(aDO + kk * 2048, FB_T * 128, 1024), id_kmn, (j > 0 || kk > 0) ? 1u : 0u);
-          }
-#pragma unroll
-          for (int kk = 0; kk < FB_T / 16; ++kk) {  // dK += dS^T Q
-            const uint32_t a_off = (kk < 4 ? off_a : off_b) + (kk & 3) * 32;
-            umma_f16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(aDS + a_off, 16, 1024),
-                        make_smem_desc(aQ + kk * 2048, FB_T * 128, 1024), id_kmn, (j > 0 || kk > 0) ? 1u : 0u);
-          }
-          // dQ partial = dS K: A = dS in MN-major form, two 64-query chunks CHUNK_BYTES apart starting at the lower
-          // of the two addresses: (a0, b) for even tiles, (b, a1) for odd tiles (rows then come out rotated by 64)
-          const uint32_t ds_first = aDS + (bq ? Cfg::CHUNK_BYTES : 0);
-#pragma unroll
-          for (int kk = 0; kk < FB_T / 16; ++kk)
-            umma_f16_ss(tmem_base + Cfg::COL_DQ + bq * D, make_smem_desc(ds_first + kk * 2048, Cfg::CHUNK_BYTES, 1024),
-                        make_smem_desc(aK + kk * 2048, FB_T * 128, 1024), id_mnmn, kk > 0 ? 1u : 0u);
-          umma_commit(&q_empty[sj]);
-          umma_commit(&dq_full[bq]);
-        }
-        if (it < n_iters) scores(1, it % ST);   // half b: its columns were read out before pds[1] of the previous tile
+        base += n_iters;
       }
     }
   } else {
@@ -195,17 +240,17 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int quarter = warp & 3;
     const int cb = cw >> 2;
     const int row = quarter * 32 + lane;
-    const int kv_idx = kv0 + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const bool kv_live = kv_idx < p.T;
 
-    auto drain_dq = [&](int j) -> bool {
-      const int bq = j & 1;
-      if (!mbar_wait(&dq_full[bq], (j >> 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) return false;
+    // dQ partial of pipeline slot g (tile `it_j` of the item described by the arguments)
+    auto drain_dq = [&](int g, int it_j, int kv_tile, int hkv, int b) -> bool {
+      const int bq = g & 1;
+      if (!mbar_wait(&dq_full[bq], (g >> 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) return false;
       tc_fence_after();
-      const int hq_j = hkv * group + j / tiles_per_head;
-      const int q_local = bq ? ((row + H) & (FB_T - 1)) : row;   // odd tiles: rows are the queries rotated by 64
-      const int q = (first_q_tile + j % tiles_per_head) * FB_T + q_local;
+      const int tiles_per_head = p.n_tiles - kv_tile;
+      const int hq_j = hkv * group + it_j / tiles_per_head;
+      const int q_local = bq ? ((row + H) & (FB_T - 1)) : row;   // odd slots: rows are the queries rotated by 64
+      const int q = (kv_tile + it_j % tiles_per_head) * FB_T + q_local;
       constexpr int DC = D / 4;
       float* dq_row = p.dq_accum + (((long long)b * p.T + q) * p.Hq + hq_j) * D + cb * DC;
       uint32_t r[16];
@@ -225,64 +270,74 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       return true;
     };
 
+    int base = 0;
     bool ok = true;
-    for (int it = 0; it < n_iters && ok; ++it) {
-      const int s = it % ST;
-      const int q0 = (first_q_tile + it % tiles_per_head) * FB_T;
-      const bool masked = (q0 < kv0 + FB_T) || (kv0 + FB_T > p.T);   // diagonal tile, or a KV tile with dead rows
-      auto half = [&](int h, auto masked_tag) -> bool {
-        constexpr bool MASKED = decltype(masked_tag)::value;
-        if (!mbar_wait(&sdp[h], it & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) return false;
-        tc_fence_after();
-        const int c0 = h * H + cb * 16;                      // first of this thread's 16 query columns in the tile
-        const float* s_lse = sStat + s * 2 * FB_T + c0;      // q_full (waited by the issuer) covers the statistics
-        const float* s_delta = s_lse + FB_T;
-        uint32_t rs[16], rd[16];
-        tmem_ld_32x16(tmem_base + Cfg::COL_ST + lane_addr + c0, rs);
-        tmem_ld_32x16(tmem_base + Cfg::COL_DPT + lane_addr + c0, rd);
-        tmem_ld_wait();
-        uint32_t pp[8], dd[8];
+    for (int rnd = 0; ok; ++rnd) {
+      int kv_tile, hkv, b;
+      if (!item_of(rnd, kv_tile, hkv, b)) break;
+      const int kv0 = kv_tile * FB_T;
+      const int kv_idx = kv0 + row;
+      const bool kv_live = kv_idx < p.T;
+      const int tiles_per_head = p.n_tiles - kv_tile;
+      const int n_iters = tiles_per_head * group;
+      for (int it = 0; it < n_iters && ok; ++it) {
+        const int g = base + it, s = g % ST;
+        const int q0 = (kv_tile + it % tiles_per_head) * FB_T;
+        const bool masked = (q0 < kv0 + FB_T) || (kv0 + FB_T > p.T);   // diagonal tile, or a KV tile with dead rows
+        auto half = [&](int h, auto masked_tag) -> bool {
+          constexpr bool MASKED = decltype(masked_tag)::value;
+          if (!mbar_wait(&sdp[h], g & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) return false;
+          tc_fence_after();
+          const int c0 = h * H + cb * 16;                      // first of this thread's 16 query columns in the tile
+          const float* s_lse = sStat + s * 2 * FB_T + c0;      // q_full (waited by the issuer) covers the statistics
+          const float* s_delta = s_lse + FB_T;
+          uint32_t rs[16], rd[16];
+          tmem_ld_32x16(tmem_base + Cfg::COL_ST + lane_addr + c0, rs);
+          tmem_ld_32x16(tmem_base + Cfg::COL_DPT + lane_addr + c0, rd);
+          tmem_ld_wait();
+          uint32_t pp[8], dd[8];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const float4 l4 = *reinterpret_cast<const float4*>(s_lse + g * 4);
-          const float4 d4 = *reinterpret_cast<const float4*>(s_delta + g * 4);
-          const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
-          const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pv[4], dv[4];
+          for (int gq = 0; gq < 4; ++gq) {
+            const float4 l4 = *reinterpret_cast<const float4*>(s_lse + gq * 4);
+            const float4 d4 = *reinterpret_cast<const float4*>(s_delta + gq * 4);
+            const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
+            const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pv[4], dv[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = g * 4 + e;
-            float pr = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse[e]));
-            if constexpr (MASKED) pr = (kv_live && (q0 + c0 + i >= kv_idx)) ? pr : 0.f;
-            pv[e] = pr;
-            dv[e] = pr * (__uint_as_float(rd[i]) - dl[e]);   // the softmax scale is applied when dQ / dK leave TMEM
+            for (int e = 0; e < 4; ++e) {
+              const int i = gq * 4 + e;
+              float pr = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse[e]));
+              if constexpr (MASKED) pr = (kv_live && (q0 + c0 + i >= kv_idx)) ? pr : 0.f;
+              pv[e] = pr;
+              dv[e] = pr * (__uint_as_float(rd[i]) - dl[e]);   // the softmax scale is applied when dQ / dK leave TMEM
+            }
+            pp[gq * 2] = pack_bf16x2(pv[0], pv[1]);
+            pp[gq * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
+            dd[gq * 2] = pack_bf16x2(dv[0], dv[1]);
+            dd[gq * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
           }
-          pp[g * 2] = pack_bf16x2(pv[0], pv[1]);
-          pp[g * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
-          dd[g * 2] = pack_bf16x2(dv[0], dv[1]);
-          dd[g * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
-        }
-        // [128 kv rows][64 q] bf16, 128 bytes per row, 16-byte units swizzled with the row (SWIZZLE_128B)
-        const int off = Cfg::chunk_off(h, it) + row * 128;
+          // [128 kv rows][64 q] bf16, 128 bytes per row, 16-byte units swizzled with the row (SWIZZLE_128B)
+          const int off = Cfg::chunk_off(h, g) + row * 128;
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int unit = (cb * 2 + u) ^ (row & 7);
-          *reinterpret_cast<uint4*>(sP + off + unit * 16) = make_uint4(pp[u * 4], pp[u * 4 + 1], pp[u * 4 + 2], pp[u * 4 + 3]);
-          *reinterpret_cast<uint4*>(sDS + off + unit * 16) = make_uint4(dd[u * 4], dd[u * 4 + 1], dd[u * 4 + 2], dd[u * 4 + 3]);
-        }
-        fence_proxy_async_smem();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&pds[h]);
-        return true;
-      };
-      if (masked) ok = half(0, std::true_type{}) && half(1, std::true_type{});
-      else ok = half(0, std::false_type{}) && half(1, std::false_type{});
-      if (ok && it > 0) ok = drain_dq(it - 1);   // overlaps the gradient products the issuer has just launched
-    }
-    if (ok && n_iters > 0) ok = drain_dq(n_iters - 1);
-    // final: dK and dV of this KV tile (dq_full of the last tile implies both are complete)
-    if (ok && n_iters > 0) {
+          for (int u = 0; u < 2; ++u) {
+            const int unit = (cb * 2 + u) ^ (row & 7);
+            *reinterpret_cast<uint4*>(sP + off + unit * 16) = make_uint4(pp[u * 4], pp[u * 4 + 1], pp[u * 4 + 2], pp[u * 4 + 3]);
+            *reinterpret_cast<uint4*>(sDS + off + unit * 16) = make_uint4(dd[u * 4], dd[u * 4 + 1], dd[u * 4 + 2], dd[u * 4 + 3]);
+          }
+          fence_proxy_async_smem();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&pds[h]);
+          return true;
+        };
+        if (masked) ok = half(0, std::true_type{}) && half(1, std::true_type{});
+        else ok = half(0, std::false_type{}) && half(1, std::false_type{});
+        // the dQ partial of the previous tile of this item: overlaps the products the issuer has just launched
+        if (ok && it > 0) ok = drain_dq(g - 1, it - 1, kv_tile, hkv, b);
+      }
+      if (!ok) break;
+      if (!drain_dq(base + n_iters - 1, n_iters - 1, kv_tile, hkv, b)) break;
+      // dK and dV of this item (dq_full of its last tile implies both are complete)
       tc_fence_after();
       constexpr int DC = D / 4;
       __nv_bfloat16* dk_row = p.dk + (long long)b * p.dk_stride_b + (long long)kv_idx * p.dk_stride_t +
@@ -293,6 +348,9 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tmem_ld_32x16(tmem_base + Cfg::COL_DK + lane_addr + cb * DC, rk);
       tmem_ld_32x16(tmem_base + Cfg::COL_DV + lane_addr + cb * DC, rv);
       tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dkv_drained);   // the next item's products may overwrite dV / dK now
       if (kv_live) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
@@ -309,7 +367,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           *reinterpret_cast<uint4*>(dv_row + u * 8) = bb;
         }
       }
-      __syncwarp();
+      base += n_iters;
     }
   }
 
