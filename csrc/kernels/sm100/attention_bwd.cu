@@ -66,6 +66,7 @@ struct FbParams {
   __nv_bfloat16 *dk, *dv;
   long long dk_stride_b, dk_stride_t, dk_stride_h, dv_stride_b, dv_stride_t, dv_stride_h;
   int* status;
+  long long* prof;     // optional (INCIN_ATTN_PROF=1): clock counters of the issuer thread and of one compute lane
 };
 
 template <int D>
@@ -487,6 +488,21 @@ __global__ void attn_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16
   }
 }
 
+// Where the backward spends its time: with INCIN_ATTN_PROF=1 the head_dim-64 kernel adds up, per launch, the clock
+// cycles its MMA issuer spends waiting on each barrier and issuing, and those one compute lane spends waiting and
+// computing.  Read (and cleared) with incin_attn_prof_read.  Off by default: the pointer is null.
+static long long* attn_prof_buffer() {
+  static long long* buf = [] () -> long long* {
+    const char* e = std::getenv("INCIN_ATTN_PROF");
+    if (!(e && e[0] == '1')) return nullptr;
+    long long* b = nullptr;
+    if (cudaMalloc(&b, 16 * sizeof(long long)) != cudaSuccess) return nullptr;
+    cudaMemset(b, 0, 16 * sizeof(long long));
+    return b;
+  }();
+  return buf;
+}
+
 }  // namespace incin
 #include "attention_bwd64.cuh"
 namespace incin {
@@ -548,6 +564,7 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.dv_stride_t = d->dv_stride_t;
   p.dv_stride_h = d->dv_stride_h;
   p.status = (int*)d->status;
+  p.prof = attn_prof_buffer();
   dim3 grid(p.n_tiles, d->Hkv, d->B);
   if (use_split) {   // persistent: one CTA per SM (or per item when there are fewer items)
     const long long items = (long long)p.n_tiles * d->Hkv * d->B;
@@ -566,6 +583,14 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
 }
 
 }  // namespace incin
+
+extern "C" int incin_attn_prof_read(long long* out16) {
+  long long* b = incin::attn_prof_buffer();
+  if (!b || !out16) return INCIN_ERR_UNSUPPORTED;
+  if (cudaMemcpy(out16, b, 16 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess) return INCIN_ERR_DRIVER;
+  cudaMemset(b, 0, 16 * sizeof(long long));
+  return INCIN_OK;
+}
 
 extern "C" int incin_flash_attn_bwd(const incin_attn_desc* d, void* stream) {
   if (!d || !d->q || !d->k || !d->v || !d->o || !d->d_o || !d->lse || !d->delta || !d->dq_accum || !d->dq ||

@@ -97,7 +97,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
       mbar_init(&sdp[s], 1);
-      mbar_init(&pds[s], FB_CWARPS);
+      mbar_init(&pds[s], FB_CWARPS / 2);   // each half is produced by its own group of 8 warps
       mbar_init(&dq_full[s], 1);
       mbar_init(&dq_drained[s], FB_CWARPS);
     }
@@ -158,43 +158,56 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       constexpr uint32_t id_half = make_idesc_bf16(FB_T, H, false, false);   // S^T / dP^T of one half: [128 kv] x [64 q]
       constexpr uint32_t id_kmn = make_idesc_bf16(FB_T, D, false, true);     // dV, dK
       constexpr uint32_t id_mnmn = make_idesc_bf16(FB_T, D, true, true);     // dQ
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), aDS = smem_u32(sDS);
+      // Shared-memory descriptors: every operand sits at a compile-time offset from the 1024-byte aligned base, so a
+      // descriptor is one add on the low word (address >> 4) plus constants.  The issuing thread is the critical path
+      // of the kernel; building descriptors field by field for each product cost more than the products themselves.
+      constexpr uint32_t kDescHi = ((1024u >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);   // SBO 1024, version, SWIZZLE_128B
+      constexpr uint32_t kLoK = (16u >> 4) << 16;                                       // K-major: LBO 16
+      constexpr uint32_t kLoMN = ((uint32_t)(FB_T * 128) >> 4) << 16;                   // MN-major: LBO 16 KB
+      static_assert(Cfg::CHUNK_BYTES == FB_T * 128, "one LBO for every MN-major operand");
+      auto desc = [&](uint32_t lo16, uint32_t lo_const) -> uint64_t {
+        return (static_cast<uint64_t>(kDescHi) << 32) | static_cast<uint64_t>(lo16 + lo_const);
+      };
+      const uint32_t b16 = (smem_u32(smem) & 0x3FFFF) >> 4;
+      const uint32_t k16 = b16 + (Cfg::OFF_K >> 4), v16 = b16 + (Cfg::OFF_V >> 4);
       // score products of half h of the tile in stage s: rows h*64.. of Q / dO are 64 x 128 bytes further on
       auto scores = [&](int h, int s) {
-        const uint32_t aQ = smem_u32(sQ + s * Cfg::TILE_BYTES) + h * (H * 128);
-        const uint32_t aDO = smem_u32(sDO + s * Cfg::TILE_BYTES) + h * (H * 128);
+        const uint32_t q16 = b16 + ((Cfg::OFF_Q + s * Cfg::TILE_BYTES + h * (H * 128)) >> 4);
+        const uint32_t do16 = b16 + ((Cfg::OFF_DO + s * Cfg::TILE_BYTES + h * (H * 128)) >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          umma_f16_ss(tmem_base + Cfg::COL_ST + h * H, make_smem_desc(aK + kk * 32, 16, 1024),
-                      make_smem_desc(aQ + kk * 32, 16, 1024), id_half, kk > 0 ? 1u : 0u);
+          umma_f16_ss(tmem_base + Cfg::COL_ST + h * H, desc(k16 + kk * 2, kLoK), desc(q16 + kk * 2, kLoK), id_half,
+                      kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          umma_f16_ss(tmem_base + Cfg::COL_DPT + h * H, make_smem_desc(aV + kk * 32, 16, 1024),
-                      make_smem_desc(aDO + kk * 32, 16, 1024), id_half, kk > 0 ? 1u : 0u);
+          umma_f16_ss(tmem_base + Cfg::COL_DPT + h * H, desc(v16 + kk * 2, kLoK), desc(do16 + kk * 2, kLoK), id_half,
+                      kk > 0 ? 1u : 0u);
         umma_commit(&sdp[h]);
       };
       int base = 0;
       bool ok = true;
+      long long t_kv = 0, t_q = 0, t_pds0 = 0, t_pds1 = 0, t_dq = 0, t_issue = 0, t_all = clock64(), tm;
+#define PROF_WAIT(acc, expr) (tm = clock64(), ok_w = (expr), acc += clock64() - tm, ok_w)
+      bool ok_w;
       for (int r = 0; ok; ++r) {
         int kv_tile, hkv, b;
         if (!item_of(r, kv_tile, hkv, b)) break;
         const int n_iters = (p.n_tiles - kv_tile) * group;
-        if (!mbar_wait(kv_full, r & 1, abort_flag, p.status, kStatusTimeoutFull)) break;
+        if (!PROF_WAIT(t_kv, mbar_wait(kv_full, r & 1, abort_flag, p.status, kStatusTimeoutFull))) break;
         for (int it = 0; it <= n_iters && ok; ++it) {
           const int g = base + it;
           if (it < n_iters) {
-            if (!mbar_wait(&q_full[g % ST], (g / ST) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+            if (!PROF_WAIT(t_q, mbar_wait(&q_full[g % ST], (g / ST) & 1, abort_flag, p.status, kStatusTimeoutFull))) { ok = false; break; }
             // half a of the previous tile has been read out of tensor memory (across items the previous item's last
             // tile was waited for through pds[1])
-            if (it > 0 && !mbar_wait(&pds[0], (g - 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+            if (it > 0 && !PROF_WAIT(t_pds0, mbar_wait(&pds[0], (g - 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull))) { ok = false; break; }
             tc_fence_after();
             scores(0, g % ST);
           }
           if (it > 0) {
             const int j = it - 1, gj = g - 1, sj = gj % ST, bq = gj & 1;
-            const uint32_t aQ = smem_u32(sQ + sj * Cfg::TILE_BYTES), aDO = smem_u32(sDO + sj * Cfg::TILE_BYTES);
-            if (!mbar_wait(&pds[1], gj & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
-            if (gj >= 2 && !mbar_wait(&dq_drained[bq], ((gj >> 1) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) {
+            if (!PROF_WAIT(t_pds1, mbar_wait(&pds[1], gj & 1, abort_flag, p.status, kStatusTimeoutTmemFull))) { ok = false; break; }
+            if (gj >= 2 && !PROF_WAIT(t_dq, mbar_wait(&dq_drained[bq], ((gj >> 1) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutTmemEmpty))) {
               ok = false;
               break;
             }
@@ -204,26 +217,27 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
               break;
             }
             tc_fence_after();
-            const uint32_t off_a = Cfg::chunk_off(0, gj), off_b = Cfg::chunk_off(1, gj);
+            const uint32_t q16 = b16 + ((Cfg::OFF_Q + sj * Cfg::TILE_BYTES) >> 4);
+            const uint32_t do16 = b16 + ((Cfg::OFF_DO + sj * Cfg::TILE_BYTES) >> 4);
+            const uint32_t half_a = Cfg::chunk_off(0, gj) >> 4, half_b = Cfg::chunk_off(1, gj) >> 4;
+            const uint32_t p16a = b16 + (Cfg::OFF_P >> 4) + half_a, p16b = b16 + (Cfg::OFF_P >> 4) + half_b;
+            const uint32_t ds16a = b16 + (Cfg::OFF_DS >> 4) + half_a, ds16b = b16 + (Cfg::OFF_DS >> 4) + half_b;
+            const uint32_t acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
-            for (int kk = 0; kk < FB_T / 16; ++kk) {  // dV += P^T dO: reduction over the 128 queries, 16 per step
-              const uint32_t a_off = (kk < 4 ? off_a : off_b) + (kk & 3) * 32;
-              umma_f16_ss(tmem_base + Cfg::COL_DV, make_smem_desc(aP + a_off, 16, 1024),
-                          make_smem_desc(aDO + kk * 2048, FB_T * 128, 1024), id_kmn, (j > 0 || kk > 0) ? 1u : 0u);
-            }
+            for (int kk = 0; kk < FB_T / 16; ++kk)   // dV += P^T dO: reduction over the 128 queries, 16 per step
+              umma_f16_ss(tmem_base + Cfg::COL_DV, desc((kk < 4 ? p16a : p16b) + (kk & 3) * 2, kLoK),
+                          desc(do16 + kk * 128, kLoMN), id_kmn, kk > 0 ? 1u : acc0);
 #pragma unroll
-            for (int kk = 0; kk < FB_T / 16; ++kk) {  // dK += dS^T Q
-              const uint32_t a_off = (kk < 4 ? off_a : off_b) + (kk & 3) * 32;
-              umma_f16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(aDS + a_off, 16, 1024),
-                          make_smem_desc(aQ + kk * 2048, FB_T * 128, 1024), id_kmn, (j > 0 || kk > 0) ? 1u : 0u);
-            }
+            for (int kk = 0; kk < FB_T / 16; ++kk)   // dK += dS^T Q
+              umma_f16_ss(tmem_base + Cfg::COL_DK, desc((kk < 4 ? ds16a : ds16b) + (kk & 3) * 2, kLoK),
+                          desc(q16 + kk * 128, kLoMN), id_kmn, kk > 0 ? 1u : acc0);
             // dQ partial = dS K: A = dS in MN-major form, two 64-query chunks CHUNK_BYTES apart starting at the
             // lower of the two addresses: (a0, b) for even tiles, (b, a1) for odd tiles (rows come out rotated by 64)
-            const uint32_t ds_first = aDS + (bq ? Cfg::CHUNK_BYTES : 0);
+            const uint32_t dsf16 = b16 + ((Cfg::OFF_DS + (bq ? Cfg::CHUNK_BYTES : 0)) >> 4);
 #pragma unroll
             for (int kk = 0; kk < FB_T / 16; ++kk)
-              umma_f16_ss(tmem_base + Cfg::COL_DQ + bq * D, make_smem_desc(ds_first + kk * 2048, Cfg::CHUNK_BYTES, 1024),
-                          make_smem_desc(aK + kk * 2048, FB_T * 128, 1024), id_mnmn, kk > 0 ? 1u : 0u);
+              umma_f16_ss(tmem_base + Cfg::COL_DQ + bq * D, desc(dsf16 + kk * 128, kLoMN), desc(k16 + kk * 128, kLoMN),
+                          id_mnmn, kk > 0 ? 1u : 0u);
             umma_commit(&q_empty[sj]);
             umma_commit(&dq_full[bq]);
             if (it == n_iters) umma_commit(kv_empty);   // last product of the item: K / V may be replaced
@@ -232,20 +246,41 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         base += n_iters;
       }
+#undef PROF_WAIT
+      if (p.prof) {
+        t_all = clock64() - t_all;
+        t_issue = t_all - t_kv - t_q - t_pds0 - t_pds1 - t_dq;
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 0), (unsigned long long)t_all);
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 1), (unsigned long long)t_kv);
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 2), (unsigned long long)t_q);
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 3), (unsigned long long)t_pds0);
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 4), (unsigned long long)t_pds1);
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 5), (unsigned long long)t_dq);
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 6), (unsigned long long)t_issue);
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 7), (unsigned long long)base);
+      }
     }
   } else {
     // ---------------------------------------------------------------- softmax-gradient threads
-    // warp -> (TMEM lane quarter = 32 KV rows, column block cb = 16 query columns of each half)
+    // Two groups of 8 warps, one per half of the query tile, run side by side: while group 0 waits for tensor memory
+    // or for its barrier, group 1 has work to issue.  Inside a group: warp -> (TMEM lane quarter = 32 KV rows,
+    // cb2 = which 32 of the half's 64 query columns).  For the dQ / dK / dV drains all 16 warps split D as before.
     const int cw = warp - 2;
     const int quarter = warp & 3;
-    const int cb = cw >> 2;
+    const int cb = cw >> 2;            // 0..3: 16-column block of D for the drains
+    const int my_half = cw >> 3;       // 0: half a, 1: half b
+    const int cb2 = (cw >> 2) & 1;
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
 
+    long long c_wait_sdp = 0, c_wait_dq = 0, c_drain = 0, c_ld0 = 0, c_chunks = 0, c_fence = 0, c_all = clock64();   // optional profile (see attn_prof_buffer)
     // dQ partial of pipeline slot g (tile `it_j` of the item described by the arguments)
     auto drain_dq = [&](int g, int it_j, int kv_tile, int hkv, int b) -> bool {
       const int bq = g & 1;
+      const long long tw = clock64();
       if (!mbar_wait(&dq_full[bq], (g >> 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) return false;
+      const long long tb = clock64();
+      c_wait_dq += tb - tw;
       tc_fence_after();
       const int tiles_per_head = p.n_tiles - kv_tile;
       const int hq_j = hkv * group + it_j / tiles_per_head;
@@ -267,6 +302,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dq_drained[bq]);
+      c_drain += clock64() - tb;
       return true;
     };
 
@@ -286,52 +322,65 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const bool masked = (q0 < kv0 + FB_T) || (kv0 + FB_T > p.T);   // diagonal tile, or a KV tile with dead rows
         auto half = [&](int h, auto masked_tag) -> bool {
           constexpr bool MASKED = decltype(masked_tag)::value;
+          const long long tw = clock64();
           if (!mbar_wait(&sdp[h], g & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) return false;
+          c_wait_sdp += clock64() - tw;
           tc_fence_after();
-          const int c0 = h * H + cb * 16;                      // first of this thread's 16 query columns in the tile
-          const float* s_lse = sStat + s * 2 * FB_T + c0;      // q_full (waited by the issuer) covers the statistics
+          const int off = Cfg::chunk_off(h, g) + row * 128;     // [128 kv rows][64 q] bf16, SWIZZLE_128B
+          // 32 query columns per thread in four chunks of 8: the tensor-memory loads of chunk c+1 are in flight while
+          // chunk c is computed (one chunk of S^T and dP^T = one 16-byte unit of P^T and of dS^T)
+          const int cbase = h * H + cb2 * 32;                   // first of this thread's query columns in the tile
+          const float* s_lse = sStat + s * 2 * FB_T + cbase;    // q_full (waited by the issuer) covers the statistics
           const float* s_delta = s_lse + FB_T;
-          uint32_t rs[16], rd[16];
-          tmem_ld_32x16(tmem_base + Cfg::COL_ST + lane_addr + c0, rs);
-          tmem_ld_32x16(tmem_base + Cfg::COL_DPT + lane_addr + c0, rd);
-          tmem_ld_wait();
-          uint32_t pp[8], dd[8];
+          uint32_t rs[2][8], rd[2][8];
+          tmem_ld_32x8(tmem_base + Cfg::COL_ST + lane_addr + cbase, rs[0]);
+          tmem_ld_32x8(tmem_base + Cfg::COL_DPT + lane_addr + cbase, rd[0]);
+          tmem_ld_wait_on(rs[0], rd[0]);
+          const long long t_a = clock64();
+          c_ld0 += t_a - tw;
 #pragma unroll
-          for (int gq = 0; gq < 4; ++gq) {
-            const float4 l4 = *reinterpret_cast<const float4*>(s_lse + gq * 4);
-            const float4 d4 = *reinterpret_cast<const float4*>(s_delta + gq * 4);
-            const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
-            const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
-            float pv[4], dv[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i = gq * 4 + e;
-              float pr = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse[e]));
-              if constexpr (MASKED) pr = (kv_live && (q0 + c0 + i >= kv_idx)) ? pr : 0.f;
-              pv[e] = pr;
-              dv[e] = pr * (__uint_as_float(rd[i]) - dl[e]);   // the softmax scale is applied when dQ / dK leave TMEM
+          for (int c = 0; c < 4; ++c) {
+            const int cur = c & 1, nxt = cur ^ 1;
+            if (c < 3) {
+              tmem_ld_32x8(tmem_base + Cfg::COL_ST + lane_addr + cbase + (c + 1) * 8, rs[nxt]);
+              tmem_ld_32x8(tmem_base + Cfg::COL_DPT + lane_addr + cbase + (c + 1) * 8, rd[nxt]);
             }
-            pp[gq * 2] = pack_bf16x2(pv[0], pv[1]);
-            pp[gq * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
-            dd[gq * 2] = pack_bf16x2(dv[0], dv[1]);
-            dd[gq * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
-          }
-          // [128 kv rows][64 q] bf16, 128 bytes per row, 16-byte units swizzled with the row (SWIZZLE_128B)
-          const int off = Cfg::chunk_off(h, g) + row * 128;
+            uint32_t pp[4], dd[4];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int unit = (cb * 2 + u) ^ (row & 7);
-            *reinterpret_cast<uint4*>(sP + off + unit * 16) = make_uint4(pp[u * 4], pp[u * 4 + 1], pp[u * 4 + 2], pp[u * 4 + 3]);
-            *reinterpret_cast<uint4*>(sDS + off + unit * 16) = make_uint4(dd[u * 4], dd[u * 4 + 1], dd[u * 4 + 2], dd[u * 4 + 3]);
+            for (int gq = 0; gq < 2; ++gq) {
+              const float4 l4 = *reinterpret_cast<const float4*>(s_lse + c * 8 + gq * 4);
+              const float4 d4 = *reinterpret_cast<const float4*>(s_delta + c * 8 + gq * 4);
+              const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
+              const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+              float pv[4], dv[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int i = gq * 4 + e;
+                float pr = exp2f(fmaf(__uint_as_float(rs[cur][i]), p.scale_log2, -lse[e]));
+                if constexpr (MASKED) pr = (kv_live && (q0 + cbase + c * 8 + i >= kv_idx)) ? pr : 0.f;
+                pv[e] = pr;
+                dv[e] = pr * (__uint_as_float(rd[cur][i]) - dl[e]);   // the softmax scale is applied when dQ / dK leave TMEM
+              }
+              pp[gq * 2] = pack_bf16x2(pv[0], pv[1]);
+              pp[gq * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
+              dd[gq * 2] = pack_bf16x2(dv[0], dv[1]);
+              dd[gq * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
+            }
+            const int unit = (cb2 * 4 + c) ^ (row & 7);
+            *reinterpret_cast<uint4*>(sP + off + unit * 16) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
+            *reinterpret_cast<uint4*>(sDS + off + unit * 16) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
+            if (c < 3) tmem_ld_wait_on(rs[nxt], rd[nxt]);
           }
+          const long long t_b = clock64();
+          c_chunks += t_b - t_a;
           fence_proxy_async_smem();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&pds[h]);
+          c_fence += clock64() - t_b;
           return true;
         };
-        if (masked) ok = half(0, std::true_type{}) && half(1, std::true_type{});
-        else ok = half(0, std::false_type{}) && half(1, std::false_type{});
+        ok = masked ? half(my_half, std::true_type{}) : half(my_half, std::false_type{});
         // the dQ partial of the previous tile of this item: overlaps the products the issuer has just launched
         if (ok && it > 0) ok = drain_dq(g - 1, it - 1, kv_tile, hkv, b);
       }
@@ -368,6 +417,18 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
       base += n_iters;
+    }
+    if (p.prof && lane == 0 && warp == 2) {
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 12), (unsigned long long)c_ld0);
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 13), (unsigned long long)c_chunks);
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 14), (unsigned long long)c_fence);
+    }
+    if (p.prof && lane == 0 && warp == 2) {
+      const int o = 8;
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + o), (unsigned long long)(clock64() - c_all));
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + o + 1), (unsigned long long)c_wait_sdp);
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + o + 2), (unsigned long long)c_wait_dq);
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + o + 3), (unsigned long long)c_drain);
     }
   }
 
