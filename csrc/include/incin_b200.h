@@ -86,7 +86,13 @@ typedef struct incin_gemm_desc {
   void* rs_dst[8];
   long long rs_slot_stride;
   void* rs_ready;
+  /* --- operand type: INCIN_GEMM_IN_BF16 (0), INCIN_GEMM_IN_FP16 or INCIN_GEMM_IN_TF32 (A and B are fp32, multiplied
+   * as tf32; K-contiguous operands only, lda / ldb multiples of 4).  The last two require out_fp32 and take no fused
+   * epilogue (bias, residual, activation), no CTA-pair tile and no fused collective. */
+  int in_dtype;
 } incin_gemm_desc;
+
+enum { INCIN_GEMM_IN_BF16 = 0, INCIN_GEMM_IN_FP16 = 1, INCIN_GEMM_IN_TF32 = 2 };
 
 int incin_gemm_bf16(const incin_gemm_desc* desc, void* stream);
 

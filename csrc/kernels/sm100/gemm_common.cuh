@@ -37,6 +37,7 @@ struct GemmKernelParams {
   int act;
   __nv_bfloat16* aux;
   int* status;
+  int in_kind;            // operands: 0 bf16, 1 fp16, 2 fp32 multiplied as tf32 (K counted in 2-byte units)
   // all-gather -> GEMM
   int ag_world, ag_rank, ag_rows_per_rank, gemm_ctas;  // gemm_ctas: CTAs [0, gemm_ctas) compute, the rest copy
   const __nv_bfloat16* ag_src[8];

@@ -240,7 +240,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc_bf16 = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      const bool tf32 = p.in_kind == 2;
+      const uint32_t idesc = p.in_kind == 0 ? idesc_bf16 : idesc_with_format(idesc_bf16, tf32 ? 2u : 0u);
       int stage = 0;
       uint32_t phase = 0;
       int iter = 0;
@@ -268,7 +270,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // MN-major: 16 K-rows of 128 B further.
             const uint64_t a_adv = A_MN ? (uint64_t)(k * 2048 >> 4) : (uint64_t)(k * 32 >> 4);
             const uint64_t b_adv = B_MN ? (uint64_t)(k * 2048 >> 4) : (uint64_t)(k * 32 >> 4);
-            umma_f16_ss(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            const uint32_t accum = (kb > w.kb0 || k > 0) ? 1u : 0u;
+            if (tf32) umma_tf32_ss(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, accum);
+            else umma_f16_ss(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, accum);
           }
           umma_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
           if (++stage == Cfg::STAGES) {
@@ -542,6 +546,29 @@ using namespace incin;
 extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (!d || !d->A || !d->B || (!d->C && d->rs_world <= 1) || d->M <= 0 || d->N <= 0 || d->K <= 0) return INCIN_ERR_ARGUMENT;
+  // Other operand types.  fp16 changes only the format field of the instruction.  fp32 operands are multiplied as
+  // tf32: a row of fp32 is moved by the same tensor maps as a row of twice as many 2-byte units (the 128-byte swizzle
+  // works on 16-byte chunks), so from here on K and the operand strides count 2-byte units; only the instruction kind
+  // differs (8 fp32 = the same 32 bytes per product).  Both write fp32 and take no fused epilogue or collective.
+  incin_gemm_desc widened;
+  const int in_kind = d->in_dtype;
+  if (in_kind != INCIN_GEMM_IN_BF16) {
+    if ((in_kind != INCIN_GEMM_IN_FP16 && in_kind != INCIN_GEMM_IN_TF32) || !d->out_fp32 || d->bias || d->residual ||
+        d->aux || d->act != INCIN_ACT_NONE || d->ag_world > 1 || d->rs_world > 1 || d->tile_n == 512)
+      return INCIN_ERR_ARGUMENT;
+    if (in_kind == INCIN_GEMM_IN_TF32) {
+      if (d->a_mn_major || d->b_mn_major) return INCIN_ERR_ARGUMENT;   // K-contiguous operands only
+      widened = *d;
+      widened.K *= 2;
+      widened.lda *= 2;
+      widened.ldb *= 2;
+      widened.a_stride_lo *= 2;
+      widened.a_stride_hi *= 2;
+      widened.b_stride_lo *= 2;
+      widened.b_stride_hi *= 2;
+      d = &widened;
+    }
+  }
   const int blo = d->batch_lo > 0 ? d->batch_lo : 1;
   const int bhi = d->batch_hi > 0 ? d->batch_hi : 1;
   const int sms = d->max_ctas > 0 ? d->max_ctas : device_sm_count();
@@ -559,7 +586,7 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   if (bn != 64 && bn != 128 && bn != 192 && bn != 256 && bn != 512) bn = 0;
   if (bn == 512 && fused_collective) bn = 0;
   const incin::TileChoice pick = incin::choose_tile(d->M, d->N, d->K, (long long)blo * bhi, bn, splits, can_split,
-                                                    !fused_collective, sms);
+                                                    !fused_collective && in_kind == INCIN_GEMM_IN_BF16, sms);
   bn = pick.bn;
   splits = pick.splits;
   const bool pair = bn == 512;
@@ -603,6 +630,7 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   p.act = d->act;
   p.aux = reinterpret_cast<__nv_bfloat16*>(d->aux);
   p.status = reinterpret_cast<int*>(d->status);
+  p.in_kind = in_kind;
   p.ag_world = d->ag_world > 1 ? d->ag_world : 0;
   p.ag_rank = d->ag_rank;
   p.ag_rows_per_rank = d->ag_rows_per_rank;

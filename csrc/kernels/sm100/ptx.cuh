@@ -172,6 +172,18 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t adesc, uin
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// same with fp32 operands read as tf32 (K = 8 per instruction: still 32 bytes along the swizzle row)
+__device__ __forceinline__ void umma_tf32_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // D[tmem] (+)= A[tmem] * B[smem desc]  (A = 128 lanes x K packed 16-bit pairs)
 __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                             uint32_t accumulate) {
@@ -330,6 +342,12 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   d |= static_cast<uint64_t>(1) << 46;  // descriptor version for sm_100
   d |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
   return d;
+}
+
+// Operand format field of an instruction descriptor built by make_idesc_bf16, replaced for the other input kinds:
+// kind::f16 takes 0 = fp16, 1 = bf16; kind::tf32 takes 2 = tf32.
+__host__ __device__ constexpr uint32_t idesc_with_format(uint32_t idesc, uint32_t fmt) {
+  return (idesc & ~((7u << 7) | (7u << 10))) | (fmt << 7) | (fmt << 10);
 }
 
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.

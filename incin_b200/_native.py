@@ -60,8 +60,11 @@ class GemmDesc(C.Structure):
         ("ag_src", c_void_p * 8), ("ag_flags", c_void_p),
         ("rs_world", c_int), ("rs_rank", c_int), ("rs_rows_per_rank", c_int), ("rs_copy_ctas", c_int),
         ("rs_dst", c_void_p * 8), ("rs_slot_stride", c_ll), ("rs_ready", c_void_p),
+        ("in_dtype", c_int),
     ]
 
+
+GEMM_IN_BF16, GEMM_IN_FP16, GEMM_IN_TF32 = 0, 1, 2
 
 _CUDA_SIGS = {
     "incin_gemm_bf16": (c_int, [C.POINTER(GemmDesc), c_void_p]),

@@ -136,12 +136,38 @@ def _ident(n: str) -> str:
     return f"r#{n}" if n in _KEYWORDS else n
 
 
+def parse_constants(include_dir: Path = INCLUDE_DIR) -> list[tuple[str, int]]:
+    """Enumerators of every (named or anonymous) enum in the headers, in declaration order, with their values."""
+    consts, seen = [], set()
+    for h in HEADERS:
+        path = include_dir / h
+        if not path.exists():
+            continue
+        src = _strip_comments(path.read_text())
+        for m in re.finditer(r"\benum\b\s*\w*\s*\{(.*?)\}", src, re.S):
+            nxt = 0
+            for item in m.group(1).split(","):
+                item = item.strip()
+                if not item:
+                    continue
+                name, _, val = (t.strip() for t in item.partition("="))
+                value = int(val, 0) if val else nxt
+                nxt = value + 1
+                if name not in seen:
+                    seen.add(name)
+                    consts.append((name, value))
+    return consts
+
+
 def render_rust(include_dir: Path = INCLUDE_DIR) -> str:
     structs, funcs = parse_headers(include_dir)
     names = {s.name for s in structs}
     out = ["// Generated from csrc/include/*.h by `python -m incin_b200 ffi`; do not edit by hand.",
            "#![allow(non_camel_case_types, non_snake_case)]", "",
            "use core::ffi::{c_char, c_int, c_longlong, c_uint, c_void};", ""]
+    for cname, cval in parse_constants(include_dir):
+        out.append(f"pub const {cname}: c_int = {cval};")
+    out.append("")
     for s in structs:
         out += ["#[repr(C)]", "#[derive(Clone, Copy)]", f"pub struct {s.name} {{"]
         for name, ct, n in s.fields:

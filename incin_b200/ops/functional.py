@@ -95,11 +95,62 @@ class _Linear(torch.autograd.Function):
         return dx, None, None, (dy if ctx.has_res else None), None
 
 
+class _LinearF32Acc(torch.autograd.Function):
+    """Linear for fp16 tensors and, under ``MathMode.FAST``, fp32 tensors (multiplied as tf32) on the same tcgen05
+    kernel as the bf16 path: fp32 accumulation and fp32 output, rounded once to the input type.  Gradients return
+    through autograd; the transposed operands the two backward products need are materialised (these types are the
+    breadth path, bf16 is the tuned one)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        x2 = _c(x).reshape(-1, x.shape[-1])
+        y = G.mm_nt_f32out(x2, _c(w))
+        if b is not None:
+            y += b.float()
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = b is not None
+        ctx.shape = x.shape
+        return y.to(x.dtype).reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _c(dy).reshape(-1, dy.shape[-1])
+        unit = 8 if dy2.dtype == torch.float16 else 4
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            if dy2.shape[1] % unit == 0:
+                dx = G.mm_nt_f32out(dy2, w.t().contiguous()).to(dy.dtype)
+            else:
+                dx = dy2 @ w
+            dx = dx.reshape(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            if dy2.shape[0] % unit == 0:
+                dw = G.mm_nt_f32out(dy2.t().contiguous(), x2.t().contiguous()).to(w.dtype)
+            else:
+                dw = dy2.t() @ x2
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def _f32acc_native(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """fp16 always, fp32 when the execution policy allows fast math (tf32); rows must start on 16-byte boundaries."""
+    if not (x.is_cuda and x.dtype == w.dtype and x.dim() >= 1 and w.dim() == 2):
+        return False
+    if x.dtype == torch.float16:
+        return x.shape[-1] % 8 == 0
+    if x.dtype == torch.float32:
+        from ..core.policy import MathMode, current_policy
+        return current_policy().math == MathMode.FAST and x.shape[-1] % 4 == 0
+    return False
+
+
 def linear(x, w, b=None, *, act=None, residual=None):
     """``act(x @ w^T + b) + residual`` with everything fused into the GEMM epilogue on CUDA."""
     if _nat(x):
         return _Linear.apply(x, w, b, residual, ACT[act])
-    y = TF.linear(x, w, b)
+    y = _LinearF32Acc.apply(x, w, b) if _f32acc_native(x, w) else TF.linear(x, w, b)
     if act == "gelu":
         y = TF.gelu(y)
     elif act == "silu":

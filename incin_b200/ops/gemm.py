@@ -64,13 +64,20 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
     ``gather`` = {world, rank, rows_per_rank, src: [ptr]*world, flags: tensor, copy_ctas} turns the launch into the
     fused all-gather -> GEMM (``a`` is then the local gathered buffer); ``scatter`` = {world, rank, rows_per_rank,
     dst: [ptr]*world, slot_stride} makes the epilogue store partial tiles into the owners' slot buffers."""
-    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "operands must be bf16"
+    assert a.dtype == b.dtype and a.dtype in _IN_KIND, "operands must both be bf16, fp16 or fp32 (multiplied as tf32)"
+    in_kind = _IN_KIND[a.dtype]
     assert out.dtype in (torch.bfloat16, torch.float32)
-    if tile_n == 0 and not accumulate and gather is None and scatter is None:
+    if in_kind != nat.GEMM_IN_BF16:
+        # fp16 / tf32 operands: fp32 output, no fused epilogue; tf32 wants K-contiguous operands
+        assert out.dtype == torch.float32 and bias is None and residual is None and aux is None and act == nat.ACT_NONE
+        assert gather is None and scatter is None and tile_n != 512
+        assert in_kind == nat.GEMM_IN_FP16 or not (a_mn or b_mn)
+    if tile_n == 0 and not accumulate and gather is None and scatter is None and in_kind == nat.GEMM_IN_BF16:
         tile_n = _tuned_tile_n(locals())
     d = nat.GemmDesc()
-    d.A = a.data_ptr() + 2 * a_offset
-    d.B = b.data_ptr() + 2 * b_offset
+    d.in_dtype = in_kind
+    d.A = a.data_ptr() + a.element_size() * a_offset
+    d.B = b.data_ptr() + b.element_size() * b_offset
     d.C = out.data_ptr() + out.element_size() * c_offset
     d.M, d.N, d.K = M, N, K
     d.lda, d.ldb, d.ldc = lda, ldb, ldc
@@ -105,6 +112,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
             d.rs_copy_ctas, d.rs_ready = scatter["copy_ctas"], scatter["ready"].data_ptr()
     nat.check(nat.cuda().incin_gemm_bf16(ctypes.byref(d), nat.stream_ptr()), "gemm")
     return out
+
+
+_IN_KIND = {torch.bfloat16: nat.GEMM_IN_BF16, torch.float16: nat.GEMM_IN_FP16, torch.float32: nat.GEMM_IN_TF32}
 
 
 def _tuned_tile_n(kw: dict) -> int:
@@ -142,6 +152,19 @@ def mm_nt(x: torch.Tensor, w: torch.Tensor, *, bias=None, residual=None, act=nat
         out = torch.empty(*x.shape[:-1], N, dtype=torch.bfloat16, device=x.device)
     return gemm(x, w, out, M=M, N=N, K=K, lda=K, ldb=K, ldc=N, bias=bias, residual=residual, act=act, aux=aux,
                 alpha=alpha, max_ctas=max_ctas)
+
+
+def mm_nt_f32out(x: torch.Tensor, w: torch.Tensor, *, alpha: float = 1.0, out: torch.Tensor | None = None,
+                 accumulate: bool = False) -> torch.Tensor:
+    """fp32 y[..., N] = x[..., K] @ w[N, K]^T on the tensor cores for bf16, fp16 or fp32 operands (fp32 operands are
+    multiplied as tf32: 10 mantissa bits per factor, fp32 accumulation).  K must be a multiple of 8 (16-bit types)
+    or 4 (fp32) so that every row starts on a 16-byte boundary."""
+    assert x.is_contiguous() and w.is_contiguous() and x.dtype == w.dtype
+    M, K = _rows(x), x.shape[-1]
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(*x.shape[:-1], N, dtype=torch.float32, device=x.device)
+    return gemm(x, w, out, M=M, N=N, K=K, lda=K, ldb=K, ldc=N, alpha=alpha, accumulate=accumulate)
 
 
 def mm_nn(dy: torch.Tensor, w: torch.Tensor, *, act=nat.ACT_NONE, aux=None, out: torch.Tensor | None = None,

@@ -3,6 +3,24 @@
 
 use core::ffi::{c_char, c_int, c_longlong, c_uint, c_void};
 
+pub const INCIN_OK: c_int = 0;
+pub const INCIN_ERR_ARGUMENT: c_int = 1;
+pub const INCIN_ERR_ALIGNMENT: c_int = 2;
+pub const INCIN_ERR_DRIVER: c_int = 3;
+pub const INCIN_ERR_TENSOR_MAP: c_int = 4;
+pub const INCIN_ERR_LAUNCH: c_int = 5;
+pub const INCIN_ERR_UNSUPPORTED: c_int = 6;
+pub const INCIN_ERR_TOO_LARGE: c_int = 7;
+pub const INCIN_ERR_PEER: c_int = 8;
+pub const INCIN_ACT_NONE: c_int = 0;
+pub const INCIN_ACT_GELU: c_int = 1;
+pub const INCIN_ACT_SILU: c_int = 2;
+pub const INCIN_ACT_DGELU: c_int = 3;
+pub const INCIN_ACT_DSILU: c_int = 4;
+pub const INCIN_GEMM_IN_BF16: c_int = 0;
+pub const INCIN_GEMM_IN_FP16: c_int = 1;
+pub const INCIN_GEMM_IN_TF32: c_int = 2;
+
 #[repr(C)]
 #[derive(Clone, Copy)]
 pub struct incin_gemm_desc {
@@ -49,6 +67,7 @@ pub struct incin_gemm_desc {
     pub rs_dst: [*mut c_void; 8],
     pub rs_slot_stride: c_longlong,
     pub rs_ready: *mut c_void,
+    pub in_dtype: c_int,
 }
 
 #[repr(C)]

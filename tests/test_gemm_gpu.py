@@ -104,3 +104,44 @@ def test_general_matmul():
     from incin_b200.ops import gemm as G
     a, b = _ref_inputs((4, 96, 160), 18), _ref_inputs((4, 160, 72), 19)
     _close(G.matmul(a, b), a.float() @ b.float())
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 2e-3), (torch.float32, 2e-3), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (300, 200, 136), (1024, 768, 772), (77, 50, 12)])
+def test_fp16_and_tf32_operands(dtype, tol, M, N, K):
+    """fp16 operands and fp32 operands multiplied as tf32 run on the same kernel with fp32 output (K need not fill
+    a 128-byte k-block: the tail is zero filled)."""
+    from incin_b200.ops import gemm as G
+    if dtype != torch.float32 and K % 8:
+        K += 8 - K % 8
+    g = torch.Generator(device="cpu").manual_seed(5)
+    x = torch.randn(M, K, generator=g).to(dtype).cuda()
+    w = torch.randn(N, K, generator=g).to(dtype).cuda()
+    out = G.mm_nt_f32out(x, w, alpha=0.5)
+    assert out.dtype == torch.float32
+    _close(out, 0.5 * (x.double() @ w.double().T), tol=tol)
+    G.check_status()
+
+
+def test_linear_fp16_and_tf32_autograd():
+    from incin_b200.core.policy import MathMode, policy_scope
+    from incin_b200.ops import functional as F
+    g = torch.Generator(device="cpu").manual_seed(9)
+    for dtype, fast in ((torch.float16, False), (torch.float32, True)):
+        x = torch.randn(4, 64, 96, generator=g).to(dtype).cuda().requires_grad_()
+        w = (torch.randn(80, 96, generator=g) * 0.1).to(dtype).cuda().requires_grad_()
+        b = torch.randn(80, generator=g).to(dtype).cuda().requires_grad_()
+        dy = torch.randn(4, 64, 80, generator=g).to(dtype).cuda()
+        with policy_scope(math=MathMode.FAST if fast else MathMode.PRECISE):
+            assert F._f32acc_native(x, w)
+            y = F.linear(x, w, b)
+            y.backward(dy)
+        xr, wr, br = (t.detach().double().requires_grad_() for t in (x, w, b))
+        yr = xr @ wr.T + br
+        yr.backward(dy.double())
+        _close(y, yr, tol=4e-3)
+        _close(x.grad, xr.grad, tol=4e-3)
+        _close(w.grad, wr.grad, tol=4e-3)
+        _close(b.grad, br.grad, tol=4e-3)
+    # fp32 without the fast-math policy keeps full precision (library path)
+    assert not F._f32acc_native(torch.zeros(8, 8, device="cuda"), torch.zeros(8, 8, device="cuda"))
