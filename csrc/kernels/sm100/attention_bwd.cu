@@ -439,53 +439,89 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-// delta[b, h, t] = sum_d O[b,t,h,d] * dO[b,t,h,d] (0 for the padding rows t >= T); one warp per (b, t, h)
+// delta[b, h, t] = sum_d O[b,t,h,d] * dO[b,t,h,d] (0 for the padding rows t >= T).  A row (b, t, h) is D bf16 =
+// LPR 16-byte loads, one per lane of a group of LPR = D / 8 lanes; every group takes DELTA_ROWS rows with all their
+// loads issued before the first is used, so that a thread keeps 2 x DELTA_ROWS 16-byte loads in flight.
+constexpr int DELTA_ROWS = 4;
+template <int LPR>
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
-                  long long B, int T, int Tpad, int H, int D, long long o_sb, long long o_st, long long o_sh,
+                  long long B, int T, int Tpad, int H, long long o_sb, long long o_st, long long o_sh,
                   long long do_sb, long long do_st, long long do_sh) {
   pdl_launch_dependents();
   pdl_wait();
-  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (w >= B * Tpad * H) return;
-  const int h = (int)(w % H);
-  const int t = (int)((w / H) % Tpad);
-  const long long b = w / ((long long)H * Tpad);
-  float s = 0.f;
-  if (t < T) {
-    const __nv_bfloat16* po = o + b * o_sb + (long long)t * o_st + (long long)h * o_sh;
-    const __nv_bfloat16* pd = d_o + b * do_sb + (long long)t * do_st + (long long)h * do_sh;
-    for (int d = lane * 2; d < D; d += 64) {
-      const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(po + d));
-      const float2 c = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pd + d));
-      s += a.x * c.x + a.y * c.y;
+  constexpr int GROUPS = 256 / LPR;                       // row groups per block
+  const int sub = threadIdx.x % LPR;
+  const long long total = B * Tpad * H;
+  const long long first = ((long long)blockIdx.x * GROUPS + threadIdx.x / LPR) * DELTA_ROWS;
+  uint4 a[DELTA_ROWS], c[DELTA_ROWS];
+#pragma unroll
+  for (int r = 0; r < DELTA_ROWS; ++r) {
+    const long long w = first + r;
+    a[r] = make_uint4(0, 0, 0, 0);
+    c[r] = make_uint4(0, 0, 0, 0);
+    if (w < total) {
+      const int h = (int)(w % H);
+      const int t = (int)((w / H) % Tpad);
+      const long long b = w / ((long long)H * Tpad);
+      if (t < T) {
+        a[r] = *reinterpret_cast<const uint4*>(o + b * o_sb + (long long)t * o_st + (long long)h * o_sh + sub * 8);
+        c[r] = *reinterpret_cast<const uint4*>(d_o + b * do_sb + (long long)t * do_st + (long long)h * do_sh + sub * 8);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < DELTA_ROWS; ++r) {
+    const uint32_t ua[4] = {a[r].x, a[r].y, a[r].z, a[r].w}, uc[4] = {c[r].x, c[r].y, c[r].z, c[r].w};
+    float s = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = unpack_bf16x2(ua[e]), y = unpack_bf16x2(uc[e]);
+      s += x.x * y.x + x.y * y.y;
     }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    const long long w = first + r;
+    if (sub == 0 && w < total) {
+      const int h = (int)(w % H);
+      const int t = (int)((w / H) % Tpad);
+      const long long b = w / ((long long)H * Tpad);
+      delta[(b * H + h) * Tpad + t] = s;
+    }
   }
-  if (lane == 0) delta[(b * H + h) * Tpad + t] = s;
 }
 
-// dq (bf16, strided) = dq_accum (fp32 [B,T,H,D] contiguous)
-__global__ void attn_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long B, int T,
-                                    int H, int D, long long sb, long long st, long long sh) {
+// dq (bf16, strided) = dq_accum (fp32 [B,T,H,D] contiguous); 8 elements (two 16-byte loads, one 16-byte store) per
+// thread and step, two steps in flight
+__global__ void __launch_bounds__(256)
+attn_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long B, int T,
+                    int H, int D, long long sb, long long st, long long sh) {
   pdl_launch_dependents();
   pdl_wait();
-  const long long n4 = B * T * H * D / 4;
+  const long long n8 = B * T * H * D / 8;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
-    const float4 v = reinterpret_cast<const float4*>(acc)[i];
-    const long long e = i * 4;
+  auto store = [&](long long i, const float4& v0, const float4& v1) {
+    const long long e = i * 8;
     const int d = (int)(e % D);
     const int h = (int)((e / D) % H);
     const int t = (int)((e / ((long long)D * H)) % T);
     const long long b = e / ((long long)D * H * T);
-    uint2 o;
-    o.x = pack_bf16x2(v.x, v.y);
-    o.y = pack_bf16x2(v.z, v.w);
-    *reinterpret_cast<uint2*>(dq + b * sb + (long long)t * st + (long long)h * sh + d) = o;
+    uint4 o;
+    o.x = pack_bf16x2(v0.x, v0.y);
+    o.y = pack_bf16x2(v0.z, v0.w);
+    o.z = pack_bf16x2(v1.x, v1.y);
+    o.w = pack_bf16x2(v1.z, v1.w);
+    *reinterpret_cast<uint4*>(dq + b * sb + (long long)t * st + (long long)h * sh + d) = o;
+  };
+  const float4* src = reinterpret_cast<const float4*>(acc);
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + stride < n8; i += 2 * stride) {
+    const float4 a0 = src[2 * i], a1 = src[2 * i + 1];
+    const float4 b0 = src[2 * (i + stride)], b1 = src[2 * (i + stride) + 1];
+    store(i, a0, a1);
+    store(i + stride, b0, b1);
   }
+  if (i < n8) store(i, src[2 * i], src[2 * i + 1]);
 }
 
 // Where the backward spends its time: with INCIN_ATTN_PROF=1 the head_dim-64 kernel adds up, per launch, the clock
@@ -519,6 +555,10 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   if (rc) return rc;
   rc = make_operand_map(&tdo, d->d_o, D, d->T, d->do_stride_t, d->Hq, d->do_stride_h, d->B, d->do_stride_b, 64, FB_T);
   if (rc) return rc;
+  // O is read and dQ written 16 bytes at a time
+  if ((reinterpret_cast<uintptr_t>(d->o) & 15) || (reinterpret_cast<uintptr_t>(d->dq) & 15) || (d->o_stride_t % 8) ||
+      (d->o_stride_h % 8) || (d->o_stride_b % 8) || (d->dq_stride_t % 8) || (d->dq_stride_h % 8) || (d->dq_stride_b % 8))
+    return INCIN_ERR_ALIGNMENT;
   // head_dim 64 runs the half-split kernel (tensor core and softmax-gradient threads overlap); INCIN_ATTN_BWD_SPLIT=0
   // selects the one-tile-at-a-time kernel instead
   static const bool split64 = [] {
@@ -537,11 +577,14 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   const long long rows = (long long)d->B * d->T * d->Hq;
   const int Tpad = (d->T + FB_T - 1) / FB_T * FB_T;
   const long long prow = (long long)d->B * Tpad * d->Hq;
-  if (launch_pdl(attn_delta_kernel, dim3((unsigned)((prow + 7) / 8)), dim3(256), 0, stream, (const __nv_bfloat16*)d->o,
-                 (const __nv_bfloat16*)d->d_o, d->delta, (long long)d->B, (int)d->T, Tpad, (int)d->Hq, D, (long long)d->o_stride_b,
-                 (long long)d->o_stride_t, (long long)d->o_stride_h, (long long)d->do_stride_b, (long long)d->do_stride_t,
-                 (long long)d->do_stride_h) != cudaSuccess)
-    return INCIN_ERR_LAUNCH;
+  {
+    constexpr int LPR = D / 8, ROWS_PER_BLOCK = 256 / LPR * DELTA_ROWS;
+    if (launch_pdl(attn_delta_kernel<LPR>, dim3((unsigned)((prow + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK)), dim3(256), 0, stream,
+                   (const __nv_bfloat16*)d->o, (const __nv_bfloat16*)d->d_o, d->delta, (long long)d->B, (int)d->T, Tpad,
+                   (int)d->Hq, (long long)d->o_stride_b, (long long)d->o_stride_t, (long long)d->o_stride_h,
+                   (long long)d->do_stride_b, (long long)d->do_stride_t, (long long)d->do_stride_h) != cudaSuccess)
+      return INCIN_ERR_LAUNCH;
+  }
   if (cudaMemsetAsync(d->dq_accum, 0, sizeof(float) * rows * D, stream) != cudaSuccess) return INCIN_ERR_LAUNCH;
   FbParams p;
   p.T = d->T;
@@ -572,8 +615,8 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
     grid = dim3((unsigned)(items < sms ? items : sms), 1, 1);
   }
   if (launch_pdl<true>(kern, grid, dim3(FB_THREADS), smem_bytes, stream, tq, tk, tv, tdo, p) != cudaSuccess) return INCIN_ERR_LAUNCH;
-  long long n4 = rows * D / 4;
-  long long blocks = (n4 + 255) / 256;
+  long long n8 = rows * D / 8;
+  long long blocks = (n8 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (launch_pdl(attn_dq_cast_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)d->dq_accum,
                  (__nv_bfloat16*)d->dq, (long long)d->B, (int)d->T, (int)d->Hq, D, (long long)d->dq_stride_b,

@@ -19,6 +19,7 @@
 // Replaces the reference's f32 SIMT 128x128x8 SGEMM
 // (crates/incin-backends/src/cuda/ops/kernels/matmul.cu:1-94), which is 2-D
 // only and has no fused epilogue.
+#include <type_traits>
 #include "gemm_common.cuh"
 #include "gemm_pair.cuh"
 
@@ -240,48 +241,55 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_bf16 = make_idesc_bf16(BM, BN, A_MN, B_MN);
-      const bool tf32 = p.in_kind == 2;
-      const uint32_t idesc = p.in_kind == 0 ? idesc_bf16 : idesc_with_format(idesc_bf16, tf32 ? 2u : 0u);
-      int stage = 0;
-      uint32_t phase = 0;
-      int iter = 0;
-      bool ok = true;
-      for (int u = cta; u < p.total_units && ok; u += n_compute, ++iter) {
-        const Unit w = decode_unit(p, u);
-        const int acc = iter & 1;
-        const uint32_t acc_phase = (iter >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
-        for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kStatusTimeoutFull)) {
-            ok = false;
-            break;
-          }
+      // The issuing thread is latency critical (one dependent instruction stream feeding the tensor pipe), so the
+      // operand kind is a compile-time constant of the loop: one copy of the loop per kind, chosen once.
+      auto issue_all = [&](auto kind_tag) {
+        constexpr int KIND = decltype(kind_tag)::value;
+        constexpr uint32_t idesc_bf16 = make_idesc_bf16(BM, BN, A_MN, B_MN);
+        constexpr uint32_t idesc = KIND == 0 ? idesc_bf16 : idesc_with_format(idesc_bf16, KIND == 2 ? 2u : 0u);
+        int stage = 0;
+        uint32_t phase = 0;
+        int iter = 0;
+        bool ok = true;
+        for (int u = cta; u < p.total_units && ok; u += n_compute, ++iter) {
+          const Unit w = decode_unit(p, u);
+          const int acc = iter & 1;
+          const uint32_t acc_phase = (iter >> 1) & 1;
+          if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) break;
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
-          const uint32_t sb = sa + Cfg::A_BYTES;
-          const uint64_t adesc = A_MN ? make_smem_desc(sa, 8192, 1024) : make_smem_desc(sa, 16, 1024);
-          const uint64_t bdesc = B_MN ? make_smem_desc(sb, 8192, 1024) : make_smem_desc(sb, 16, 1024);
+          const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
+          for (int kb = w.kb0; kb < w.kb1; ++kb) {
+            if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kStatusTimeoutFull)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+            const uint32_t sb = sa + Cfg::A_BYTES;
+            const uint64_t adesc = A_MN ? make_smem_desc(sa, 8192, 1024) : make_smem_desc(sa, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc(sb, 8192, 1024) : make_smem_desc(sb, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // K-major: 16 bf16 = 32 B further along the swizzle row.
-            // MN-major: 16 K-rows of 128 B further.
-            const uint64_t a_adv = A_MN ? (uint64_t)(k * 2048 >> 4) : (uint64_t)(k * 32 >> 4);
-            const uint64_t b_adv = B_MN ? (uint64_t)(k * 2048 >> 4) : (uint64_t)(k * 32 >> 4);
-            const uint32_t accum = (kb > w.kb0 || k > 0) ? 1u : 0u;
-            if (tf32) umma_tf32_ss(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, accum);
-            else umma_f16_ss(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, accum);
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              // K-major: 16 bf16 = 32 B further along the swizzle row.
+              // MN-major: 16 K-rows of 128 B further.
+              const uint64_t a_adv = A_MN ? (uint64_t)(k * 2048 >> 4) : (uint64_t)(k * 32 >> 4);
+              const uint64_t b_adv = B_MN ? (uint64_t)(k * 2048 >> 4) : (uint64_t)(k * 32 >> 4);
+              const uint32_t accum = (kb > w.kb0 || k > 0) ? 1u : 0u;
+              if constexpr (KIND == 2) umma_tf32_ss(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, accum);
+              else umma_f16_ss(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, accum);
+            }
+            umma_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
+            if (++stage == Cfg::STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
           }
-          umma_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
-          if (++stage == Cfg::STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
+          if (ok) umma_commit(&tfull_bar[acc]);  // accumulator complete
         }
-        if (ok) umma_commit(&tfull_bar[acc]);  // accumulator complete
-      }
+      };
+      if (p.in_kind == 0) issue_all(std::integral_constant<int, 0>{});
+      else if (p.in_kind == 1) issue_all(std::integral_constant<int, 1>{});
+      else issue_all(std::integral_constant<int, 2>{});
     }
   } else {
     // ------------------------------------------------------------- epilogue (8 warps: 4 lane quarters x 2 column halves)
