@@ -247,6 +247,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         constexpr int KIND = decltype(kind_tag)::value;
         constexpr uint32_t idesc_bf16 = make_idesc_bf16(BM, BN, A_MN, B_MN);
         constexpr uint32_t idesc = KIND == 0 ? idesc_bf16 : idesc_with_format(idesc_bf16, KIND == 2 ? 2u : 0u);
+        // low / high halves of the shared-memory descriptors of stage 0 (LBO 16 for K-major, 8 KB for MN-major operands)
+        const uint64_t a_desc0 = A_MN ? make_smem_desc(smem_u32(smem), 8192, 1024) : make_smem_desc(smem_u32(smem), 16, 1024);
+        const uint32_t a_lo0 = static_cast<uint32_t>(a_desc0), desc_hi = static_cast<uint32_t>(a_desc0 >> 32);
+        constexpr uint32_t lbo_k = (16u >> 4) << 16, lbo_mn = (8192u >> 4) << 16;
+        const uint32_t b_lo_off = (Cfg::A_BYTES >> 4) + (B_MN ? lbo_mn : lbo_k) - (A_MN ? lbo_mn : lbo_k);
         int stage = 0;
         uint32_t phase = 0;
         int iter = 0;
@@ -263,20 +268,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               ok = false;
               break;
             }
-            tc_fence_after();
-            const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
-            const uint32_t sb = sa + Cfg::A_BYTES;
-            const uint64_t adesc = A_MN ? make_smem_desc(sa, 8192, 1024) : make_smem_desc(sa, 16, 1024);
-            const uint64_t bdesc = B_MN ? make_smem_desc(sb, 8192, 1024) : make_smem_desc(sb, 16, 1024);
+            if constexpr (KIND == 2) {
+              const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+              const uint32_t sb = sa + Cfg::A_BYTES;
+              const uint64_t adesc = make_smem_desc(sa, 16, 1024), bdesc = make_smem_desc(sb, 16, 1024);
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k) {
-              // K-major: 16 bf16 = 32 B further along the swizzle row.
-              // MN-major: 16 K-rows of 128 B further.
-              const uint64_t a_adv = A_MN ? (uint64_t)(k * 2048 >> 4) : (uint64_t)(k * 32 >> 4);
-              const uint64_t b_adv = B_MN ? (uint64_t)(k * 2048 >> 4) : (uint64_t)(k * 32 >> 4);
-              const uint32_t accum = (kb > w.kb0 || k > 0) ? 1u : 0u;
-              if constexpr (KIND == 2) umma_tf32_ss(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, accum);
-              else umma_f16_ss(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, accum);
+              for (int k = 0; k < BK / UMMA_K; ++k)
+                umma_tf32_ss(d_tmem, adesc + (uint64_t)(k * 32 >> 4), bdesc + (uint64_t)(k * 32 >> 4), idesc,
+                             (kb > w.kb0 || k > 0) ? 1u : 0u);
+            } else {
+              // descriptors: high halves are constants of the kernel, the low half is the stage's address field plus
+              // the step inside the k-block (K-major: 16 elements = 32 B along the swizzle row; MN-major: 16 rows of
+              // 128 B)
+              const uint32_t a_lo = a_lo0 + stage * (Cfg::STAGE_BYTES >> 4), b_lo = a_lo + b_lo_off;
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k)
+                umma_f16_ss_lohi(d_tmem, a_lo + (A_MN ? (k * 2048 >> 4) : (k * 32 >> 4)), desc_hi,
+                                 b_lo + (B_MN ? (k * 2048 >> 4) : (k * 32 >> 4)), desc_hi, idesc,
+                                 (kb > w.kb0 || k > 0) ? 1u : 0u);
             }
             umma_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
             if (++stage == Cfg::STAGES) {
