@@ -306,19 +306,35 @@ norm_bwd_param_partial_vec(const __nv_bfloat16* __restrict__ dy, const __nv_bflo
   }
 }
 
-// Stage 2: 32 columns x 8 chunk lanes per block.  Each thread adds every 8th partial (independent, coalesced loads),
-// then the 8 lanes of a column are combined in a fixed order, so the result does not depend on scheduling.
-__global__ void __launch_bounds__(256)
+// Stage 2: 32 columns x 32 chunk lanes per block.  Each thread adds every 32nd partial (independent, coalesced loads,
+// four in flight), then the 32 lanes of a column are combined in a fixed order, so the result does not depend on
+// scheduling.
+constexpr int PF_LANES = 32;
+__global__ void __launch_bounds__(32 * PF_LANES)
 norm_bwd_param_final(const float* __restrict__ scratch, float* __restrict__ dgamma, float* __restrict__ dbeta, int C,
                      int chunks) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float sa[8][33], sb[8][33];
+  __shared__ float sa[PF_LANES][33], sb[PF_LANES][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + tx;
   float a = 0.f, b = 0.f;
   if (c < C) {
-    for (int k = ty; k < chunks; k += 8) {
+    int k = ty;
+    for (; k + 3 * PF_LANES < chunks; k += 4 * PF_LANES) {
+      float va[4], vb[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        va[u] = scratch[((long long)(k + u * PF_LANES) * 2 + 0) * C + c];
+        vb[u] = scratch[((long long)(k + u * PF_LANES) * 2 + 1) * C + c];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        a += va[u];
+        b += vb[u];
+      }
+    }
+    for (; k < chunks; k += PF_LANES) {
       a += scratch[((long long)k * 2 + 0) * C + c];
       b += scratch[((long long)k * 2 + 1) * C + c];
     }
@@ -328,7 +344,7 @@ norm_bwd_param_final(const float* __restrict__ scratch, float* __restrict__ dgam
   __syncthreads();
   if (ty == 0 && c < C) {
 #pragma unroll
-    for (int t = 1; t < 8; ++t) {
+    for (int t = 1; t < PF_LANES; ++t) {
       a += sa[t][tx];
       b += sb[t][tx];
     }
@@ -337,7 +353,145 @@ norm_bwd_param_final(const float* __restrict__ scratch, float* __restrict__ dgam
   }
 }
 
-static int param_chunks(long long rows) {
+// ----------------------------------------------------------------------------- backward: dx and stage 1 in one pass
+// For C <= 1024 (C % 8 == 0) a warp keeps its whole row of x and dy in registers, so dx and the per-column partial
+// sums of dgamma / dbeta come out of ONE read of x and dy: block b owns rows [b * rows_per, ...), its 8 warps take every
+// 8th row and add d * xhat and d into per-lane column accumulators, which are then combined in warp order (fixed, so
+// the result does not depend on scheduling) and written to scratch[b][{g,b}][C] for norm_bwd_param_final.
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = unpack_bf16x2(w[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+// The row is held as the raw 16-byte loads (bf16) and unpacked where it is used, which keeps the kernel at two
+// blocks per SM (the fp32 column accumulators already take 16 registers per 8 columns).
+template <bool RMS, int ITER>
+__global__ void __launch_bounds__(NORM_WARPS * 32, ITER <= 3 ? 2 : 1)
+norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                      const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dx_add,
+                      __nv_bfloat16* __restrict__ dx, float* __restrict__ scratch, long long rows, int C,
+                      long long rows_per) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float sred[2][ITER * 256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long r0 = (long long)blockIdx.x * rows_per;
+  const long long r1 = r0 + rows_per < rows ? r0 + rows_per : rows;
+  uint4 graw[ITER];
+  float gacc[ITER][8], bacc[ITER][8];
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+    const int c = it * 256 + lane * 8;
+    graw[it] = c < C ? *reinterpret_cast<const uint4*>(gamma + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      gacc[it][i] = 0.f;
+      bacc[it][i] = 0.f;
+    }
+  }
+  const float inv_c = 1.f / C;
+  for (long long r = r0 + warp; r < r1; r += NORM_WARPS) {
+    const float mean = RMS ? 0.f : mean_in[r];
+    const float rstd = rstd_in[r];
+    uint4 xraw[ITER], draw[ITER];
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const int c = it * 256 + lane * 8;
+      const bool in = c < C;
+      xraw[it] = in ? *reinterpret_cast<const uint4*>(x + r * C + c) : make_uint4(0, 0, 0, 0);
+      draw[it] = in ? *reinterpret_cast<const uint4*>(dy + r * C + c) : make_uint4(0, 0, 0, 0);   // d = 0 past C
+    }
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      float f[8], d[8], g[8];
+      unpack8(xraw[it], f);
+      unpack8(draw[it], d);
+      unpack8(graw[it], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = (f[i] - mean) * rstd;
+        const float gd = g[i] * d[i];
+        s1 += gd;
+        s2 += gd * xh;
+        gacc[it][i] += d[i] * xh;
+        bacc[it][i] += d[i];
+      }
+    }
+    s1 = RMS ? 0.f : warp_sum(s1) * inv_c;
+    s2 = warp_sum(s2) * inv_c;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const int c = it * 256 + lane * 8;
+      if (c < C) {
+        float f[8], d[8], g[8], o[8];
+        unpack8(xraw[it], f);
+        unpack8(draw[it], d);
+        unpack8(graw[it], g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (g[i] * d[i] - s1 - (f[i] - mean) * rstd * s2);
+        if (dx_add) {
+          float a[8];
+          load8(dx_add + r * C + c, a);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += a[i];
+        }
+        store8(dx + r * C + c, o);
+      }
+    }
+  }
+  // combine the 8 warps in warp order; element (it, lane, i) lives at it*256 + i*32 + lane so that a warp touches 32
+  // different banks
+  for (int w = 0; w < NORM_WARPS; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int it = 0; it < ITER; ++it)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int j = it * 256 + i * 32 + lane;
+          if (w == 0) {
+            sred[0][j] = gacc[it][i];
+            sred[1][j] = bacc[it][i];
+          } else {
+            sred[0][j] += gacc[it][i];
+            sred[1][j] += bacc[it][i];
+          }
+        }
+    }
+    __syncthreads();
+  }
+  for (int j = threadIdx.x; j < ITER * 256; j += NORM_WARPS * 32) {
+    const int c = (j & ~255) + (j & 31) * 8 + ((j >> 5) & 7);
+    if (c < C) {
+      scratch[((long long)blockIdx.x * 2 + 0) * C + c] = sred[0][j];
+      scratch[((long long)blockIdx.x * 2 + 1) * C + c] = sred[1][j];
+    }
+  }
+}
+
+static bool fused_bwd_ok(int C) { return (C % 8) == 0 && C <= 1024; }
+
+// blocks of the fused kernel = partial sums per column: one wave of two blocks per SM, within the 4 MiB of partial
+// sums the allocation-free entry point owns
+static long long fused_rows_per(long long rows, int C) {
+  long long blocks = (rows + NORM_WARPS - 1) / NORM_WARPS;
+  long long cap = (1ll << 20) / (2ll * C);
+  if (cap > 296) cap = 296;   // two blocks per SM: one wave
+  if (blocks > cap) blocks = cap;
+  return (rows + blocks - 1) / blocks;
+}
+
+static int param_chunks(long long rows, int C) {
+  if (fused_bwd_ok(C)) {
+    const long long rp = fused_rows_per(rows, C);
+    return (int)((rows + rp - 1) / rp);
+  }
   long long c = (rows + 127) / 128;
   if (c > 64) c = 64;
   if (c < 1) c = 1;
@@ -349,13 +503,29 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, con
                            const void* dx_add, void* dx, float* dgamma, float* dbeta, float* scratch, long long rows,
                            int C, cudaStream_t s) {
   if (rows <= 0 || C <= 0) return INCIN_ERR_ARGUMENT;
+  if (dgamma && fused_bwd_ok(C)) {
+    if (!scratch) return INCIN_ERR_ARGUMENT;
+    const long long rp = fused_rows_per(rows, C);
+    const int chunks = param_chunks(rows, C);
+    const int iters = (C + 255) / 256;
+    auto go = [&](auto kern) {
+      launch_pdl(kern, dim3((unsigned)chunks), dim3(NORM_WARPS * 32), 0, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                 (const __nv_bfloat16*)gamma, mean, rstd, (const __nv_bfloat16*)dx_add, (__nv_bfloat16*)dx, scratch, rows, C, rp);
+    };
+    if (iters == 1) go(norm_bwd_fused_kernel<RMS, 1>);
+    else if (iters == 2) go(norm_bwd_fused_kernel<RMS, 2>);
+    else if (iters == 3) go(norm_bwd_fused_kernel<RMS, 3>);
+    else go(norm_bwd_fused_kernel<RMS, 4>);
+    launch_pdl(norm_bwd_param_final, dim3((C + 31) / 32), dim3(32 * PF_LANES), 0, s, scratch, dgamma, dbeta, C, chunks);
+    return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
+  }
   const unsigned blocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
   launch_pdl(norm_bwd_dx_kernel<RMS>, dim3(blocks), dim3(NORM_WARPS * 32), 0, s, 
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd,
       (const __nv_bfloat16*)dx_add, (__nv_bfloat16*)dx, rows, C);
   if (dgamma) {
     if (!scratch) return INCIN_ERR_ARGUMENT;
-    const int chunks = param_chunks(rows);
+    const int chunks = param_chunks(rows, C);
     if ((C % 8) == 0) {
       dim3 grid((C + 255) / 256, chunks);
       launch_pdl(norm_bwd_param_partial_vec<RMS>, dim3(grid), dim3(256), 0, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, mean,
@@ -365,7 +535,7 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, con
       launch_pdl(norm_bwd_param_partial<RMS>, dim3(grid), dim3(32 * PG_TY), 0, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                                mean, rstd, scratch, rows, C, chunks);
     }
-    launch_pdl(norm_bwd_param_final, dim3((C + 31) / 32), dim3(256), 0, s, scratch, dgamma, dbeta, C, chunks);
+    launch_pdl(norm_bwd_param_final, dim3((C + 31) / 32), dim3(32 * PF_LANES), 0, s, scratch, dgamma, dbeta, C, chunks);
   }
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
@@ -394,7 +564,7 @@ extern "C" int incin_rmsnorm_fwd(const void* x, const void* gamma, void* y, floa
 }
 
 extern "C" long long incin_layernorm_bwd_scratch_floats(long long rows, int C) {
-  return (long long)param_chunks(rows) * 2 * C;
+  return (long long)param_chunks(rows, C) * 2 * C;
 }
 
 extern "C" int incin_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,

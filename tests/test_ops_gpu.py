@@ -19,7 +19,7 @@ def close(a, b, tol=2e-2):
     assert err <= tol * (b.abs().max().item() + 1e-6), f"err {err}"
 
 
-@pytest.mark.parametrize("rows,C", [(64, 768), (333, 1024), (17, 100), (8, 4096)])
+@pytest.mark.parametrize("rows,C", [(64, 768), (333, 1024), (17, 100), (8, 4096), (5000, 768), (3, 264)])
 def test_layernorm_fwd_bwd(rows, C):
     from incin_b200.ops import kernels as K
     x, g, b, dy, add = rnd((rows, C), 1), rnd((C,), 2), rnd((C,), 3), rnd((rows, C), 4), rnd((rows, C), 5)
@@ -37,7 +37,7 @@ def test_layernorm_fwd_bwd(rows, C):
     close(db, bf.grad)
 
 
-@pytest.mark.parametrize("rows,C", [(64, 2048), (33, 96)])
+@pytest.mark.parametrize("rows,C", [(64, 2048), (33, 96), (3000, 512)])
 def test_rmsnorm_fwd_bwd(rows, C):
     from incin_b200.ops import kernels as K
     x, g, dy = rnd((rows, C), 1), rnd((C,), 2), rnd((rows, C), 4)
