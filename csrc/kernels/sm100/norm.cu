@@ -42,6 +42,16 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
   *reinterpret_cast<uint4*>(p) = u;
 }
 
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = unpack_bf16x2(w[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
 // ----------------------------------------------------------------------------- forward
 template <bool RMS>
 __global__ void __launch_bounds__(NORM_WARPS * 32)
@@ -116,6 +126,94 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
       if (beta) o += __bfloat162float(beta[c]);
       yr[c] = __float2bfloat16(o);
     }
+  }
+}
+
+// Forward for C <= 1024 (C % 8 == 0): the row is read once with all its 16-byte loads in flight and stays packed in
+// registers for the mean, the centred variance and the output.
+template <bool RMS, int ITER>
+__global__ void __launch_bounds__(NORM_WARPS * 32)
+norm_fwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                    const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
+                    float* __restrict__ rstd_out, long long rows, int C, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  uint4 raw[ITER];
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+    const int c = it * 256 + lane * 8;
+    raw[it] = c < C ? *reinterpret_cast<const uint4*>(x + row * C + c) : make_uint4(0, 0, 0, 0);
+  }
+  const float inv_c = 1.f / C;
+  float mean = 0.f;
+  if (!RMS) {
+    float s = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      float f[8];
+      unpack8(raw[it], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += f[i];
+    }
+    mean = warp_sum(s) * inv_c;
+  }
+  float q = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+    if (it * 256 + lane * 8 < C) {
+      float f[8];
+      unpack8(raw[it], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float d = f[i] - mean;
+        q += d * d;
+      }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(q) * inv_c + eps);
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+    const int c = it * 256 + lane * 8;
+    if (c < C) {
+      float f[8], g[8], o[8];
+      unpack8(raw[it], f);
+      load8(gamma + c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = (f[i] - mean) * rstd * g[i];
+      if (beta) {
+        float b[8];
+        load8(beta + c, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += b[i];
+      }
+      store8(y + row * C + c, o);
+    }
+  }
+}
+
+template <bool RMS>
+static void norm_fwd_launch(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                            long long rows, int C, float eps, cudaStream_t s) {
+  const unsigned blocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
+  auto go = [&](auto kern) {
+    launch_pdl(kern, dim3(blocks), dim3(NORM_WARPS * 32), 0, s, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma,
+               (const __nv_bfloat16*)beta, (__nv_bfloat16*)y, mean, rstd, rows, C, eps);
+  };
+  if ((C % 8) == 0 && C <= 1024) {
+    const int iters = (C + 255) / 256;
+    if (iters == 1) go(norm_fwd_reg_kernel<RMS, 1>);
+    else if (iters == 2) go(norm_fwd_reg_kernel<RMS, 2>);
+    else if (iters == 3) go(norm_fwd_reg_kernel<RMS, 3>);
+    else go(norm_fwd_reg_kernel<RMS, 4>);
+  } else {
+    go(norm_fwd_kernel<RMS>);
   }
 }
 
@@ -358,20 +456,11 @@ norm_bwd_param_final(const float* __restrict__ scratch, float* __restrict__ dgam
 // sums of dgamma / dbeta come out of ONE read of x and dy: block b owns rows [b * rows_per, ...), its 8 warps take every
 // 8th row and add d * xhat and d into per-lane column accumulators, which are then combined in warp order (fixed, so
 // the result does not depend on scheduling) and written to scratch[b][{g,b}][C] for norm_bwd_param_final.
-__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
-  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = unpack_bf16x2(w[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-
-// The row is held as the raw 16-byte loads (bf16) and unpacked where it is used, which keeps the kernel at two
-// blocks per SM (the fp32 column accumulators already take 16 registers per 8 columns).
+// The row is held as the raw 16-byte loads (bf16) and unpacked where it is used; the per-column accumulators of each
+// warp live in shared memory (element (it, i, lane) at it*256 + i*32 + lane: a warp touches 32 different banks), which
+// keeps the kernel under 85 registers so that three blocks (24 warps) per SM have loads in flight.
 template <bool RMS, int ITER>
-__global__ void __launch_bounds__(NORM_WARPS * 32, ITER <= 3 ? 2 : 1)
+__global__ void __launch_bounds__(NORM_WARPS * 32, 3)
 norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                       const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
                       const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dx_add,
@@ -379,22 +468,19 @@ norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
                       long long rows_per) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float sred[2][ITER * 256];
+  extern __shared__ float acc_smem[];                     // [NORM_WARPS][2][ITER * 256]
+  constexpr int W = ITER * 256;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* gacc = acc_smem + (warp * 2 + 0) * W;
+  float* bacc = acc_smem + (warp * 2 + 1) * W;
+#pragma unroll
+  for (int j = lane; j < W; j += 32) {
+    gacc[j] = 0.f;
+    bacc[j] = 0.f;
+  }
+  __syncwarp();
   const long long r0 = (long long)blockIdx.x * rows_per;
   const long long r1 = r0 + rows_per < rows ? r0 + rows_per : rows;
-  uint4 graw[ITER];
-  float gacc[ITER][8], bacc[ITER][8];
-#pragma unroll
-  for (int it = 0; it < ITER; ++it) {
-    const int c = it * 256 + lane * 8;
-    graw[it] = c < C ? *reinterpret_cast<const uint4*>(gamma + c) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      gacc[it][i] = 0.f;
-      bacc[it][i] = 0.f;
-    }
-  }
   const float inv_c = 1.f / C;
   for (long long r = r0 + warp; r < r1; r += NORM_WARPS) {
     const float mean = RMS ? 0.f : mean_in[r];
@@ -410,18 +496,24 @@ norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int it = 0; it < ITER; ++it) {
+      const int c = it * 256 + lane * 8;
       float f[8], d[8], g[8];
       unpack8(xraw[it], f);
       unpack8(draw[it], d);
-      unpack8(graw[it], g);
+      if (c < C) {
+        load8(gamma + c, g);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) g[i] = 0.f;
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float xh = (f[i] - mean) * rstd;
         const float gd = g[i] * d[i];
         s1 += gd;
         s2 += gd * xh;
-        gacc[it][i] += d[i] * xh;
-        bacc[it][i] += d[i];
+        gacc[it * 256 + i * 32 + lane] += d[i] * xh;
+        bacc[it * 256 + i * 32 + lane] += d[i];
       }
     }
     s1 = RMS ? 0.f : warp_sum(s1) * inv_c;
@@ -433,7 +525,7 @@ norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
         float f[8], d[8], g[8], o[8];
         unpack8(xraw[it], f);
         unpack8(draw[it], d);
-        unpack8(graw[it], g);
+        load8(gamma + c, g);
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = rstd * (g[i] * d[i] - s1 - (f[i] - mean) * rstd * s2);
         if (dx_add) {
@@ -446,43 +538,31 @@ norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
       }
     }
   }
-  // combine the 8 warps in warp order; element (it, lane, i) lives at it*256 + i*32 + lane so that a warp touches 32
-  // different banks
-  for (int w = 0; w < NORM_WARPS; ++w) {
-    if (warp == w) {
-#pragma unroll
-      for (int it = 0; it < ITER; ++it)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int j = it * 256 + i * 32 + lane;
-          if (w == 0) {
-            sred[0][j] = gacc[it][i];
-            sred[1][j] = bacc[it][i];
-          } else {
-            sred[0][j] += gacc[it][i];
-            sred[1][j] += bacc[it][i];
-          }
-        }
-    }
-    __syncthreads();
-  }
-  for (int j = threadIdx.x; j < ITER * 256; j += NORM_WARPS * 32) {
+  __syncthreads();
+  // the 8 warps' accumulators are added in warp order
+  for (int j = threadIdx.x; j < W; j += NORM_WARPS * 32) {
     const int c = (j & ~255) + (j & 31) * 8 + ((j >> 5) & 7);
     if (c < C) {
-      scratch[((long long)blockIdx.x * 2 + 0) * C + c] = sred[0][j];
-      scratch[((long long)blockIdx.x * 2 + 1) * C + c] = sred[1][j];
+      float a = 0.f, bsum = 0.f;
+#pragma unroll
+      for (int w = 0; w < NORM_WARPS; ++w) {
+        a += acc_smem[(w * 2 + 0) * W + j];
+        bsum += acc_smem[(w * 2 + 1) * W + j];
+      }
+      scratch[((long long)blockIdx.x * 2 + 0) * C + c] = a;
+      scratch[((long long)blockIdx.x * 2 + 1) * C + c] = bsum;
     }
   }
 }
 
 static bool fused_bwd_ok(int C) { return (C % 8) == 0 && C <= 1024; }
 
-// blocks of the fused kernel = partial sums per column: one wave of two blocks per SM, within the 4 MiB of partial
+// blocks of the fused kernel = partial sums per column: one wave of three blocks per SM, within the 4 MiB of partial
 // sums the allocation-free entry point owns
 static long long fused_rows_per(long long rows, int C) {
   long long blocks = (rows + NORM_WARPS - 1) / NORM_WARPS;
   long long cap = (1ll << 20) / (2ll * C);
-  if (cap > 296) cap = 296;   // two blocks per SM: one wave
+  if (cap > 444) cap = 444;   // three blocks per SM: one wave
   if (blocks > cap) blocks = cap;
   return (rows + blocks - 1) / blocks;
 }
@@ -508,8 +588,14 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, con
     const long long rp = fused_rows_per(rows, C);
     const int chunks = param_chunks(rows, C);
     const int iters = (C + 255) / 256;
+    const size_t acc_bytes = (size_t)NORM_WARPS * 2 * iters * 256 * sizeof(float);   // 16 KB per 256 columns
+    static bool attr_set[5] = {false, false, false, false, false};   // per kernel (RMS is a template argument here)
     auto go = [&](auto kern) {
-      launch_pdl(kern, dim3((unsigned)chunks), dim3(NORM_WARPS * 32), 0, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+      if (!attr_set[iters]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)acc_bytes) != cudaSuccess) return;
+        attr_set[iters] = true;
+      }
+      launch_pdl(kern, dim3((unsigned)chunks), dim3(NORM_WARPS * 32), acc_bytes, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                  (const __nv_bfloat16*)gamma, mean, rstd, (const __nv_bfloat16*)dx_add, (__nv_bfloat16*)dx, scratch, rows, C, rp);
     };
     if (iters == 1) go(norm_bwd_fused_kernel<RMS, 1>);
@@ -547,19 +633,14 @@ using namespace incin;
 extern "C" int incin_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
                                    float* rstd, long long rows, int C, float eps, void* stream) {
   if (rows <= 0 || C <= 0 || !x || !gamma || !y || !rstd) return INCIN_ERR_ARGUMENT;
-  const unsigned blocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
-  launch_pdl(norm_fwd_kernel<false>, dim3(blocks), dim3(NORM_WARPS * 32), 0, (cudaStream_t)stream, 
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, (const __nv_bfloat16*)beta, (__nv_bfloat16*)y, mean, rstd,
-      rows, C, eps);
+  norm_fwd_launch<false>(x, gamma, beta, y, mean, rstd, rows, C, eps, (cudaStream_t)stream);
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
 
 extern "C" int incin_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd, long long rows, int C,
                                  float eps, void* stream) {
   if (rows <= 0 || C <= 0 || !x || !gamma || !y || !rstd) return INCIN_ERR_ARGUMENT;
-  const unsigned blocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
-  launch_pdl(norm_fwd_kernel<true>, dim3(blocks), dim3(NORM_WARPS * 32), 0, (cudaStream_t)stream, 
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, nullptr, (__nv_bfloat16*)y, nullptr, rstd, rows, C, eps);
+  norm_fwd_launch<true>(x, gamma, nullptr, y, nullptr, rstd, rows, C, eps, (cudaStream_t)stream);
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
 

@@ -140,6 +140,10 @@ def bench_bandwidth(args) -> None:
         print(json.dumps(r), flush=True)
 
     rec("layernorm_fwd 8192x768", timeit(lambda: K.layernorm_fwd(x, g, b, 1e-5)), 2 * x.numel() * 2)
+    ys, means, rstds = K.layernorm_fwd(x, g, b, 1e-5)
+    dgs, dbs = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+    rec("layernorm_bwd 8192x768 (+residual gradient)",
+        timeit(lambda: K.layernorm_bwd(ys, x, g, means, rstds, ys, dgs, dbs)), 4 * x.numel() * 2)
     rec("layernorm_fwd 65536x4096", timeit(lambda: K.layernorm_fwd(xb, gb, None, 1e-5)), 2 * xb.numel() * 2)
     y, mean, rstd = K.layernorm_fwd(xb, gb, None, 1e-5)
     dg = torch.zeros(big_c, device="cuda")
