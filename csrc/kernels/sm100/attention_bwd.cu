@@ -443,7 +443,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // LPR 16-byte loads, one per lane of a group of LPR = D / 8 lanes; every group takes DELTA_ROWS rows with all their
 // loads issued before the first is used, so that a thread keeps 2 x DELTA_ROWS 16-byte loads in flight.
 constexpr int DELTA_ROWS = 4;
-template <int LPR>
+// IDX is the type of the row / element counters: 32-bit whenever the problem allows, because the 64-bit divisions that
+// split a counter into (b, t, h) otherwise cost more than the loads.
+template <int LPR, typename IDX>
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
                   long long B, int T, int Tpad, int H, long long o_sb, long long o_st, long long o_sh,
@@ -452,24 +454,35 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
   pdl_wait();
   constexpr int GROUPS = 256 / LPR;                       // row groups per block
   const int sub = threadIdx.x % LPR;
-  const long long total = B * Tpad * H;
-  const long long first = ((long long)blockIdx.x * GROUPS + threadIdx.x / LPR) * DELTA_ROWS;
+  const IDX total = (IDX)(B * Tpad * H);
+  const IDX first = ((IDX)blockIdx.x * GROUPS + threadIdx.x / LPR) * DELTA_ROWS;
+  // (b, t, h) of the first row; the following rows step h, then t, then b
+  int h0 = (int)(first % (IDX)H);
+  int t0 = (int)((first / (IDX)H) % (IDX)Tpad);
+  long long b0 = (long long)(first / ((IDX)H * (IDX)Tpad));
   uint4 a[DELTA_ROWS], c[DELTA_ROWS];
+  {
+    int h = h0, t = t0;
+    long long b = b0;
 #pragma unroll
-  for (int r = 0; r < DELTA_ROWS; ++r) {
-    const long long w = first + r;
-    a[r] = make_uint4(0, 0, 0, 0);
-    c[r] = make_uint4(0, 0, 0, 0);
-    if (w < total) {
-      const int h = (int)(w % H);
-      const int t = (int)((w / H) % Tpad);
-      const long long b = w / ((long long)H * Tpad);
-      if (t < T) {
+    for (int r = 0; r < DELTA_ROWS; ++r) {
+      a[r] = make_uint4(0, 0, 0, 0);
+      c[r] = make_uint4(0, 0, 0, 0);
+      if (first + (IDX)r < total && t < T) {
         a[r] = *reinterpret_cast<const uint4*>(o + b * o_sb + (long long)t * o_st + (long long)h * o_sh + sub * 8);
         c[r] = *reinterpret_cast<const uint4*>(d_o + b * do_sb + (long long)t * do_st + (long long)h * do_sh + sub * 8);
       }
+      if (++h == H) {
+        h = 0;
+        if (++t == Tpad) {
+          t = 0;
+          ++b;
+        }
+      }
     }
   }
+  int h = h0, t = t0;
+  long long b = b0;
 #pragma unroll
   for (int r = 0; r < DELTA_ROWS; ++r) {
     const uint32_t ua[4] = {a[r].x, a[r].y, a[r].z, a[r].w}, uc[4] = {c[r].x, c[r].y, c[r].z, c[r].w};
@@ -481,31 +494,35 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
     }
 #pragma unroll
     for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    const long long w = first + r;
-    if (sub == 0 && w < total) {
-      const int h = (int)(w % H);
-      const int t = (int)((w / H) % Tpad);
-      const long long b = w / ((long long)H * Tpad);
-      delta[(b * H + h) * Tpad + t] = s;
+    if (sub == 0 && first + (IDX)r < total) delta[(b * H + h) * Tpad + t] = s;
+    if (++h == H) {
+      h = 0;
+      if (++t == Tpad) {
+        t = 0;
+        ++b;
+      }
     }
   }
 }
 
 // dq (bf16, strided) = dq_accum (fp32 [B,T,H,D] contiguous); 8 elements (two 16-byte loads, one 16-byte store) per
 // thread and step, two steps in flight
+template <typename IDX>
 __global__ void __launch_bounds__(256)
 attn_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long B, int T,
                     int H, int D, long long sb, long long st, long long sh) {
   pdl_launch_dependents();
   pdl_wait();
-  const long long n8 = B * T * H * D / 8;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  auto store = [&](long long i, const float4& v0, const float4& v1) {
-    const long long e = i * 8;
-    const int d = (int)(e % D);
-    const int h = (int)((e / D) % H);
-    const int t = (int)((e / ((long long)D * H)) % T);
-    const long long b = e / ((long long)D * H * T);
+  const IDX n8 = (IDX)(B * T * H * D / 8);
+  const IDX stride = (IDX)gridDim.x * blockDim.x;
+  const IDX d8 = (IDX)(D / 8);
+  auto store = [&](IDX i, const float4& v0, const float4& v1) {
+    const int d = (int)(i % d8) * 8;
+    const IDX row = i / d8;                       // (b, t, h)
+    const int h = (int)(row % (IDX)H);
+    const IDX bt = row / (IDX)H;
+    const int t = (int)(bt % (IDX)T);
+    const long long b = (long long)(bt / (IDX)T);
     uint4 o;
     o.x = pack_bf16x2(v0.x, v0.y);
     o.y = pack_bf16x2(v0.z, v0.w);
@@ -514,14 +531,14 @@ attn_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ d
     *reinterpret_cast<uint4*>(dq + b * sb + (long long)t * st + (long long)h * sh + d) = o;
   };
   const float4* src = reinterpret_cast<const float4*>(acc);
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x;
   for (; i + stride < n8; i += 2 * stride) {
-    const float4 a0 = src[2 * i], a1 = src[2 * i + 1];
-    const float4 b0 = src[2 * (i + stride)], b1 = src[2 * (i + stride) + 1];
+    const float4 a0 = src[2 * (long long)i], a1 = src[2 * (long long)i + 1];
+    const float4 b0 = src[2 * (long long)(i + stride)], b1 = src[2 * (long long)(i + stride) + 1];
     store(i, a0, a1);
     store(i + stride, b0, b1);
   }
-  if (i < n8) store(i, src[2 * i], src[2 * i + 1]);
+  if (i < n8) store(i, src[2 * (long long)i], src[2 * (long long)i + 1]);
 }
 
 // Where the backward spends its time: with INCIN_ATTN_PROF=1 the head_dim-64 kernel adds up, per launch, the clock
@@ -577,12 +594,16 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   const long long rows = (long long)d->B * d->T * d->Hq;
   const int Tpad = (d->T + FB_T - 1) / FB_T * FB_T;
   const long long prow = (long long)d->B * Tpad * d->Hq;
+  const bool idx32 = prow * D < (1ll << 30);   // row and element counters (and their strides) fit 32 bits
   {
     constexpr int LPR = D / 8, ROWS_PER_BLOCK = 256 / LPR * DELTA_ROWS;
-    if (launch_pdl(attn_delta_kernel<LPR>, dim3((unsigned)((prow + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK)), dim3(256), 0, stream,
-                   (const __nv_bfloat16*)d->o, (const __nv_bfloat16*)d->d_o, d->delta, (long long)d->B, (int)d->T, Tpad,
-                   (int)d->Hq, (long long)d->o_stride_b, (long long)d->o_stride_t, (long long)d->o_stride_h,
-                   (long long)d->do_stride_b, (long long)d->do_stride_t, (long long)d->do_stride_h) != cudaSuccess)
+    auto go = [&](auto kern) {
+      return launch_pdl(kern, dim3((unsigned)((prow + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK)), dim3(256), 0, stream,
+                        (const __nv_bfloat16*)d->o, (const __nv_bfloat16*)d->d_o, d->delta, (long long)d->B, (int)d->T, Tpad,
+                        (int)d->Hq, (long long)d->o_stride_b, (long long)d->o_stride_t, (long long)d->o_stride_h,
+                        (long long)d->do_stride_b, (long long)d->do_stride_t, (long long)d->do_stride_h);
+    };
+    if ((idx32 ? go(attn_delta_kernel<LPR, unsigned>) : go(attn_delta_kernel<LPR, long long>)) != cudaSuccess)
       return INCIN_ERR_LAUNCH;
   }
   if (cudaMemsetAsync(d->dq_accum, 0, sizeof(float) * rows * D, stream) != cudaSuccess) return INCIN_ERR_LAUNCH;
@@ -618,9 +639,12 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   long long n8 = rows * D / 8;
   long long blocks = (n8 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  if (launch_pdl(attn_dq_cast_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)d->dq_accum,
-                 (__nv_bfloat16*)d->dq, (long long)d->B, (int)d->T, (int)d->Hq, D, (long long)d->dq_stride_b,
-                 (long long)d->dq_stride_t, (long long)d->dq_stride_h) != cudaSuccess)
+  auto cast = [&](auto kern) {
+    return launch_pdl(kern, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)d->dq_accum, (__nv_bfloat16*)d->dq,
+                      (long long)d->B, (int)d->T, (int)d->Hq, D, (long long)d->dq_stride_b, (long long)d->dq_stride_t,
+                      (long long)d->dq_stride_h);
+  };
+  if ((idx32 ? cast(attn_dq_cast_kernel<unsigned>) : cast(attn_dq_cast_kernel<long long>)) != cudaSuccess)
     return INCIN_ERR_LAUNCH;
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
