@@ -90,6 +90,9 @@ typedef struct incin_gemm_desc {
    * as tf32; K-contiguous operands only, lda / ldb multiples of 4).  The last two require out_fp32 and take no fused
    * epilogue (bias, residual, activation), no CTA-pair tile and no fused collective. */
   int in_dtype;
+  /* --- optional device scalar (fp32) multiplied into alpha when the epilogue runs: lets a gradient that only exists
+   * on the GPU (the upstream gradient of a loss) scale a product without a launch of its own. */
+  const void* alpha_ptr;
 } incin_gemm_desc;
 
 enum { INCIN_GEMM_IN_BF16 = 0, INCIN_GEMM_IN_FP16 = 1, INCIN_GEMM_IN_TF32 = 2 };
@@ -129,6 +132,11 @@ int incin_xent_fwd(const void* logits, const int64_t* targets, float* loss, floa
 /* dlogits = (softmax - onehot) * (*dloss) * scale, written in place over logits (columns >= V get 0) */
 int incin_xent_bwd(void* logits, const int64_t* targets, const float* lse, const float* dloss, float scale,
                    long long rows, int V, long long ld, void* stream);
+/* loss, log-sum-exp and gradient in one launch: logits are overwritten by (softmax - onehot) * scale (columns >= V get
+ * 0, rows whose target is out of range get 0); the upstream gradient of the loss is left to the consumer
+ * (incin_gemm_desc.alpha_ptr). */
+int incin_xent_fused(void* logits, const int64_t* targets, float* loss, float* lse, float scale, long long rows, int V,
+                     long long ld, void* stream);
 /* out[0] = mean(x[0..n)) : deterministic single-block tree reduction */
 int incin_mean_f32(const float* x, float* out, long long n, void* stream);
 

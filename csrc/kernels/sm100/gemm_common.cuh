@@ -32,6 +32,7 @@ struct GemmKernelParams {
   long long ldc, c_stride_lo, c_stride_hi;
   int out_fp32, accumulate;
   float alpha;
+  const float* alpha_ptr;   // optional device scalar multiplied into alpha (an upstream gradient that lives on the GPU)
   const __nv_bfloat16* bias;
   const __nv_bfloat16* residual;
   int act;
@@ -94,10 +95,10 @@ __device__ __forceinline__ Unit decode_unit(const GemmKernelParams& p, int u) {
 // starting at column nc.  alpha, bias, GELU / SiLU (+ pre-activation side output), activation-gradient masks,
 // residual, then a bf16 or fp32 store (plain, read-modify-write, or atomic for split-K).
 __device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, const uint32_t (&r)[32], void* c_ptr,
-                                               long long cbase, int nc, bool vec_ok) {
+                                               long long cbase, int nc, bool vec_ok, float alpha) {
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
         const bool full = (nc + 32 <= p.N) && vec_ok;
         if (p.bias) {
           if (full) {

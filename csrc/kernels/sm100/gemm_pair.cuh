@@ -184,6 +184,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     // ------------------------------------------------------------- epilogue (8 warps per CTA: 4 lane quarters x 2 halves)
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
+    const float alpha = p.alpha_ptr ? p.alpha * __ldg(p.alpha_ptr) : p.alpha;
     constexpr int CHUNKS_PER_HALF = Cfg::BN / 64;
     const int row_in_tile = quarter * 32 + lane;
     int iter = 0;
@@ -204,7 +205,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * Cfg::ACC_STRIDE + c * 32, r);
         tmem_ld_wait();
         const int nc = n0 + c * 32;
-        if (row_ok && nc < p.N) epilogue_chunk(p, r, p.C, cbase, nc, vec_ok);
+        if (row_ok && nc < p.N) epilogue_chunk(p, r, p.C, cbase, nc, vec_ok, alpha);
         __syncwarp();
       }
       tc_fence_before();

@@ -304,6 +304,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ------------------------------------------------------------- epilogue (8 warps: 4 lane quarters x 2 column halves)
     const int quarter = warp & 3;  // TMEM lanes a warp may touch: 32 * (warp % 4)
     const int half = (warp - 2) >> 2;
+    const float alpha = p.alpha_ptr ? p.alpha * __ldg(p.alpha_ptr) : p.alpha;
     constexpr int CHUNKS_PER_HALF = BN / 64;
     const int row_in_tile = quarter * 32 + lane;
     int iter = 0;
@@ -335,7 +336,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * Cfg::ACC_STRIDE + c * 32, r);
         tmem_ld_wait();
         const int nc = n0 + c * 32;
-        if (row_ok && nc < p.N) epilogue_chunk(p, r, c_ptr, cbase, nc, vec_ok);
+        if (row_ok && nc < p.N) epilogue_chunk(p, r, c_ptr, cbase, nc, vec_ok, alpha);
         __syncwarp();  // tcgen05.ld is warp-collective: reconverge before the next chunk
       }
       tc_fence_before();
@@ -642,6 +643,7 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   p.out_fp32 = d->out_fp32;
   p.accumulate = d->accumulate;
   p.alpha = d->alpha;
+  p.alpha_ptr = reinterpret_cast<const float*>(d->alpha_ptr);
   p.bias = reinterpret_cast<const __nv_bfloat16*>(d->bias);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(d->residual);
   p.act = d->act;

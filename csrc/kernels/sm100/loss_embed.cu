@@ -106,15 +106,9 @@ __global__ void embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dout, con
 // ----------------------------------------------------------------------------- cross entropy
 constexpr int XENT_THREADS = 512;
 
-__global__ void __launch_bounds__(XENT_THREADS)
-xent_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
-                float* __restrict__ loss, float* __restrict__ lse_out, int V, long long ld) {
-  pdl_launch_dependents();
-  pdl_wait();
-  __shared__ float sh[32];
-  const long long row = blockIdx.x;
-  const __nv_bfloat16* lr = logits + row * ld;
-  // online log-sum-exp: running max m and sum s of exp(x - m)
+// log-sum-exp of one row, computed by the whole block (online: running max m and sum s of exp(x - m)); every thread
+// returns the same value
+__device__ __forceinline__ float xent_row_lse(const __nv_bfloat16* __restrict__ lr, int V, long long ld, float* sh) {
   float m = -CUDART_INF_F, s = 0.f;
   const bool vec = (ld % 8 == 0);
   if (vec) {
@@ -160,25 +154,12 @@ xent_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __restr
   const float gm = block_max<XENT_THREADS>(m, sh);
   const float part = (m == -CUDART_INF_F) ? 0.f : s * __expf(m - gm);
   const float gs = block_sum<XENT_THREADS>(part, sh);
-  if (threadIdx.x == 0) {
-    const float lse = gm + logf(gs);
-    lse_out[row] = lse;
-    const long long t = targets[row];
-    loss[row] = (t >= 0 && t < V) ? lse - __bfloat162float(lr[t]) : 0.f;  // out-of-range = ignored row
-  }
+  return gm + logf(gs);
 }
 
-__global__ void __launch_bounds__(XENT_THREADS)
-xent_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
-                const float* __restrict__ lse_in, const float* __restrict__ dloss, float scale, int V, long long ld) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const long long row = blockIdx.x;
-  __nv_bfloat16* lr = logits + row * ld;
-  const float lse = lse_in[row];
-  const long long t = targets[row];
-  const bool live = (t >= 0 && t < V);
-  const float g = live ? (dloss ? dloss[0] : 1.f) * scale : 0.f;
+// the row becomes its own gradient: (softmax - onehot(t)) * g, zero in the padding columns [V, ld)
+__device__ __forceinline__ void xent_row_grad(__nv_bfloat16* __restrict__ lr, long long t, float lse, float g, int V,
+                                              long long ld) {
   const int LD = (int)ld;
   if (ld % 8 == 0) {
     for (int c = threadIdx.x * 8; c < LD; c += XENT_THREADS * 8) {
@@ -201,6 +182,56 @@ xent_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ 
       lr[c] = __float2bfloat16(p);
     }
   }
+}
+
+__global__ void __launch_bounds__(XENT_THREADS)
+xent_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
+                float* __restrict__ loss, float* __restrict__ lse_out, int V, long long ld) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float sh[32];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + row * ld;
+  const float lse = xent_row_lse(lr, V, ld, sh);
+  if (threadIdx.x == 0) {
+    lse_out[row] = lse;
+    const long long t = targets[row];
+    loss[row] = (t >= 0 && t < V) ? lse - __bfloat162float(lr[t]) : 0.f;  // out-of-range = ignored row
+  }
+}
+
+__global__ void __launch_bounds__(XENT_THREADS)
+xent_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
+                const float* __restrict__ lse_in, const float* __restrict__ dloss, float scale, int V, long long ld) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long row = blockIdx.x;
+  const long long t = targets[row];
+  const bool live = (t >= 0 && t < V);
+  const float g = live ? (dloss ? dloss[0] : 1.f) * scale : 0.f;
+  xent_row_grad(logits + row * ld, t, lse_in[row], g, V, ld);
+}
+
+// Loss and gradient in one launch: the row is read for its log-sum-exp, read again (from L2: a row is at most a few
+// hundred KB and was just touched by this block) and overwritten by (softmax - onehot) * scale.  The caller applies the
+// upstream gradient of the loss as a device scalar in the GEMMs that consume the row gradients.
+__global__ void __launch_bounds__(XENT_THREADS)
+xent_fused_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets, float* __restrict__ loss,
+                  float* __restrict__ lse_out, float scale, int V, long long ld) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float sh[32];
+  const long long row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  const long long t = targets[row];
+  const bool live = (t >= 0 && t < V);
+  const float lse = xent_row_lse(lr, V, ld, sh);
+  if (threadIdx.x == 0) {
+    lse_out[row] = lse;
+    loss[row] = live ? lse - __bfloat162float(lr[t]) : 0.f;
+  }
+  __syncthreads();   // the target logit has been read before any thread overwrites the row
+  xent_row_grad(lr, t, lse, live ? scale : 0.f, V, ld);
 }
 
 __global__ void __launch_bounds__(1024) mean_kernel(const float* __restrict__ x, float* __restrict__ out, long long n) {
@@ -365,6 +396,14 @@ extern "C" int incin_xent_fwd(const void* logits, const int64_t* targets, float*
   launch_pdl(xent_fwd_kernel, dim3((unsigned)rows), dim3(XENT_THREADS), 0, (cudaStream_t)stream, (const __nv_bfloat16*)logits, targets,
                                                                               loss, lse, V, ld);
   return CHECK_LAUNCH();
+}
+
+extern "C" int incin_xent_fused(void* logits, const int64_t* targets, float* loss, float* lse, float scale,
+                                long long rows, int V, long long ld, void* stream) {
+  if (!logits || !targets || !loss || !lse || rows <= 0 || V <= 0 || ld < V) return INCIN_ERR_ARGUMENT;
+  launch_pdl(xent_fused_kernel, dim3((unsigned)rows), dim3(XENT_THREADS), 0, (cudaStream_t)stream, (__nv_bfloat16*)logits,
+             targets, loss, lse, scale, V, ld);
+  return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
 
 extern "C" int incin_xent_bwd(void* logits, const int64_t* targets, const float* lse, const float* dloss, float scale,

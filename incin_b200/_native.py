@@ -60,7 +60,7 @@ class GemmDesc(C.Structure):
         ("ag_src", c_void_p * 8), ("ag_flags", c_void_p),
         ("rs_world", c_int), ("rs_rank", c_int), ("rs_rows_per_rank", c_int), ("rs_copy_ctas", c_int),
         ("rs_dst", c_void_p * 8), ("rs_slot_stride", c_ll), ("rs_ready", c_void_p),
-        ("in_dtype", c_int),
+        ("in_dtype", c_int), ("alpha_ptr", c_void_p),
     ]
 
 
@@ -77,6 +77,7 @@ _CUDA_SIGS = {
     "incin_embedding_bwd": (c_int, [c_void_p] * 4 + [c_ll, c_int, c_int, c_void_p]),
     "incin_xent_fwd": (c_int, [c_void_p] * 4 + [c_ll, c_int, c_ll, c_void_p]),
     "incin_xent_bwd": (c_int, [c_void_p] * 4 + [c_float, c_ll, c_int, c_ll, c_void_p]),
+    "incin_xent_fused": (c_int, [c_void_p] * 4 + [c_float, c_ll, c_int, c_ll, c_void_p]),
     "incin_mean_f32": (c_int, [c_void_p, c_void_p, c_ll, c_void_p]),
     "incin_causal_softmax_fwd": (c_int, [c_void_p, c_ll, c_int, c_float, c_void_p]),
     "incin_causal_softmax_bwd": (c_int, [c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p]),

@@ -117,7 +117,6 @@ class GPT2(nn.Module):
         for b in self.blocks:
             x = b(x)
         h = F.layer_norm(x, self.lnf_g, self.lnf_b, cfg.ln_eps)
-        logits = F.linear(h, self.wte)  # tied LM head over the padded vocabulary
         if targets is None:
-            return logits[..., : cfg.vocab_size]
-        return F.cross_entropy(logits, targets, cfg.vocab_size)
+            return F.linear(h, self.wte)[..., : cfg.vocab_size]   # tied LM head over the padded vocabulary
+        return F.linear_cross_entropy(h, self.wte, targets, cfg.vocab_size)

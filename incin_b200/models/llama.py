@@ -113,7 +113,6 @@ class Llama(nn.Module):
         for b in self.blocks:
             x = b(x)
         h = F.rms_norm(x, self.final_norm, cfg.rms_eps)
-        logits = F.linear(h, self.lm_head)
         if targets is None:
-            return logits
-        return F.cross_entropy(logits, targets, cfg.vocab_size)
+            return F.linear(h, self.lm_head)
+        return F.linear_cross_entropy(h, self.lm_head, targets, cfg.vocab_size)

@@ -120,8 +120,7 @@ class LlamaTP(nn.Module):
         for b in self.blocks:
             x = b(x, tp, B, T)
         h = F.rms_norm(x, self.final_norm, cfg.rms_eps)
-        logits = F.linear(h, self.lm_head)
-        loss = F.cross_entropy(logits, targets.reshape(-1)[lo:lo + Ml], cfg.vocab_size)
+        loss = F.linear_cross_entropy(h, self.lm_head, targets.reshape(-1)[lo:lo + Ml], cfg.vocab_size)
         return loss * (1.0 / tp.world)
 
 

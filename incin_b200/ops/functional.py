@@ -346,6 +346,44 @@ class _CrossEntropy(torch.autograd.Function):
         return l2.view(ctx.shape), None, None
 
 
+class _LinearCrossEntropy(torch.autograd.Function):
+    """``mean CE(x @ w^T, targets)`` as one op: the logits are produced by the GEMM, turned into per-row losses AND
+    into their own gradient by one kernel (one read and one write of the [rows, vocab] buffer instead of two reads and
+    a write), and the backward scales the two products that consume that gradient by the upstream gradient of the
+    loss, read from the device by their epilogues."""
+
+    @staticmethod
+    def forward(ctx, x, w, targets, V):
+        x2 = _c(x).reshape(-1, x.shape[-1])
+        t = _c(targets.reshape(-1))
+        logits = G.mm_nt(x2, w, max_ctas=_max_ctas)
+        loss_rows, _ = K.xent_fused_(logits, t, 1.0 / logits.shape[0], V)
+        ctx.save_for_backward(x2, w, logits)
+        ctx.x_shape = x.shape
+        return K.mean_f32(loss_rows)
+
+    @staticmethod
+    def backward(ctx, dloss):
+        x2, w, dlogits = ctx.saved_tensors
+        g = _c(dloss.float()).reshape(1)
+        if w.requires_grad:
+            G.mm_tn_accum(dlogits, x2, main_grad(w), max_ctas=_max_ctas, alpha_dev=g)
+            _ready(w)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = G.mm_nn(dlogits, w, max_ctas=_max_ctas, alpha_dev=g).reshape(ctx.x_shape)
+        return dx, None, None, None
+
+
+def linear_cross_entropy(x, w, targets, num_classes: int | None = None):
+    """Mean cross-entropy of ``x @ w^T`` against ``targets`` (``w`` may carry padded rows past ``num_classes``).
+    On CUDA bf16 this never keeps logits and their gradient as two tensors; elsewhere it is linear + cross_entropy."""
+    V = num_classes or w.shape[0]
+    if _nat(x) and torch.is_grad_enabled() and (x.requires_grad or w.requires_grad):
+        return _LinearCrossEntropy.apply(x, w, targets, V)
+    return cross_entropy(linear(x, w), targets, V)
+
+
 def cross_entropy(logits, targets, num_classes: int | None = None):
     """Mean CE of ``logits[..., :num_classes]`` (extra padded columns are ignored)."""
     V = num_classes or logits.shape[-1]

@@ -59,7 +59,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
          bias: torch.Tensor | None = None, residual: torch.Tensor | None = None, act: int = nat.ACT_NONE,
          aux: torch.Tensor | None = None, splits: int = 1, tile_n: int = 0, max_ctas: int = 0,
          a_offset: int = 0, b_offset: int = 0, c_offset: int = 0, gather: dict | None = None,
-         scatter: dict | None = None) -> torch.Tensor:
+         scatter: dict | None = None, alpha_dev: torch.Tensor | None = None) -> torch.Tensor:
     """Launch one (batched) GEMM on the current stream.  Offsets/strides are in elements.
     ``gather`` = {world, rank, rows_per_rank, src: [ptr]*world, flags: tensor, copy_ctas} turns the launch into the
     fused all-gather -> GEMM (``a`` is then the local gathered buffer); ``scatter`` = {world, rank, rows_per_rank,
@@ -89,6 +89,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
     d.out_fp32 = int(out.dtype == torch.float32)
     d.accumulate = int(accumulate)
     d.alpha = alpha
+    if alpha_dev is not None:   # fp32 device scalar multiplied into alpha by the epilogue
+        assert alpha_dev.dtype == torch.float32 and alpha_dev.numel() == 1 and alpha_dev.is_cuda
+        d.alpha_ptr = alpha_dev.data_ptr()
     d.bias = nat.ptr(bias)
     d.residual = nat.ptr(residual)
     d.act = act
@@ -168,7 +171,7 @@ def mm_nt_f32out(x: torch.Tensor, w: torch.Tensor, *, alpha: float = 1.0, out: t
 
 
 def mm_nn(dy: torch.Tensor, w: torch.Tensor, *, act=nat.ACT_NONE, aux=None, out: torch.Tensor | None = None,
-          max_ctas: int = 0) -> torch.Tensor:
+          max_ctas: int = 0, alpha_dev: torch.Tensor | None = None) -> torch.Tensor:
     """dx[..., K] = dy[..., N] @ w[N, K] (data gradient of Linear); optional act'(aux) mask."""
     assert dy.is_contiguous() and w.is_contiguous()
     M, N = _rows(dy), dy.shape[-1]
@@ -176,11 +179,12 @@ def mm_nn(dy: torch.Tensor, w: torch.Tensor, *, act=nat.ACT_NONE, aux=None, out:
     if out is None:
         out = torch.empty(*dy.shape[:-1], K, dtype=torch.bfloat16, device=dy.device)
     # reduction runs over N: A = dy (k-contiguous), B[K, N] is w stored [N(k)][K(n)] -> MN-major
-    return gemm(dy, w, out, M=M, N=K, K=N, lda=N, ldb=K, ldc=K, b_mn=True, act=act, aux=aux, max_ctas=max_ctas)
+    return gemm(dy, w, out, M=M, N=K, K=N, lda=N, ldb=K, ldc=K, b_mn=True, act=act, aux=aux, max_ctas=max_ctas,
+                alpha_dev=alpha_dev)
 
 
 def mm_tn_accum(dy: torch.Tensor, x: torch.Tensor, grad: torch.Tensor, *, splits: int | None = None,
-                max_ctas: int = 0) -> torch.Tensor:
+                max_ctas: int = 0, alpha_dev: torch.Tensor | None = None) -> torch.Tensor:
     """grad[N, K] (fp32) += dy[M, N]^T @ x[M, K] (weight gradient, split-K with fp32 atomics)."""
     assert dy.is_contiguous() and x.is_contiguous() and grad.dtype == torch.float32
     M, N = _rows(dy), dy.shape[-1]
@@ -188,7 +192,7 @@ def mm_tn_accum(dy: torch.Tensor, x: torch.Tensor, grad: torch.Tensor, *, splits
     if splits is None:
         splits = auto_splits(N, K, M)
     return gemm(dy, x, grad, M=N, N=K, K=M, lda=N, ldb=K, ldc=K, a_mn=True, b_mn=True, accumulate=True,
-                splits=splits, max_ctas=max_ctas)
+                splits=splits, max_ctas=max_ctas, alpha_dev=alpha_dev)
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:

@@ -100,6 +100,16 @@ def xent_bwd_(logits2d, targets, lse, dloss, scale, V):
     return logits2d
 
 
+def xent_fused_(logits2d, targets, scale, V):
+    """Per-row loss and log-sum-exp; ``logits2d`` is overwritten by ``(softmax - onehot) * scale``."""
+    rows, ld = logits2d.shape[0], logits2d.stride(0)
+    loss = torch.empty(rows, dtype=F32, device=logits2d.device)
+    lse = torch.empty(rows, dtype=F32, device=logits2d.device)
+    nat.check(nat.cuda().incin_xent_fused(logits2d.data_ptr(), targets.data_ptr(), loss.data_ptr(), lse.data_ptr(), scale,
+                                         rows, V, ld, _s()), "xent_fused")
+    return loss, lse
+
+
 def mean_f32(x):
     out = torch.empty((), dtype=F32, device=x.device)
     nat.check(nat.cuda().incin_mean_f32(x.data_ptr(), out.data_ptr(), x.numel(), _s()), "mean")

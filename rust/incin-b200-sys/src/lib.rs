@@ -68,6 +68,7 @@ pub struct incin_gemm_desc {
     pub rs_slot_stride: c_longlong,
     pub rs_ready: *mut c_void,
     pub in_dtype: c_int,
+    pub alpha_ptr: *const c_void,
 }
 
 #[repr(C)]
@@ -269,5 +270,6 @@ extern "C" {
     pub fn incin_tri(x: *const c_void, out: *mut c_void, batch: c_longlong, rows: c_longlong, cols: c_longlong, diagonal: c_longlong, upper: c_int, elem_bytes: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_where(cond: *const u8, a: *const c_void, b: *const c_void, out: *mut c_void, n: c_longlong, elem_bytes: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_xent_bwd(logits: *mut c_void, targets: *const i64, lse: *const f32, dloss: *const f32, scale: f32, rows: c_longlong, V: c_int, ld: c_longlong, stream: *mut c_void) -> c_int;
+    pub fn incin_xent_fused(logits: *mut c_void, targets: *const i64, loss: *mut f32, lse: *mut f32, scale: f32, rows: c_longlong, V: c_int, ld: c_longlong, stream: *mut c_void) -> c_int;
     pub fn incin_xent_fwd(logits: *const c_void, targets: *const i64, loss: *mut f32, lse: *mut f32, rows: c_longlong, V: c_int, ld: c_longlong, stream: *mut c_void) -> c_int;
 }

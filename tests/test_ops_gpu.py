@@ -176,3 +176,23 @@ def test_philox_and_dropout():
     keep = (y != 0).float().mean().item()
     assert abs(keep - 0.75) < 5e-3
     assert abs(y.float().mean().item() - 1.0) < 1e-2
+
+
+def test_linear_cross_entropy_fused():
+    """Loss and gradients of the fused LM-head + cross-entropy op against linear -> cross_entropy in fp32, with an
+    upstream gradient other than one (it reaches the two products as a device scalar)."""
+    from incin_b200.ops import functional as F
+    rows, C, V, Vpad = 300, 256, 1000, 1024
+    x = rnd((3, 100, C), 1).requires_grad_()
+    w = rnd((Vpad, C), 2, scale=0.05).requires_grad_()
+    tgt = torch.randint(0, V, (3, 100), generator=torch.Generator().manual_seed(3)).cuda()
+    w.main_grad = torch.zeros(Vpad, C, device="cuda")
+    loss = F.linear_cross_entropy(x, w, tgt, V)
+    (loss * 3.0).backward()
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    ref = TF.cross_entropy((xf.reshape(-1, C) @ wf.T)[:, :V], tgt.reshape(-1))
+    (ref * 3.0).backward()
+    assert abs(loss.item() - ref.item()) < 2e-2 * abs(ref.item())
+    close(x.grad, xf.grad, tol=3e-2)
+    close(w.main_grad, wf.grad, tol=3e-2)
+    assert w.main_grad[V:].abs().max().item() == 0.0      # padded vocabulary rows get no gradient
