@@ -23,6 +23,8 @@
 
 namespace incin {
 
+int make_f32_reduce_map(CUtensorMap* out, void* ptr, long long inner, long long rows, long long ld, long long batch_lo,
+                        long long stride_lo, long long batch_hi, long long stride_hi, int box_rows);
 int make_operand_map(CUtensorMap* out, const void* ptr, long long inner, long long rows, long long ld,
                      long long batch_lo, long long stride_lo, long long batch_hi, long long stride_hi, int box_inner,
                      int box_rows);
@@ -56,6 +58,7 @@ struct FbCfg {
 };
 
 struct FbParams {
+  alignas(64) CUtensorMap tm_dq;   // fp32 dq_accum as {D, T, Hq, B}, 32 x 128 boxes (head_dim-64 kernel: bulk reduce-adds)
   int T, Hq, Hkv, n_tiles;
   int batch;           // B (the persistent kernel enumerates its work items itself)
   float scale, scale_log2;
@@ -619,6 +622,11 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.lse = d->lse;
   p.delta = d->delta;
   p.dq_accum = d->dq_accum;
+  if (use_split) {
+    rc = make_f32_reduce_map(&p.tm_dq, d->dq_accum, D, d->T, (long long)d->Hq * D, d->Hq, D, d->B,
+                             (long long)d->T * d->Hq * D, FB_T);
+    if (rc) return rc;
+  }
   p.dk = (__nv_bfloat16*)d->dk;
   p.dv = (__nv_bfloat16*)d->dv;
   p.dk_stride_b = d->dk_stride_b;

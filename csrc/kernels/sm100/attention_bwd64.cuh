@@ -40,8 +40,11 @@ struct Fb64 {
   static constexpr int OFF_P = OFF_DO + ST * TILE_BYTES;      // [a0][b][a1]
   static constexpr int OFF_DS = OFF_P + 3 * CHUNK_BYTES;      // [a0][b][a1]
   static constexpr int OFF_STAT = OFF_DS + 3 * CHUNK_BYTES;   // lse[128], delta[128] per stage
-  static constexpr int OFF_BAR = OFF_STAT + ST * 2 * FB_T * 4;
-  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static constexpr int OFF_DQS = OFF_STAT + ST * 2 * FB_T * 4;   // dQ staging: two [128 q][32 fp32] boxes, SWIZZLE_128B
+  static constexpr int DQS_BYTES = FB_T * 32 * 4;
+  static constexpr int OFF_BAR = OFF_DQS + 2 * DQS_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256;                // the window itself is declared 1024-byte aligned
+  static_assert(OFF_DQS % 1024 == 0 && SMEM_BYTES <= 227 * 1024, "shared-memory plan");
   static constexpr int COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384, TMEM_COLS = 512;
   // byte offset of half h of tile `it` inside a [a0][b][a1] triple
   __device__ static constexpr int chunk_off(int h, int it) { return h ? CHUNK_BYTES : ((it & 1) ? 2 * CHUNK_BYTES : 0); }
@@ -49,11 +52,18 @@ struct Fb64 {
 
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const FbParams p) {
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                   const __grid_constant__ FbParams p) {
   using Cfg = Fb64;
   constexpr int D = Cfg::D, ST = Cfg::ST, H = Cfg::H;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // The plan fills the 227 KB an SM offers, so there is no room to round the base up: the window is declared aligned
+  // and the kernel refuses to run (status word, nothing touched) should the base ever not be.
+  extern __shared__ __align__(1024) uint8_t smem_aligned[];
+  uint8_t* smem = smem_aligned;
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kStatusBadArgument);
+    return;
+  }
   uint8_t* sK = smem + Cfg::OFF_K;
   uint8_t* sV = smem + Cfg::OFF_V;
   uint8_t* sQ = smem + Cfg::OFF_Q;
@@ -71,7 +81,10 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* dq_drained = bars + 11;  // [2]  dQ partial buffer read out (one arrival per warp)
   uint64_t* kv_empty = bars + 13;    // every product of the current item has been committed: K / V may be replaced
   uint64_t* dkv_drained = bars + 14; // dK / dV of the current item have been read out (one arrival per warp)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* stg_free = bars + 15;    // [2]  per compute group: the previous bulk reduce has read the dQ staging box
+  uint64_t* stg_full = bars + 17;    // [2]  per compute group: all 8 warps have written their part of the box
+  uint8_t* sDQS = smem + Cfg::OFF_DQS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -103,12 +116,17 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     mbar_init(kv_empty, 1);
     mbar_init(dkv_drained, FB_CWARPS);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&stg_free[s], 1);
+      mbar_init(&stg_full[s], FB_CWARPS / 2);
+    }
     *abort_flag = 0;
     mbar_init_fence();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmDO);
+    tma_prefetch_desc(&p.tm_dq);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -274,7 +292,12 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
 
     long long c_wait_sdp = 0, c_wait_dq = 0, c_drain = 0, c_ld0 = 0, c_chunks = 0, c_fence = 0, c_all = clock64();   // optional profile (see attn_prof_buffer)
-    // dQ partial of pipeline slot g (tile `it_j` of the item described by the arguments)
+    // dQ partial of pipeline slot g (tile `it_j` of the item described by the arguments).  Tensor memory hands every
+    // lane one query row, so adding it to global memory from registers would be one 16-byte `red` per lane and row;
+    // instead each compute group stages its 32 columns as a [128 q][32] fp32 box in shared memory (128-byte swizzle:
+    // conflict free for row-per-lane stores) and one thread adds the box to dq_accum with a bulk tensor reduce.
+    const bool elected = (cw == my_half * (FB_CWARPS / 2)) && lane == 0;
+    uint8_t* stage_box = sDQS + my_half * Cfg::DQS_BYTES;
     auto drain_dq = [&](int g, int it_j, int kv_tile, int hkv, int b) -> bool {
       const int bq = g & 1;
       const long long tw = clock64();
@@ -282,26 +305,38 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const long long tb = clock64();
       c_wait_dq += tb - tw;
       tc_fence_after();
-      const int tiles_per_head = p.n_tiles - kv_tile;
-      const int hq_j = hkv * group + it_j / tiles_per_head;
-      const int q_local = bq ? ((row + H) & (FB_T - 1)) : row;   // odd slots: rows are the queries rotated by 64
-      const int q = (kv_tile + it_j % tiles_per_head) * FB_T + q_local;
-      constexpr int DC = D / 4;
-      float* dq_row = p.dq_accum + (((long long)b * p.T + q) * p.Hq + hq_j) * D + cb * DC;
       uint32_t r[16];
-      tmem_ld_32x16(tmem_base + Cfg::COL_DQ + bq * D + lane_addr + cb * DC, r);
+      tmem_ld_32x16(tmem_base + Cfg::COL_DQ + bq * D + lane_addr + cb * 16, r);
       tmem_ld_wait();
-      if (q < p.T) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + u * 4),
-                       "f"(__uint_as_float(r[u * 4]) * p.scale), "f"(__uint_as_float(r[u * 4 + 1]) * p.scale),
-                       "f"(__uint_as_float(r[u * 4 + 2]) * p.scale), "f"(__uint_as_float(r[u * 4 + 3]) * p.scale)
-                       : "memory");
-      }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&dq_drained[bq]);
+      if (lane == 0) mbar_arrive(&dq_drained[bq]);   // the tensor-memory buffer may be overwritten
+      // the box is free once the previous reduce of this group has read it
+      if (elected) {
+        bulk_wait_read_all();
+        mbar_arrive(&stg_free[my_half]);
+      }
+      if (!mbar_wait(&stg_free[my_half], g & 1, abort_flag, p.status, kStatusTimeoutEmpty)) return false;
+      const int q_local = bq ? ((row + H) & (FB_T - 1)) : row;   // odd slots: rows are the queries rotated by 64
+      uint8_t* srow = stage_box + q_local * 128;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int unit = ((cb & 1) * 4 + u) ^ (q_local & 7);
+        *reinterpret_cast<float4*>(srow + unit * 16) =
+            make_float4(__uint_as_float(r[u * 4]) * p.scale, __uint_as_float(r[u * 4 + 1]) * p.scale,
+                        __uint_as_float(r[u * 4 + 2]) * p.scale, __uint_as_float(r[u * 4 + 3]) * p.scale);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&stg_full[my_half]);
+      if (elected) {
+        if (!mbar_wait(&stg_full[my_half], g & 1, abort_flag, p.status, kStatusTimeoutFull)) return false;
+        const int tiles_per_head = p.n_tiles - kv_tile;
+        const int hq_j = hkv * group + it_j / tiles_per_head;
+        const int q0 = (kv_tile + it_j % tiles_per_head) * FB_T;
+        tma_reduce_add_4d(&p.tm_dq, stage_box, my_half * 32, q0, hq_j, b);   // rows past T are clipped by the map
+        bulk_commit();
+      }
       c_drain += clock64() - tb;
       return true;
     };
@@ -418,6 +453,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       base += n_iters;
     }
+    if (elected) bulk_wait_all();   // the staged boxes stay valid until their reduces have completed
     if (p.prof && lane == 0 && warp == 2) {
       atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 12), (unsigned long long)c_ld0);
       atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 13), (unsigned long long)c_chunks);

@@ -412,6 +412,30 @@ int make_operand_map(CUtensorMap* out, const void* ptr, long long inner, long lo
   return r == CUDA_SUCCESS ? INCIN_OK : INCIN_ERR_TENSOR_MAP;
 }
 
+// Tensor map over an fp32 tensor for tiled reduce-adds from 128-byte swizzled shared memory: dims {inner, rows,
+// batch_lo, batch_hi}, strides in elements; box = {32 columns (128 bytes), box_rows, 1, 1}.
+int make_f32_reduce_map(CUtensorMap* out, void* ptr, long long inner, long long rows, long long ld, long long batch_lo,
+                        long long stride_lo, long long batch_hi, long long stride_hi, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return INCIN_ERR_DRIVER;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ld % 4) || (batch_lo > 1 && stride_lo % 4) || (batch_hi > 1 && stride_hi % 4) ||
+      inner % 32)
+    return INCIN_ERR_ALIGNMENT;
+  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)batch_lo, (cuuint64_t)batch_hi};
+  cuuint64_t strides[3] = {(cuuint64_t)ld * 4, (cuuint64_t)(batch_lo > 1 ? stride_lo : ld * rows) * 4,
+                           (cuuint64_t)(batch_hi > 1 ? stride_hi : ld * rows) * 4};
+  cuuint32_t box[4] = {32, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? INCIN_OK : INCIN_ERR_TENSOR_MAP;
+}
+
 static int g_num_sms = 0;
 int device_sm_count() {
   if (g_num_sms == 0) {

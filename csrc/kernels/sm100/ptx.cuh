@@ -126,6 +126,22 @@ __device__ __forceinline__ void bulk_store_1d(void* gdst, const void* smem_src, 
                "r"(smem_u32(smem_src)), "r"(bytes)
                : "memory");
 }
+// Tiled reduce-add of a shared-memory box into global memory (element type and box come from the tensor map); the x
+// coordinate times the element size must be a multiple of 16 bytes and no coordinate may be negative.  Completion is
+// tracked by bulk groups: bulk_commit() after issuing, bulk_wait_read_all() before the shared-memory box is reused.
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(smem_src))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// barrier among `threads` threads of the CTA (a multiple of 32) on hardware barrier `id` (1..15; 0 is __syncthreads)
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 // commit the bulk stores issued so far and wait until their writes have completed
 __device__ __forceinline__ void bulk_commit_wait_all() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
