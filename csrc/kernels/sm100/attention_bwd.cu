@@ -586,13 +586,15 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
     return !(e && e[0] == '0');
   }();
   const bool use_split = (D == 64) && split64;
-  auto kern = use_split ? flash_bwd64_kernel : flash_bwd_kernel<D>;
+  const bool prof = use_split && attn_prof_buffer() != nullptr;
+  auto kern = use_split ? (prof ? flash_bwd64_kernel<true> : flash_bwd64_kernel<false>) : flash_bwd_kernel<D>;
   const int smem_bytes = use_split ? Fb64::SMEM_BYTES : Cfg::SMEM_BYTES;
-  static bool attr[2] = {false, false};
-  if (!attr[use_split]) {
+  static bool attr[3] = {false, false, false};
+  const int which = use_split ? (prof ? 2 : 1) : 0;
+  if (!attr[which]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
       return INCIN_ERR_LAUNCH;
-    attr[use_split] = true;
+    attr[which] = true;
   }
   const long long rows = (long long)d->B * d->T * d->Hq;
   const int Tpad = (d->T + FB_T - 1) / FB_T * FB_T;

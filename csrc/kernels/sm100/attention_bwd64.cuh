@@ -50,6 +50,9 @@ struct Fb64 {
   __device__ static constexpr int chunk_off(int h, int it) { return h ? CHUNK_BYTES : ((it & 1) ? 2 * CHUNK_BYTES : 0); }
 };
 
+// PROF: add up clock intervals of the issuing thread and of one compute lane into p.prof (a second instantiation, so
+// that the production kernel carries no clock reads).
+template <bool PROF>
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -64,6 +67,10 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kStatusBadArgument);
     return;
   }
+  auto now = [] () -> long long {
+    if constexpr (PROF) return clock64();
+    else return 0ll;
+  };
   uint8_t* sK = smem + Cfg::OFF_K;
   uint8_t* sV = smem + Cfg::OFF_V;
   uint8_t* sQ = smem + Cfg::OFF_Q;
@@ -204,8 +211,8 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       };
       int base = 0;
       bool ok = true;
-      long long t_kv = 0, t_q = 0, t_pds0 = 0, t_pds1 = 0, t_dq = 0, t_issue = 0, t_all = clock64(), tm;
-#define PROF_WAIT(acc, expr) (tm = clock64(), ok_w = (expr), acc += clock64() - tm, ok_w)
+      long long t_kv = 0, t_q = 0, t_pds0 = 0, t_pds1 = 0, t_dq = 0, t_issue = 0, t_all = now(), tm;
+#define PROF_WAIT(acc, expr) (tm = now(), ok_w = (expr), acc += now() - tm, ok_w)
       bool ok_w;
       for (int r = 0; ok; ++r) {
         int kv_tile, hkv, b;
@@ -265,8 +272,8 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         base += n_iters;
       }
 #undef PROF_WAIT
-      if (p.prof) {
-        t_all = clock64() - t_all;
+      if constexpr (PROF) {
+        t_all = now() - t_all;
         t_issue = t_all - t_kv - t_q - t_pds0 - t_pds1 - t_dq;
         atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 0), (unsigned long long)t_all);
         atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 1), (unsigned long long)t_kv);
@@ -291,7 +298,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
 
-    long long c_wait_sdp = 0, c_wait_dq = 0, c_drain = 0, c_ld0 = 0, c_chunks = 0, c_fence = 0, c_all = clock64();   // optional profile (see attn_prof_buffer)
+    long long c_wait_sdp = 0, c_wait_dq = 0, c_drain = 0, c_ld0 = 0, c_chunks = 0, c_fence = 0, c_all = now();   // optional profile (see attn_prof_buffer)
     // dQ partial of pipeline slot g (tile `it_j` of the item described by the arguments).  Tensor memory hands every
     // lane one query row, so adding it to global memory from registers would be one 16-byte `red` per lane and row;
     // instead each compute group stages its 32 columns as a [128 q][32] fp32 box in shared memory (128-byte swizzle:
@@ -300,9 +307,9 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint8_t* stage_box = sDQS + my_half * Cfg::DQS_BYTES;
     auto drain_dq = [&](int g, int it_j, int kv_tile, int hkv, int b) -> bool {
       const int bq = g & 1;
-      const long long tw = clock64();
+      const long long tw = now();
       if (!mbar_wait(&dq_full[bq], (g >> 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) return false;
-      const long long tb = clock64();
+      const long long tb = now();
       c_wait_dq += tb - tw;
       tc_fence_after();
       uint32_t r[16];
@@ -337,7 +344,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_reduce_add_4d(&p.tm_dq, stage_box, my_half * 32, q0, hq_j, b);   // rows past T are clipped by the map
         bulk_commit();
       }
-      c_drain += clock64() - tb;
+      c_drain += now() - tb;
       return true;
     };
 
@@ -357,9 +364,9 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const bool masked = (q0 < kv0 + FB_T) || (kv0 + FB_T > p.T);   // diagonal tile, or a KV tile with dead rows
         auto half = [&](int h, auto masked_tag) -> bool {
           constexpr bool MASKED = decltype(masked_tag)::value;
-          const long long tw = clock64();
+          const long long tw = now();
           if (!mbar_wait(&sdp[h], g & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) return false;
-          c_wait_sdp += clock64() - tw;
+          c_wait_sdp += now() - tw;
           tc_fence_after();
           const int off = Cfg::chunk_off(h, g) + row * 128;     // [128 kv rows][64 q] bf16, SWIZZLE_128B
           // 32 query columns per thread in four chunks of 8: the tensor-memory loads of chunk c+1 are in flight while
@@ -371,7 +378,7 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tmem_ld_32x8(tmem_base + Cfg::COL_ST + lane_addr + cbase, rs[0]);
           tmem_ld_32x8(tmem_base + Cfg::COL_DPT + lane_addr + cbase, rd[0]);
           tmem_ld_wait_on(rs[0], rd[0]);
-          const long long t_a = clock64();
+          const long long t_a = now();
           c_ld0 += t_a - tw;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -406,13 +413,13 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             *reinterpret_cast<uint4*>(sDS + off + unit * 16) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
             if (c < 3) tmem_ld_wait_on(rs[nxt], rd[nxt]);
           }
-          const long long t_b = clock64();
+          const long long t_b = now();
           c_chunks += t_b - t_a;
           fence_proxy_async_smem();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&pds[h]);
-          c_fence += clock64() - t_b;
+          c_fence += now() - t_b;
           return true;
         };
         ok = masked ? half(my_half, std::true_type{}) : half(my_half, std::false_type{});
@@ -454,14 +461,14 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       base += n_iters;
     }
     if (elected) bulk_wait_all();   // the staged boxes stay valid until their reduces have completed
-    if (p.prof && lane == 0 && warp == 2) {
+    if (PROF && lane == 0 && warp == 2) {
       atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 12), (unsigned long long)c_ld0);
       atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 13), (unsigned long long)c_chunks);
       atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 14), (unsigned long long)c_fence);
     }
-    if (p.prof && lane == 0 && warp == 2) {
+    if (PROF && lane == 0 && warp == 2) {
       const int o = 8;
-      atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + o), (unsigned long long)(clock64() - c_all));
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + o), (unsigned long long)(now() - c_all));
       atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + o + 1), (unsigned long long)c_wait_sdp);
       atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + o + 2), (unsigned long long)c_wait_dq);
       atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + o + 3), (unsigned long long)c_drain);

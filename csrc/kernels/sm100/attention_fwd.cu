@@ -7,7 +7,9 @@
 // accumulates O += P V in tensor memory.  O is only rescaled when the running max grew by more than
 // 2^8 (the final division by the row sum makes the result exact either way), and the rescale is a
 // tcgen05.ld / tcgen05.st round trip over the 128 accumulator lanes.  Two CTAs fit per SM (96 KB
-// shared memory, 256 TMEM columns each) so one CTA's exponentials overlap the other's MMAs.
+// shared memory, 256 TMEM columns each) so one CTA's exponentials overlap the other's MMAs.  Inside a CTA the
+// next score product S_{j+1} is issued as soon as the softmax threads hold S_j in registers (barrier s_free), and
+// O += P_j V_j signals its own barrier (pv_done), so both products run under the softmax math of the next tile.
 //
 // The reference has no attention kernel in use: its CPU path materialises softmax(QK^T s + mask) V
 // (crates/incin-backends/src/cpu/ops/shape_ops.rs:1245-1269) and CUDA reports SDPA as unsupported;
@@ -68,9 +70,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* k_empty = bars + 3;    // [2]
   uint64_t* v_full = bars + 5;     // 1
   uint64_t* v_empty = bars + 6;    // 1
-  uint64_t* s_full = bars + 7;     // 1: S_j ready (and every earlier MMA, incl. PV_{j-1}, finished)
-  uint64_t* p_full = bars + 8;     // 128 arrivals: P_j in shared memory, O rescaled
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* s_full = bars + 7;     // 1: S_j is in tensor memory
+  uint64_t* p_full = bars + 8;     // one arrival per softmax warp: P_j in shared memory, O rescaled
+  uint64_t* s_free = bars + 9;     // one arrival per softmax warp: S_j has been read into registers
+  uint64_t* pv_done = bars + 10;   // 1: O += P_j V_j has finished (P_j's shared memory and O may be touched again)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -92,6 +96,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(v_empty, 1);
     mbar_init(s_full, 1);
     mbar_init(p_full, 4);   // one arrival per softmax warp
+    mbar_init(s_free, 4);
+    mbar_init(pv_done, 1);
     *abort_flag = 0;
     mbar_init_fence();
     tma_prefetch_desc(&tmQ);
@@ -132,10 +138,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(FA_BM, BN, false, false);
       constexpr uint32_t idesc_o = make_idesc_bf16(FA_BM, D, false, true);
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusTimeoutFull);
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      // S_{j+1} = Q K_{j+1}^T is issued as soon as the softmax threads have S_j in registers, so it and O += P_j V_j
+      // run while they work on the exponentials of tile j+1; the chain of a tile is then the softmax math alone.
+      auto issue_s = [&](int j) -> bool {
         const int ks = j & 1;
-        if (!mbar_wait(&k_full[ks], (j >> 1) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+        if (!mbar_wait(&k_full[ks], (j >> 1) & 1, abort_flag, p.status, kStatusTimeoutFull)) return false;
+        if (j > 0 && !mbar_wait(s_free, (j - 1) & 1, abort_flag, p.status, kStatusTimeoutTmemEmpty)) return false;
         tc_fence_after();
         const uint32_t aq = smem_u32(sQ), bk = smem_u32(sK + ks * Cfg::K_BYTES);
 #pragma unroll
@@ -146,6 +154,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         umma_commit(&k_empty[ks]);
         umma_commit(s_full);
+        return true;
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusTimeoutFull);
+      ok = ok && issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
         if (!mbar_wait(p_full, j & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
         if (!mbar_wait(v_full, j & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
         tc_fence_after();
@@ -157,8 +171,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_f16_ss(tmem_O, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(v_empty);
+        umma_commit(pv_done);
       }
-      if (ok) umma_commit(s_full);  // phase n_tiles: every PV has finished
     }
   } else {
     // ------------------------------------------------------------------ softmax / correction / epilogue
@@ -179,6 +193,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int c = 0; c < BN / 32; ++c)
         tmem_ld_32x32(tmem_S + lane_addr + c * 32, reinterpret_cast<uint32_t(&)[32]>(r[c * 32]));
       tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);   // the next score product may overwrite S
       if (need_mask) {  // masked scores become -inf, so the code below needs no further tests
 #pragma unroll
         for (int i = 0; i < BN; ++i) {
@@ -204,6 +221,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m_ref = mx;
         l_sum *= alpha;
       }
+      // P = exp2(s * scale - m_ref) as packed bf16, kept in registers (in place of the scores they came from) while
+      // O += P_{j-1} V_{j-1} may still be running; four independent sum chains
+      const float neg_m = -m_ref;
+      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < BN; i += 2) {
+        const float e0 = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
+        const float e1 = exp2f(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
+        ls4[i & 3] += e0;
+        ls4[(i & 3) + 1] += e1;
+        r[i >> 1] = pack_bf16x2(e0, e1);
+      }
+      // that product must have finished before O is rescaled or P's shared memory is written again
+      if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+      tc_fence_after();
       if (j > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
@@ -216,27 +248,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         tmem_st_wait();
       }
-      // P = exp2(s * scale - m_ref) as bf16 into 128B-swizzled shared memory; four independent sum chains
-      const float neg_m = -m_ref;
-      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+      // P into 128B-swizzled shared memory: 16-byte unit ^ (row % 8)
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
         uint8_t* prow = sP + (c >> 1) * (FA_BM * 128) + row * 128;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          float e[8];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            e[k] = exp2f(fmaf(__uint_as_float(r[c * 32 + u * 8 + k]), p.scale_log2, neg_m));
-            ls4[k & 3] += e[k];
-          }
-          uint4 o;
-          o.x = pack_bf16x2(e[0], e[1]);
-          o.y = pack_bf16x2(e[2], e[3]);
-          o.z = pack_bf16x2(e[4], e[5]);
-          o.w = pack_bf16x2(e[6], e[7]);
-          const int unit = ((c & 1) * 4 + u) ^ (row & 7);  // 128B swizzle: 16-byte unit ^ (row % 8)
-          *reinterpret_cast<uint4*>(prow + unit * 16) = o;
+          const int w0 = (c * 32 + u * 8) >> 1;
+          const int unit = ((c & 1) * 4 + u) ^ (row & 7);
+          *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(r[w0], r[w0 + 1], r[w0 + 2], r[w0 + 3]);
         }
       }
       l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
@@ -245,7 +265,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       __syncwarp();                        // every lane's writes and fences precede the single arrival of its warp
       if (lane == 0) mbar_arrive(p_full);
     }
-    if (ok && mbar_wait(s_full, n_tiles & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) {
+    if (ok && mbar_wait(pv_done, (n_tiles - 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) {
       tc_fence_after();
       const float inv = 1.0f / l_sum;
       const bool live_row = q_idx < p.T;
