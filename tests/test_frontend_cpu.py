@@ -338,3 +338,26 @@ def test_native_mlp_benchmark_matches_pytorch_cpu():
     b, _ = train_torch(steps=100)
     assert abs(a[0] - 2.3025) < 1e-3 and a[-1] < 0.7
     assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5
+
+
+def test_linear_cross_entropy_cpu_twin_and_model_loss():
+    """Off the GPU the fused LM-head loss is linear followed by cross_entropy over the first `num_classes` columns, and
+    the GPT-2 model routes its training loss through it."""
+    from incin_b200.models.gpt2 import GPT2, GPT2Config
+    from incin_b200.ops import functional as F
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2, 5, 16, generator=g, requires_grad=True)
+    w = torch.randn(40, 16, generator=g, requires_grad=True)
+    t = torch.randint(0, 33, (2, 5), generator=g)
+    loss = F.linear_cross_entropy(x, w, t, 33)
+    loss.backward()
+    ref = torch.nn.functional.cross_entropy((x.detach().reshape(-1, 16) @ w.detach().T)[:, :33], t.reshape(-1))
+    assert abs(loss.item() - ref.item()) < 1e-6
+    assert w.grad[33:].abs().max().item() == 0.0          # padded vocabulary rows take no gradient
+    cfg = GPT2Config(vocab_size=50, n_layer=1, n_head=2, d_model=16, d_mlp=32, max_seq=8)
+    m = GPT2(cfg)
+    tok = torch.randint(0, 50, (2, 8), generator=g)
+    logits = m(tok)
+    l2 = m(tok, tok)
+    assert logits.shape[-1] == 50 and torch.isfinite(l2)
+    assert abs(l2.item() - torch.nn.functional.cross_entropy(logits.reshape(-1, 50).float(), tok.reshape(-1)).item()) < 1e-4
