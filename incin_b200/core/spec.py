@@ -252,12 +252,14 @@ CUDA_CAPABILITIES: tuple[CapabilityRule, ...] = (
     CapabilityRule("matmul", _BF, SupportLevel.NATIVE, "gemm_tcgen05 (TMA + tcgen05.mma + TMEM)"),
     CapabilityRule("bmm", _BF, SupportLevel.NATIVE, "gemm_tcgen05 batched (4-D tensor maps)"),
     CapabilityRule("addmm", _BF, SupportLevel.NATIVE, "gemm_tcgen05 bias/residual epilogue"),
-    CapabilityRule("matmul", (DTypeId.F32, DTypeId.F16), SupportLevel.COMPOSED, "cast to bf16 + gemm_tcgen05"),
+    CapabilityRule("matmul", (DTypeId.F16,), SupportLevel.NATIVE, "gemm_tcgen05, fp16 operands, fp32 accumulate and output"),
+    CapabilityRule("matmul", (DTypeId.F32,), SupportLevel.NATIVE, "gemm_tcgen05 kind::tf32 (MathMode.FAST; else cuBLAS fp32)"),
     CapabilityRule("sdpa", _BF, SupportLevel.NATIVE, "flash_fwd/flash_bwd (online softmax on tcgen05)"),
     CapabilityRule("layer_norm", _BF, SupportLevel.NATIVE, "norm_fwd/norm_bwd"),
     CapabilityRule("rms_norm", _BF, SupportLevel.NATIVE, "norm_fwd/norm_bwd<RMS>"),
     CapabilityRule("embedding", _BF, SupportLevel.NATIVE, "embedding_fwd/bwd"),
     CapabilityRule("cross_entropy", _BF, SupportLevel.NATIVE, "xent_fwd/bwd (online log-sum-exp)"),
+    CapabilityRule("linear_cross_entropy", _BF, SupportLevel.NATIVE, "gemm_tcgen05 + xent_fused (loss and gradient in one pass)"),
     CapabilityRule("softmax", _BF + (DTypeId.F32,), SupportLevel.NATIVE, "fused pointwise/row kernels"),
     CapabilityRule("unary", _F, SupportLevel.NATIVE, "NVRTC-fused pointwise chain (sm_100a)"),
     CapabilityRule("add", _F, SupportLevel.NATIVE, "NVRTC-fused pointwise chain (sm_100a)"),
