@@ -156,6 +156,8 @@ def bench_bandwidth(args) -> None:
     loss, lse = K.xent_fwd(logits, tgt, V)
     one = torch.ones(1, device="cuda")
     rec("xent_bwd 8192x50304", timeit(lambda: K.xent_bwd_(logits, tgt, lse, one, 1.0, V)), 2 * logits.numel() * 2)
+    rec("xent_fused 8192x50304 (loss + gradient in place)", timeit(lambda: K.xent_fused_(logits, tgt, 1.0 / 8192, V)),
+        2 * logits.numel() * 2)
     n = 124 * 1000 * 1000
     w, m, v, gr = (torch.zeros(n, device="cuda") for _ in range(4))
     sh = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
