@@ -93,3 +93,76 @@ class TrainStep:
                 dst.copy_(src, non_blocking=True)
         self.graph.replay()
         return self.static_loss
+
+
+class StepPipeline:
+    """Feeds a training step from pinned host batches without putting the copies or the loss read-back on the critical
+    path.  ``submit(*host_tensors)`` copies the batch to a device staging slot on a copy stream (while the previous step
+    still runs), enqueues the step on the current stream once the copy has landed and starts an asynchronous copy of
+    that step's loss into pinned memory; ``pop()`` returns the oldest outstanding loss as a float, blocking only until
+    that step has finished.  With ``depth`` slots, ``depth - 1`` steps can be in flight before a ``pop`` is needed::
+
+        pipe = StepPipeline(step)
+        for i, (tok, tgt) in enumerate(loader):        # pinned host tensors
+            pipe.submit(tok, tgt)
+            if i:
+                log(pipe.pop())                        # loss of step i - 1
+        log(pipe.pop())
+
+    ``step`` is any callable taking device tensors and returning a device loss (a :class:`TrainStep`, typically).
+    Every step's inputs cross host -> device and every step's loss crosses device -> host; only the waiting moves.
+    """
+
+    def __init__(self, step: Callable[..., torch.Tensor], depth: int = 2, device: torch.device | None = None):
+        if depth < 2:
+            raise ValueError("depth must be at least 2 (one slot being filled while another one runs)")
+        self.step = step
+        self.depth = depth
+        self.device = device or getattr(step, "device", None) or torch.device("cuda", torch.cuda.current_device())
+        self.copy_stream = torch.cuda.Stream(device=self.device)
+        self._staging: list[list[torch.Tensor] | None] = [None] * depth
+        self._loss_host = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(depth)]
+        self._ev_in = [torch.cuda.Event() for _ in range(depth)]
+        self._ev_free: list[torch.cuda.Event | None] = [None] * depth
+        self._ev_loss = [torch.cuda.Event() for _ in range(depth)]
+        self.submitted = 0
+        self.popped = 0
+
+    @property
+    def outstanding(self) -> int:
+        return self.submitted - self.popped
+
+    def submit(self, *host_inputs: torch.Tensor) -> None:
+        if self.outstanding >= self.depth:
+            raise RuntimeError(f"{self.outstanding} losses outstanding: call pop() before submitting another step")
+        k = self.submitted % self.depth
+        if self._staging[k] is None or any(s.shape != h.shape or s.dtype != h.dtype
+                                           for s, h in zip(self._staging[k], host_inputs)):
+            self._staging[k] = [torch.empty(h.shape, dtype=h.dtype, device=self.device) for h in host_inputs]
+            self._ev_free[k] = None
+        main = torch.cuda.current_stream(self.device)
+        if self._ev_free[k] is not None:
+            self.copy_stream.wait_event(self._ev_free[k])      # the step that last read this slot has consumed it
+        with torch.cuda.stream(self.copy_stream):
+            for dst, src in zip(self._staging[k], host_inputs):
+                dst.copy_(src, non_blocking=True)
+            self._ev_in[k].record(self.copy_stream)
+        main.wait_event(self._ev_in[k])
+        loss = self.step(*self._staging[k])
+        ev = torch.cuda.Event()
+        ev.record(main)
+        self._ev_free[k] = ev
+        self._loss_host[k].copy_(loss.detach().float().reshape(()), non_blocking=True)
+        self._ev_loss[k].record(main)
+        self.submitted += 1
+
+    def pop(self) -> float:
+        if self.outstanding <= 0:
+            raise RuntimeError("no step outstanding")
+        k = self.popped % self.depth
+        self._ev_loss[k].synchronize()
+        self.popped += 1
+        return float(self._loss_host[k])
+
+    def drain(self) -> list[float]:
+        return [self.pop() for _ in range(self.outstanding)]

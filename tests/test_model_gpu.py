@@ -53,3 +53,29 @@ def test_training_reduces_loss(use_graph):
     if use_graph:
         assert step.graph is not None, "CUDA graph capture of the training step failed"
     G.check_status()
+
+
+def test_step_pipeline_matches_sequential_steps():
+    """Feeding pinned host batches through StepPipeline (copy stream, lagged loss read) gives the losses of the same
+    steps run one by one with device inputs and a blocking read."""
+    from incin_b200.engine import StepPipeline, TrainStep
+    from incin_b200.optim import AdamW, ParamStore
+    cfg, cpu, gpu_a, tok, tgt = _setup("auto")
+    gpu_b = copy.deepcopy(gpu_a)
+    g = torch.Generator().manual_seed(7)
+    batches = [(torch.randint(0, cfg.vocab_size, (4, 128), generator=g).pin_memory(),
+                torch.randint(0, cfg.vocab_size, (4, 128), generator=g).pin_memory()) for _ in range(8)]
+    step_a = TrainStep(gpu_a, AdamW(ParamStore(gpu_a.named_parameters()), lr=1e-3))
+    ref = [step_a(t.cuda(), y.cuda()).item() for t, y in batches]
+    step_b = TrainStep(gpu_b, AdamW(ParamStore(gpu_b.named_parameters()), lr=1e-3))
+    pipe = StepPipeline(step_b)
+    got = []
+    for i, (t, y) in enumerate(batches):
+        pipe.submit(t, y)
+        if i:
+            got.append(pipe.pop())
+    got += pipe.drain()
+    assert pipe.outstanding == 0 and len(got) == len(ref)
+    assert max(abs(a - b) for a, b in zip(got, ref)) < 2e-2, (got, ref)
+    with pytest.raises(RuntimeError):
+        pipe.pop()
