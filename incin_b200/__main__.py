@@ -48,6 +48,10 @@ def main(argv=None) -> int:
     i = sub.add_parser("inspect"); i.add_argument("path")
     w = sub.add_parser("watch"); w.add_argument("path"); w.add_argument("--once", action="store_true")
     n = sub.add_parser("new"); n.add_argument("name")
+    t = sub.add_parser("translate", help="explain a pasted shape error (arguments, or standard input when there are none)")
+    t.add_argument("message", nargs="*")
+    t.add_argument("--raw", action="store_true", help="print the message unchanged")
+    t.add_argument("--explain", action="store_true", help="add the rule of the operation family")
     a = ap.parse_args(argv)
     if a.cmd == "doctor":
         from .doctor import doctor
@@ -90,6 +94,10 @@ def main(argv=None) -> int:
             print(render(a.path))
         else:
             watch(a.path)
+    elif a.cmd == "translate":
+        from .diagnostics import translate
+        text = " ".join(a.message) if a.message else sys.stdin.read()
+        print(text.rstrip() if a.raw else translate(text, with_rule=a.explain))
     elif a.cmd == "new":
         d = Path(a.name)
         if d.exists():

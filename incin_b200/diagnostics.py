@@ -31,6 +31,27 @@ _CONV = re.compile(r"expected input\[([\d, ]+)\] to have (\d+) channels, but got
 _TP = re.compile(r"shard \[(\d+), (\d+)\] does not fit the tensor-parallel buffers \[(\d+), (\d+)\]")
 _TMA = re.compile(r"misaligned operand")
 _INDEX = re.compile(r"index (-?\d+) is out of bounds for dimension (\d+) with size (\d+)")
+_STACK = re.compile(r"stack expects each tensor to be equal size, but got \[([\d, ]*)\] at entry (\d+) and \[([\d, ]*)\] at entry (\d+)")
+_DIM_RANGE = re.compile(r"Dimension out of range \(expected to be in range of \[(-?\d+), (-?\d+)\], but got (-?\d+)\)")
+_NARROW = re.compile(r"start \((-?\d+)\) \+ length \((-?\d+)\) exceeds dimension size \((\d+)\)")
+_POOL = re.compile(r"Given input size: \(([\dx]+)\)\. Calculated output size: \(([\dx]+)\)\. Output size is too small")
+_KERNEL = re.compile(r"Calculated padded input size per channel: \(([\d x]+)\)\. Kernel size: \(([\d x]+)\)\. Kernel size can't be greater")
+
+# one sentence per operation family: what the shapes have to satisfy
+RULES = {
+    "matmul": "[M, K] times [K, N] gives [M, N]: the inner extents K must be equal (leading batch axes broadcast).",
+    "broadcast": "Aligned from the last axis, two extents must be equal or one of them must be 1.",
+    "reshape": "The number of elements (product of the extents) must be the same before and after; one axis may be -1.",
+    "concat": "Every axis except the concatenation axis must have the same extent in all inputs.",
+    "stack": "All inputs of a stack must have exactly the same shape; the new axis has one entry per input.",
+    "conv2d": "Input is [N, C, H, W], weight [O, C / groups, kH, kW]: C must agree and the padded H, W must cover the kernel.",
+    "pool2d": "The (padded) spatial extents H, W must be at least the kernel extents, or the output would be empty.",
+    "index": "Indices count from 0; -k addresses the k-th entry from the end; both must stay inside the axis.",
+    "slice": "start + length of a slice must not exceed the extent of the axis it is taken from.",
+    "axis": "An axis argument of a rank-r tensor must lie in [-r, r - 1] (transpose, reductions, flatten, softmax ...).",
+    "tensor-parallel": "Rows per rank are a multiple of 128 and fit max_rows_per_rank; sharded widths fit max_cols.",
+    "gemm": "TMA moves 16-byte units: bf16 row strides and offsets are multiples of 8 elements (4 for fp32).",
+}
 
 
 def explain(message: str) -> Diagnosis | None:
@@ -80,7 +101,42 @@ def explain(message: str) -> Diagnosis | None:
     if m:
         i, dim, size = map(int, m.groups())
         return Diagnosis("index", f"index {i} on axis {dim} of extent {size}", f"valid indices are {-size}..{size - 1}")
+    m = _STACK.search(message)
+    if m:
+        a, ia, b, ib = m.group(1), int(m.group(2)), m.group(3), int(m.group(4))
+        return Diagnosis("stack", f"input #{ia} is [{a}] but input #{ib} is [{b}]",
+                         "stack needs identical shapes; to join along an existing axis use concat instead")
+    m = _DIM_RANGE.search(message)
+    if m:
+        lo, hi, got = map(int, m.groups())
+        return Diagnosis("axis", f"axis {got} was given to a rank-{hi + 1} tensor",
+                         f"valid axes are {lo}..{hi}; a missing batch axis (unsqueeze) is the usual cause")
+    m = _NARROW.search(message)
+    if m:
+        start, length, size = map(int, m.groups())
+        return Diagnosis("slice", f"[{start}, {start + length}) reaches past the axis of extent {size}",
+                         f"the longest slice starting at {start} has length {max(size - start, 0)}")
+    m = _POOL.search(message)
+    if m:
+        return Diagnosis("pool2d", f"an input of {m.group(1)} would give an output of {m.group(2)}",
+                         "the window is larger than the (padded) input: lower kernel_size / stride or add padding")
+    m = _KERNEL.search(message)
+    if m:
+        return Diagnosis("conv2d", f"the kernel ({m.group(2).strip()}) does not fit the padded input ({m.group(1).strip()})",
+                         "raise padding, shrink the kernel, or check that H and W were not swapped with the channel axis")
     return None
+
+
+def translate(message: str, *, with_rule: bool = False) -> str:
+    """The text the ``translate`` command prints for a pasted error message: the message itself, the diagnosis
+    underneath when one of the parsers recognises it, and (``with_rule``) the rule of that operation family."""
+    d = explain(message)
+    if d is None:
+        return message.rstrip()
+    out = [message.rstrip(), str(d)]
+    if with_rule and d.op in RULES:
+        out.append(f"  rule: {RULES[d.op]}")
+    return "\n".join(out)
 
 
 @contextlib.contextmanager

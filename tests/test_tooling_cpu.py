@@ -334,3 +334,32 @@ def test_tensor_creation_is_seeded_and_graph_passes():
     g = G.trace(lambda x, w: x @ w + (w * 2.0).sum(), torch.randn(3, 4), torch.randn(4, 5))
     assert [g.nodes[i].op for i in G.constant_fold(g, {1})] == ["mul", "sum"]
     assert list(G.weight_prepack_plan(g, {1})) == [1]
+
+
+def test_translate_command_and_shape_error_parsers(capsys):
+    """`translate` explains a pasted error: every parser is fed the message PyTorch really raises for its case."""
+    import torch.nn.functional as TF
+    from incin_b200.__main__ import main
+    from incin_b200.diagnostics import RULES, explain, translate
+    cases = {
+        "axis": lambda: torch.zeros(2, 3).transpose(0, 3),
+        "slice": lambda: torch.zeros(12).narrow(0, 5, 10),
+        "pool2d": lambda: TF.max_pool2d(torch.zeros(1, 3, 2, 2), 3),
+        "conv2d": lambda: TF.conv2d(torch.zeros(1, 1, 2, 2), torch.zeros(1, 1, 3, 3)),
+        "stack": lambda: torch.stack([torch.zeros(2, 3), torch.zeros(2, 4)]),
+        "matmul": lambda: torch.zeros(4, 8) @ torch.zeros(16, 8),
+        "concat": lambda: torch.cat([torch.zeros(2, 3), torch.zeros(3, 4)], 1),
+    }
+    for op, fn in cases.items():
+        with pytest.raises(Exception) as ei:
+            fn()
+        d = explain(str(ei.value))
+        assert d is not None and d.op == op and op in RULES, (op, str(ei.value))
+    assert "[5, 15)" in translate("start (5) + length (10) exceeds dimension size (12).")
+    assert translate("nothing to see here") == "nothing to see here"
+    msg = "mat1 and mat2 shapes cannot be multiplied (4x8 and 16x8)"
+    assert main(["translate", "--explain", msg]) == 0
+    out = capsys.readouterr().out
+    assert "looks transposed" in out and "rule:" in out
+    assert main(["translate", "--raw", msg]) == 0
+    assert capsys.readouterr().out.strip() == msg
