@@ -31,6 +31,46 @@ print("final loss", losses[-1])
 '''
 
 
+def _passthrough(a) -> int:
+    """`run`, `test`, `bench`: the counterpart of the reference CLI's cargo pass-through with its diagnostic humaniser
+    (crates/incin/src/bin/cargo-incin.rs:174-200): the wrapped program runs unchanged, shape errors come out explained."""
+    import subprocess
+    from .diagnostics import explain
+    if a.cmd == "run":
+        import runpy
+        import traceback
+        old_argv = sys.argv
+        sys.argv = [a.script, *a.args]
+        try:
+            runpy.run_path(a.script, run_name="__main__")
+            return 0
+        except SystemExit as e:
+            return int(e.code or 0) if not isinstance(e.code, str) else 1
+        except Exception as e:   # noqa: BLE001 - the point is to report whatever the script raised
+            traceback.print_exc()
+            d = explain(str(e))
+            if d is not None:
+                print(d, file=sys.stderr)
+            return 1
+        finally:
+            sys.argv = old_argv
+    if a.cmd == "bench":
+        bench = Path(__file__).resolve().parent.parent / "bench.py"
+        if not bench.exists():
+            print(f"{bench} not found (bench runs from a source tree)", file=sys.stderr)
+            return 1
+        return subprocess.call([sys.executable, str(bench), *a.args])
+    proc = subprocess.Popen([sys.executable, "-m", "pytest", *a.args], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                            text=True)
+    for line in proc.stdout:
+        sys.stdout.write(line)
+        if line.startswith("E "):
+            d = explain(line)
+            if d is not None:
+                sys.stdout.write("".join(f"E   {ln}\n" for ln in str(d).splitlines()))
+    return proc.wait()
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="incin_b200")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -52,6 +92,16 @@ def main(argv=None) -> int:
     t.add_argument("message", nargs="*")
     t.add_argument("--raw", action="store_true", help="print the message unchanged")
     t.add_argument("--explain", action="store_true", help="add the rule of the operation family")
+    sub.add_parser("run", help="run SCRIPT [ARGS...]; a shape error ends with its explanation")
+    sub.add_parser("test", help="pytest pass-through; error lines get their explanation appended")
+    sub.add_parser("bench", help="run bench.py of the source tree with the given flags")
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] in ("run", "test", "bench"):      # everything after the command belongs to the wrapped program
+        import types
+        if argv[0] == "run" and len(argv) < 2:
+            ap.error("run needs a script")
+        return _passthrough(types.SimpleNamespace(cmd=argv[0], script=argv[1] if argv[0] == "run" else None,
+                                                  args=argv[2:] if argv[0] == "run" else argv[1:]))
     a = ap.parse_args(argv)
     if a.cmd == "doctor":
         from .doctor import doctor

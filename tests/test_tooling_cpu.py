@@ -363,3 +363,15 @@ def test_translate_command_and_shape_error_parsers(capsys):
     assert "looks transposed" in out and "rule:" in out
     assert main(["translate", "--raw", msg]) == 0
     assert capsys.readouterr().out.strip() == msg
+
+
+def test_cli_run_passthrough_explains_shape_errors(tmp_path, capsys):
+    from incin_b200.__main__ import main
+    bad = tmp_path / "bad.py"
+    bad.write_text("import sys, torch\nprint('args', sys.argv[1:])\ntorch.zeros(4, 8) @ torch.zeros(16, 8)\n")
+    assert main(["run", str(bad), "--flag", "1"]) == 1
+    cap = capsys.readouterr()
+    assert "args ['--flag', '1']" in cap.out and "[matmul]" in cap.err and "looks transposed" in cap.err
+    good = tmp_path / "good.py"
+    good.write_text("print('fine')\n")
+    assert main(["run", str(good)]) == 0
