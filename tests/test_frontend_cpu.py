@@ -361,3 +361,36 @@ def test_linear_cross_entropy_cpu_twin_and_model_loss():
     l2 = m(tok, tok)
     assert logits.shape[-1] == 50 and torch.isfinite(l2)
     assert abs(l2.item() - torch.nn.functional.cross_entropy(logits.reshape(-1, 50).float(), tok.reshape(-1)).item()) < 1e-4
+
+
+def test_gradcheck_on_functional_ops_and_detects_a_wrong_backward():
+    """Central differences against the analytic gradients of the CPU twins of the model ops, and against a deliberately
+    wrong backward (which must be reported)."""
+    from incin_b200.gradcheck import gradcheck
+    from incin_b200.ops import functional as F
+    g = torch.Generator().manual_seed(3)
+    r = lambda *s: torch.randn(*s, generator=g, requires_grad=True)   # noqa: E731
+    gradcheck(lambda x, w, b: F.linear(x, w, b, act="gelu"), [r(3, 8), r(5, 8), r(5)])
+    gradcheck(lambda x, gm, bt: F.layer_norm(x, gm, bt, 1e-5), [r(4, 16), r(16), r(16)])
+    gradcheck(lambda x, gm: F.rms_norm(x, gm, 1e-5), [r(4, 16), r(16)])
+    tgt = torch.randint(0, 7, (6,), generator=g)
+    gradcheck(lambda lg: F.cross_entropy(lg, tgt, 7), [r(6, 8)])
+    gradcheck(lambda x, w: F.linear_cross_entropy(x, w, tgt, 7), [r(6, 4), r(8, 4)])
+    gradcheck(lambda x, w1, b1, w2, b2: F.mlp(x, w1, b1, w2, b2, act="gelu", residual=x),
+              [r(3, 6), r(12, 6), r(12), r(6, 12), r(6)])
+
+    class Wrong(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, x):
+            ctx.save_for_backward(x)
+            return x * x
+
+        @staticmethod
+        def backward(ctx, dy):
+            (x,) = ctx.saved_tensors
+            return dy * x          # should be 2 x dy
+
+    found = gradcheck(Wrong.apply, [r(5)], raise_on_failure=False)
+    assert found and "central difference" in str(found[0])
+    with pytest.raises(AssertionError):
+        gradcheck(Wrong.apply, [r(5)])

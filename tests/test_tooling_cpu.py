@@ -375,3 +375,13 @@ def test_cli_run_passthrough_explains_shape_errors(tmp_path, capsys):
     good = tmp_path / "good.py"
     good.write_text("print('fine')\n")
     assert main(["run", str(good)]) == 0
+
+
+def test_capability_document_matches_the_registries():
+    """docs/capabilities.md is generated: a change of the registries without regenerating it fails here."""
+    from pathlib import Path
+    from incin_b200.__main__ import CAPABILITIES_HEADER
+    from incin_b200.doctor import capability_report
+    doc = Path(__file__).resolve().parent.parent / "docs" / "capabilities.md"
+    assert doc.read_text() == CAPABILITIES_HEADER + capability_report(), \
+        "run `python -m incin_b200 capabilities --write` after changing incin_b200/core/spec.py"
