@@ -394,3 +394,65 @@ def test_gradcheck_on_functional_ops_and_detects_a_wrong_backward():
     assert found and "central difference" in str(found[0])
     with pytest.raises(AssertionError):
         gradcheck(Wrong.apply, [r(5)])
+
+
+def test_shape_algebra_fuzz_against_torch():
+    """Seeded fuzz of the shape algebra (spatial geometry, reshape inference, batched matmul shapes) against what
+    PyTorch computes, including the rejected cases (the reference fuzzes its shape proofs against an
+    integer oracle: crates/incin-core/tests/{spatial_geometry,rank_matrix,shape_buf}.rs)."""
+    import random
+    import torch.nn.functional as TF
+    from incin_b200.core.shapes import ShapeError, conv2d_out, matmul_shape, reshape_infer
+    rng = random.Random(1234)
+    ok = bad = 0
+    for _ in range(300):
+        h, w = rng.randint(1, 20), rng.randint(1, 20)
+        k = (rng.randint(1, 5), rng.randint(1, 5))
+        st = (rng.randint(1, 3), rng.randint(1, 3))
+        pd = (rng.randint(0, 2), rng.randint(0, 2))
+        dl = (rng.randint(1, 2), rng.randint(1, 2))
+        x = torch.zeros(1, 2, h, w)          # real tensors: the meta kernels do not reject an oversized window
+        wt = torch.zeros(3, 2, *k)
+        try:
+            ref = tuple(TF.conv2d(x, wt, stride=st, padding=pd, dilation=dl).shape[-2:])
+        except RuntimeError:
+            ref = None
+        try:
+            got = conv2d_out(h, w, k, st, pd, dl)
+        except ShapeError:
+            got = None
+        assert got == ref, (h, w, k, st, pd, dl, got, ref)
+        ok += ref is not None
+        bad += ref is None
+    assert ok > 100 and bad > 10
+    for _ in range(300):
+        dims = [rng.randint(1, 6) for _ in range(rng.randint(1, 4))]
+        n = 1
+        for d in dims:
+            n *= d
+        target = [rng.randint(1, 6) for _ in range(rng.randint(1, 4))]
+        if rng.random() < 0.6:
+            target[rng.randrange(len(target))] = -1
+        try:
+            ref = tuple(torch.empty(dims, device="meta").reshape(target).shape)
+        except RuntimeError:
+            ref = None
+        try:
+            got = reshape_infer(n, target)
+        except ShapeError:
+            got = None
+        assert got == ref, (dims, target, got, ref)
+    for _ in range(300):
+        batch_a = [rng.choice([1, 2, 3]) for _ in range(rng.randint(0, 2))]
+        batch_b = [rng.choice([1, 2, 3]) for _ in range(rng.randint(0, 2))]
+        m, k1, k2, n = rng.randint(1, 5), rng.randint(1, 4), rng.randint(1, 4), rng.randint(1, 5)
+        a, b = batch_a + [m, k1], batch_b + [k2, n]
+        try:
+            ref = tuple((torch.empty(a, device="meta") @ torch.empty(b, device="meta")).shape)
+        except RuntimeError:
+            ref = None
+        try:
+            got = tuple(d.size for d in matmul_shape(a, b).dims)
+        except ShapeError:
+            got = None
+        assert got == ref, (a, b, got, ref)
