@@ -5,8 +5,9 @@
 //! (`idx!`), a tape with `backward()`, layer builders, `AdamW` / `Sgd`, a `Trainer` with a plan, and a
 //! `DistributedContext::from_env()` with typed meshes (`mesh!`) and placements.  The default backend is the CPU one:
 //! everything in [`tensor`], [`autograd`], [`nn`], [`optim`] and [`train`] runs on the C++ CPU oracle and tape of
-//! `libincin_host.so`; [`dist`] wraps its TCP rendezvous and the reference (host-memory) collective transport; [`gpu`]
-//! is the typed front end of the sm_100a kernels in `libincin_sm100.so`, which work on device pointers the caller owns.
+//! `libincin_host.so`; [`io`] reads and writes safetensors files with the tensor names of the Python package;
+//! [`dist`] wraps its TCP rendezvous and the reference (host-memory) collective transport; [`gpu`] is the typed
+//! front end of the sm_100a kernels in `libincin_sm100.so`, which work on device pointers the caller owns.
 //!
 //! ```ignore
 //! use incin_b200::prelude::*;
@@ -24,6 +25,7 @@
 pub mod autograd;
 pub mod dist;
 pub mod gpu;
+pub mod io;
 pub mod nn;
 pub mod optim;
 pub mod shape;
@@ -33,6 +35,7 @@ pub mod train;
 pub mod prelude {
     pub use crate::autograd::{no_grad, Gradients, Var};
     pub use crate::dist::{DistributedContext, Mesh, Placement, ReduceOp, ReferenceTransport, Rendezvous};
+    pub use crate::io::{load_safetensors, save_safetensors, Format, NamedTensor};
     pub use crate::nn::{Linear, Mlp, Module};
     pub use crate::optim::{AdamW, Optimizer, Sgd};
     pub use crate::shape::{DynShape, Shape, Shape1, Shape2, Shape3, Shape4, ShapeError, DYN};

@@ -135,3 +135,24 @@ fn reference_transport_and_mesh() {
     let ctx = DistributedContext::from_env().unwrap();
     assert!(ctx.rank < ctx.world);
 }
+
+#[test]
+fn safetensors_roundtrip_keeps_names_shapes_and_values() {
+    let dir = std::env::temp_dir().join(format!("incin_b200_facade_{}", std::process::id()));
+    std::fs::create_dir_all(&dir).unwrap();
+    let path = dir.join("mlp.safetensors");
+    let model = Mlp::build((8, 16, 2), 3);
+    model.save(Format::Safetensors, &path).unwrap();
+    let tensors = load_safetensors(&path).unwrap();
+    let names: Vec<&str> = tensors.iter().map(|t| t.name.as_str()).collect();
+    assert_eq!(names, vec!["0.weight", "0.bias", "2.weight", "2.bias"]);
+    assert_eq!(tensors[0].shape, vec![16, 8]);
+    assert_eq!(tensors[0].data, model.fc1.weight);
+    let mut other = Mlp::build((8, 16, 2), 4);
+    assert_ne!(other.fc2.bias, model.fc2.bias);
+    other.load(&path).unwrap();
+    assert_eq!(other.fc2.bias, model.fc2.bias);
+    let mut wrong = Mlp::build((8, 32, 2), 0);
+    assert!(wrong.load(&path).is_err());
+    std::fs::remove_dir_all(&dir).unwrap();
+}
