@@ -1,6 +1,6 @@
-/* C ABI of libincin_host.so: CPU oracle kernels, tape autograd, N-rank TCP rendezvous and the reference
- * (in-process, host-memory) collective transport.  Every function is plain C, thread-compatible, and allocates only
- * what its result needs. */
+/* C ABI of libincin_host.so: CPU oracle kernels, tape autograd, N-rank TCP rendezvous, the reference
+ * (in-process, host-memory) collective transport and the host runtime (digest, batch loader, telemetry sink).
+ * Every function is plain C, thread-compatible, and allocates only what its result needs. */
 #ifndef INCIN_HOST_H
 #define INCIN_HOST_H
 #include <stdint.h>
@@ -58,6 +58,28 @@ int incin_ref_all_gather(const void* const* in, void* const* out, int world, int
 int incin_ref_reduce_scatter(const void* const* in, void* const* out, int world, int64_t n, int dtype, int op);
 int incin_ref_all_to_all(const void* const* in, void* const* out, int world, int64_t n, int dtype);
 int incin_ref_send_recv(const void* const* in, void* const* out, int world, int64_t n, int dtype, int src, int dst);
+
+/* ---- runtime: digest (FNV-1a 64: plan hashes, mesh ids, autotune identities) ---- */
+uint64_t incin_digest_init(void);
+uint64_t incin_digest_bytes(uint64_t state, const void* data, int64_t n);
+uint64_t incin_digest_number(uint64_t state, uint64_t v);
+uint64_t incin_digest_field(uint64_t state, const void* data, int64_t n);
+uint64_t incin_fnv1a64(const void* data, int64_t n);
+
+/* ---- runtime: batch loader (worker threads, ordered delivery, bounded prefetch ring) ---- */
+int64_t incin_loader_create(const void* a, int64_t row_bytes_a, const void* b, int64_t row_bytes_b, int64_t n_rows, int64_t batch, int shuffle, int drop_last, uint64_t seed, int workers, int depth);
+int64_t incin_loader_start(int64_t h, uint64_t epoch);
+int incin_loader_next(int64_t h, void* out_a, void* out_b, int64_t* rows_out);
+int incin_loader_order(int64_t h, int64_t* out);
+void incin_loader_destroy(int64_t h);
+
+/* ---- runtime: telemetry sink (JSON lines, bounded queue, background writer) ---- */
+int64_t incin_telemetry_open(const char* path, int64_t capacity);
+int incin_telemetry_scalar(int64_t h, const char* name, double value, int64_t step);
+int incin_telemetry_memory(int64_t h, int device, int64_t allocated, int64_t reserved, int64_t step);
+int incin_telemetry_raw(int64_t h, const char* json_line);
+int64_t incin_telemetry_flush(int64_t h);
+int64_t incin_telemetry_close(int64_t h);
 
 #ifdef __cplusplus
 }

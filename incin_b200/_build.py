@@ -4,8 +4,9 @@ Two shared objects are produced under ``incin_b200/lib``:
 
 * ``libincin_sm100.so`` — every CUDA kernel, compiled by nvcc for
   ``compute_100a/sm_100a`` only (no fat binary, no PTX for other targets).
-* ``libincin_host.so``  — the C++ host runtime that needs no GPU: CPU oracle,
-  rendezvous, plan hashing, reference transport, telemetry writer, data loader.
+* ``libincin_host.so``  — the C++ host runtime that needs no GPU: CPU oracle and
+  tape autograd (``cpu_ref``), rendezvous and reference transport (``comm``),
+  plan-hash digest, batch loader and telemetry sink (``runtime``).
 
 Both export a plain C ABI and are loaded with ``ctypes``; they do not link
 against libtorch, so a rebuild takes seconds.  Objects are cached under

@@ -75,13 +75,19 @@ def _to(batch, device):
 class DataLoader:
     def __init__(self, dataset: Dataset, batch_size: int = 1, shuffle: bool = False, workers: int = 0,
                  collate: Callable = default_collate, drop_last: bool = False, seed: int = 0, device=None,
-                 pin_memory: bool | None = None):
+                 pin_memory: bool | None = None, native: bool = False):
         if batch_size < 1:
             raise ValueError("batch_size must be >= 1")
         self.dataset, self.batch_size, self.shuffle, self.workers = dataset, batch_size, shuffle, workers
         self.collate, self.drop_last, self.seed, self.epoch = collate, drop_last, seed, 0
         self.device = torch.device(device) if device is not None else None
         self.pin = (self.device is not None and self.device.type == "cuda") if pin_memory is None else pin_memory
+        # native=True: batches of a TensorDataset are gathered by the C++ loader (csrc/runtime/loader.cpp: worker
+        # threads, ordered delivery, bounded ring) instead of Python threads.  Its permutation is its own (splitmix64
+        # Fisher-Yates of seed + epoch), so the batch sequence differs from the Python path for the same seed.
+        self.native = bool(native) and isinstance(dataset, TensorDataset) and collate is default_collate \
+            and 1 <= len(dataset.tensors) <= 2 and all(t.device.type == "cpu" for t in dataset.tensors)
+        self._native_loader = None
 
     def __len__(self):
         n = len(self.dataset)
@@ -101,7 +107,22 @@ class DataLoader:
         b = self.collate([self.dataset[i] for i in idx])
         return _pin(b) if self.pin else b
 
+    def _native_iter(self):
+        from ..runtime import NativeBatchLoader
+        if self._native_loader is None:
+            ts = self.dataset.tensors
+            self._native_loader = NativeBatchLoader(ts[0], ts[1] if len(ts) == 2 else None, batch_size=self.batch_size,
+                                                    shuffle=self.shuffle, drop_last=self.drop_last, seed=self.seed,
+                                                    workers=max(self.workers, 1), prefetch=4, pin=False)
+        self._native_loader.epoch = self.epoch
+        for b in self._native_loader:
+            b = b if isinstance(b, tuple) else (b,)     # fresh tensors per batch (the loader is not in pinned-ring mode)
+            yield _pin(b) if self.pin else b
+
     def _host_iter(self):
+        if self.native:
+            yield from self._native_iter()
+            return
         if self.workers <= 0:
             for idx in self._batches():
                 yield self._load(idx)

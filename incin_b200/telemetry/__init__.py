@@ -77,6 +77,13 @@ class FileTransport:
         self._f.close()
 
 
+def native_transport(path=None, capacity: int = BULK_CAP):
+    """A transport backed by the native sink (csrc/runtime/telemetry.cpp): ``send`` only queues the line, a C++ thread
+    appends it to the file, and a full queue drops (and counts) instead of blocking the training loop."""
+    from ..runtime import NativeTelemetrySink
+    return NativeTelemetrySink(Path(path) if path else run_dir() / f"{uuid7()}.jsonl", capacity)
+
+
 class SocketTransport:
     """Local IPC: a unix datagram-free stream socket a viewer listens on."""
 

@@ -191,6 +191,10 @@ extern "C" {
     pub fn incin_cpu_unary_f32(x: *const f32, y: *mut f32, n: i64, op: c_int);
     pub fn incin_cumsum(x: *const c_void, out: *mut c_void, outer: c_longlong, n: c_longlong, inner: c_longlong, is_bf16: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_dequantize_q8_0(packed: *const c_void, out: *mut c_void, n: c_longlong, out_bf16: c_int, stream: *mut c_void) -> c_int;
+    pub fn incin_digest_bytes(state: u64, data: *const c_void, n: i64) -> u64;
+    pub fn incin_digest_field(state: u64, data: *const c_void, n: i64) -> u64;
+    pub fn incin_digest_init() -> u64;
+    pub fn incin_digest_number(state: u64, v: u64) -> u64;
     pub fn incin_dp_pad_bytes() -> c_int;
     pub fn incin_dp_reduce_adamw(desc: *const incin_dp_desc, stream: *mut c_void) -> c_int;
     pub fn incin_dropout_bf16(x: *const c_void, y: *mut c_void, n: c_longlong, p: f32, seed: u64, offset: u64, stream: *mut c_void) -> c_int;
@@ -200,6 +204,7 @@ extern "C" {
     pub fn incin_fill_f32(x: *mut f32, value: f32, n: c_longlong, stream: *mut c_void) -> c_int;
     pub fn incin_flash_attn_bwd(desc: *const incin_attn_desc, stream: *mut c_void) -> c_int;
     pub fn incin_flash_attn_fwd(desc: *const incin_attn_desc, stream: *mut c_void) -> c_int;
+    pub fn incin_fnv1a64(data: *const c_void, n: i64) -> u64;
     pub fn incin_gather_last(src: *const c_void, index: *const c_longlong, out: *mut c_void, rows: c_longlong, n_src: c_longlong, n_idx: c_longlong, elem_bytes: c_int, err_flag: *mut c_int, stream: *mut c_void) -> c_int;
     pub fn incin_gather_rows(src: *const c_void, index: *const c_longlong, out: *mut c_void, n_idx: c_longlong, row_elems: c_longlong, src_rows: c_longlong, elem_bytes: c_int, err_flag: *mut c_int, stream: *mut c_void) -> c_int;
     pub fn incin_gemm_bf16(desc: *const incin_gemm_desc, stream: *mut c_void) -> c_int;
@@ -208,6 +213,11 @@ extern "C" {
     pub fn incin_layernorm_bwd_noalloc(dy: *const c_void, x: *const c_void, gamma: *const c_void, mean: *const f32, rstd: *const f32, dx_add: *const c_void, dx: *mut c_void, dgamma: *mut f32, dbeta: *mut f32, rows: c_longlong, C: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_layernorm_bwd_scratch_floats(rows: c_longlong, C: c_int) -> c_longlong;
     pub fn incin_layernorm_fwd(x: *const c_void, gamma: *const c_void, beta: *const c_void, y: *mut c_void, mean: *mut f32, rstd: *mut f32, rows: c_longlong, C: c_int, eps: f32, stream: *mut c_void) -> c_int;
+    pub fn incin_loader_create(a: *const c_void, row_bytes_a: i64, b: *const c_void, row_bytes_b: i64, n_rows: i64, batch: i64, shuffle: c_int, drop_last: c_int, seed: u64, workers: c_int, depth: c_int) -> i64;
+    pub fn incin_loader_destroy(h: i64);
+    pub fn incin_loader_next(h: i64, out_a: *mut c_void, out_b: *mut c_void, rows_out: *mut i64) -> c_int;
+    pub fn incin_loader_order(h: i64, out: *mut i64) -> c_int;
+    pub fn incin_loader_start(h: i64, epoch: u64) -> i64;
     pub fn incin_masked_fill(x: *const c_void, mask: *const u8, out: *mut c_void, value: f32, n: c_longlong, is_bf16: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_maxpool2d_bwd(dy: *const c_void, argmax: *const c_int, dx: *mut c_void, g: *const incin_conv_geom, is_bf16: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_maxpool2d_fwd(x: *const c_void, y: *mut c_void, argmax: *mut c_int, g: *const incin_conv_geom, is_bf16: c_int, stream: *mut c_void) -> c_int;
@@ -267,6 +277,12 @@ extern "C" {
     pub fn incin_tape_set_nan_policy(p: c_int);
     pub fn incin_tape_tensor(data: *const f32, rows: i64, cols: i64, requires_grad: c_int) -> i64;
     pub fn incin_tape_tensor_id(h: i64) -> u64;
+    pub fn incin_telemetry_close(h: i64) -> i64;
+    pub fn incin_telemetry_flush(h: i64) -> i64;
+    pub fn incin_telemetry_memory(h: i64, device: c_int, allocated: i64, reserved: i64, step: i64) -> c_int;
+    pub fn incin_telemetry_open(path: *const c_char, capacity: i64) -> i64;
+    pub fn incin_telemetry_raw(h: i64, json_line: *const c_char) -> c_int;
+    pub fn incin_telemetry_scalar(h: i64, name: *const c_char, value: f64, step: i64) -> c_int;
     pub fn incin_tri(x: *const c_void, out: *mut c_void, batch: c_longlong, rows: c_longlong, cols: c_longlong, diagonal: c_longlong, upper: c_int, elem_bytes: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_where(cond: *const u8, a: *const c_void, b: *const c_void, out: *mut c_void, n: c_longlong, elem_bytes: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_xent_bwd(logits: *mut c_void, targets: *const i64, lse: *const f32, dloss: *const f32, scale: f32, rows: c_longlong, V: c_int, ld: c_longlong, stream: *mut c_void) -> c_int;
