@@ -6,7 +6,7 @@
 //! `DistributedContext::from_env()` with typed meshes (`mesh!`) and placements.  The default backend is the CPU one:
 //! everything in [`tensor`], [`autograd`], [`nn`], [`optim`] and [`train`] runs on the C++ CPU oracle and tape of
 //! `libincin_host.so`; [`io`] reads and writes safetensors files with the tensor names of the Python package;
-//! [`dist`] wraps its TCP rendezvous and the reference (host-memory) collective transport; [`gpu`] is the typed
+//! [`runtime`] wraps the native digest, batch loader and telemetry sink; [`dist`] wraps its TCP rendezvous and the reference (host-memory) collective transport; [`gpu`] is the typed
 //! front end of the sm_100a kernels in `libincin_sm100.so`, which work on device pointers the caller owns.
 //!
 //! ```ignore
@@ -28,6 +28,7 @@ pub mod gpu;
 pub mod io;
 pub mod nn;
 pub mod optim;
+pub mod runtime;
 pub mod shape;
 pub mod tensor;
 pub mod train;

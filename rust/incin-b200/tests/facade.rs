@@ -156,3 +156,42 @@ fn safetensors_roundtrip_keeps_names_shapes_and_values() {
     assert!(wrong.load(&path).is_err());
     std::fs::remove_dir_all(&dir).unwrap();
 }
+
+#[test]
+fn native_runtime_digest_loader_and_telemetry() {
+    use incin_b200::runtime::{BatchLoader, Digest, TelemetrySink};
+    assert_eq!(Digest::new().finish(), 0xCBF29CE484222325);
+    assert_eq!(Digest::new().bytes(b"a").finish(), 0xAF63DC4C8601EC8C);      // published FNV-1a 64 vector
+    assert_ne!(Digest::new().text("ab").finish(), Digest::new().text("a").text("b").finish());   // fields are length-prefixed
+
+    let inputs: Vec<f32> = (0..40).map(|v| v as f32).collect();               // 20 rows of 2
+    let targets: Vec<i64> = (0..20).collect();
+    let mut seen = Vec::new();
+    for workers in [1usize, 4] {
+        let mut ld = BatchLoader::new(&inputs, 2, Some(&targets), 6, true, false, 3, workers, 2).unwrap();
+        assert_eq!(ld.start(0), 4);
+        let mut order = Vec::new();
+        while let Some(b) = ld.next_batch() {
+            assert_eq!(b.inputs.len(), b.rows * 2);
+            for (i, t) in b.targets.iter().enumerate() {
+                assert_eq!(b.inputs[2 * i], (2 * t) as f32);                   // rows of both arrays stay aligned
+            }
+            order.extend(b.targets);
+        }
+        let mut sorted = order.clone();
+        sorted.sort();
+        assert_eq!(sorted, targets);
+        seen.push(order);
+    }
+    assert_eq!(seen[0], seen[1]);                                             // independent of the worker count
+
+    let path = std::env::temp_dir().join(format!("incin_b200_telemetry_{}.jsonl", std::process::id()));
+    {
+        let sink = TelemetrySink::open(&path, 64).unwrap();
+        assert!(sink.scalar("loss", 0.5, 1));
+        assert_eq!(sink.flush(), 0);
+    }
+    let text = std::fs::read_to_string(&path).unwrap();
+    assert!(text.contains("\"kind\":\"scalar\"") && text.contains("\"name\":\"loss\""));
+    std::fs::remove_file(&path).unwrap();
+}
