@@ -73,6 +73,9 @@ int incin_loader_next(int64_t h, void* out_a, void* out_b, int64_t* rows_out);
 int incin_loader_order(int64_t h, int64_t* out);
 void incin_loader_destroy(int64_t h);
 
+/* ---- runtime: arena planning by liveness (greedy first fit; skip[i] != 0 leaves buffer i out, offset -1) ---- */
+int64_t incin_memplan_first_fit(int64_t n, const int64_t* sizes, const int64_t* first, const int64_t* last, const uint8_t* skip, int64_t* offsets_out);
+
 /* ---- runtime: telemetry sink (JSON lines, bounded queue, background writer) ---- */
 int64_t incin_telemetry_open(const char* path, int64_t capacity);
 int incin_telemetry_scalar(int64_t h, const char* name, double value, int64_t step);

@@ -51,8 +51,14 @@ def host_sources() -> list[Path]:
     return out
 
 
-def _headers_mtime() -> float:
-    hs = list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh")) + list(CSRC.rglob("*.hpp"))
+def _headers_mtime(cuda: bool = True) -> float:
+    """Newest header an object of that library can depend on: ``incin_host.h`` declares the host library only, so a
+    change there does not rebuild the CUDA objects (and the ``.cuh`` headers do not rebuild the host objects)."""
+    cuda_abi = {"incin_b200.h", "incin_comm.h", "incin_b200_noalloc.h"}
+    hs = [h for h in CSRC.rglob("*.h") if (h.name in cuda_abi if cuda else h.name not in cuda_abi)]
+    hs += list(CSRC.rglob("*.hpp"))
+    if cuda:
+        hs += list(CSRC.rglob("*.cuh"))
     return max((h.stat().st_mtime for h in hs), default=0.0)
 
 
@@ -106,7 +112,7 @@ def build_host(force: bool = False) -> Path | None:
         return None
     OBJDIR.mkdir(exist_ok=True)
     LIBDIR.mkdir(exist_ok=True)
-    hdr = _headers_mtime()
+    hdr = _headers_mtime(cuda=False)
     jobs, objs = [], []
     for src in srcs:
         obj = OBJDIR / (src.parent.name + "_" + src.stem + ".o")

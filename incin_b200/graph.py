@@ -224,6 +224,23 @@ def liveness(g: Graph) -> dict[int, tuple[int, int]]:
     return {n.id: (n.id, last[n.id]) for n in g.nodes}
 
 
+def _plan_memory_native(g: Graph, live, size) -> "MemoryPlan | None":
+    """The same greedy first fit in native code (csrc/runtime/memplan.cpp); ``None`` when the host library is absent,
+    in which case the Python loop below runs.  ``INCIN_NATIVE_MEMPLAN=0`` forces the Python path."""
+    import os
+    if os.environ.get("INCIN_NATIVE_MEMPLAN", "1") == "0":
+        return None
+    try:
+        from .runtime import first_fit_arena
+        nodes = list(g.nodes)
+        offs, peak = first_fit_arena([size[n.id] for n in nodes], [live[n.id][0] for n in nodes],
+                                     [live[n.id][1] for n in nodes], [n.op == "input" for n in nodes])
+    except (OSError, RuntimeError, AttributeError):
+        return None
+    offsets = {n.id: o for n, o in zip(nodes, offs) if n.op != "input"}
+    return MemoryPlan(offsets, peak, sum(size[n.id] for n in nodes if n.op != "input"))
+
+
 def plan_memory(g: Graph, align: int = 256) -> MemoryPlan:
     """Greedy first-fit reuse of a single arena by liveness (``AllocationPlanner``)."""
     live = liveness(g)
@@ -233,6 +250,9 @@ def plan_memory(g: Graph, align: int = 256) -> MemoryPlan:
         for d in n.shape:
             numel *= d
         size[n.id] = (numel * _ESZ.get(n.dtype, 4) + align - 1) // align * align
+    planned = _plan_memory_native(g, live, size)
+    if planned is not None:
+        return planned
     placed: list[tuple[int, int, int, int]] = []   # (offset, size, first, last)
     offsets, peak = {}, 0
     for n in g.nodes:

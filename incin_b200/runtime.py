@@ -5,6 +5,7 @@
 * :class:`NativeBatchLoader` — worker threads gather rows of in-memory tensors into batches, delivered in order through
   a bounded ring (``loader.cpp``); the batch sequence depends only on (seed, epoch, batch size), not on the number of
   workers.
+* :func:`first_fit_arena` — arena planning by liveness (``memplan.cpp``), the planner of compiled plans.
 * :class:`NativeTelemetrySink` — JSON-lines events through a bounded queue and a background writer thread
   (``telemetry.cpp``), in the schema of :mod:`incin_b200.telemetry`.
 """
@@ -43,6 +44,8 @@ def _lib():
         h.incin_loader_order.argtypes = [i64, vp]
         h.incin_loader_destroy.restype = None
         h.incin_loader_destroy.argtypes = [i64]
+        h.incin_memplan_first_fit.restype = i64
+        h.incin_memplan_first_fit.argtypes = [i64, vp, vp, vp, vp, vp]
         h.incin_telemetry_open.restype = i64
         h.incin_telemetry_open.argtypes = [cp, i64]
         h.incin_telemetry_scalar.restype = C.c_int
@@ -169,6 +172,25 @@ class NativeBatchLoader:
             self.close()
         except Exception:   # interpreter shutdown: the library may already be gone
             pass
+
+
+# ------------------------------------------------------------------------------------------------------ memory plan
+def first_fit_arena(sizes: list[int], first: list[int], last: list[int], skip: list[bool] | None = None
+                    ) -> tuple[list[int], int]:
+    """Offsets (``-1`` for skipped buffers) and arena size of the greedy first-fit plan (``memplan.cpp``)."""
+    n = len(sizes)
+    if not (len(first) == len(last) == n) or (skip is not None and len(skip) != n):
+        raise ValueError("sizes, first, last (and skip) must have the same length")
+    a = torch.tensor(sizes, dtype=torch.int64)
+    f = torch.tensor(first, dtype=torch.int64)
+    la = torch.tensor(last, dtype=torch.int64)
+    sk = torch.tensor([1 if s else 0 for s in skip], dtype=torch.uint8) if skip is not None else None
+    out = torch.empty(n, dtype=torch.int64)
+    peak = _lib().incin_memplan_first_fit(n, a.data_ptr(), f.data_ptr(), la.data_ptr(),
+                                          sk.data_ptr() if sk is not None else None, out.data_ptr())
+    if peak < 0:
+        raise ValueError("the native planner rejected its arguments")
+    return out.tolist(), int(peak)
 
 
 # ------------------------------------------------------------------------------------------------------ telemetry

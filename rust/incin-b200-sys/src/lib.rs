@@ -222,6 +222,7 @@ extern "C" {
     pub fn incin_maxpool2d_bwd(dy: *const c_void, argmax: *const c_int, dx: *mut c_void, g: *const incin_conv_geom, is_bf16: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_maxpool2d_fwd(x: *const c_void, y: *mut c_void, argmax: *mut c_int, g: *const incin_conv_geom, is_bf16: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_mean_f32(x: *const f32, out: *mut f32, n: c_longlong, stream: *mut c_void) -> c_int;
+    pub fn incin_memplan_first_fit(n: i64, sizes: *const i64, first: *const i64, last: *const i64, skip: *const u8, offsets_out: *mut i64) -> i64;
     pub fn incin_p2p_send(peer_dst: *mut c_void, src: *const c_void, bytes: c_longlong, peer_flag: *mut c_void, seq: c_uint, stream: *mut c_void) -> c_int;
     pub fn incin_p2p_wait(local_flag: *const c_void, seq: c_uint, status: *mut c_void, timeout_ms: c_longlong, stream: *mut c_void) -> c_int;
     pub fn incin_peer_barrier(pads: *const *mut c_void, world: c_int, rank: c_int, slot: c_int, status: *mut c_void, stream: *mut c_void) -> c_int;

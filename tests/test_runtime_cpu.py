@@ -146,3 +146,51 @@ def test_dataloader_native_path_and_emitter_over_the_native_sink(tmp_path):
         em.close()
     evs = telemetry.read_run(tmp_path / "e.jsonl")
     assert [e.step for e in evs if e.kind == "scalar"] == list(range(10))
+
+
+def test_native_arena_planner_equals_the_python_planner(monkeypatch):
+    """Random lifetimes: the native first fit and the Python loop place every buffer at the same offset; no two
+    buffers that are alive together overlap."""
+    import incin_b200.graph as G
+    from incin_b200.runtime import first_fit_arena
+    rng = random.Random(9)
+    for _ in range(40):
+        n = rng.randint(1, 40)
+        sizes = [256 * rng.randint(0, 20) for _ in range(n)]
+        first = list(range(n))
+        last = [i + rng.randint(0, 12) for i in range(n)]
+        skip = [rng.random() < 0.15 for _ in range(n)]
+        offs, peak = first_fit_arena(sizes, first, last, skip)
+        placed, ref, ref_peak = [], [], 0          # the Python algorithm of plan_memory, on plain lists
+        for i in range(n):
+            if skip[i]:
+                ref.append(-1)
+                continue
+            busy = sorted((o, s) for o, s, pf, pl in placed if not (pl < first[i] or pf > last[i]))
+            off = 0
+            for o, s in busy:
+                if off + sizes[i] <= o:
+                    break
+                off = max(off, o + s)
+            ref.append(off)
+            placed.append((off, sizes[i], first[i], last[i]))
+            ref_peak = max(ref_peak, off + sizes[i])
+        assert offs == ref and peak == ref_peak
+        for i in range(n):
+            for j in range(i):
+                if skip[i] or skip[j] or last[j] < first[i] or first[j] > last[i] or not sizes[i] or not sizes[j]:
+                    continue
+                assert offs[i] + sizes[i] <= offs[j] or offs[j] + sizes[j] <= offs[i]
+    # plan_memory gives the same plan through either path
+    def fn(a, b):
+        c = a + b
+        d = torch.relu(c)
+        e = d * b
+        return (e + c).sum()
+    g = G.trace(fn, torch.randn(8, 8), torch.randn(8, 8))
+    native = G.plan_memory(g)
+    monkeypatch.setenv("INCIN_NATIVE_MEMPLAN", "0")
+    python = G.plan_memory(g)
+    assert native.offsets == python.offsets and native.peak_bytes == python.peak_bytes
+    with pytest.raises(ValueError):
+        first_fit_arena([1], [0, 1], [0])
