@@ -76,6 +76,9 @@ void incin_loader_destroy(int64_t h);
 /* ---- runtime: arena planning by liveness (greedy first fit; skip[i] != 0 leaves buffer i out, offset -1) ---- */
 int64_t incin_memplan_first_fit(int64_t n, const int64_t* sizes, const int64_t* first, const int64_t* last, const uint8_t* skip, int64_t* offsets_out);
 
+/* ---- runtime: parallel positional reads of byte ranges of one file into caller buffers (0 ok, 1 open, 2 read, 3 args) ---- */
+int incin_file_read_ranges(const char* path, int64_t n, const int64_t* offsets, const int64_t* sizes, void* const* dst, int threads);
+
 /* ---- runtime: telemetry sink (JSON lines, bounded queue, background writer) ---- */
 int64_t incin_telemetry_open(const char* path, int64_t capacity);
 int incin_telemetry_scalar(int64_t h, const char* name, double value, int64_t step);

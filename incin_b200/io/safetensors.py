@@ -22,7 +22,7 @@ _TS = {v: k for k, v in _ST.items()}
 
 def _bytes(t: torch.Tensor) -> bytes:
     t = t.detach().cpu().contiguous()
-    return t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+    return t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""   # reshape: 0-dim tensors too
 
 
 def save_safetensors(tensors: dict[str, torch.Tensor], path, metadata: dict[str, str] | None = None) -> None:
@@ -90,9 +90,27 @@ def read_header(path, limits: ResourceLimits = DEFAULT_LIMITS) -> tuple[dict, in
     return header, 8 + n
 
 
-def load_safetensors(path, limits: ResourceLimits = DEFAULT_LIMITS, names=None) -> dict[str, torch.Tensor]:
+def load_safetensors(path, limits: ResourceLimits = DEFAULT_LIMITS, names=None, *, threads: int = 0,
+                     pin_memory: bool = False) -> dict[str, torch.Tensor]:
+    """``threads > 0`` reads the tensor bytes with that many native readers straight into the result tensors
+    (csrc/runtime/fileio.cpp; ``pin_memory`` makes those pinned, ready for an asynchronous copy to the device): the
+    way to load multi-GB shards.  The header is validated against ``limits`` first in either case."""
     header, base = read_header(path, limits)
     out = {}
+    if threads > 0:
+        from ..runtime import read_ranges
+        ranges = []
+        for name, meta in header.items():
+            if name == "__metadata__" or (names is not None and name not in names):
+                continue
+            lo, _ = meta["data_offsets"]
+            t = torch.empty(meta["shape"], dtype=_TS[meta["dtype"]])
+            if pin_memory and torch.cuda.is_available() and t.numel():
+                t = t.pin_memory()
+            out[name] = t
+            ranges.append((base + lo, t))
+        read_ranges(path, ranges, threads)
+        return out
     with open(path, "rb") as f:
         for name, meta in header.items():
             if name == "__metadata__" or (names is not None and name not in names):

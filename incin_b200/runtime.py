@@ -6,6 +6,8 @@
   a bounded ring (``loader.cpp``); the batch sequence depends only on (seed, epoch, batch size), not on the number of
   workers.
 * :func:`first_fit_arena` — arena planning by liveness (``memplan.cpp``), the planner of compiled plans.
+* :func:`read_ranges` — parallel positional reads of byte ranges into host tensors (``fileio.cpp``), behind the
+  threaded safetensors loader.
 * :class:`NativeTelemetrySink` — JSON-lines events through a bounded queue and a background writer thread
   (``telemetry.cpp``), in the schema of :mod:`incin_b200.telemetry`.
 """
@@ -46,6 +48,8 @@ def _lib():
         h.incin_loader_destroy.argtypes = [i64]
         h.incin_memplan_first_fit.restype = i64
         h.incin_memplan_first_fit.argtypes = [i64, vp, vp, vp, vp, vp]
+        h.incin_file_read_ranges.restype = C.c_int
+        h.incin_file_read_ranges.argtypes = [cp, i64, vp, vp, vp, C.c_int]
         h.incin_telemetry_open.restype = i64
         h.incin_telemetry_open.argtypes = [cp, i64]
         h.incin_telemetry_scalar.restype = C.c_int
@@ -191,6 +195,28 @@ def first_fit_arena(sizes: list[int], first: list[int], last: list[int], skip: l
     if peak < 0:
         raise ValueError("the native planner rejected its arguments")
     return out.tolist(), int(peak)
+
+
+# ------------------------------------------------------------------------------------------------------ file reads
+def read_ranges(path, ranges: list[tuple[int, torch.Tensor]], threads: int = 8) -> None:
+    """Fill each (contiguous, host) tensor with the bytes of ``path`` starting at its offset, with ``threads`` native
+    readers (``fileio.cpp``).  Raises ``OSError`` when the file cannot be opened or ends early."""
+    n = len(ranges)
+    if n == 0:
+        return
+    for _, t in ranges:
+        if t.device.type != "cpu" or not t.is_contiguous():
+            raise ValueError("destinations must be contiguous host tensors")
+    offs = torch.tensor([o for o, _ in ranges], dtype=torch.int64)
+    sizes = torch.tensor([t.numel() * t.element_size() for _, t in ranges], dtype=torch.int64)
+    ptrs = (C.c_void_p * n)(*[t.data_ptr() if t.numel() else None for _, t in ranges])
+    rc = _lib().incin_file_read_ranges(str(path).encode(), n, offs.data_ptr(), sizes.data_ptr(), ptrs, threads)
+    if rc == 1:
+        raise OSError(f"cannot open {path}")
+    if rc == 2:
+        raise OSError(f"{path}: read error or file shorter than its header says")
+    if rc:
+        raise ValueError("bad arguments to the native reader")
 
 
 # ------------------------------------------------------------------------------------------------------ telemetry

@@ -201,6 +201,7 @@ extern "C" {
     pub fn incin_embedding_bwd(dout: *const c_void, tokens: *const i64, dwte: *mut f32, dwpe: *mut f32, B: c_longlong, T: c_int, C: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_embedding_bwd_sorted(dout: *const c_void, order: *const c_longlong, seg_start: *const c_longlong, seg_token: *const c_longlong, n_segments: c_longlong, dwte: *mut f32, dwpe: *mut f32, B: c_longlong, T: c_int, C: c_int, vocab: c_longlong, stream: *mut c_void) -> c_int;
     pub fn incin_embedding_fwd(tokens: *const i64, wte: *const c_void, wpe: *const c_void, out: *mut c_void, B: c_longlong, T: c_int, C: c_int, stream: *mut c_void) -> c_int;
+    pub fn incin_file_read_ranges(path: *const c_char, n: i64, offsets: *const i64, sizes: *const i64, dst: *const *mut c_void, threads: c_int) -> c_int;
     pub fn incin_fill_f32(x: *mut f32, value: f32, n: c_longlong, stream: *mut c_void) -> c_int;
     pub fn incin_flash_attn_bwd(desc: *const incin_attn_desc, stream: *mut c_void) -> c_int;
     pub fn incin_flash_attn_fwd(desc: *const incin_attn_desc, stream: *mut c_void) -> c_int;

@@ -194,3 +194,34 @@ def test_native_arena_planner_equals_the_python_planner(monkeypatch):
     assert native.offsets == python.offsets and native.peak_bytes == python.peak_bytes
     with pytest.raises(ValueError):
         first_fit_arena([1], [0, 1], [0])
+
+
+def test_threaded_safetensors_load_equals_the_plain_one(tmp_path):
+    from incin_b200.io.safetensors import load_safetensors, save_safetensors
+    g = torch.Generator().manual_seed(2)
+    tensors = {
+        "a.weight": torch.randn(300, 257, generator=g),
+        "a.bias": torch.randn(257, generator=g).to(torch.bfloat16),
+        "ids": torch.randint(0, 1000, (4097,), generator=g),
+        "half": torch.randn(3, 5, 7, generator=g).to(torch.float16),
+        "mask": torch.randint(0, 2, (33,), generator=g).to(torch.uint8),
+        "empty": torch.empty(0, 4),
+        "scalar": torch.tensor(3.5),
+    }
+    path = tmp_path / "m.safetensors"
+    save_safetensors(tensors, path, metadata={"step": "7"})
+    plain = load_safetensors(path)
+    for threads in (1, 4):
+        fast = load_safetensors(path, threads=threads)
+        assert fast.keys() == plain.keys() == tensors.keys()
+        for k in tensors:
+            assert fast[k].dtype == tensors[k].dtype and fast[k].shape == tensors[k].shape
+            assert torch.equal(fast[k], plain[k]) and torch.equal(fast[k], tensors[k])
+    only = load_safetensors(path, names={"ids"}, threads=2)
+    assert list(only) == ["ids"] and torch.equal(only["ids"], tensors["ids"])
+    # a file that ends before its last tensor does is an error, not a tensor of garbage
+    from incin_b200.runtime import read_ranges
+    with pytest.raises(OSError):
+        read_ranges(path, [(path.stat().st_size - 8, torch.empty(16, dtype=torch.uint8))], 2)
+    with pytest.raises(OSError):
+        read_ranges(tmp_path / "missing.bin", [(0, torch.empty(4, dtype=torch.uint8))], 1)
