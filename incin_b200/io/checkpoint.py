@@ -127,15 +127,17 @@ def save_checkpoint(directory, module: torch.nn.Module, world_size: int = 1,
     os.replace(tmp, d / "manifest.json")   # the manifest lands last: its presence marks a complete checkpoint
 
 
-def load_checkpoint(directory, module: torch.nn.Module, optimizer=None, limits: ResourceLimits = DEFAULT_LIMITS) -> dict:
+def load_checkpoint(directory, module: torch.nn.Module, optimizer=None, limits: ResourceLimits = DEFAULT_LIMITS,
+                    threads: int = 0) -> dict:
+    """``threads > 0`` reads the tensor files with that many native readers (see ``load_safetensors``)."""
     d = Path(directory)
     man = GlobalCheckpointManifest.from_json((d / "manifest.json").read_text())
     if man.version != MANIFEST_VERSION:
         raise ValueError(f"unsupported checkpoint manifest version {man.version}")
-    load_state_dict(module, load_safetensors(d / "model.safetensors", limits))
+    load_state_dict(module, load_safetensors(d / "model.safetensors", limits, threads=threads))
     if optimizer is not None and (d / "optimizer.safetensors").exists():
         from .safetensors import load_metadata
-        osd = load_safetensors(d / "optimizer.safetensors", limits)
+        osd = load_safetensors(d / "optimizer.safetensors", limits, threads=threads)
         osd["step_count"] = int(load_metadata(d / "optimizer.safetensors").get("step_count", "0"))
         optimizer.load_state_dict(osd)
     tj = d / "trainer.json"
@@ -143,11 +145,11 @@ def load_checkpoint(directory, module: torch.nn.Module, optimizer=None, limits: 
 
 
 def load_resharded_checkpoint(directory, rank: int, world_size: int,
-                              limits: ResourceLimits = DEFAULT_LIMITS) -> dict[str, torch.Tensor]:
+                              limits: ResourceLimits = DEFAULT_LIMITS, threads: int = 0) -> dict[str, torch.Tensor]:
     """Rank-local tensors for a job of ``world_size`` ranks, whatever world size wrote the checkpoint."""
     d = Path(directory)
     man = GlobalCheckpointManifest.from_json((d / "manifest.json").read_text())
-    full = load_safetensors(d / "model.safetensors", limits)
+    full = load_safetensors(d / "model.safetensors", limits, threads=threads)
     out = {}
     for name, meta in man.tensors.items():
         t = full[name]

@@ -188,8 +188,11 @@ def test_checkpoint_roundtrip_resharding_and_limits(tmp_path):
     extra = io.load_checkpoint(tmp_path, m2, opt2)
     assert torch.equal(m[0].weight, m2[0].weight) and torch.equal(opt.m, opt2.m) and opt2.step_count == 1
     assert extra["scheduler"]["last_step"] == 7
+    m3 = nn.seq(nn.Linear(16, 8), nn.ReLU(), nn.Linear(8, 4))
+    io.load_checkpoint(tmp_path, m3, threads=3)                     # native threaded readers give the same tensors
+    assert torch.equal(m[2].weight, m3[2].weight)
     for world in (2, 4):
-        parts = [io.load_resharded_checkpoint(tmp_path, r, world) for r in range(world)]
+        parts = [io.load_resharded_checkpoint(tmp_path, r, world, threads=2 if world == 4 else 0) for r in range(world)]
         assert torch.equal(torch.cat([p["0.weight."] for p in parts], 0), m[0].weight.detach())
         assert torch.equal(torch.cat([p["2.weight."] for p in parts], 1), m[2].weight.detach())
         assert torch.equal(parts[1]["0.bias."], m[0].bias.detach())
