@@ -589,13 +589,9 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   const bool prof = use_split && attn_prof_buffer() != nullptr;
   auto kern = use_split ? (prof ? flash_bwd64_kernel<true> : flash_bwd64_kernel<false>) : flash_bwd_kernel<D>;
   const int smem_bytes = use_split ? Fb64::SMEM_BYTES : Cfg::SMEM_BYTES;
-  static bool attr[3] = {false, false, false};
+  static PerDeviceFlags attr[3];
   const int which = use_split ? (prof ? 2 : 1) : 0;
-  if (!attr[which]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
-      return INCIN_ERR_LAUNCH;
-    attr[which] = true;
-  }
+  if (!ensure_dynamic_smem(kern, smem_bytes, attr[which])) return INCIN_ERR_LAUNCH;
   const long long rows = (long long)d->B * d->T * d->Hq;
   const int Tpad = (d->T + FB_T - 1) / FB_T * FB_T;
   const long long prow = (long long)d->B * Tpad * d->Hq;

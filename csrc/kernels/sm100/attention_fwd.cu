@@ -315,12 +315,8 @@ static int launch_fwd(const incin_attn_desc* d, cudaStream_t stream) {
   rc = make_operand_map(&tv, d->v, D, d->T, d->v_stride_t, d->Hkv, d->v_stride_h, d->B, d->v_stride_b, 64, BN);
   if (rc) return rc;
   auto kern = flash_fwd_kernel<D, BN>;
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
-      return INCIN_ERR_LAUNCH;
-    attr = true;
-  }
+  static PerDeviceFlags attr;
+  if (!ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, attr)) return INCIN_ERR_LAUNCH;
   FaParams p;
   p.T = d->T;
   p.Hq = d->Hq;

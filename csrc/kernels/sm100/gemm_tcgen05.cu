@@ -452,12 +452,8 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmKe
                       cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
-      return INCIN_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static PerDeviceFlags attr_set;
+  if (!ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, attr_set)) return INCIN_ERR_LAUNCH;
   int grid = p.total_units < max_ctas ? p.total_units : max_ctas;
   GemmKernelParams q = p;
   if (p.ag_world > 1 || p.rs_push) {
@@ -491,10 +487,10 @@ template <bool A_MN, bool B_MN>
 static int launch_pair_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmKernelParams& p, int tiles_m2, int max_ctas,
                            cudaStream_t stream) {
   auto kern = gemm_tcgen05_pair_kernel<A_MN, B_MN>;
-  static int max_clusters = 0;
+  static PerDeviceFlags attr_set;
+  if (!ensure_dynamic_smem(kern, PairCfg::SMEM_BYTES, attr_set)) return INCIN_ERR_LAUNCH;
+  static int max_clusters = 0;   // the same for every B200 of a node
   if (max_clusters == 0) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES) != cudaSuccess)
-      return INCIN_ERR_LAUNCH;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 74, 1, 1);
     cfg.blockDim = dim3(GEMM_THREADS, 1, 1);

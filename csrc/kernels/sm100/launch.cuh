@@ -35,6 +35,28 @@ inline int pdl_mode() {
   return mode;
 }
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-DEVICE property of a kernel, so "already set" is remembered per
+// device: a process that launches on a second GPU sets it there too instead of launching with the 48 KB default.
+// A static instance is zero-initialised; flags are read and written with atomics because any host thread may launch.
+constexpr int kMaxDevicesPerProcess = 64;
+struct PerDeviceFlags {
+  unsigned char set[kMaxDevicesPerProcess];
+};
+
+template <typename Kern>
+inline bool ensure_dynamic_smem(Kern kern, int bytes, PerDeviceFlags& flags) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  const bool tracked = dev >= 0 && dev < kMaxDevicesPerProcess;
+  if (tracked && __atomic_load_n(&flags.set[dev], __ATOMIC_ACQUIRE)) return true;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  if (tracked) __atomic_store_n(&flags.set[dev], (unsigned char)1, __ATOMIC_RELEASE);
+  return true;
+}
+
 template <bool HEAVY = false, typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args&&... args) {

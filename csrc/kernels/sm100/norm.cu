@@ -589,11 +589,12 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, con
     const int chunks = param_chunks(rows, C);
     const int iters = (C + 255) / 256;
     const size_t acc_bytes = (size_t)NORM_WARPS * 2 * iters * 256 * sizeof(float);   // 16 KB per 256 columns
-    static bool attr_set[5] = {false, false, false, false, false};   // per kernel (RMS is a template argument here)
+    static PerDeviceFlags attr_set[5];   // per kernel (RMS is a template argument here) and per device
+    bool attr_ok = true;
     auto go = [&](auto kern) {
-      if (!attr_set[iters]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)acc_bytes) != cudaSuccess) return;
-        attr_set[iters] = true;
+      if (!ensure_dynamic_smem(kern, (int)acc_bytes, attr_set[iters])) {
+        attr_ok = false;   // nothing was launched: the partial sums must not be reduced either
+        return;
       }
       launch_pdl(kern, dim3((unsigned)chunks), dim3(NORM_WARPS * 32), acc_bytes, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                  (const __nv_bfloat16*)gamma, mean, rstd, (const __nv_bfloat16*)dx_add, (__nv_bfloat16*)dx, scratch, rows, C, rp);
@@ -602,6 +603,7 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, con
     else if (iters == 2) go(norm_bwd_fused_kernel<RMS, 2>);
     else if (iters == 3) go(norm_bwd_fused_kernel<RMS, 3>);
     else go(norm_bwd_fused_kernel<RMS, 4>);
+    if (!attr_ok) return INCIN_ERR_DRIVER;
     launch_pdl(norm_bwd_param_final, dim3((C + 31) / 32), dim3(32 * PF_LANES), 0, s, scratch, dgamma, dbeta, C, chunks);
     return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
   }

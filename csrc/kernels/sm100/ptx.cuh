@@ -113,7 +113,9 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       "r"(c3)
       : "memory");
 }
-// untiled bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16), local memory only
+// untiled bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16).  The source may be this
+// GPU's memory or a peer-mapped buffer of another GPU (the all-gather copy CTAs of the GEMM pull peers' shards with
+// it); it never carries a cluster-multicast qualifier.
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_u32(smem_dst)),

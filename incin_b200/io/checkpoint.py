@@ -107,6 +107,13 @@ def save_checkpoint(directory, module: torch.nn.Module, world_size: int = 1,
     d = Path(directory)
     d.mkdir(parents=True, exist_ok=True)
     sd = state_dict(module)
+    store = getattr(optimizer, "store", None)
+    if store is not None:
+        # flat optimiser: the module parameters are views of the low-precision shadow; the fp32 master weights are
+        # the state to keep, under the same (trailing-dot) names
+        for name, master in store.named_master():
+            if name + "." in sd:
+                sd[name + "."] = master.detach()
     placements = placements or {}
     man = GlobalCheckpointManifest(MANIFEST_VERSION, world_size, {})
     for k, t in sd.items():
@@ -134,7 +141,18 @@ def load_checkpoint(directory, module: torch.nn.Module, optimizer=None, limits: 
     man = GlobalCheckpointManifest.from_json((d / "manifest.json").read_text())
     if man.version != MANIFEST_VERSION:
         raise ValueError(f"unsupported checkpoint manifest version {man.version}")
-    load_state_dict(module, load_safetensors(d / "model.safetensors", limits, threads=threads))
+    sd = load_safetensors(d / "model.safetensors", limits, threads=threads)
+    load_state_dict(module, sd)
+    store = getattr(optimizer, "store", None)
+    if store is not None:
+        # the parameters just written are views of the shadow; the optimiser steps from the fp32 master, which
+        # must receive the loaded values too (else the next step recomputes the shadow from stale masters)
+        with torch.no_grad():
+            for name, master in store.named_master():
+                v = sd.get(name + ".", sd.get(name))
+                if v is not None:
+                    master.copy_(v.to(device=master.device, dtype=master.dtype).reshape(master.shape))
+            store.sync_shadow_from_master()
     if optimizer is not None and (d / "optimizer.safetensors").exists():
         from .safetensors import load_metadata
         osd = load_safetensors(d / "optimizer.safetensors", limits, threads=threads)

@@ -61,16 +61,32 @@ def read_header(path, limits: ResourceLimits = DEFAULT_LIMITS) -> tuple[dict, in
             raise LimitError("file too short for a safetensors header")
         (n,) = struct.unpack("<Q", raw)
         limits.check("header size", n, min(limits.max_header_bytes, size - 8))
-        header = json.loads(f.read(n))
+        try:
+            header = json.loads(f.read(n))
+        except (ValueError, UnicodeDecodeError) as e:
+            raise LimitError(f"safetensors header is not valid JSON: {e}") from None
     if not isinstance(header, dict):
         raise LimitError("safetensors header is not an object")
+
+    def _int(v) -> bool:
+        return isinstance(v, int) and not isinstance(v, bool)
     limits.check("tensor count", len(header), limits.max_tensor_count)
     total = 0
     for name, meta in header.items():
         if name == "__metadata__":
+            if not isinstance(meta, dict) or not all(isinstance(v, str) for v in meta.values()):
+                raise LimitError("__metadata__ is not an object of strings")
             limits.check("metadata entries", len(meta), limits.max_metadata_entries)
             continue
         limits.check("name length", len(name.encode()), limits.max_name_bytes)
+        # the header is untrusted: every entry must be {dtype: str, shape: [int >= 0], data_offsets: [int, int]}
+        if not isinstance(meta, dict) or not isinstance(meta.get("dtype"), str):
+            raise LimitError(f"{name}: entry is not an object with a dtype string")
+        shape, offs = meta.get("shape"), meta.get("data_offsets")
+        if not isinstance(shape, list) or not all(_int(d) and d >= 0 for d in shape):
+            raise LimitError(f"{name}: shape is not a list of non-negative integers")
+        if not isinstance(offs, list) or len(offs) != 2 or not all(_int(o) for o in offs):
+            raise LimitError(f"{name}: data_offsets is not a pair of integers")
         limits.check("rank", len(meta["shape"]), limits.max_rank)
         for d in meta["shape"]:
             limits.check("dimension", d, limits.max_dimension)

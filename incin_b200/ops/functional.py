@@ -87,11 +87,15 @@ class _Linear(torch.autograd.Function):
         dpre = K.act_bwd(dy, aux, ctx.act) if ctx.act != nat.ACT_NONE else dy
         if w.requires_grad:
             G.mm_tn_accum(dpre, x, main_grad(w), max_ctas=_max_ctas)
-            _ready(w)
         if ctx.has_bias and ctx.bias.requires_grad:
             K.colsum_accum(dpre, main_grad(ctx.bias))
-            _ready(ctx.bias)
         dx = G.mm_nn(dpre, w, max_ctas=_max_ctas) if ctx.needs_input_grad[0] else None
+        # A ready callback may launch the data-parallel update, which overwrites w on another stream: it is
+        # called only after the last kernel that reads w (the data-gradient product above) has been enqueued.
+        if w.requires_grad:
+            _ready(w)
+        if ctx.has_bias and ctx.bias.requires_grad:
+            _ready(ctx.bias)
         return dx, None, None, (dy if ctx.has_res else None), None
 
 
@@ -176,17 +180,20 @@ class _MLP(torch.autograd.Function):
         x, w1, w2, pre, h = ctx.saved_tensors
         dy = _c(dy)
         G.mm_tn_accum(dy, h, main_grad(w2), max_ctas=_max_ctas)
-        _ready(w2)
         if ctx.b2 is not None:
             K.colsum_accum(dy, main_grad(ctx.b2))
-            _ready(ctx.b2)
         dpre = G.mm_nn(dy, w2, act=_DACT[ctx.act], aux=pre, max_ctas=_max_ctas)
+        # ready callbacks come after the last enqueued reader of each weight (they may start its update)
+        _ready(w2)
+        if ctx.b2 is not None:
+            _ready(ctx.b2)
         G.mm_tn_accum(dpre, x, main_grad(w1), max_ctas=_max_ctas)
-        _ready(w1)
         if ctx.b1 is not None:
             K.colsum_accum(dpre, main_grad(ctx.b1))
-            _ready(ctx.b1)
         dx = G.mm_nn(dpre, w1, max_ctas=_max_ctas) if ctx.needs_input_grad[0] else None
+        _ready(w1)
+        if ctx.b1 is not None:
+            _ready(ctx.b1)
         return dx, None, None, None, None, (dy if ctx.has_res else None), None
 
 
@@ -368,10 +375,11 @@ class _LinearCrossEntropy(torch.autograd.Function):
         g = _c(dloss.float()).reshape(1)
         if w.requires_grad:
             G.mm_tn_accum(dlogits, x2, main_grad(w), max_ctas=_max_ctas, alpha_dev=g)
-            _ready(w)
         dx = None
         if ctx.needs_input_grad[0]:
             dx = G.mm_nn(dlogits, w, max_ctas=_max_ctas, alpha_dev=g).reshape(ctx.x_shape)
+        if w.requires_grad:
+            _ready(w)   # after the data-gradient product, the last reader of w
         return dx, None, None, None
 
 

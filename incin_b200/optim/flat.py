@@ -108,13 +108,21 @@ class _FlatOptimizer:
     """Shared hyper-parameter plumbing: values live in an 8-float device tensor that the kernel reads, so a
     captured CUDA graph of the step stays valid while lr and the step counter change between replays."""
 
+    HYPER_RING = 8   # host-side staging slots: at most this many steps may be enqueued ahead of the device
+
     def __init__(self, store: ParamStore, lr: float):
         self.store = store
         self.lr = float(lr)
         self.step_count = 0
-        self._hyper_host = torch.zeros(8, dtype=torch.float32)
+        # The host-to-device copy of the hyper-parameters reads pinned memory when it EXECUTES, not when it is
+        # enqueued, so a single staging buffer would let step N pick up step N+1's lr and step count whenever the
+        # host runs ahead (graph replay, pipelined steps).  Each step therefore gets its own slot of a small ring;
+        # a slot is rewritten only after the event recorded behind its previous copy has completed.
+        self._hyper_ring = [torch.zeros(8, dtype=torch.float32) for _ in range(self.HYPER_RING)]
+        self._hyper_events: list = [None] * self.HYPER_RING
         if store.device.type == "cuda":
-            self._hyper_host = self._hyper_host.pin_memory()
+            self._hyper_ring = [h.pin_memory() for h in self._hyper_ring]
+        self._hyper_host = self._hyper_ring[0]
         self.hyper = torch.zeros(8, dtype=torch.float32, device=store.device)
         self.grad_scale = 1.0
 
@@ -124,8 +132,17 @@ class _FlatOptimizer:
     def prepare_step(self) -> None:
         """Advance the step counter and push hyper-parameters to the device (outside any graph capture)."""
         self.step_count += 1
+        slot = self.step_count % self.HYPER_RING
+        ev = self._hyper_events[slot]
+        if ev is not None:
+            ev.synchronize()      # the copy that last read this slot has run
+        self._hyper_host = self._hyper_ring[slot]
         self._fill_hyper()
         self.hyper.copy_(self._hyper_host, non_blocking=True)
+        if self.hyper.is_cuda:
+            if ev is None:
+                ev = self._hyper_events[slot] = torch.cuda.Event()
+            ev.record()
 
     def launch(self) -> None:
         """Enqueue the update kernel on the current stream (capturable)."""

@@ -189,7 +189,6 @@ class _ColumnParallel(torch.autograd.Function):
             if w.requires_grad:
                 G.gemm(dy, gathered, main_grad(w), M=n, N=Kd, K=M, lda=n_total, ldb=Kd, ldc=Kd, a_mn=True, b_mn=True,
                        accumulate=True, splits=G.auto_splits(n, Kd, M), a_offset=off)
-                _ready(w)
             off += n
         # dx = dy @ [W0; W1; ...]: partial over the output shards -> reduce-scatter over rows
         if len(weights) == 1:
@@ -197,6 +196,9 @@ class _ColumnParallel(torch.autograd.Function):
         else:
             wcat = torch.cat(list(weights), dim=0)
             dx = tp.gemm_scatter(dy, wcat, b_mn=True)
+        for w in weights:      # after the last enqueued reader of the weights (a ready callback may start their update)
+            if w.requires_grad:
+                _ready(w)
         return (dx, None) + (None,) * len(weights)
 
 

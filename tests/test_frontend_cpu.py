@@ -206,6 +206,75 @@ def test_checkpoint_roundtrip_resharding_and_limits(tmp_path):
         io.load_safetensors(bad)
 
 
+def test_checkpoint_resume_restores_fp32_master_of_flat_optimizer(tmp_path):
+    """With a low-precision shadow the optimiser steps from fp32 master weights: a resumed run must get those
+    back (not the rounded shadow, not its own fresh initialisation) and then take bit-identical steps."""
+    from incin_b200.optim import AdamW, make_store
+
+    def build(seed):
+        nn.manual_seed(seed)
+        m = nn.seq(nn.Linear(16, 8), nn.ReLU(), nn.Linear(8, 4))
+        return m, AdamW(make_store(m, compute_dtype=torch.bfloat16), lr=1e-2)
+
+    def one_step(m, opt, x):
+        opt.zero_grad()
+        m(x.to(torch.bfloat16)).float().sum().backward()
+        opt.store.collect_autograd_grads()
+        opt.step()
+
+    x = torch.randn(3, 16)
+    m, opt = build(1)
+    one_step(m, opt, x)
+    io.save_checkpoint(tmp_path, m, optimizer=opt)
+    saved = io.load_safetensors(tmp_path / "model.safetensors")
+    assert saved["0.weight."].dtype == torch.float32                       # the master, not the bf16 shadow
+    m2, opt2 = build(2)                                                    # different initial weights
+    io.load_checkpoint(tmp_path, m2, opt2)
+    assert torch.equal(opt.store.master, opt2.store.master)
+    assert torch.equal(opt.store.shadow, opt2.store.shadow) and torch.equal(m[0].weight, m2[0].weight)
+    one_step(m, opt, x)
+    one_step(m2, opt2, x)
+    assert torch.equal(opt.store.master, opt2.store.master) and torch.equal(m[2].weight, m2[2].weight)
+
+
+def test_flat_optimizer_hyper_ring_keeps_steps_apart():
+    from incin_b200.optim import AdamW, make_store
+    nn.manual_seed(0)
+    m = nn.seq(nn.Linear(4, 4))
+    opt = AdamW(make_store(m), lr=1.0)
+    seen = []
+    for step in range(1, 2 * opt.HYPER_RING + 2):
+        opt.set_lr(1.0 / step)
+        opt.prepare_step()
+        seen.append(opt._hyper_host)
+        assert float(opt.hyper[5]) == step and abs(float(opt.hyper[0]) - 1.0 / step) < 1e-7
+    assert len({id(h) for h in seen[:opt.HYPER_RING]}) == opt.HYPER_RING   # consecutive steps never share a slot
+
+
+def test_safetensors_malformed_headers_raise_limit_error(tmp_path):
+    import struct
+
+    def write(header: bytes, payload: bytes = b""):
+        p = tmp_path / "m.safetensors"
+        p.write_bytes(struct.pack("<Q", len(header)) + header + payload)
+        return p
+
+    cases = [
+        b'{"a": 3}',                                                              # entry is not an object
+        b'{"a": {"dtype": "F32", "shape": [2]}}',                                 # missing offsets
+        b'{"a": {"dtype": "F32", "shape": [-1, -4], "data_offsets": [0, 16]}}',   # negative dims (numel 4 would match)
+        b'{"a": {"dtype": "F32", "shape": [1.5], "data_offsets": [0, 4]}}',       # non-integer dim
+        b'{"a": {"dtype": "F32", "shape": "x", "data_offsets": [0, 4]}}',
+        b'{"a": {"dtype": 7, "shape": [1], "data_offsets": [0, 4]}}',
+        b'{"a": {"dtype": "F32", "shape": [1], "data_offsets": [0, "4"]}}',
+        b'{"__metadata__": [1, 2]}',
+        b'{not json',
+    ]
+    for h in cases:
+        with pytest.raises(io.LimitError):
+            io.load_safetensors(write(h, b"\0" * 16))
+
+
 def test_exporters_and_quantisation(tmp_path):
     from incin_b200.ops.quant import dequantize_q8_0, quantize_q8_0, quantized_matmul
     w = torch.randn(8, 64)
