@@ -561,36 +561,40 @@ static long long* attn_prof_buffer() {
 
 }  // namespace incin
 #include "attention_bwd64.cuh"
+#include "attention_bwd128.cuh"
 namespace incin {
 
 template <int D>
 static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   using Cfg = FbCfg<D>;
+  // head_dim 64 runs the half-split kernel and head_dim 128 the kernel pipelined over 64-query steps (tensor core and
+  // softmax-gradient threads overlap in both); INCIN_ATTN_BWD_SPLIT=0 selects the one-tile-at-a-time kernel instead
+  static const bool split_on = [] {
+    const char* e = std::getenv("INCIN_ATTN_BWD_SPLIT");
+    return !(e && e[0] == '0');
+  }();
+  const bool use_split = (D == 64) && split_on;
+  const bool use_steps = (D == 128) && split_on;
+  const int q_box_rows = use_steps ? Fb128::TQ : FB_T;   // rows of one Q / dO load
   CUtensorMap tq, tk, tv, tdo;
-  int rc = make_operand_map(&tq, d->q, D, d->T, d->q_stride_t, d->Hq, d->q_stride_h, d->B, d->q_stride_b, 64, FB_T);
+  int rc = make_operand_map(&tq, d->q, D, d->T, d->q_stride_t, d->Hq, d->q_stride_h, d->B, d->q_stride_b, 64, q_box_rows);
   if (rc) return rc;
   rc = make_operand_map(&tk, d->k, D, d->T, d->k_stride_t, d->Hkv, d->k_stride_h, d->B, d->k_stride_b, 64, FB_T);
   if (rc) return rc;
   rc = make_operand_map(&tv, d->v, D, d->T, d->v_stride_t, d->Hkv, d->v_stride_h, d->B, d->v_stride_b, 64, FB_T);
   if (rc) return rc;
-  rc = make_operand_map(&tdo, d->d_o, D, d->T, d->do_stride_t, d->Hq, d->do_stride_h, d->B, d->do_stride_b, 64, FB_T);
+  rc = make_operand_map(&tdo, d->d_o, D, d->T, d->do_stride_t, d->Hq, d->do_stride_h, d->B, d->do_stride_b, 64, q_box_rows);
   if (rc) return rc;
   // O is read and dQ written 16 bytes at a time
   if ((reinterpret_cast<uintptr_t>(d->o) & 15) || (reinterpret_cast<uintptr_t>(d->dq) & 15) || (d->o_stride_t % 8) ||
       (d->o_stride_h % 8) || (d->o_stride_b % 8) || (d->dq_stride_t % 8) || (d->dq_stride_h % 8) || (d->dq_stride_b % 8))
     return INCIN_ERR_ALIGNMENT;
-  // head_dim 64 runs the half-split kernel (tensor core and softmax-gradient threads overlap); INCIN_ATTN_BWD_SPLIT=0
-  // selects the one-tile-at-a-time kernel instead
-  static const bool split64 = [] {
-    const char* e = std::getenv("INCIN_ATTN_BWD_SPLIT");
-    return !(e && e[0] == '0');
-  }();
-  const bool use_split = (D == 64) && split64;
-  const bool prof = use_split && attn_prof_buffer() != nullptr;
-  auto kern = use_split ? (prof ? flash_bwd64_kernel<true> : flash_bwd64_kernel<false>) : flash_bwd_kernel<D>;
-  const int smem_bytes = use_split ? Fb64::SMEM_BYTES : Cfg::SMEM_BYTES;
-  static PerDeviceFlags attr[3];
-  const int which = use_split ? (prof ? 2 : 1) : 0;
+  const bool prof = (use_split || use_steps) && attn_prof_buffer() != nullptr;
+  auto kern = use_split ? (prof ? flash_bwd64_kernel<true> : flash_bwd64_kernel<false>)
+                        : (use_steps ? (prof ? flash_bwd128_kernel<true> : flash_bwd128_kernel<false>) : flash_bwd_kernel<D>);
+  const int smem_bytes = use_split ? Fb64::SMEM_BYTES : (use_steps ? Fb128::SMEM_BYTES : Cfg::SMEM_BYTES);
+  static PerDeviceFlags attr[5];
+  const int which = use_split ? (prof ? 2 : 1) : (use_steps ? (prof ? 4 : 3) : 0);
   if (!ensure_dynamic_smem(kern, smem_bytes, attr[which])) return INCIN_ERR_LAUNCH;
   const long long rows = (long long)d->B * d->T * d->Hq;
   const int Tpad = (d->T + FB_T - 1) / FB_T * FB_T;
@@ -620,9 +624,9 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.lse = d->lse;
   p.delta = d->delta;
   p.dq_accum = d->dq_accum;
-  if (use_split) {
+  if (use_split || use_steps) {   // dQ partials leave through bulk tensor reduces of 32-column boxes
     rc = make_f32_reduce_map(&p.tm_dq, d->dq_accum, D, d->T, (long long)d->Hq * D, d->Hq, D, d->B,
-                             (long long)d->T * d->Hq * D, FB_T);
+                             (long long)d->T * d->Hq * D, use_steps ? Fb128::TQ : FB_T);
     if (rc) return rc;
   }
   p.dk = (__nv_bfloat16*)d->dk;
@@ -636,7 +640,7 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
   p.status = (int*)d->status;
   p.prof = attn_prof_buffer();
   dim3 grid(p.n_tiles, d->Hkv, d->B);
-  if (use_split) {   // persistent: one CTA per SM (or per item when there are fewer items)
+  if (use_split || use_steps) {   // persistent: one CTA per SM (or per item when there are fewer items)
     const long long items = (long long)p.n_tiles * d->Hkv * d->B;
     static const int sms = [] { int dev = 0, n = 148; cudaGetDevice(&dev); cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev); return n; }();
     grid = dim3((unsigned)(items < sms ? items : sms), 1, 1);
@@ -657,11 +661,19 @@ static int launch_bwd(const incin_attn_desc* d, cudaStream_t stream) {
 
 }  // namespace incin
 
+// Experiment switches of the profiling instantiation of the head_dim-128 backward (slot 15 of the profile buffer);
+// only has an effect with INCIN_ATTN_PROF=1.
+extern "C" int incin_attn_prof_flags(long long flags) {
+  long long* b = incin::attn_prof_buffer();
+  if (!b) return INCIN_ERR_UNSUPPORTED;
+  return cudaMemcpy(b + 15, &flags, sizeof(long long), cudaMemcpyHostToDevice) == cudaSuccess ? INCIN_OK : INCIN_ERR_DRIVER;
+}
+
 extern "C" int incin_attn_prof_read(long long* out16) {
   long long* b = incin::attn_prof_buffer();
   if (!b || !out16) return INCIN_ERR_UNSUPPORTED;
   if (cudaMemcpy(out16, b, 16 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess) return INCIN_ERR_DRIVER;
-  cudaMemset(b, 0, 16 * sizeof(long long));
+  cudaMemset(b, 0, 15 * sizeof(long long));   // slot 15 holds the experiment switches
   return INCIN_OK;
 }
 

@@ -166,12 +166,41 @@ def bench_bandwidth(args) -> None:
     rec("fill_f32 124M", timeit(lambda: K.fill_f32_(gr, 0.0)), n * 4)
 
 
+def attention_error_vs_cpu(qkv: torch.Tensor, do: torch.Tensor, H: int, D: int, b: int, h: int) -> dict:
+    """Max abs error of the product path's output and gradients for one (batch, head) slice against an fp32 CPU
+    reference of the same math (scores, causal mask, softmax, weighted sum; gradients by CPU autograd): the oracle
+    the reference's CPU backend defines (crates/incin-backends/src/cpu/ops/shape_ops.rs:1245-1269)."""
+    import math
+    from incin_b200.ops import functional as F
+    B, T, _ = qkv.shape
+    x = qkv.detach().clone().requires_grad_()
+    out = F.causal_attention(x, H, D)
+    out.backward(do)
+    xs = qkv.detach().view(B, T, 3 * H, D)
+    q, k, v = (xs[b, :, i * H + h].float().cpu().requires_grad_() for i in range(3))
+    s = (q @ k.t()) * (1.0 / math.sqrt(D))
+    s = s.masked_fill(~torch.ones(T, T, dtype=torch.bool).tril(), float("-inf"))
+    ref = torch.softmax(s, dim=-1) @ v
+    ref.backward(do.view(B, T, H, D)[b, :, h].float().cpu())
+    g = x.grad.view(B, T, 3 * H, D)
+    got = {"out": out.detach().view(B, T, H, D)[b, :, h], "dq": g[b, :, h], "dk": g[b, :, H + h], "dv": g[b, :, 2 * H + h]}
+    want = {"out": ref.detach(), "dq": q.grad, "dk": k.grad, "dv": v.grad}
+    res = {}
+    for name in got:
+        a, r = got[name].float().cpu(), want[name]
+        res[f"max_abs_err_{name}"] = round(float((a - r).abs().max()), 5)
+        res[f"ref_max_{name}"] = round(float(r.abs().max()), 4)
+    return res
+
+
 def bench_attention(args) -> None:
     from incin_b200.ops import functional as F
     pk = peaks()
     for (B, H, T, D) in [(8, 12, 1024, 64), (8, 32, 4096, 128)] if not args.one else [tuple(args.one) + (args.head_dim,)]:
-        qkv = (torch.randn(B, T, 3 * H * D, device="cuda") * 0.5).bfloat16().requires_grad_()
-        do = torch.randn(B, T, H * D, device="cuda").bfloat16()
+        # Q, K, V and dO ~ N(0, 1) from seed 0, softmax scale 1 / sqrt(head_dim)
+        gen = torch.Generator(device="cuda").manual_seed(0)
+        qkv = torch.randn(B, T, 3 * H * D, device="cuda", generator=gen).bfloat16().requires_grad_()
+        do = torch.randn(B, T, H * D, device="cuda", generator=gen).bfloat16()
         for impl in args.impls.split(","):
             F.set_attention_impl(impl)
             if impl == "composed" and B * H * T * T * 2 > 12e9:
@@ -189,6 +218,10 @@ def bench_attention(args) -> None:
                               "fwd_bwd_tflops": round(3.5 * fl_f / t_fb / 1e9, 1),
                               "frac_of_measured_burst": round(3.5 * fl_f / t_fb / 1e9 / pk["bf16_tflops"], 3)}),
                   flush=True)
+            if impl in ("auto", "flash") and not args.no_check:
+                err = attention_error_vs_cpu(qkv, do, H, D, B - 1, H - 1)
+                print(json.dumps({"B": B, "H": H, "T": T, "D": D, "impl": impl, "slice": [B - 1, H - 1],
+                                  "vs": "fp32 CPU reference", **err}), flush=True)
         # library reference (baseline, not product): torch SDPA
         q, k, v = (torch.randn(B, H, T, D, device="cuda").bfloat16().requires_grad_() for _ in range(3))
         dob = torch.randn(B, H, T, D, device="cuda").bfloat16()
@@ -212,6 +245,7 @@ def main() -> None:
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-lib", action="store_true", help="skip the cuBLAS / SDPA comparison")
+    ap.add_argument("--no-check", action="store_true", help="attention: skip the error check against the fp32 CPU reference")
     args = ap.parse_args()
     {"gemm": bench_gemm, "bandwidth": bench_bandwidth, "attention": bench_attention}[args.op](args)
 

@@ -23,9 +23,17 @@ def _err(a, b):
     return (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-6)
 
 
+def _elementwise(a, b, what):
+    from _tol import check_close
+    # P and dS are rounded to bf16 before the second products, so gradients carry a few bf16 ulps of noise
+    check_close(a, b, rtol=3e-2, atol_rms=8e-2, min_cos=0.9998, what=what)
+
+
 @pytest.mark.parametrize("B,T,Hq,Hkv,D", [(1, 128, 1, 1, 64), (2, 256, 2, 2, 64), (1, 384, 4, 2, 64), (2, 200, 2, 1, 64),
                                           (1, 128, 1, 1, 128), (1, 512, 2, 2, 128), (1, 320, 4, 1, 128),
-                                          (1, 1024, 2, 2, 64), (2, 640, 6, 2, 64)])
+                                          (1, 1024, 2, 2, 64), (2, 640, 6, 2, 64),
+                                          (1, 2048, 2, 1, 128), (2, 1000, 4, 2, 128), (1, 64, 2, 2, 128),
+                                          (1, 2304, 1, 1, 128)])
 def test_flash_fwd_bwd(B, T, Hq, Hkv, D):
     from incin_b200.ops import attention as A
     from incin_b200.ops import gemm as G
@@ -45,6 +53,10 @@ def test_flash_fwd_bwd(B, T, Hq, Hkv, D):
     assert _err(q1.grad, qf.grad) < 3e-2, ("dq", _err(q1.grad, qf.grad))
     assert _err(k1.grad, kf.grad) < 3e-2, ("dk", _err(k1.grad, kf.grad))
     assert _err(v1.grad, vf.grad) < 3e-2, ("dv", _err(v1.grad, vf.grad))
+    _elementwise(out, ref, f"attn out T{T} D{D}")
+    _elementwise(q1.grad, qf.grad, f"attn dq T{T} D{D}")
+    _elementwise(k1.grad, kf.grad, f"attn dk T{T} D{D}")
+    _elementwise(v1.grad, vf.grad, f"attn dv T{T} D{D}")
 
 
 def test_flash_packed_matches_composed():

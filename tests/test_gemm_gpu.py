@@ -11,10 +11,14 @@ def _ref_inputs(shape, seed):
 
 
 def _close(out, ref, tol=2e-2):
+    from _tol import check_close
+    fp32_out = out.dtype == torch.float32
     out, ref = out.float(), ref.float()
     err = (out - ref).abs().max().item()
     scale = ref.abs().max().item() + 1e-6
     assert err <= tol * scale, f"max abs err {err} vs scale {scale}"
+    # elementwise: bf16 outputs carry two ulps of rounding, fp32 outputs only the accumulation order
+    check_close(out, ref, rtol=4e-3 if fp32_out else 1.6e-2, atol_rms=4e-3 if fp32_out else 1.5e-2, what="gemm")
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 256), (300, 200, 136), (1024, 768, 768), (77, 50, 8)])
