@@ -95,7 +95,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer (one per CTA)
-    if (lane == 0) {
+    // the whole warp walks the loop (warp-uniform waits and coordinate arithmetic); one elected lane issues the copies
+    const bool lead_lane = elect_one() != 0;
+    {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -110,9 +112,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           }
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
-          if (leader) mbar_expect_tx(&full_bar[stage], 2 * Cfg::STAGE_BYTES);
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
           const int k0 = kb * BK;
+          if (lead_lane) {
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * Cfg::STAGE_BYTES);
           if (!A_MN) {
             tma_load_4d_pair(sa, &tmA, bar, k0, m0, w.b_lo, w.b_hi);
           } else {
@@ -126,6 +129,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             for (int c = 0; c < Cfg::BN_CTA / 64; ++c)
               tma_load_4d_pair(sb + c * 8192, &tmB, bar, n0 + c * 64, k0, w.b_lo, w.b_hi);
           }
+          }
+          __syncwarp();
           if (++stage == Cfg::STAGES) {
             stage = 0;
             phase ^= 1;
@@ -135,7 +140,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer (leader CTA only)
-    if (leader && lane == 0) {
+    // the whole warp of the leader CTA walks the loop; one elected lane issues
+    const bool lead_lane = elect_one() != 0;
+    if (leader) {
       constexpr uint32_t idesc = make_idesc_bf16(256, Cfg::BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
@@ -162,18 +169,21 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t a_adv = A_MN ? (uint64_t)(k * 2048 >> 4) : (uint64_t)(k * 32 >> 4);
             const uint64_t b_adv = B_MN ? (uint64_t)(k * 2048 >> 4) : (uint64_t)(k * 32 >> 4);
-            umma_f16_ss_pair(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+            if (lead_lane) umma_f16_ss_pair(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           // the stage is free in BOTH CTAs once these MMAs have read it
           const uint32_t eb = smem_u32(&empty_bar[stage]);
-          umma_commit_pair(map_to_cta(eb, 0));
-          umma_commit_pair(map_to_cta(eb, 1));
+          if (lead_lane) {
+            umma_commit_pair(map_to_cta(eb, 0));
+            umma_commit_pair(map_to_cta(eb, 1));
+          }
+          __syncwarp();
           if (++stage == Cfg::STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) {   // accumulator complete: tell the epilogue warps of both CTAs
+        if (ok && lead_lane) {   // accumulator complete: tell the epilogue warps of both CTAs
           const uint32_t tb = smem_u32(&tfull_bar[acc]);
           umma_commit_pair(map_to_cta(tb, 0));
           umma_commit_pair(map_to_cta(tb, 1));

@@ -183,7 +183,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    // The whole warp walks the loop so that waits, loop control and coordinate arithmetic stay warp-uniform; one
+    // elected lane issues the copies.
+    const bool leader = elect_one() != 0;
+    {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -215,8 +218,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
-          mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
           const int k0 = kb * BK;
+          if (leader) {
+          mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
           if (!A_MN) {
             tma_load_4d(sa, &tmA, &full_bar[stage], k0, m0, w.b_lo, w.b_hi);
           } else {
@@ -231,6 +235,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int c = 0; c < BN / 64; ++c)
               tma_load_4d(sb + c * 8192, &tmB, &full_bar[stage], n0 + c * 64, k0, w.b_lo, w.b_hi);
           }
+          }
+          __syncwarp();
           if (++stage == Cfg::STAGES) {
             stage = 0;
             phase ^= 1;
@@ -240,7 +246,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop (warp-uniform waits and descriptor arithmetic); one elected lane issues.
+    const bool leader = elect_one() != 0;
+    {
       // The issuing thread is latency critical (one dependent instruction stream feeding the tensor pipe), so the
       // operand kind is a compile-time constant of the loop: one copy of the loop per kind, chosen once.
       auto issue_all = [&](auto kind_tag) {
@@ -274,7 +282,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               const uint64_t adesc = make_smem_desc(sa, 16, 1024), bdesc = make_smem_desc(sb, 16, 1024);
 #pragma unroll
               for (int k = 0; k < BK / UMMA_K; ++k)
-                umma_tf32_ss(d_tmem, adesc + (uint64_t)(k * 32 >> 4), bdesc + (uint64_t)(k * 32 >> 4), idesc,
+                if (leader) umma_tf32_ss(d_tmem, adesc + (uint64_t)(k * 32 >> 4), bdesc + (uint64_t)(k * 32 >> 4), idesc,
                              (kb > w.kb0 || k > 0) ? 1u : 0u);
             } else {
               // descriptors: high halves are constants of the kernel, the low half is the stage's address field plus
@@ -283,17 +291,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               const uint32_t a_lo = a_lo0 + stage * (Cfg::STAGE_BYTES >> 4), b_lo = a_lo + b_lo_off;
 #pragma unroll
               for (int k = 0; k < BK / UMMA_K; ++k)
-                umma_f16_ss_lohi(d_tmem, a_lo + (A_MN ? (k * 2048 >> 4) : (k * 32 >> 4)), desc_hi,
+                if (leader) umma_f16_ss_lohi(d_tmem, a_lo + (A_MN ? (k * 2048 >> 4) : (k * 32 >> 4)), desc_hi,
                                  b_lo + (B_MN ? (k * 2048 >> 4) : (k * 32 >> 4)), desc_hi, idesc,
                                  (kb > w.kb0 || k > 0) ? 1u : 0u);
             }
-            umma_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
+            if (leader) umma_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
+            __syncwarp();
             if (++stage == Cfg::STAGES) {
               stage = 0;
               phase ^= 1;
             }
           }
-          if (ok) umma_commit(&tfull_bar[acc]);  // accumulator complete
+          if (ok && leader) umma_commit(&tfull_bar[acc]);  // accumulator complete
         }
       };
       if (p.in_kind == 0) issue_all(std::integral_constant<int, 0>{});
