@@ -163,7 +163,9 @@ flash_bwd128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    // (the whole warp walks the loop: warp-uniform waits and address arithmetic; one elected lane issues the copies)
+    const bool leader = elect_one() != 0;
+    {
       int base = 0;   // query steps handed to the pipeline so far (all roles count the same way)
       bool ok = true;
       for (int r = 0; ok; ++r) {
@@ -174,27 +176,32 @@ flash_bwd128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int n_iters = steps_per_head * group;
         // K / V of the previous item are still operands until its last product has been committed
         if (r > 0 && !mbar_wait(kv_empty, (r - 1) & 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
-        mbar_expect_tx(kv_full, 2 * Cfg::KV_BYTES);
+        if (leader) {
+          mbar_expect_tx(kv_full, 2 * Cfg::KV_BYTES);
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          tma_load_4d(sK + c * Cfg::KV_CHUNK, &tmK, kv_full, c * 64, kv0, hkv, b);
-          tma_load_4d(sV + c * Cfg::KV_CHUNK, &tmV, kv_full, c * 64, kv0, hkv, b);
+          for (int c = 0; c < D / 64; ++c) {
+            tma_load_4d(sK + c * Cfg::KV_CHUNK, &tmK, kv_full, c * 64, kv0, hkv, b);
+            tma_load_4d(sV + c * Cfg::KV_CHUNK, &tmV, kv_full, c * 64, kv0, hkv, b);
+          }
         }
         for (int it = 0; it < n_iters; ++it) {
           const int g = base + it, s = g % ST;
           const int hq = hkv * group + it / steps_per_head;
           const int q0 = (2 * kv_tile + it % steps_per_head) * TQ;
           if (!mbar_wait(&q_empty[s], ((g / ST) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) { ok = false; break; }
-          mbar_expect_tx(&q_full[s], 2 * Cfg::Q_BYTES + 2 * TQ * 4);
+          if (leader) {
+            mbar_expect_tx(&q_full[s], 2 * Cfg::Q_BYTES + 2 * TQ * 4);
 #pragma unroll
-          for (int c = 0; c < D / 64; ++c) {
-            tma_load_4d(sQ + s * Cfg::Q_BYTES + c * Cfg::Q_CHUNK, &tmQ, &q_full[s], c * 64, q0, hq, b);
-            tma_load_4d(sDO + s * Cfg::Q_BYTES + c * Cfg::Q_CHUNK, &tmDO, &q_full[s], c * 64, q0, hq, b);
+            for (int c = 0; c < D / 64; ++c) {
+              tma_load_4d(sQ + s * Cfg::Q_BYTES + c * Cfg::Q_CHUNK, &tmQ, &q_full[s], c * 64, q0, hq, b);
+              tma_load_4d(sDO + s * Cfg::Q_BYTES + c * Cfg::Q_CHUNK, &tmDO, &q_full[s], c * 64, q0, hq, b);
+            }
+            // per-query statistics of this step: two 256-byte bulk copies (rows are padded to the 128-row tile edge)
+            const long long stat = ((long long)b * p.Hq + hq) * p.Tpad + q0;
+            bulk_load_1d(sStat + s * 2 * TQ, p.lse + stat, TQ * 4, &q_full[s]);
+            bulk_load_1d(sStat + s * 2 * TQ + TQ, p.delta + stat, TQ * 4, &q_full[s]);
           }
-          // per-query statistics of this step: two 256-byte bulk copies (rows are padded to the 128-row tile edge)
-          const long long stat = ((long long)b * p.Hq + hq) * p.Tpad + q0;
-          bulk_load_1d(sStat + s * 2 * TQ, p.lse + stat, TQ * 4, &q_full[s]);
-          bulk_load_1d(sStat + s * 2 * TQ + TQ, p.delta + stat, TQ * 4, &q_full[s]);
+          __syncwarp();
         }
         base += n_iters;
       }

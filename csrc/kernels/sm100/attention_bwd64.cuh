@@ -148,7 +148,9 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    // (the whole warp walks the loop: warp-uniform waits and address arithmetic; one elected lane issues the copies)
+    const bool leader = elect_one() != 0;
+    {
       int base = 0;   // query tiles handed to the pipeline so far (all roles count the same way)
       bool ok = true;
       for (int r = 0; ok; ++r) {
@@ -159,27 +161,34 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int n_iters = tiles_per_head * group;
         // K / V of the previous item are still operands until its last product has been committed
         if (r > 0 && !mbar_wait(kv_empty, (r - 1) & 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
-        mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
-        tma_load_4d(sK, &tmK, kv_full, 0, kv0, hkv, b);
-        tma_load_4d(sV, &tmV, kv_full, 0, kv0, hkv, b);
+        if (leader) {
+          mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
+          tma_load_4d(sK, &tmK, kv_full, 0, kv0, hkv, b);
+          tma_load_4d(sV, &tmV, kv_full, 0, kv0, hkv, b);
+        }
         for (int it = 0; it < n_iters; ++it) {
           const int g = base + it, s = g % ST;
           const int hq = hkv * group + it / tiles_per_head;
           const int q0 = (kv_tile + it % tiles_per_head) * FB_T;
           if (!mbar_wait(&q_empty[s], ((g / ST) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) { ok = false; break; }
-          mbar_expect_tx(&q_full[s], 2 * Cfg::TILE_BYTES + 2 * FB_T * 4);
-          tma_load_4d(sQ + s * Cfg::TILE_BYTES, &tmQ, &q_full[s], 0, q0, hq, b);
-          tma_load_4d(sDO + s * Cfg::TILE_BYTES, &tmDO, &q_full[s], 0, q0, hq, b);
-          const long long stat = ((long long)b * p.Hq + hq) * p.Tpad + q0;
-          bulk_load_1d(sStat + s * 2 * FB_T, p.lse + stat, FB_T * 4, &q_full[s]);
-          bulk_load_1d(sStat + s * 2 * FB_T + FB_T, p.delta + stat, FB_T * 4, &q_full[s]);
+          if (leader) {
+            mbar_expect_tx(&q_full[s], 2 * Cfg::TILE_BYTES + 2 * FB_T * 4);
+            tma_load_4d(sQ + s * Cfg::TILE_BYTES, &tmQ, &q_full[s], 0, q0, hq, b);
+            tma_load_4d(sDO + s * Cfg::TILE_BYTES, &tmDO, &q_full[s], 0, q0, hq, b);
+            const long long stat = ((long long)b * p.Hq + hq) * p.Tpad + q0;
+            bulk_load_1d(sStat + s * 2 * FB_T, p.lse + stat, FB_T * 4, &q_full[s]);
+            bulk_load_1d(sStat + s * 2 * FB_T + FB_T, p.delta + stat, FB_T * 4, &q_full[s]);
+          }
+          __syncwarp();
         }
         base += n_iters;
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // (the whole warp walks the loop; one elected lane executes the tcgen05 instructions)
+    const bool leader = elect_one() != 0;
+    {
       constexpr uint32_t id_half = make_idesc_bf16(FB_T, H, false, false);   // S^T / dP^T of one half: [128 kv] x [64 q]
       constexpr uint32_t id_kmn = make_idesc_bf16(FB_T, D, false, true);     // dV, dK
       constexpr uint32_t id_mnmn = make_idesc_bf16(FB_T, D, true, true);     // dQ
@@ -201,13 +210,13 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint32_t do16 = b16 + ((Cfg::OFF_DO + s * Cfg::TILE_BYTES + h * (H * 128)) >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          umma_f16_ss(tmem_base + Cfg::COL_ST + h * H, desc(k16 + kk * 2, kLoK), desc(q16 + kk * 2, kLoK), id_half,
+          if (leader) umma_f16_ss(tmem_base + Cfg::COL_ST + h * H, desc(k16 + kk * 2, kLoK), desc(q16 + kk * 2, kLoK), id_half,
                       kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          umma_f16_ss(tmem_base + Cfg::COL_DPT + h * H, desc(v16 + kk * 2, kLoK), desc(do16 + kk * 2, kLoK), id_half,
+          if (leader) umma_f16_ss(tmem_base + Cfg::COL_DPT + h * H, desc(v16 + kk * 2, kLoK), desc(do16 + kk * 2, kLoK), id_half,
                       kk > 0 ? 1u : 0u);
-        umma_commit(&sdp[h]);
+        if (leader) umma_commit(&sdp[h]);
       };
       int base = 0;
       bool ok = true;
@@ -250,29 +259,32 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const uint32_t acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
             for (int kk = 0; kk < FB_T / 16; ++kk)   // dV += P^T dO: reduction over the 128 queries, 16 per step
-              umma_f16_ss(tmem_base + Cfg::COL_DV, desc((kk < 4 ? p16a : p16b) + (kk & 3) * 2, kLoK),
+              if (leader) umma_f16_ss(tmem_base + Cfg::COL_DV, desc((kk < 4 ? p16a : p16b) + (kk & 3) * 2, kLoK),
                           desc(do16 + kk * 128, kLoMN), id_kmn, kk > 0 ? 1u : acc0);
 #pragma unroll
             for (int kk = 0; kk < FB_T / 16; ++kk)   // dK += dS^T Q
-              umma_f16_ss(tmem_base + Cfg::COL_DK, desc((kk < 4 ? ds16a : ds16b) + (kk & 3) * 2, kLoK),
+              if (leader) umma_f16_ss(tmem_base + Cfg::COL_DK, desc((kk < 4 ? ds16a : ds16b) + (kk & 3) * 2, kLoK),
                           desc(q16 + kk * 128, kLoMN), id_kmn, kk > 0 ? 1u : acc0);
             // dQ partial = dS K: A = dS in MN-major form, two 64-query chunks CHUNK_BYTES apart starting at the
             // lower of the two addresses: (a0, b) for even tiles, (b, a1) for odd tiles (rows come out rotated by 64)
             const uint32_t dsf16 = b16 + ((Cfg::OFF_DS + (bq ? Cfg::CHUNK_BYTES : 0)) >> 4);
 #pragma unroll
             for (int kk = 0; kk < FB_T / 16; ++kk)
-              umma_f16_ss(tmem_base + Cfg::COL_DQ + bq * D, desc(dsf16 + kk * 128, kLoMN), desc(k16 + kk * 128, kLoMN),
+              if (leader) umma_f16_ss(tmem_base + Cfg::COL_DQ + bq * D, desc(dsf16 + kk * 128, kLoMN), desc(k16 + kk * 128, kLoMN),
                           id_mnmn, kk > 0 ? 1u : 0u);
-            umma_commit(&q_empty[sj]);
-            umma_commit(&dq_full[bq]);
-            if (it == n_iters) umma_commit(kv_empty);   // last product of the item: K / V may be replaced
+            if (leader) {
+              umma_commit(&q_empty[sj]);
+              umma_commit(&dq_full[bq]);
+              if (it == n_iters) umma_commit(kv_empty);   // last product of the item: K / V may be replaced
+            }
+            __syncwarp();
           }
           if (it < n_iters) scores(1, g % ST);   // half b: its columns were read out before pds[1] of the previous tile
         }
         base += n_iters;
       }
 #undef PROF_WAIT
-      if constexpr (PROF) {
+      if (PROF && leader) {
         t_all = now() - t_all;
         t_issue = t_all - t_kv - t_q - t_pds0 - t_pds1 - t_dq;
         atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + 0), (unsigned long long)t_all);

@@ -117,25 +117,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   pdl_wait();                // no global memory was touched above
 
   if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(q_full, Cfg::Q_BYTES);
+    // producer: the whole warp walks the loop (warp-uniform waits and address arithmetic), one elected lane issues
+    const bool leader = elect_one() != 0;
+    {
+      if (leader) {
+        mbar_expect_tx(q_full, Cfg::Q_BYTES);
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c) tma_load_4d(sQ + c * (FA_BM * 128), &tmQ, q_full, c * 64, q0, hq, b);
+        for (int c = 0; c < D / 64; ++c) tma_load_4d(sQ + c * (FA_BM * 128), &tmQ, q_full, c * 64, q0, hq, b);
+      }
       for (int j = 0; j < n_tiles; ++j) {
         const int ks = j & 1;
         if (!mbar_wait(&k_empty[ks], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
-        mbar_expect_tx(&k_full[ks], Cfg::K_BYTES);
+        if (leader) {
+          mbar_expect_tx(&k_full[ks], Cfg::K_BYTES);
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(sK + ks * Cfg::K_BYTES + c * (BN * 128), &tmK, &k_full[ks], c * 64, j * BN, hkv, b);
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_4d(sK + ks * Cfg::K_BYTES + c * (BN * 128), &tmK, &k_full[ks], c * 64, j * BN, hkv, b);
+        }
         if (!mbar_wait(v_empty, (j & 1) ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
-        mbar_expect_tx(v_full, Cfg::V_BYTES);
+        if (leader) {
+          mbar_expect_tx(v_full, Cfg::V_BYTES);
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) tma_load_4d(sV + c * (BN * 128), &tmV, v_full, c * 64, j * BN, hkv, b);
+          for (int c = 0; c < D / 64; ++c) tma_load_4d(sV + c * (BN * 128), &tmV, v_full, c * 64, j * BN, hkv, b);
+        }
+        __syncwarp();
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // issuer: the whole warp walks the loop, one elected lane executes the tcgen05 instructions
+    const bool leader = elect_one() != 0;
+    {
       constexpr uint32_t idesc_s = make_idesc_bf16(FA_BM, BN, false, false);
       constexpr uint32_t idesc_o = make_idesc_bf16(FA_BM, D, false, true);
       // S_{j+1} = Q K_{j+1}^T is issued as soon as the softmax threads have S_j in registers, so it and O += P_j V_j
@@ -150,10 +161,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint64_t ad = make_smem_desc(aq + (kk >> 2) * (FA_BM * 128) + (kk & 3) * 32, 16, 1024);
           const uint64_t bd = make_smem_desc(bk + (kk >> 2) * (BN * 128) + (kk & 3) * 32, 16, 1024);
-          umma_f16_ss(tmem_S, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
+          if (leader) umma_f16_ss(tmem_S, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&k_empty[ks]);
-        umma_commit(s_full);
+        if (leader) {
+          umma_commit(&k_empty[ks]);
+          umma_commit(s_full);
+        }
+        __syncwarp();
         return true;
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusTimeoutFull);
@@ -168,10 +182,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int kk = 0; kk < BN / 16; ++kk) {
           const uint64_t ad = make_smem_desc(ap + (kk >> 2) * (FA_BM * 128) + (kk & 3) * 32, 16, 1024);
           const uint64_t bd = make_smem_desc(bv + kk * 2048, BN * 128, 1024);  // V^T: MN-major, 16 kv rows per step
-          umma_f16_ss(tmem_O, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          if (leader) umma_f16_ss(tmem_O, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(v_empty);
-        umma_commit(pv_done);
+        if (leader) {
+          umma_commit(v_empty);
+          umma_commit(pv_done);
+        }
+        __syncwarp();
       }
     }
   } else {

@@ -1,6 +1,6 @@
 // CTA-pair variant of the tcgen05 GEMM (cta_group::2): two CTAs of a 2-CTA cluster, on neighbouring SMs, compute
 // one 256 x 256 output tile.  Each CTA loads 128 rows of A and 128 of the tile's 256 B rows per k-block (32 KB per
-// stage, seven stages), the leader CTA issues M=256, N=256 MMAs for the pair, and each CTA's tensor memory receives
+// stage, seven stages, or six plus the output staging area), the leader CTA issues M=256, N=256 MMAs for the pair, and each CTA's tensor memory receives
 // the accumulator of its own 128 rows.  Per FLOP a CTA reads one third less shared memory than the single-CTA
 // 128 x 256 tile, which is the bound of that kernel; the operand traffic from L2 halves for B.
 //
@@ -16,16 +16,19 @@
 
 namespace incin {
 
+template <bool STG = true>
 struct PairCfg {
   static constexpr int BN = 256;                 // tile N (pair)
   static constexpr int BN_CTA = 128;             // B rows each CTA loads
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN_CTA * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = 7;
+  static constexpr int STAGES = STG ? 6 : 7;     // 192 KB of operands + 32 KB of output staging, or 224 KB of operands
   static constexpr int ACC_STRIDE = 256;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int STG_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = STG_OFF + (STG ? STG_BYTES : 0);
+  static constexpr int SMEM_BYTES = BAR_OFF + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 // tile order of the pair kernel: 256-row blocks, m fastest (neighbouring pairs share a B tile in L2)
@@ -46,14 +49,15 @@ __device__ __forceinline__ Unit decode_pair_unit(const GemmKernelParams& p, int 
 }
 
 // p.tiles_n counts 256-wide tiles here; p.total_units = tiles_m2 * tiles_n * batch * splits
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool STG>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux,
                          const GemmKernelParams p, const int tiles_m2) {
-  using Cfg = PairCfg;
+  using Cfg = PairCfg<STG>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
   uint64_t* full_bar = bars;                      // [STAGES]  (the leader's are the ones in use)
   uint64_t* empty_bar = bars + Cfg::STAGES;       // [STAGES]
   uint64_t* tfull_bar = bars + 2 * Cfg::STAGES;   // [2]
@@ -81,6 +85,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     mbar_init_fence();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (p.tma_out && p.out_fp32) tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
@@ -209,6 +214,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       const bool row_ok = m < p.M;
       const long long cbase = (long long)w.b_lo * p.c_stride_lo + (long long)w.b_hi * p.c_stride_hi + (long long)m * p.ldc;
       const bool vec_ok = (p.ldc % 8 == 0) && (p.c_stride_lo % 8 == 0) && (p.c_stride_hi % 8 == 0);
+      if (STG && p.tma_out) {
+        const int col_first = half * (Cfg::BN / 2);
+        epilogue_staged(p, &tmC, &tmAux, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * Cfg::ACC_STRIDE + col_first,
+                        smem + Cfg::STG_OFF + (warp - 2) * STG_WARP_BYTES, w.m_blk * 256 + (int)rank * BM + quarter * 32,
+                        n0 + col_first, Cfg::BN / 2, w.b_lo, w.b_hi, cbase, row_ok, alpha, lane);
+      } else {
 #pragma unroll 1
       for (int c = half * CHUNKS_PER_HALF; c < (half + 1) * CHUNKS_PER_HALF; ++c) {
         uint32_t r[32];
@@ -218,10 +229,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         if (row_ok && nc < p.N) epilogue_chunk(p, r, p.C, cbase, nc, vec_ok, alpha);
         __syncwarp();
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
     }
+    if (STG && p.tma_out && p.out_fp32 && lane == 0) bulk_wait_all();   // this warp's staged boxes have been written before the CTA retires
   }
 
   // common exit: every thread of both CTAs arrives here, also after a timed-out wait

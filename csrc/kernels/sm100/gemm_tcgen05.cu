@@ -28,17 +28,23 @@
 #include <string>
 #include <cstring>
 #include <cstdio>
+#include <cstdlib>
+
+#ifndef INCIN_GEMM_TMA_OUT_DEFAULT
+#define INCIN_GEMM_TMA_OUT_DEFAULT 4
+#endif
 
 namespace incin {
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool STG>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux,
                     const GemmKernelParams p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, STG>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
   uint64_t* full_bar = bars;                      // [STAGES]
   uint64_t* empty_bar = bars + Cfg::STAGES;       // [STAGES]
   uint64_t* tfull_bar = bars + 2 * Cfg::STAGES;   // [2]
@@ -68,6 +74,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     mbar_init_fence();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (p.tma_out && p.out_fp32) tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -339,6 +346,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       const bool vec_ok = (p.ldc % 8 == 0) && (p.c_stride_lo % 8 == 0) && (p.c_stride_hi % 8 == 0);
+      if (STG && p.tma_out) {
+        // the two warps of a lane quarter split the tile's columns in multiples of 64: 128 + 128, 128 + 64, 64 + 64, 64 + 0
+        constexpr int COLS0 = (BN / 64 + 1) / 2 * 64;
+        const int col_first = half ? COLS0 : 0, ncols = half ? BN - COLS0 : COLS0;
+        epilogue_staged(p, &tmC, &tmAux, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * Cfg::ACC_STRIDE + col_first,
+                        smem + Cfg::STG_OFF + (warp - 2) * STG_WARP_BYTES, w.m_blk * BM + quarter * 32, n0 + col_first, ncols,
+                        w.b_lo, w.b_hi, cbase, row_ok, alpha, lane);
+      } else {
 #pragma unroll 1
       for (int c = half * CHUNKS_PER_HALF; c < (half + 1) * CHUNKS_PER_HALF; ++c) {
         uint32_t r[32];
@@ -347,6 +362,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int nc = n0 + c * 32;
         if (row_ok && nc < p.N) epilogue_chunk(p, r, c_ptr, cbase, nc, vec_ok, alpha);
         __syncwarp();  // tcgen05.ld is warp-collective: reconverge before the next chunk
+      }
       }
       tc_fence_before();
       __syncwarp();
@@ -358,6 +374,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
     }
+    if (STG && p.tma_out && p.out_fp32 && lane == 0) bulk_wait_all();   // this warp's staged boxes have been written before the CTA retires
   }
 
   // common exit: every thread arrives here, also after a timed-out wait
@@ -432,9 +449,8 @@ int make_f32_reduce_map(CUtensorMap* out, void* ptr, long long inner, long long 
     cudaFree(nullptr);
     ctx_bound = true;
   }
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ld % 4) || (batch_lo > 1 && stride_lo % 4) || (batch_hi > 1 && stride_hi % 4) ||
-      inner % 32)
-    return INCIN_ERR_ALIGNMENT;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ld % 4) || (batch_lo > 1 && stride_lo % 4) || (batch_hi > 1 && stride_hi % 4))
+    return INCIN_ERR_ALIGNMENT;   // (a box that reaches past `inner` or `rows` is clipped, so neither needs to be a multiple of the box)
   cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)batch_lo, (cuuint64_t)batch_hi};
   cuuint64_t strides[3] = {(cuuint64_t)ld * 4, (cuuint64_t)(batch_lo > 1 ? stride_lo : ld * rows) * 4,
                            (cuuint64_t)(batch_hi > 1 ? stride_hi : ld * rows) * 4};
@@ -456,11 +472,11 @@ int device_sm_count() {
   return g_num_sms;
 }
 
-template <int BN, bool A_MN, bool B_MN>
-static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmKernelParams& p, int max_ctas,
-                      cudaStream_t stream) {
-  using Cfg = GemmCfg<BN>;
-  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN>;
+template <int BN, bool A_MN, bool B_MN, bool STG>
+static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
+                      const GemmKernelParams& p, int max_ctas, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN, STG>;
+  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, STG>;
   static PerDeviceFlags attr_set;
   if (!ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, attr_set)) return INCIN_ERR_LAUNCH;
   int grid = p.total_units < max_ctas ? p.total_units : max_ctas;
@@ -476,34 +492,42 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmKe
   }
   // fused-collective launches wait on other GPUs: those stay ordinary launches
   if (q.ag_world > 1 || q.rs_world > 1) {
-    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, q);
+    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, tc, tx, q);
     return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
   }
-  return launch_pdl<true>(kern, dim3(grid), dim3(GEMM_THREADS), Cfg::SMEM_BYTES, stream, ta, tb, q) == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
+  return launch_pdl<true>(kern, dim3(grid), dim3(GEMM_THREADS), Cfg::SMEM_BYTES, stream, ta, tb, tc, tx, q) == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
 
 template <int BN>
-static int launch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb,
-                        const GemmKernelParams& p, int max_ctas, cudaStream_t s) {
-  if (!a_mn && !b_mn) return launch_cfg<BN, false, false>(ta, tb, p, max_ctas, s);
-  if (!a_mn && b_mn) return launch_cfg<BN, false, true>(ta, tb, p, max_ctas, s);
-  if (a_mn && !b_mn) return launch_cfg<BN, true, false>(ta, tb, p, max_ctas, s);
-  return launch_cfg<BN, true, true>(ta, tb, p, max_ctas, s);
+static int launch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                        const CUtensorMap& tx, const GemmKernelParams& p, int max_ctas, cudaStream_t s) {
+  // 128 x 256 tiles always carry the staging area (it costs them no operand stage); the others only when asked to
+  if (p.tma_out || BN == 256) {
+    if (!a_mn && !b_mn) return launch_cfg<BN, false, false, true>(ta, tb, tc, tx, p, max_ctas, s);
+    if (!a_mn && b_mn) return launch_cfg<BN, false, true, true>(ta, tb, tc, tx, p, max_ctas, s);
+    if (a_mn && !b_mn) return launch_cfg<BN, true, false, true>(ta, tb, tc, tx, p, max_ctas, s);
+    return launch_cfg<BN, true, true, true>(ta, tb, tc, tx, p, max_ctas, s);
+  }
+  if (!a_mn && !b_mn) return launch_cfg<BN, false, false, false>(ta, tb, tc, tx, p, max_ctas, s);
+  if (!a_mn && b_mn) return launch_cfg<BN, false, true, false>(ta, tb, tc, tx, p, max_ctas, s);
+  if (a_mn && !b_mn) return launch_cfg<BN, true, false, false>(ta, tb, tc, tx, p, max_ctas, s);
+  return launch_cfg<BN, true, true, false>(ta, tb, tc, tx, p, max_ctas, s);
 }
 
 // CTA-pair kernel launch: as many clusters as the device can hold at once (at most one CTA per SM).
-template <bool A_MN, bool B_MN>
-static int launch_pair_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmKernelParams& p, int tiles_m2, int max_ctas,
-                           cudaStream_t stream) {
-  auto kern = gemm_tcgen05_pair_kernel<A_MN, B_MN>;
+template <bool A_MN, bool B_MN, bool STG>
+static int launch_pair_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
+                           const GemmKernelParams& p, int tiles_m2, int max_ctas, cudaStream_t stream) {
+  using PCfg = PairCfg<STG>;
+  auto kern = gemm_tcgen05_pair_kernel<A_MN, B_MN, STG>;
   static PerDeviceFlags attr_set;
-  if (!ensure_dynamic_smem(kern, PairCfg::SMEM_BYTES, attr_set)) return INCIN_ERR_LAUNCH;
+  if (!ensure_dynamic_smem(kern, PCfg::SMEM_BYTES, attr_set)) return INCIN_ERR_LAUNCH;
   static int max_clusters = 0;   // the same for every B200 of a node
   if (max_clusters == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 74, 1, 1);
     cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
+    cfg.dynamicSmemBytes = PCfg::SMEM_BYTES;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2;
@@ -521,17 +545,23 @@ static int launch_pair_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const G
   int pairs = max_clusters < max_ctas / 2 ? max_clusters : max_ctas / 2;
   if (pairs > p.total_units) pairs = p.total_units;
   if (pairs < 1) return INCIN_ERR_ARGUMENT;
-  return launch_pdl<true>(kern, dim3(2 * pairs), dim3(GEMM_THREADS), PairCfg::SMEM_BYTES, stream, ta, tb, p, tiles_m2) == cudaSuccess
+  return launch_pdl<true>(kern, dim3(2 * pairs), dim3(GEMM_THREADS), PCfg::SMEM_BYTES, stream, ta, tb, tc, tx, p, tiles_m2) == cudaSuccess
              ? INCIN_OK
              : INCIN_ERR_LAUNCH;
 }
 
-static int launch_pair(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmKernelParams& p,
-                       int tiles_m2, int max_ctas, cudaStream_t s) {
-  if (!a_mn && !b_mn) return launch_pair_cfg<false, false>(ta, tb, p, tiles_m2, max_ctas, s);
-  if (!a_mn && b_mn) return launch_pair_cfg<false, true>(ta, tb, p, tiles_m2, max_ctas, s);
-  if (a_mn && !b_mn) return launch_pair_cfg<true, false>(ta, tb, p, tiles_m2, max_ctas, s);
-  return launch_pair_cfg<true, true>(ta, tb, p, tiles_m2, max_ctas, s);
+static int launch_pair(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                       const CUtensorMap& tx, const GemmKernelParams& p, int tiles_m2, int max_ctas, cudaStream_t s) {
+  if (p.tma_out) {
+    if (!a_mn && !b_mn) return launch_pair_cfg<false, false, true>(ta, tb, tc, tx, p, tiles_m2, max_ctas, s);
+    if (!a_mn && b_mn) return launch_pair_cfg<false, true, true>(ta, tb, tc, tx, p, tiles_m2, max_ctas, s);
+    if (a_mn && !b_mn) return launch_pair_cfg<true, false, true>(ta, tb, tc, tx, p, tiles_m2, max_ctas, s);
+    return launch_pair_cfg<true, true, true>(ta, tb, tc, tx, p, tiles_m2, max_ctas, s);
+  }
+  if (!a_mn && !b_mn) return launch_pair_cfg<false, false, false>(ta, tb, tc, tx, p, tiles_m2, max_ctas, s);
+  if (!a_mn && b_mn) return launch_pair_cfg<false, true, false>(ta, tb, tc, tx, p, tiles_m2, max_ctas, s);
+  if (a_mn && !b_mn) return launch_pair_cfg<true, false, false>(ta, tb, tc, tx, p, tiles_m2, max_ctas, s);
+  return launch_pair_cfg<true, true, false>(ta, tb, tc, tx, p, tiles_m2, max_ctas, s);
 }
 
 // Pick the tile and the split-K factor that minimise a cost model fitted to per-launch CUDA-event timings on a B200
@@ -712,12 +742,43 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
       if (!p.rs_dst[r]) return INCIN_ERR_ARGUMENT;
   }
 
+  // Output through staged bulk tensor stores where C (and the side output) can be described by a tensor map: 16-byte
+  // aligned base and row / batch strides, results written to this GPU's memory (the reduce-scatter modes keep their
+  // per-thread stores to peers).  INCIN_GEMM_TMA_OUT is a mask of the output kinds that take the staged path:
+  // 1 = bf16 without side output, 2 = bf16 with the pre-activation side output, 4 = fp32 (plain and accumulating),
+  // 8 = also for long reductions (otherwise only K / splits <= 1024 and the 128 x 256 tile, whose staging area costs
+  // no operand stage).  Default 4.  Measured on one B200: staging bf16 outputs makes an isolated K = 768 product with a
+  // cold L2 14 % faster (the epilogue of a 128 x 256 tile drops from about 6 us), but inside the captured GPT-2 training
+  // step, where operands come from a warm L2 and the main loop is bound by shared-memory bandwidth, the extra 64 KB of
+  // shared-memory traffic per tile made the step 0.3-0.6 ms (3-5 %) slower, with bulk tensor stores and with row-wise
+  // stores alike; accumulating fp32 outputs through bulk reduce-adds were 0.05-0.09 ms faster.
+  static const int tma_out_mask = [] {
+    const char* e = std::getenv("INCIN_GEMM_TMA_OUT");
+    return e ? std::atoi(e) : INCIN_GEMM_TMA_OUT_DEFAULT;
+  }();
+  const bool with_pre = d->aux && (d->act == INCIN_ACT_GELU || d->act == INCIN_ACT_SILU);
+  const int out_kind = d->out_fp32 ? 4 : (with_pre ? 2 : 1);
+  const bool tma_out_on = (tma_out_mask & out_kind) != 0;
+  const bool tma_out_all = (tma_out_mask & 8) != 0;
+  CUtensorMap tc = ta, tx = ta;
+  p.tma_out = 0;
+  const bool short_k = (kb_total + splits - 1) / splits <= 16;
+  if (tma_out_on && !p.rs_world && d->C && (short_k || bn == 256 || tma_out_all)) {
+    if (d->out_fp32) {
+      p.tma_out = (!with_pre && make_f32_reduce_map(&tc, d->C, d->N, d->M, d->ldc, blo, d->c_stride_lo, bhi, d->c_stride_hi, 32) == INCIN_OK) ? 1 : 0;
+    } else {   // bf16 rows leave with 16-byte stores: C (and the side output) 16-byte aligned with strides in multiples of 8
+      const bool ok16 = !(reinterpret_cast<uintptr_t>(d->C) & 15) && (!with_pre || !(reinterpret_cast<uintptr_t>(d->aux) & 15)) &&
+                        d->ldc % 8 == 0 && (blo == 1 || d->c_stride_lo % 8 == 0) && (bhi == 1 || d->c_stride_hi % 8 == 0);
+      p.tma_out = ok16 ? 1 : 0;
+    }
+  }
+
   const bool amn = d->a_mn_major != 0, bmn = d->b_mn_major != 0;
-  if (pair) return incin::launch_pair(amn, bmn, ta, tb, p, tiles_m2, sms, stream);
+  if (pair) return incin::launch_pair(amn, bmn, ta, tb, tc, tx, p, tiles_m2, sms, stream);
   int rc2;
-  if (bn == 64) rc2 = incin::launch_major<64>(amn, bmn, ta, tb, p, sms, stream);
-  else if (bn == 128) rc2 = incin::launch_major<128>(amn, bmn, ta, tb, p, sms, stream);
-  else if (bn == 192) rc2 = incin::launch_major<192>(amn, bmn, ta, tb, p, sms, stream);
-  else rc2 = incin::launch_major<256>(amn, bmn, ta, tb, p, sms, stream);
+  if (bn == 64) rc2 = incin::launch_major<64>(amn, bmn, ta, tb, tc, tx, p, sms, stream);
+  else if (bn == 128) rc2 = incin::launch_major<128>(amn, bmn, ta, tb, tc, tx, p, sms, stream);
+  else if (bn == 192) rc2 = incin::launch_major<192>(amn, bmn, ta, tb, tc, tx, p, sms, stream);
+  else rc2 = incin::launch_major<256>(amn, bmn, ta, tb, tc, tx, p, sms, stream);
   return rc2;
 }

@@ -137,6 +137,14 @@ __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const vo
                "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(smem_src))
                : "memory");
 }
+// Tiled store of a shared-memory box into global memory (same rules as the reduce: x * element size a multiple of
+// 16 bytes, no negative coordinate; the part of the box beyond the tensor's extents is not written).
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(smem_src))
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }

@@ -3,8 +3,8 @@
 Counterpart of crates/incin-backends/src/codegen/pointwise.rs (``PointwiseExpr``: Arg / Const /
 Unary(17) / Binary(7) / Ternary(Clamp, Fma); layouts Contiguous / Strided / ScalarBroadcast; renderers for
 CUDA, WGSL and MSL) and of the template renderer crates/incin-backends/src/kernel.rs (dtype / layout / access
-specialisation, ``KernelKey`` cache ids).  Only the CUDA target exists here; the arithmetic of the WGSL/MSL
-targets is covered by the ops themselves (``gelu_tanh`` is the WGSL shader's GELU).
+specialisation, ``KernelKey`` cache ids).  The CUDA target is the one that runs; :mod:`incin_b200.codegen.shading`
+renders the same expressions as WGSL and MSL source text (``gelu_tanh`` is the WGSL shader's GELU).
 
 Differences by design: a whole chain of ops becomes ONE kernel (the reference fuses adjacent pairs at most),
 scalars are kernel ARGUMENTS (the reference bakes each scalar into the source text and recompiles per value:
@@ -24,7 +24,8 @@ UNARY = {
     "gelu_tanh": "(0.5f * {x} * (1.0f + tanhf(0.79788456f * ({x} + 0.044715f * {x} * {x} * {x}))))",
     "exp": "__expf({x})", "log": "__logf({x})", "sqrt": "sqrtf({x})", "rsqrt": "rsqrtf({x})", "neg": "(-{x})",
     "abs": "fabsf({x})", "sign": "(({x} > 0.0f) - ({x} < 0.0f))", "mish": "({x} * tanhf(log1pf(__expf({x}))))",
-    "recip": "(1.0f / {x})", "square": "({x} * {x})",
+    "recip": "(1.0f / {x})", "square": "({x} * {x})", "sin": "__sinf({x})", "cos": "__cosf({x})",
+    "floor": "floorf({x})", "ceil": "ceilf({x})",
 }
 BINARY = {"add": "({a} + {b})", "sub": "({a} - {b})", "mul": "({a} * {b})", "div": "({a} / {b})",
           "max": "fmaxf({a}, {b})", "min": "fminf({a}, {b})", "pow": "powf({a}, {b})"}

@@ -23,6 +23,7 @@ def test_every_unary_binary_ternary_op_matches_torch():
         "gelu": torch.nn.functional.gelu, "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh"),
         "exp": torch.exp, "log": torch.log, "sqrt": torch.sqrt, "rsqrt": torch.rsqrt, "neg": torch.neg, "abs": torch.abs,
         "sign": torch.sign, "mish": torch.nn.functional.mish, "recip": torch.reciprocal, "square": torch.square,
+        "sin": torch.sin, "cos": torch.cos, "floor": torch.floor, "ceil": torch.ceil,
     }
     assert set(ref_unary) == set(UNARY)
     for op, ref in ref_unary.items():

@@ -90,6 +90,29 @@ def test_shape_buckets():
 
 
 # ------------------------------------------------------------------------------------------------ codegen
+def test_wgsl_and_msl_text_emitters_cover_every_op():
+    """Substring checks, as the reference tests its shader emitters (crates/incin-backends/src/codegen/pointwise.rs:342-499)."""
+    from incin_b200.codegen import pointwise as PW
+    from incin_b200.codegen.shading import _BINARY, _TERNARY, _UNARY, render_msl, render_wgsl
+    assert set(_UNARY) == set(PW.UNARY) and set(_BINARY) == set(PW.BINARY) and set(_TERNARY) == set(PW.TERNARY)
+    e = Ternary("fma", Unary("gelu_tanh", Arg(0)), Scalar(0), Binary("max", Arg(1), Const(0.5)))
+    w = render_wgsl(e, "f32", workgroup_size=64)
+    assert "@group(0) @binding(0) var<storage, read> in0: array<f32>;" in w
+    assert "@group(0) @binding(2) var<storage, read_write> out_data: array<f32>;" in w
+    assert "@compute @workgroup_size(64, 1, 1)" in w and "if (idx >= arrayLength(&out_data)) { return; }" in w
+    assert "fma((0.5 * val0 * (1.0 + tanh(0.79788456 * (val0 + 0.044715 * val0 * val0 * val0)))), scalars.s0, max(val1, 0.5))" in w
+    assert "var<uniform> scalars: Scalars;" in w
+    m = render_msl(e, "bf16", name="fused0")
+    assert "kernel void fused0(" in m and "device const half* in1 [[buffer(1)]]," in m and "device half* out_data [[buffer(2)]]," in m
+    assert "uint idx [[thread_position_in_grid]]" in m and "fmax(val1, 0.5f)" in m and "static_cast<half>(" in m
+    assert "enable f16;" in render_wgsl(Unary("rsqrt", Arg(0)), "f16") and "inverseSqrt(val0)" in render_wgsl(Unary("rsqrt", Arg(0)))
+    assert "let val1 = f32(in1[0]);" in render_wgsl(Binary("add", Arg(0), Arg(1)), scalar_broadcast=1)
+    for op in PW.UNARY:
+        assert "val0" in render_wgsl(Unary(op, Arg(0))) and "val0" in render_msl(Unary(op, Arg(0)))
+    with pytest.raises(ValueError):
+        render_wgsl(Const(float("inf")) + Arg(0))
+
+
 def test_render_every_op_and_reject_bad_trees():
     e = Ternary("fma", Unary("gelu_tanh", Arg(0)), Scalar(0), Binary("max", Arg(1), Const(0.5)))
     assert count_args(e) == (2, 1)
