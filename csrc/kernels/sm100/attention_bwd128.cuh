@@ -8,10 +8,10 @@
 // steps are in flight at any time:
 //
 //   tensor core : S dP (j) | dV dK dQ^T (j-1) | S dP (j+1) | dV dK dQ^T (j) | ...
-//   group j&1   :     softmax-gradient (j)  ->  read out dQ^T (j)            (8 warps)
-//   other group :     ... (j-1), read out dQ^T (j-1)  |  softmax-gradient (j+1) ...
+//   group 0     :     softmax-gradient (j)        | softmax-gradient (j+1)       ...      (8 warps)
+//   group 1     :  ... read out dQ^T (j-1), stage, reduce | read out dQ^T (j) ...           (8 warps)
 //
-// Step j uses buffer j & 1 of everything and is worked on by compute group j & 1 (two groups of 8 warps).  Per step:
+// Step j uses buffer j & 1 of everything.  Per step:
 //     S^T  = K Q^T   [128 kv x 64 q]      dP^T = V dO^T
 //     dV  += P^T dO  [128 kv x 128 d]     dK  += dS^T Q          (reduction over the 64 queries)
 //     dQ^T = K^T dS  [128 d  x 64 q]                             (reduction over the 128 kv rows)
@@ -314,18 +314,19 @@ flash_bwd128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else {
     // ---------------------------------------------------------------- softmax-gradient threads
-    // Two groups of 8 warps; group g works on the steps with (global step index) & 1 == g.  Inside a group:
-    // warp -> (TMEM lane quarter = 32 KV rows, cb2 = which 32 of the step's 64 query columns).
+    // Two groups of 8 warps with different roles, both working on every step: group 0 turns S^T / dP^T into P^T / dS^T,
+    // group 1 reads the dQ^T partial out of tensor memory, stages it and has it added to the accumulator.  Split by
+    // role (rather than by step parity) the tail of the read-out — shared-memory stores, fence, the wait for the
+    // group's other warps, issuing the reduces — runs beside the next step's softmax-gradient math instead of in
+    // front of it.  Inside a group: warp -> (TMEM lane quarter, cb2 = which 32 of the step's 64 query columns).
     const int cw = warp - 2;
     const int quarter = warp & 3;
-    const int my_grp = cw >> 3;
+    const int role = cw >> 3;          // 0: softmax-gradient, 1: dQ read-out
     const int cb2 = (cw >> 2) & 1;
     const int cb = cw >> 2;            // 0..3: 32-column block of head_dim for the dK / dV write-out
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const bool elected = (cw == my_grp * (FB_CWARPS / 2)) && lane == 0;   // issues this group's bulk reduces
-    // dQ box of this warp's 32 head_dim lanes: boxes 0, 1 live in the step's P^T buffer, boxes 2, 3 in its dS^T buffer
-    uint8_t* my_box = (quarter < 2 ? sP : sDS) + my_grp * Cfg::PT_BYTES + (quarter & 1) * (TQ * 128);
+    const bool elected = (cw == FB_CWARPS / 2) && lane == 0;   // issues the bulk reduces
 
     int base = 0;
     bool ok = true;
@@ -338,93 +339,102 @@ flash_bwd128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const bool kv_live = kv_idx < p.T;
       const int steps_per_head = n_steps_total - 2 * kv_tile;
       const int n_iters = steps_per_head * group;
-      for (int it = ((base & 1) == my_grp) ? 0 : 1; it < n_iters && ok; it += 2) {
-        const int gi = base + it, s = gi % ST;      // gi & 1 == my_grp
-        const int q0 = (2 * kv_tile + it % steps_per_head) * TQ;
-        const int hq = hkv * group + it / steps_per_head;
-        const bool masked = (q0 < kv0 + FB_T) || (kv0 + FB_T > p.T);   // a diagonal step, or a KV tile with dead rows
-        const long long t0 = now();
-        if (!mbar_wait(&sdp[my_grp], (gi >> 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
-        const long long t1 = now();
-        tc_fence_after();
-        // P^T / dS^T of this buffer were the dQ boxes of the group's previous step: its reduces must have read them
-        if (gi >= 2) {
-          if (elected) {
-            bulk_wait_read_all();
-            mbar_arrive(&stg_free[my_grp]);
-          }
-          if (!mbar_wait(&stg_free[my_grp], ((gi >> 1) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) { ok = false; break; }
-        }
-        auto softmax_grad = [&](auto masked_tag) {
-          constexpr bool MASKED = decltype(masked_tag)::value;
-          const int off = my_grp * Cfg::PT_BYTES + row * 128;      // [128 kv rows][64 q] bf16, SWIZZLE_128B
-          // 32 query columns per thread in four chunks of 8: the tensor-memory loads of chunk c+1 are in flight while
-          // chunk c is computed (one chunk of S^T and dP^T = one 16-byte unit of P^T and of dS^T)
-          const uint32_t tcol = lane_addr + my_grp * TQ + cb2 * 32;
-          const float* s_lse = sStat + s * 2 * TQ + cb2 * 32;      // q_full (waited by the issuer) covers the statistics
-          const float* s_delta = s_lse + TQ;
-          uint32_t rs[2][8], rd[2][8];
-          tmem_ld_32x8(tmem_base + Cfg::COL_ST + tcol, rs[0]);
-          tmem_ld_32x8(tmem_base + Cfg::COL_DPT + tcol, rd[0]);
-          tmem_ld_wait_on(rs[0], rd[0]);
+      if (role == 0) {
+        for (int it = 0; it < n_iters && ok; ++it) {
+          const int gi = base + it, s = gi % ST, g = gi & 1;
+          const int q0 = (2 * kv_tile + it % steps_per_head) * TQ;
+          const bool masked = (q0 < kv0 + FB_T) || (kv0 + FB_T > p.T);   // a diagonal step, or a KV tile with dead rows
+          const long long t0 = now();
+          if (!mbar_wait(&sdp[g], (gi >> 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+          // P^T / dS^T of this buffer were the dQ boxes of step gi - 2: its reduces must have read them
+          if (gi >= 2 && !mbar_wait(&stg_free[g], ((gi >> 1) & 1) ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) { ok = false; break; }
+          const long long t1 = now();
+          tc_fence_after();
+          auto softmax_grad = [&](auto masked_tag) {
+            constexpr bool MASKED = decltype(masked_tag)::value;
+            const int off = g * Cfg::PT_BYTES + row * 128;      // [128 kv rows][64 q] bf16, SWIZZLE_128B
+            // 32 query columns per thread in four chunks of 8: the tensor-memory loads of chunk c+1 are in flight while
+            // chunk c is computed (one chunk of S^T and dP^T = one 16-byte unit of P^T and of dS^T)
+            const uint32_t tcol = lane_addr + g * TQ + cb2 * 32;
+            const float* s_lse = sStat + s * 2 * TQ + cb2 * 32;      // q_full (waited by the issuer) covers the statistics
+            const float* s_delta = s_lse + TQ;
+            uint32_t rs[2][8], rd[2][8];
+            tmem_ld_32x8(tmem_base + Cfg::COL_ST + tcol, rs[0]);
+            tmem_ld_32x8(tmem_base + Cfg::COL_DPT + tcol, rd[0]);
+            tmem_ld_wait_on(rs[0], rd[0]);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int cur = c & 1, nxt = cur ^ 1;
-            if (c < 3) {
-              tmem_ld_32x8(tmem_base + Cfg::COL_ST + tcol + (c + 1) * 8, rs[nxt]);
-              tmem_ld_32x8(tmem_base + Cfg::COL_DPT + tcol + (c + 1) * 8, rd[nxt]);
-            }
-            uint32_t pp[4], dd[4];
-#pragma unroll
-            for (int gq = 0; gq < 2; ++gq) {
-              const float4 l4 = *reinterpret_cast<const float4*>(s_lse + c * 8 + gq * 4);
-              const float4 d4 = *reinterpret_cast<const float4*>(s_delta + c * 8 + gq * 4);
-              const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
-              const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
-              float pv[4], dv[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int i = gq * 4 + e;
-                float pr = exp2f(fmaf(__uint_as_float(rs[cur][i]), p.scale_log2, -lse[e]));
-                if constexpr (MASKED) pr = (kv_live && (q0 + cb2 * 32 + c * 8 + i >= kv_idx)) ? pr : 0.f;
-                pv[e] = pr;
-                dv[e] = pr * (__uint_as_float(rd[cur][i]) - dl[e]);   // the softmax scale is applied when dQ / dK leave TMEM
+            for (int c = 0; c < 4; ++c) {
+              const int cur = c & 1, nxt = cur ^ 1;
+              if (c < 3) {
+                tmem_ld_32x8(tmem_base + Cfg::COL_ST + tcol + (c + 1) * 8, rs[nxt]);
+                tmem_ld_32x8(tmem_base + Cfg::COL_DPT + tcol + (c + 1) * 8, rd[nxt]);
               }
-              pp[gq * 2] = pack_bf16x2(pv[0], pv[1]);
-              pp[gq * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
-              dd[gq * 2] = pack_bf16x2(dv[0], dv[1]);
-              dd[gq * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
+              uint32_t pp[4], dd[4];
+#pragma unroll
+              for (int gq = 0; gq < 2; ++gq) {
+                const float4 l4 = *reinterpret_cast<const float4*>(s_lse + c * 8 + gq * 4);
+                const float4 d4 = *reinterpret_cast<const float4*>(s_delta + c * 8 + gq * 4);
+                const float lse[4] = {l4.x, l4.y, l4.z, l4.w};
+                const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+                float pv[4], dv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int i = gq * 4 + e;
+                  float pr = exp2f(fmaf(__uint_as_float(rs[cur][i]), p.scale_log2, -lse[e]));
+                  if constexpr (MASKED) pr = (kv_live && (q0 + cb2 * 32 + c * 8 + i >= kv_idx)) ? pr : 0.f;
+                  pv[e] = pr;
+                  dv[e] = pr * (__uint_as_float(rd[cur][i]) - dl[e]);   // the softmax scale is applied when dQ / dK leave TMEM
+                }
+                pp[gq * 2] = pack_bf16x2(pv[0], pv[1]);
+                pp[gq * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
+                dd[gq * 2] = pack_bf16x2(dv[0], dv[1]);
+                dd[gq * 2 + 1] = pack_bf16x2(dv[2], dv[3]);
+              }
+              const int unit = (cb2 * 4 + c) ^ (row & 7);
+              if (!(PROF && (dbg & 2))) {
+                *reinterpret_cast<uint4*>(sP + off + unit * 16) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
+                *reinterpret_cast<uint4*>(sDS + off + unit * 16) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
+              }
+              if (c < 3) tmem_ld_wait_on(rs[nxt], rd[nxt]);
             }
-            const int unit = (cb2 * 4 + c) ^ (row & 7);
-            if (!(PROF && (dbg & 2))) {
-              *reinterpret_cast<uint4*>(sP + off + unit * 16) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
-              *reinterpret_cast<uint4*>(sDS + off + unit * 16) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
-            }
-            if (c < 3) tmem_ld_wait_on(rs[nxt], rd[nxt]);
+          };
+          if (masked) softmax_grad(std::true_type{});
+          else softmax_grad(std::false_type{});
+          fence_proxy_async_smem();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&pds[g]);
+          if constexpr (PROF) {
+            const long long t2 = now();
+            c_wait_sdp += t1 - t0; c_soft += t2 - t1; ++c_steps;
           }
-        };
-        if (masked) softmax_grad(std::true_type{});
-        else softmax_grad(std::false_type{});
-        fence_proxy_async_smem();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&pds[my_grp]);
-        const long long t2 = now();
-
-        // dQ^T partial of this step: lanes are head_dim, columns are the 64 queries; this warp reads 32 lanes x 32
-        // queries, stages them as rows of its box, and one thread of the group adds the four boxes to the accumulator
-        if (!mbar_wait(&dq_full[my_grp], (gi >> 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
-        const long long t3 = now();
-        tc_fence_after();
-        {
+        }
+      } else {
+        for (int it = 0; it < n_iters && ok; ++it) {
+          const int gi = base + it, g = gi & 1;
+          const int q0 = (2 * kv_tile + it % steps_per_head) * TQ;
+          const int hq = hkv * group + it / steps_per_head;
+          // the reduces of the previous step have read their boxes: P^T / dS^T of that buffer may be rewritten
+          if (elected && gi >= 1) {
+            bulk_wait_read_all();
+            mbar_arrive(&stg_free[(gi - 1) & 1]);
+          }
+          // dQ^T partial of this step: lanes are head_dim, columns are the 64 queries; this warp reads 32 lanes x 32
+          // queries and stages them as rows of its box; one thread adds the four boxes to the accumulator.  Boxes 0, 1
+          // live in the step's P^T buffer, boxes 2, 3 in its dS^T buffer (both dead once dq_full has arrived).
+          const long long t2 = now();
+          if (!mbar_wait(&dq_full[g], (gi >> 1) & 1, abort_flag, p.status, kStatusTimeoutTmemFull)) { ok = false; break; }
+          const long long t3 = now();
+          tc_fence_after();
           uint32_t r0[16], r1[16];
-          const uint32_t tcol = lane_addr + my_grp * TQ + cb2 * 32;
+          const uint32_t tcol = lane_addr + g * TQ + cb2 * 32;
           tmem_ld_32x16(tmem_base + Cfg::COL_DPT + tcol, r0);
           tmem_ld_32x16(tmem_base + Cfg::COL_DPT + tcol + 16, r1);
           tmem_ld_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&dq_drained[my_grp]);   // the buffer may be overwritten by the scores of step gi + 2
+          if (lane == 0) mbar_arrive(&dq_drained[g]);   // the buffer may be overwritten by the scores of step gi + 2
+          uint8_t* my_box = (quarter < 2 ? sP : sDS) + g * Cfg::PT_BYTES + (quarter & 1) * (TQ * 128);
           if (!(PROF && (dbg & 1))) {
             // row q of box `quarter` = this warp's 32 floats of dQ[q][quarter * 32 ..]: one conflict-free 128-byte row
             // per store instruction (128-byte swizzle: 16-byte unit u of row r sits at u ^ (r & 7))
@@ -437,20 +447,20 @@ flash_bwd128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&stg_full[my_grp]);
+          if (lane == 0) mbar_arrive(&stg_full[g]);
           if (elected) {
-            if (!mbar_wait(&stg_full[my_grp], (gi >> 1) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+            if (!mbar_wait(&stg_full[g], (gi >> 1) & 1, abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
             if (!(PROF && (dbg & 1))) {
 #pragma unroll
               for (int bx = 0; bx < 4; ++bx)   // rows past T are clipped by the tensor map
-                tma_reduce_add_4d(&p.tm_dq, (bx < 2 ? sP : sDS) + my_grp * Cfg::PT_BYTES + (bx & 1) * (TQ * 128), bx * 32, q0, hq, b);
-              bulk_commit();
+                tma_reduce_add_4d(&p.tm_dq, (bx < 2 ? sP : sDS) + g * Cfg::PT_BYTES + (bx & 1) * (TQ * 128), bx * 32, q0, hq, b);
             }
+            bulk_commit();
           }
-        }
-        if constexpr (PROF) {
-          const long long t4 = now();
-          c_wait_sdp += t1 - t0; c_soft += t2 - t1; c_wait_dq += t3 - t2; c_drain += t4 - t3; ++c_steps;
+          if constexpr (PROF) {
+            const long long t4 = now();
+            c_wait_dq += t3 - t2; c_drain += t4 - t3;
+          }
         }
       }
       if (!ok) break;
@@ -498,10 +508,10 @@ flash_bwd128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       base += n_iters;
       c_dkv += now() - t5;
     }
-    if (PROF && lane == 0 && warp == 2) {
+    if (PROF && lane == 0 && (warp == 2 || warp == 2 + FB_CWARPS / 2)) {   // one lane of each role
       auto add = [&](int i, long long v) { atomicAdd(reinterpret_cast<unsigned long long*>(p.prof + i), (unsigned long long)v); };
-      add(8, now() - c_all); add(9, c_wait_sdp); add(10, c_soft); add(11, c_wait_dq); add(12, c_drain); add(13, c_dkv);
-      add(14, c_steps);
+      if (role == 0) { add(8, now() - c_all); add(9, c_wait_sdp); add(10, c_soft); add(13, c_dkv); add(14, c_steps); }
+      else { add(11, c_wait_dq); add(12, c_drain); }
     }
     if (elected) bulk_wait_all();   // the boxes stay valid until their reduces have completed
   }
