@@ -72,7 +72,7 @@ def timeit(fn, iters: int = 10, warmup: int = 3) -> float:
     return max(both - only_flush, 1e-6) / iters
 
 
-def bench_gemm(args) -> None:
+def bench_gemm(args) -> list:
     from incin_b200.ops import gemm as G
     pk = peaks()
     shapes = [  # (name, M, N, K, kind)
@@ -86,6 +86,8 @@ def bench_gemm(args) -> None:
     ]
     if args.one:
         shapes = [("custom", args.one[0], args.one[1], args.one[2], args.kind)]
+    if getattr(args, "shapes", None):
+        shapes = [sh for sh in shapes if sh[0] in args.shapes]
     rows = []
     for name, M, N, K, kind in shapes:
         if kind == "nt":
@@ -119,6 +121,7 @@ def bench_gemm(args) -> None:
                      "cublas_tflops": None if t_lib is None else round(fl / t_lib / 1e9, 1)})
         print(json.dumps(rows[-1]), flush=True)
     G.check_status()
+    return rows
 
 
 def bench_bandwidth(args) -> None:
@@ -193,9 +196,15 @@ def attention_error_vs_cpu(qkv: torch.Tensor, do: torch.Tensor, H: int, D: int, 
     return res
 
 
-def bench_attention(args) -> None:
+def bench_attention(args) -> list:
     from incin_b200.ops import functional as F
     pk = peaks()
+    out_rows = []
+
+    def emit(row):
+        out_rows.append(row)
+        print(json.dumps(row), flush=True)
+
     for (B, H, T, D) in [(8, 12, 1024, 64), (8, 32, 4096, 128)] if not args.one else [tuple(args.one) + (args.head_dim,)]:
         # Q, K, V and dO ~ N(0, 1) from seed 0, softmax scale 1 / sqrt(head_dim)
         gen = torch.Generator(device="cuda").manual_seed(0)
@@ -213,15 +222,13 @@ def bench_attention(args) -> None:
                 o.backward(do)
             t_fb = timeit(fb, args.iters)
             fl_f = 4.0 * B * H * T * T * D / 2
-            print(json.dumps({"B": B, "H": H, "T": T, "D": D, "impl": impl, "fwd_ms": round(t_f, 4),
-                              "fwd_tflops": round(fl_f / t_f / 1e9, 1), "fwd_bwd_ms": round(t_fb, 4),
-                              "fwd_bwd_tflops": round(3.5 * fl_f / t_fb / 1e9, 1),
-                              "frac_of_measured_burst": round(3.5 * fl_f / t_fb / 1e9 / pk["bf16_tflops"], 3)}),
-                  flush=True)
+            emit({"B": B, "H": H, "T": T, "D": D, "impl": impl, "fwd_ms": round(t_f, 4),
+                  "fwd_tflops": round(fl_f / t_f / 1e9, 1), "fwd_bwd_ms": round(t_fb, 4),
+                  "fwd_bwd_tflops": round(3.5 * fl_f / t_fb / 1e9, 1),
+                  "frac_of_measured_burst": round(3.5 * fl_f / t_fb / 1e9 / pk["bf16_tflops"], 3)})
             if impl in ("auto", "flash") and not args.no_check:
                 err = attention_error_vs_cpu(qkv, do, H, D, B - 1, H - 1)
-                print(json.dumps({"B": B, "H": H, "T": T, "D": D, "impl": impl, "slice": [B - 1, H - 1],
-                                  "vs": "fp32 CPU reference", **err}), flush=True)
+                emit({"B": B, "H": H, "T": T, "D": D, "impl": impl, "slice": [B - 1, H - 1], "vs": "fp32 CPU reference", **err})
         # library reference (baseline, not product): torch SDPA
         q, k, v = (torch.randn(B, H, T, D, device="cuda").bfloat16().requires_grad_() for _ in range(3))
         dob = torch.randn(B, H, T, D, device="cuda").bfloat16()
@@ -231,8 +238,9 @@ def bench_attention(args) -> None:
         if not args.no_lib:
             t = timeit(sd, args.iters)
             fl_f = 4.0 * B * H * T * T * D / 2
-            print(json.dumps({"B": B, "H": H, "T": T, "D": D, "impl": "torch-sdpa", "fwd_bwd_ms": round(t, 4),
-                              "fwd_bwd_tflops": round(3.5 * fl_f / t / 1e9, 1)}), flush=True)
+            emit({"B": B, "H": H, "T": T, "D": D, "impl": "torch-sdpa", "fwd_bwd_ms": round(t, 4),
+                  "fwd_bwd_tflops": round(3.5 * fl_f / t / 1e9, 1)})
+    return out_rows
 
 
 def main() -> None:

@@ -17,6 +17,85 @@ import torch
 import torch.distributed as dist
 
 
+def run(model_name: str, tp: int, dp: int, batch: int, seq: int, steps: int = 5, warmup: int = 3,
+        collectives: str = "fused", use_graph: bool = True, layers: int = 0) -> dict | None:
+    """One measurement inside an initialised process group of ``tp * dp`` ranks (one GPU each, current device set).
+    Returns the result row on rank 0, None elsewhere.  Everything it allocates is released before it returns."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    rank, world = dist.get_rank(), dist.get_world_size()
+    assert world == tp * dp, f"world {world} != tp {tp} x dp {dp}"
+    from incin_b200.engine import TrainStep
+    from incin_b200.models.llama import LlamaConfig
+    from incin_b200.models.llama_tp import LlamaTP, TPOptimizer
+    from incin_b200.ops import gemm as G
+    from incin_b200.parallel.mesh import mesh
+    from incin_b200.parallel.tp import TensorParallel
+
+    cfg = {"llama-1b": LlamaConfig.llama_1b, "llama-3b": LlamaConfig.llama_3b, "llama-tiny": LlamaConfig.tiny}[model_name]()
+    if layers:
+        cfg.n_layer = layers
+    spec = mesh(dp=dp, tp=tp)
+    d, _, t = spec.coords(rank)
+    tp_group = dp_group = None
+    if dp > 1:
+        tp_groups = [dist.new_group([spec.rank_of(dd, 0, tt) for tt in range(tp)]) for dd in range(dp)]
+        dp_groups = [dist.new_group([spec.rank_of(dd, 0, tt) for dd in range(dp)]) for tt in range(tp)]
+        tp_group, dp_group = tp_groups[d], dp_groups[t]
+    B, T = batch, seq
+    Ml = B * T // tp
+    tpc = TensorParallel(dev, tp_group, max_rows_per_rank=Ml, max_cols=cfg.d_model, mode=collectives)
+    torch.manual_seed(0)
+    model = LlamaTP(cfg, tp, t)
+    with torch.no_grad():       # random-init N(0, 0.02) directly on the shards (no full model on the host)
+        g = torch.Generator().manual_seed(1000 + t)
+        for name, p in model.named_parameters():
+            if p.dim() >= 2:
+                if name in ("embed", "lm_head"):
+                    p.normal_(0.0, cfg.init_std, generator=torch.Generator().manual_seed(7 + (name == "lm_head")))
+                else:
+                    p.normal_(0.0, cfg.init_std, generator=g)
+    model = model.to(dev)
+    model.tp = tpc
+    opt = TPOptimizer(model, tpc, dev, lr=3e-4, dp_group=dp_group, world_group=None)
+    step = TrainStep(model, opt, use_graph=use_graph and collectives == "fused")
+    gen = torch.Generator().manual_seed(99 + d)
+    tok = torch.randint(0, cfg.vocab_size, (B, T), generator=gen).to(dev)
+    tgt = torch.randint(0, cfg.vocab_size, (B, T), generator=gen).to(dev)
+    losses = []
+    for _ in range(max(warmup, 3)):
+        losses.append(float(step(tok, tgt)))
+    G.check_status(dev)
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        loss = step(tok, tgt)
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    lt = loss.detach().clone()
+    dist.all_reduce(lt)
+    G.check_status(dev)
+    row = None
+    if rank == 0:
+        ms_step = float(ms) / steps
+        tokens = B * T * dp
+        flops = cfg.flops_per_token(T) * tokens / world / (ms_step / 1e3)
+        row = {"metric": "train tokens/sec", "model": model_name, "layers": cfg.n_layer, "tp": tp, "dp": dp,
+               "collectives": collectives, "global_batch": B * dp, "seq_len": T, "value": tokens / (ms_step / 1e3),
+               "ms_per_step": ms_step, "n_gpus": world, "steps": steps, "model_tflops_per_gpu": flops / 1e12,
+               "cuda_graph": step.graph is not None, "loss_first": losses[0], "loss_last": float(lt) / dp,
+               "dtype": "bf16", "data": "synthetic"}
+    del step, opt, model, tpc, tok, tgt, loss
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return row
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="llama-1b", choices=["llama-1b", "llama-3b", "llama-tiny"])
@@ -35,72 +114,10 @@ def main():
     dev = torch.device("cuda", local)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     dist.init_process_group("nccl", device_id=dev)
-    rank, world = dist.get_rank(), dist.get_world_size()
-    assert world == args.tp * args.dp, f"world {world} != tp {args.tp} x dp {args.dp}"
-    from incin_b200.engine import TrainStep
-    from incin_b200.models.llama import LlamaConfig
-    from incin_b200.models.llama_tp import LlamaTP, TPOptimizer
-    from incin_b200.ops import gemm as G
-    from incin_b200.parallel.mesh import mesh
-    from incin_b200.parallel.tp import TensorParallel
-
-    cfg = {"llama-1b": LlamaConfig.llama_1b, "llama-3b": LlamaConfig.llama_3b, "llama-tiny": LlamaConfig.tiny}[args.model]()
-    if args.layers:
-        cfg.n_layer = args.layers
-    spec = mesh(dp=args.dp, tp=args.tp)
-    d, _, t = spec.coords(rank)
-    tp_groups = [dist.new_group([spec.rank_of(dd, 0, tt) for tt in range(args.tp)]) for dd in range(args.dp)]
-    dp_groups = [dist.new_group([spec.rank_of(dd, 0, tt) for dd in range(args.dp)]) for tt in range(args.tp)]
-    tp_group = tp_groups[d] if args.dp > 1 else None
-    dp_group = dp_groups[t] if args.dp > 1 else None
-    B, T = args.batch, args.seq
-    Ml = B * T // args.tp
-    tpc = TensorParallel(dev, tp_group, max_rows_per_rank=Ml, max_cols=cfg.d_model, mode=args.collectives)
-    torch.manual_seed(0)
-    model = LlamaTP(cfg, args.tp, t)
-    with torch.no_grad():       # random-init N(0, 0.02) directly on the shards (no full model on the host)
-        g = torch.Generator().manual_seed(1000 + t)
-        for name, p in model.named_parameters():
-            if p.dim() >= 2:
-                if name in ("embed", "lm_head"):
-                    p.normal_(0.0, cfg.init_std, generator=torch.Generator().manual_seed(7 + (name == "lm_head")))
-                else:
-                    p.normal_(0.0, cfg.init_std, generator=g)
-    model = model.to(dev)
-    model.tp = tpc
-    opt = TPOptimizer(model, tpc, dev, lr=3e-4, dp_group=dp_group, world_group=None)
-    step = TrainStep(model, opt, use_graph=not args.no_graph and args.collectives == "fused")
-    gen = torch.Generator().manual_seed(99 + d)
-    tok = torch.randint(0, cfg.vocab_size, (B, T), generator=gen).to(dev)
-    tgt = torch.randint(0, cfg.vocab_size, (B, T), generator=gen).to(dev)
-    losses = []
-    for _ in range(max(args.warmup, 3)):
-        losses.append(float(step(tok, tgt)))
-    G.check_status(dev)
-    dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        loss = step(tok, tgt)
-    e1.record()
-    dist.barrier()
-    torch.cuda.synchronize()
-    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    lt = loss.clone()
-    dist.all_reduce(lt)
-    G.check_status(dev)
-    if rank == 0:
-        ms_step = float(ms) / args.steps
-        tokens = B * T * args.dp
-        flops = cfg.flops_per_token(T) * tokens / world / (ms_step / 1e3)
-        print(json.dumps({"metric": "train tokens/sec", "model": args.model, "layers": cfg.n_layer, "tp": args.tp,
-                          "dp": args.dp, "collectives": args.collectives, "global_batch": B * args.dp, "seq_len": T,
-                          "value": tokens / (ms_step / 1e3), "ms_per_step": ms_step, "n_gpus": world,
-                          "model_tflops_per_gpu": flops / 1e12, "cuda_graph": step.graph is not None,
-                          "loss_first": losses[0], "loss_last": float(lt) / args.dp, "dtype": "bf16",
-                          "data": "synthetic"}), flush=True)
+    row = run(args.model, args.tp, args.dp, args.batch, args.seq, args.steps, args.warmup, args.collectives,
+              use_graph=not args.no_graph, layers=args.layers)
+    if row is not None:
+        print(json.dumps(row), flush=True)
     dist.destroy_process_group()
 
 
