@@ -123,7 +123,7 @@ def reference_arm(args) -> None:
                       "produced; it also has no transformer model or multi-device fit"}))
 
 
-def extra_measurements(args, world: int, rank: int, device) -> dict:
+def extra_measurements(args, world: int, rank: int, device, ctx=None) -> dict:
     """The other benchmark configurations (see the module docstring).  Every entry is guarded: a failure is recorded
     as text and never costs the headline number, which has been computed before this runs."""
     import contextlib
@@ -175,10 +175,11 @@ def extra_measurements(args, world: int, rank: int, device) -> dict:
         def tp_pair(model, tp, dp, batch, seq):
             out = {}
             for arm in ("fused", "nccl"):
-                row = TB.run(model, tp, dp, batch, seq, steps=5, warmup=3, collectives=arm)
+                row = TB.run(model, tp, dp, batch, seq, steps=5, warmup=3, collectives=arm, ctx=ctx)
                 if row is not None:
                     out[arm] = {k: row[k] for k in ("value", "ms_per_step", "global_batch", "seq_len", "cuda_graph",
-                                                    "model_tflops_per_gpu", "loss_first", "loss_last")}
+                                                    "model_tflops_per_gpu", "loss_first", "loss_last",
+                                                    "plan_validated_launches")}
             return out
 
         guarded(f"llama_1b_tp{world}", lambda: tp_pair("llama-1b", world, 1, 16, 2048))
@@ -221,6 +222,22 @@ def main() -> None:
 
     reducer = None
     dp_kind = "none"
+    # The repo's own rendezvous (INCIN_RANK / INCIN_WORLD_SIZE / INCIN_RENDEZVOUS_ADDR, or torchrun's RANK / WORLD_SIZE /
+    # MASTER_ADDR with MASTER_PORT + 1): plan agreement before peer mappings, IPC handles over its control channel,
+    # every fused launch checked against the agreed plan.  INCIN_BENCH_RENDEZVOUS=0 leaves the plumbing to torch.distributed.
+    ctx = session = None
+    control_plane = "torch.distributed"
+    if world > 1 and args.impl == "ours" and os.environ.get("INCIN_BENCH_RENDEZVOUS", "1") != "0":
+        try:
+            from incin_b200.parallel.context import DistributedContext
+            from incin_b200.parallel.mesh import mesh as mesh_spec
+            from incin_b200.parallel.session import bind_session
+            ctx = DistributedContext.from_env()
+            session = bind_session(ctx, mesh_spec(dp=world))
+            control_plane = "incin rendezvous (plan preflight, handle exchange, launch cursor)"
+        except Exception as e:   # noqa: BLE001 - the benchmark still runs on the torch.distributed plumbing
+            ctx = session = None
+            control_plane = f"torch.distributed (rendezvous unavailable: {type(e).__name__})"
     if args.impl == "torch":
         from incin_b200.baseline_torch import build_torch_baseline
         step, dp_kind = build_torch_baseline(cfg, device, world)
@@ -230,7 +247,7 @@ def main() -> None:
         allocator = None
         if world > 1:
             from incin_b200.parallel import dp as DP
-            reducer, allocator, dp_kind = DP.make_reducer(args.dp, device)
+            reducer, allocator, dp_kind = DP.make_reducer(args.dp, device, session=session)
         store = ParamStore(model.named_parameters(), allocator=allocator)
         opt = AdamW(store, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
         if reducer is not None:
@@ -338,7 +355,8 @@ def main() -> None:
             "impl": args.impl,
             "config": {"model": args.model, "global_batch": B * world, "micro_batch_per_gpu": B, "seq_len": T,
                        "parallelism": f"dp{world}", "optimizer": "AdamW fp32 master + bf16 shadow",
-                       "dp_reduction": dp_kind, "cuda_graph": graph_used,
+                       "dp_reduction": dp_kind, "cuda_graph": graph_used, "control_plane": control_plane,
+                       "plan_validated_launches": (session.launches if session is not None else 0),
                        "attention": args.attention,
                        "l2": "no explicit flush: one step touches ~2.5 GB of parameters/optimizer state plus GBs "
                              "of activations, far larger than the 126 MB L2"},
@@ -372,7 +390,7 @@ def main() -> None:
         import gc
         gc.collect()
         torch.cuda.empty_cache()
-        extra = extra_measurements(args, world, rank, device)
+        extra = extra_measurements(args, world, rank, device, ctx)
         dog.cancel()
         if out is not None:
             out["extra"] = extra

@@ -18,9 +18,12 @@ import torch.distributed as dist
 
 
 def run(model_name: str, tp: int, dp: int, batch: int, seq: int, steps: int = 5, warmup: int = 3,
-        collectives: str = "fused", use_graph: bool = True, layers: int = 0) -> dict | None:
+        collectives: str = "fused", use_graph: bool = True, layers: int = 0, ctx=None) -> dict | None:
     """One measurement inside an initialised process group of ``tp * dp`` ranks (one GPU each, current device set).
-    Returns the result row on rank 0, None elsewhere.  Everything it allocates is released before it returns."""
+    Returns the result row on rank 0, None elsewhere.  Everything it allocates is released before it returns.
+    ``ctx``: a rendezvous context of the job; the fused arm then runs under the plan contract (the step's collectives
+    are agreed on before any peer mapping is opened, handles travel over the context's control channel, every fused
+    launch is checked against the plan)."""
     dev = torch.device("cuda", torch.cuda.current_device())
     rank, world = dist.get_rank(), dist.get_world_size()
     assert world == tp * dp, f"world {world} != tp {tp} x dp {dp}"
@@ -43,7 +46,16 @@ def run(model_name: str, tp: int, dp: int, batch: int, seq: int, steps: int = 5,
         tp_group, dp_group = tp_groups[d], dp_groups[t]
     B, T = batch, seq
     Ml = B * T // tp
-    tpc = TensorParallel(dev, tp_group, max_rows_per_rank=Ml, max_cols=cfg.d_model, mode=collectives)
+    session = plan = tp_ranks = dp_ranks = None
+    if ctx is not None and collectives == "fused":
+        from incin_b200.models.llama_tp import tensor_parallel_plan
+        from incin_b200.parallel.session import bind_session
+        session = bind_session(ctx, spec)
+        plan = tensor_parallel_plan(cfg, session.mesh, rank, B * T)
+        tp_ranks = [spec.rank_of(d, 0, tt) for tt in range(tp)]
+        dp_ranks = [spec.rank_of(dd, 0, t) for dd in range(dp)]
+    tpc = TensorParallel(dev, tp_group, max_rows_per_rank=Ml, max_cols=cfg.d_model, mode=collectives, session=session,
+                         plan=plan, ranks=tp_ranks)
     torch.manual_seed(0)
     model = LlamaTP(cfg, tp, t)
     with torch.no_grad():       # random-init N(0, 0.02) directly on the shards (no full model on the host)
@@ -56,7 +68,7 @@ def run(model_name: str, tp: int, dp: int, batch: int, seq: int, steps: int = 5,
                     p.normal_(0.0, cfg.init_std, generator=g)
     model = model.to(dev)
     model.tp = tpc
-    opt = TPOptimizer(model, tpc, dev, lr=3e-4, dp_group=dp_group, world_group=None)
+    opt = TPOptimizer(model, tpc, dev, lr=3e-4, dp_group=dp_group, world_group=None, session=session, dp_ranks=dp_ranks)
     step = TrainStep(model, opt, use_graph=use_graph and collectives == "fused")
     gen = torch.Generator().manual_seed(99 + d)
     tok = torch.randint(0, cfg.vocab_size, (B, T), generator=gen).to(dev)
@@ -87,7 +99,8 @@ def run(model_name: str, tp: int, dp: int, batch: int, seq: int, steps: int = 5,
         row = {"metric": "train tokens/sec", "model": model_name, "layers": cfg.n_layer, "tp": tp, "dp": dp,
                "collectives": collectives, "global_batch": B * dp, "seq_len": T, "value": tokens / (ms_step / 1e3),
                "ms_per_step": ms_step, "n_gpus": world, "steps": steps, "model_tflops_per_gpu": flops / 1e12,
-               "cuda_graph": step.graph is not None, "loss_first": losses[0], "loss_last": float(lt) / dp,
+               "cuda_graph": step.graph is not None, "loss_first": losses[0] * tp, "loss_last": float(lt) / dp,
+               "plan_validated_launches": (session.launches if session is not None else 0),
                "dtype": "bf16", "data": "synthetic"}
     del step, opt, model, tpc, tok, tgt, loss
     import gc

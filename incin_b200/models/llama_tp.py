@@ -57,16 +57,43 @@ class LlamaBlockTP(nn.Module):
             self.gate_up_w.copy_(torch.cat([gu[rank * self.fl:(rank + 1) * self.fl], gu[Fd + rank * self.fl:Fd + (rank + 1) * self.fl]]))
             self.down_w.copy_(full.down_w.detach()[:, rank * self.fl:(rank + 1) * self.fl])
 
-    def forward(self, x_shard, tp: TensorParallel, B: int, T: int):
+    def forward(self, x_shard, tp: TensorParallel, B: int, T: int, layer: int = 0):
         cfg, D = self.cfg, self.cfg.head_dim
+        i = 4 * layer                                                                  # plan ids of this block's four linears
         res, h = F.rmsnorm_fork(x_shard, self.attn_norm, cfg.rms_eps)
-        qkv = column_parallel_linear(h, tp, self.q_w, self.kv_w)                       # [B*T, (hq + 2 hkv) D]
+        qkv = column_parallel_linear(h, tp, self.q_w, self.kv_w, tp_id=i)              # [B*T, (hq + 2 hkv) D]
         qkv = F.rope(qkv.view(B, T, self.hq + 2 * self.hkv, D), self.hq + self.hkv, D, cfg.rope_theta)
         a = F.gqa_attention(qkv.view(B, T, -1), self.hq, self.hkv, D)                  # [B, T, hq D]
-        x_shard = row_parallel_linear(a.view(B * T, self.hq * D), tp, self.o_w, res)   # [B*T / tp, C]
+        x_shard = row_parallel_linear(a.view(B * T, self.hq * D), tp, self.o_w, res, tp_id=i + 1)   # [B*T / tp, C]
         res, h = F.rmsnorm_fork(x_shard, self.ffn_norm, cfg.rms_eps)
-        g = F.swiglu(column_parallel_linear(h, tp, self.gate_up_w))                    # [B*T, F / tp]
-        return row_parallel_linear(g, tp, self.down_w, res)
+        g = F.swiglu(column_parallel_linear(h, tp, self.gate_up_w, tp_id=i + 2))       # [B*T, F / tp]
+        return row_parallel_linear(g, tp, self.down_w, res, tp_id=i + 3)
+
+
+def tensor_parallel_plan(cfg: LlamaConfig, mesh, rank: int, tokens: int):
+    """The tensor-parallel collectives of ONE training step of :class:`LlamaTP` in launch order, as a
+    :class:`~incin_b200.parallel.plan.CollectivePlan`: per block, forward = all-gather (QKV), reduce-scatter
+    (attention output), all-gather (gate / up), reduce-scatter (down); then the backward pass block by block in
+    reverse, every linear running the adjoint of its forward collective.  ``tokens`` = B * T of the group.
+    Linear ``k`` of block ``l`` has plan id ``4 l + k``; ids ``2 id`` / ``2 id + 1`` tag its forward / backward launch."""
+    from ..parallel.strategies import TensorParallelPlanBuilder
+    b = TensorParallelPlanBuilder(mesh, rank)
+    c = cfg.d_model
+    col_in = (tokens, c)                       # gathered activation of both column-parallel linears
+    row_out = (tokens, c)                      # partial product of both row-parallel linears
+    for layer in range(cfg.n_layer):
+        i = 4 * layer
+        b.push_column(2 * i, col_in, 0)
+        b.push_row_scatter(2 * (i + 1), row_out, 0)
+        b.push_column(2 * (i + 2), col_in, 0)
+        b.push_row_scatter(2 * (i + 3), row_out, 0)
+    for layer in reversed(range(cfg.n_layer)):
+        i = 4 * layer
+        b.push_column(2 * (i + 3) + 1, (tokens, c), 0)           # d(down): all-gather of the output-gradient shards
+        b.push_row_scatter(2 * (i + 2) + 1, (tokens, c), 0)      # d(gate / up): reduce-scatter of the input gradient
+        b.push_column(2 * (i + 1) + 1, (tokens, c), 0)           # d(attention output)
+        b.push_row_scatter(2 * i + 1, (tokens, c), 0)            # d(QKV)
+    return b.finish()
 
 
 class LlamaTP(nn.Module):
@@ -117,8 +144,9 @@ class LlamaTP(nn.Module):
         lo = tp.rank * Ml
         tok = tokens.reshape(-1)[lo:lo + Ml].reshape(1, Ml)
         x = F.embedding(tok, self.embed, None).view(Ml, cfg.d_model)
-        for b in self.blocks:
-            x = b(x, tp, B, T)
+        tp.begin_step()
+        for li, b in enumerate(self.blocks):
+            x = b(x, tp, B, T, li)
         h = F.rms_norm(x, self.final_norm, cfg.rms_eps)
         loss = F.linear_cross_entropy(h, self.lm_head, targets.reshape(-1)[lo:lo + Ml], cfg.vocab_size)
         return loss * (1.0 / tp.world)
@@ -131,20 +159,27 @@ class TPOptimizer:
     data-parallel reduction when there is a data axis)."""
 
     def __init__(self, model: LlamaTP, tp: TensorParallel, device, *, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
-                 dp_group=None, world_group=None):
+                 dp_group=None, world_group=None, session=None, dp_ranks=None):
+        """``session``: the collective session of the job (plan agreement before peer mappings, handles over its
+        control channel); the reducers take it with the ranks of their groups (``tp.ranks``, ``dp_ranks``)."""
         from ..optim.flat import AdamW, ParamStore
         from ..parallel.dp import FusedReducer
         import torch.distributed as dist
         self.model, self.tp, self.device = model, tp, device
         dp = dist.get_world_size(dp_group) if dp_group is not None else 1
         # replicated group: reduced over every rank that holds a copy (tp x dp)
-        self.rep_reducer = FusedReducer(device, world_group if dp > 1 else tp.group, overlap=False)
+        from ..parallel.mesh import Axis
+        rep_ranks = None
+        if session is not None and session.ctx is not None:
+            rep_ranks = list(range(session.ctx.world)) if dp > 1 else tp.ranks
+        self.rep_reducer = FusedReducer(device, world_group if dp > 1 else tp.group, overlap=False, session=session,
+                                        ranks=rep_ranks, axis=Axis.TENSOR, plan_ranks=tp.ranks)
         self.rep_store = ParamStore(model.replicated_parameters(), allocator=self.rep_reducer.allocator)
         self.rep_opt = AdamW(self.rep_store, lr=lr, betas=betas, weight_decay=weight_decay)
         self.rep_reducer.attach(self.rep_store, self.rep_opt)
         self.rep_opt.grad_scale = float(tp.world)          # sum over tp (local losses carry 1/tp), mean over dp
         # sharded group
-        self.dp_reducer = FusedReducer(device, dp_group, overlap=False) if dp > 1 else None
+        self.dp_reducer = FusedReducer(device, dp_group, overlap=False, session=session, ranks=dp_ranks) if dp > 1 else None
         alloc = self.dp_reducer.allocator if self.dp_reducer else None
         self.kv_share = model.kv_shared()
         self._grad_buf = None
@@ -157,7 +192,7 @@ class TPOptimizer:
                     return holder["g"].typed(torch.float32, n)
                 return torch.zeros(n, dtype=dtype, device=dev)
             self.sh_store = ParamStore(model.sharded_parameters(), allocator=alloc)
-            self._grad_buf = holder["g"].exchange(tp.group)
+            self._grad_buf = holder["g"].exchange(tp.group, session=session, ranks=tp.ranks)
         else:
             self.sh_store = ParamStore(model.sharded_parameters(), allocator=alloc)
             if self.dp_reducer is not None and self.kv_share > 1:

@@ -21,7 +21,10 @@ import torch
 import torch.distributed as dist
 
 from .. import _native as nat
+from ..core.dtype import DTypeId
 from ..ops.gemm import status_word
+from .placement import Reduction
+from .plan import CollectiveKind
 from .symm import SymmetricBuffer
 
 MAX_PEERS = 8
@@ -70,10 +73,26 @@ class FusedReducer:
     kind = "fused p2p reduce-scatter + adamw + all-gather (one kernel per bucket)"
 
     def __init__(self, device: torch.device, group=None, *, overlap: bool = True, bucket_elems: int = 16 << 20,
-                 ctas_overlap: int = 24, ctas_tail: int = 64):
+                 ctas_overlap: int = 24, ctas_tail: int = 64, session=None, ranks: list[int] | None = None, axis=None,
+                 plan_ranks: list[int] | None = None):
+        """``session`` (a :class:`~incin_b200.parallel.session.CollectiveSession`) puts the reducer under the plan
+        contract: ``attach`` builds the step's plan (one all-reduce(mean) per bucket, chained), agrees on its hash
+        among ``ranks`` BEFORE any peer mapping is opened, moves the IPC handles over the session's control channel
+        and checks every bucket launch against the plan cursor.  ``axis``: the mesh axis reduced over (default DATA);
+        ``plan_ranks``: the ranks of that axis' group when the reduction spans more than one mesh axis (the plan is
+        then agreed within the axis group, whose ranks the plan names, while buffers are shared among ``ranks``)."""
         self.device, self.group = device, group
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        self.session, self.lane, self.axis = session, None, axis
+        if session is not None and ranks is None and group is not None:
+            ranks = dist.get_process_group_ranks(group)
+        self.ranks = ranks
+        self.plan_ranks = plan_ranks if plan_ranks is not None else ranks
+        if session is not None and session.ctx is not None:
+            job_ranks = ranks if ranks is not None else list(range(session.ctx.world))
+            self.world, self.rank = len(job_ranks), job_ranks.index(session.ctx.rank)
+        else:
+            self.world = dist.get_world_size(group)
+            self.rank = dist.get_rank(group)
         if self.world > MAX_PEERS:
             raise ValueError(f"fused reducer supports up to {MAX_PEERS} ranks per node")
         self.overlap = overlap
@@ -96,21 +115,19 @@ class FusedReducer:
         opt.reducer = self
         shadow_buf = next(b for b in self._bufs if b.ptr == store.shadow.data_ptr())
         grad_buf = next(b for b in self._bufs if b.ptr == store.grad.data_ptr())
-        self.pad = SymmetricBuffer(nat.cuda().incin_dp_pad_bytes(), self.device)
-        for b in (shadow_buf, grad_buf, self.pad):
-            b.exchange(self.group)
-        self.shadow_buf, self.grad_buf = shadow_buf, grad_buf
         # buckets: contiguous ranges of the flat buffer, cut at parameter boundaries
-        bounds = [0]
-        for name, p, off, numel in store.entries:
-            if off - bounds[-1] >= self.bucket_elems:
-                bounds.append(off)
-        bounds.append(store.numel)
-        self.buckets = [(bounds[i], bounds[i + 1]) for i in range(len(bounds) - 1) if bounds[i + 1] > bounds[i]]
-        if not self.overlap:
-            self.buckets = [(0, store.numel)]
+        self.buckets = bucket_ranges(store.entries, store.numel, self.bucket_elems if self.overlap else 0)
         if len(self.buckets) > MAX_SLOTS:
             raise ValueError("too many gradient buckets")
+        if self.session is not None:
+            # the plan first: a rank whose buckets differ (other model, other bucket size) is rejected here, before
+            # any of its memory is mapped into a peer
+            self.lane = self.session.agree(reducer_plan(self.session.mesh, self.session.rank, self.buckets, self.axis),
+                                           self.plan_ranks, self.group if self.plan_ranks is self.ranks else None)
+        self.pad = SymmetricBuffer(nat.cuda().incin_dp_pad_bytes(), self.device)
+        for b in (shadow_buf, grad_buf, self.pad):
+            b.exchange(self.group, session=self.session, ranks=self.ranks)
+        self.shadow_buf, self.grad_buf = shadow_buf, grad_buf
         self._descs = [self._make_desc(i, lo, hi) for i, (lo, hi) in enumerate(self.buckets)]
         # readiness bookkeeping: a bucket is ready when every parameter overlapping it is complete
         self._entry_buckets: dict[int, list[int]] = {}
@@ -124,7 +141,10 @@ class FusedReducer:
                 p._grad_ready = self._on_ready
         if self.overlap:
             self.comm_stream = torch.cuda.Stream(device=self.device)
-        dist.barrier(group=self.group)
+        if self.session is not None and self.session.ctx is not None:
+            self.session.barrier(self.ranks)
+        else:
+            dist.barrier(group=self.group)
 
     def _make_desc(self, slot: int, lo: int, hi: int) -> DpDesc:
         d = DpDesc()
@@ -141,11 +161,17 @@ class FusedReducer:
         return d
 
     def begin_step(self) -> None:
+        if self.lane is not None:
+            self.lane.begin_step()
         self._uses_left = {id(p): getattr(p, "_grad_uses", 1) for _, p, _, _ in self.store.entries}
         self._need_left = list(self._bucket_need)
         self._launched = [False] * len(self.buckets)
+        self._next = 0
 
     def _launch(self, i: int, stream: torch.cuda.Stream) -> None:
+        if self.lane is not None:    # fail-stop state, then: is bucket i the next collective of the agreed plan?
+            lo, hi = self.buckets[i]
+            self.lane.launch(tag=i, kind=CollectiveKind.all_reduce(Reduction.MEAN), elements=hi - lo, dtype=DTypeId.F32)
         nat.check(nat.cuda().incin_dp_reduce_adamw(C.byref(self._descs[i]), stream.cuda_stream), "dp_reduce_adamw")
         self._launched[i] = True
 
@@ -156,10 +182,12 @@ class FusedReducer:
             return
         for i in self._entry_buckets[key]:
             self._need_left[i] -= 1
-            if self._need_left[i] == 0 and not self._launched[i]:
-                cur = torch.cuda.current_stream()
-                self.comm_stream.wait_stream(cur)
-                self._launch(i, self.comm_stream)
+        # buckets start in plan order (the order every rank agreed on): the first not yet started one, once complete
+        while self._next < len(self.buckets) and self._need_left[self._next] == 0:
+            cur = torch.cuda.current_stream()
+            self.comm_stream.wait_stream(cur)
+            self._launch(self._next, self.comm_stream)
+            self._next += 1
 
     def finish_step(self, opt) -> None:
         cur = torch.cuda.current_stream()
@@ -174,15 +202,39 @@ class FusedReducer:
             self._launch(0, cur)
 
 
-def make_reducer(kind: str, device: torch.device, group=None):
+def bucket_ranges(entries, numel: int, bucket_elems: int) -> list[tuple[int, int]]:
+    """Contiguous ranges of the flat buffer cut at parameter boundaries, at least ``bucket_elems`` long each (0 = one
+    bucket for everything)."""
+    if bucket_elems <= 0:
+        return [(0, numel)]
+    bounds = [0]
+    for name, p, off, n in entries:
+        if off - bounds[-1] >= bucket_elems:
+            bounds.append(off)
+    bounds.append(numel)
+    return [(bounds[i], bounds[i + 1]) for i in range(len(bounds) - 1) if bounds[i + 1] > bounds[i]]
+
+
+def reducer_plan(mesh, rank: int, buckets, axis=None):
+    """The gradient reduction of one step as a plan: one all-reduce(mean) of fp32 elements per bucket, in launch order,
+    each depending on the one before (crates/incin-core/src/dist/data_parallel.rs:136-245 plans one per parameter)."""
+    from .mesh import Axis
+    from .strategies import DataParallelPlanBuilder
+    b = DataParallelPlanBuilder(mesh, rank, axis or Axis.DATA)
+    for i, (lo, hi) in enumerate(buckets):
+        b.push(i, hi - lo, DTypeId.F32)
+    return b.finish()
+
+
+def make_reducer(kind: str, device: torch.device, group=None, session=None):
     """Returns ``(reducer, allocator, description)`` for ``bench.py`` / the Trainer."""
     if kind in ("fused", "fused-overlap"):
         import os
         r = FusedReducer(device, group, overlap=True, ctas_overlap=int(os.environ.get("INCIN_DP_OVERLAP_CTAS", "8")),
-                         bucket_elems=int(os.environ.get("INCIN_DP_BUCKET_ELEMS", str(16 << 20))))
+                         bucket_elems=int(os.environ.get("INCIN_DP_BUCKET_ELEMS", str(16 << 20))), session=session)
         return r, r.allocator, r.kind + " overlapped with backward"
     if kind in ("auto", "fused-tail"):
-        r = FusedReducer(device, group, overlap=False)
+        r = FusedReducer(device, group, overlap=False, session=session)
         return r, r.allocator, r.kind + " after backward"
     r = NcclReducer(group)
     return r, r.allocator, r.kind

@@ -26,13 +26,16 @@ from .plan import CollectiveKind, CollectivePlan, CollectivePlanBuilder, PlanErr
 class DataParallelPlanBuilder:
     """``push(gradient_id, elements, dtype)`` per bucket, in the order the backward pass completes them."""
 
-    def __init__(self, mesh: DeviceMesh, rank: int = 0):
+    def __init__(self, mesh: DeviceMesh, rank: int = 0, axis: Axis = Axis.DATA):
+        """``axis``: the mesh axis the gradients are averaged over (DATA; TENSOR for the replicated parameters of a
+        tensor-parallel model, whose gradients are partial over the token shards of the tensor-parallel group)."""
         self._b = CollectivePlanBuilder(mesh, rank)
         self._last: int | None = None
+        self.axis = axis
 
     def push(self, gradient_id: int, elements: int, dtype: DTypeId = DTypeId.F32) -> int:
-        seq = self._b.push(gradient_id, Axis.DATA, CollectiveKind.all_reduce(Reduction.MEAN), elements, dtype,
-                           Partial(Reduction.MEAN, Axis.DATA), Replicated(), depends_on=self._last)
+        seq = self._b.push(gradient_id, self.axis, CollectiveKind.all_reduce(Reduction.MEAN), elements, dtype,
+                           Partial(Reduction.MEAN, self.axis), Replicated(), depends_on=self._last)
         self._last = seq
         return seq
 

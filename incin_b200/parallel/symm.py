@@ -50,12 +50,22 @@ class SymmetricBuffer:
         t = self.local_bytes.view(dtype)
         return t if numel is None else t[:numel]
 
-    def exchange(self, group=None) -> "SymmetricBuffer":
-        """Collective: share this buffer's handle with every rank of the group and map theirs."""
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
-        handles: list = [None] * self.world
-        dist.all_gather_object(handles, bytes(self._handle.raw), group=group)
+    def exchange(self, group=None, session=None, ranks: list[int] | None = None) -> "SymmetricBuffer":
+        """Collective: share this buffer's handle with every rank of the group and map theirs.  With a
+        :class:`~incin_b200.parallel.session.CollectiveSession` that owns a rendezvous context the handles travel over
+        the repo's own control channel (``ranks`` = the job ranks of this group, in group order); otherwise over
+        ``torch.distributed``."""
+        if session is not None and session.ctx is not None:
+            if ranks is None:
+                ranks = (dist.get_process_group_ranks(group) if group is not None else list(range(session.ctx.world)))
+            self.world, self.rank = len(ranks), ranks.index(session.ctx.rank)
+            session.ensure_active()
+            handles = session.allgather(bytes(self._handle.raw), ranks)
+        else:
+            self.world = dist.get_world_size(group)
+            self.rank = dist.get_rank(group)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(self._handle.raw), group=group)
         self.ptrs = []
         with torch.cuda.device(self.device):
             for r, h in enumerate(handles):
@@ -66,7 +76,10 @@ class SymmetricBuffer:
                 nat.check(nat.cuda().incin_symm_open(h, C.byref(p)), f"symm_open(rank {r})")
                 self.ptrs.append(p.value)
                 self._opened.append(p.value)
-        dist.barrier(group=group)
+        if session is not None and session.ctx is not None:
+            session.barrier(ranks)
+        else:
+            dist.barrier(group=group)
         return self
 
     def close(self) -> None:

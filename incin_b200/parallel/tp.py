@@ -28,10 +28,15 @@ import torch
 import torch.distributed as dist
 
 from .. import _native as nat
+from ..core.dtype import DTypeId
 from ..ops import gemm as G
 from ..ops import kernels as K
 from ..ops.functional import _ready, main_grad
 from ..ops.gemm import status_word
+from .placement import (Partial, Placement, PlacementError, PlacementTransition, Reduction, Replicated, Sharded,
+                        validate_transition)
+from .plan import CollectiveKind
+from .strategies import TensorParallelCollective, tp_tag
 from .symm import SymmetricBuffer
 
 nat.register_cuda_signatures({
@@ -45,13 +50,29 @@ class TensorParallel:
     """Per-process context of one tensor-parallel group (all ranks of ``group`` on one NVSwitch node)."""
 
     def __init__(self, device: torch.device, group=None, *, max_rows_per_rank: int, max_cols: int, copy_ctas: int = 0,
-                 mode: str = "fused"):
+                 mode: str = "fused", session=None, plan=None, ranks: list[int] | None = None):
         """``mode="nccl"`` is the baseline arm (not the product): the same layers with NCCL all-gather /
-        reduce-scatter as separate launches around the local GEMM."""
+        reduce-scatter as separate launches around the local GEMM.
+
+        ``session`` (a :class:`~incin_b200.parallel.session.CollectiveSession`) with ``plan`` (the step's collectives in
+        launch order, e.g. ``models.llama_tp.tensor_parallel_plan``) puts the group under the plan contract: the plan
+        hash is agreed among ``ranks`` (the job ranks of this group) FIRST — a divergent rank is rejected before any
+        peer-mapped buffer exists — the IPC handles then travel over the session's control channel, and every fused
+        launch that is given a tag is checked against the plan cursor."""
         assert mode in ("fused", "nccl")
         self.mode = mode
         self.device, self.group = device, group
-        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.session, self.lane = session, None
+        if session is not None and ranks is None and group is not None:
+            ranks = dist.get_process_group_ranks(group)
+        self.ranks = ranks
+        if session is not None and plan is not None:
+            self.lane = session.agree(plan, ranks, group)       # raises PreflightError before anything is opened
+        if session is not None and session.ctx is not None:
+            job_ranks = ranks if ranks is not None else list(range(session.ctx.world))
+            self.world, self.rank = len(job_ranks), job_ranks.index(session.ctx.rank)
+        else:
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if self.world > 8:
             raise ValueError("a tensor-parallel group spans at most the 8 GPUs of one node")
         if max_rows_per_rank % 128:
@@ -59,13 +80,26 @@ class TensorParallel:
         self.rows, self.cols = max_rows_per_rank, max_cols
         self.copy_ctas = copy_ctas          # 0 = choose per call from the copy volume and the GEMM size
         shard_bytes = max_rows_per_rank * max_cols * 2
-        self.shard = [SymmetricBuffer(shard_bytes, device).exchange(group) for _ in range(2)]
-        self.slots = [SymmetricBuffer(self.world * shard_bytes, device).exchange(group) for _ in range(2)]
-        self.pad = SymmetricBuffer(nat.cuda().incin_barrier_pad_bytes(), device).exchange(group)
+        ex = dict(session=session, ranks=ranks)
+        self.shard = [SymmetricBuffer(shard_bytes, device).exchange(group, **ex) for _ in range(2)]
+        self.slots = [SymmetricBuffer(self.world * shard_bytes, device).exchange(group, **ex) for _ in range(2)]
+        self.pad = SymmetricBuffer(nat.cuda().incin_barrier_pad_bytes(), device).exchange(group, **ex)
         self._pad_ptrs = torch.tensor(self.pad.ptrs, dtype=torch.int64, device=device)
         self._shard_parity = self._slot_parity = 0
         self._barrier_slot = 0
-        dist.barrier(group=group)
+        if session is not None and session.ctx is not None:
+            session.barrier(ranks)
+        else:
+            dist.barrier(group=group)
+
+    def begin_step(self) -> None:
+        """Rewind the plan cursor: the plan describes one training step."""
+        if self.lane is not None:
+            self.lane.begin_step()
+
+    def _planned(self, tag, kind, elements: int) -> None:
+        if self.lane is not None and tag is not None:
+            self.lane.launch(tag=tag, kind=kind, elements=elements, dtype=DTypeId.BF16)
 
     # ------------------------------------------------------------------------------------------------ primitives
     COPY_CTA_GBS = 26.0      # measured: bytes one copy CTA moves through its shared-memory staging ring per second
@@ -91,10 +125,11 @@ class TensorParallel:
                                                status_word(self.device).data_ptr(), nat.stream_ptr()), "peer_barrier")
 
     def gather_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, out: torch.Tensor | None = None,
-                    ldc: int | None = None, c_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+                    ldc: int | None = None, c_offset: int = 0, tag: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
         """``(all_gather(x_shard) @ W^T, gathered)``: x_shard ``[Ml, Kd]`` bf16, W ``[N, Kd]`` (or ``[Kd, N]`` with
         ``b_mn``).  Returns the product ``[tp*Ml, N]`` and the gathered input (kept for the weight gradient)."""
         Ml, Kd = x_shard.shape
+        self._planned(tag, CollectiveKind.all_gather(), Ml * Kd)      # Sharded(0) -> Replicated: Ml x Kd elements in
         if self.mode == "nccl":
             M = Ml * self.world
             N = w.shape[1] if b_mn else w.shape[0]
@@ -125,12 +160,13 @@ class TensorParallel:
         return out, gathered
 
     def gemm_scatter(self, a: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False,
-                     residual: torch.Tensor | None = None) -> torch.Tensor:
+                     residual: torch.Tensor | None = None, tag: int | None = None) -> torch.Tensor:
         """``reduce_scatter(a @ W^T) (+ residual)``: a ``[M, Kd]`` (full rows, local K shard), W ``[N, Kd]`` (or
         ``[Kd, N]`` with ``b_mn``) -> ``[M / tp, N]`` rows owned by this rank."""
         M, Kd = a.shape
         N = w.shape[1] if b_mn else w.shape[0]
         Ml = M // self.world
+        self._planned(tag, CollectiveKind.reduce_scatter(Reduction.SUM), M * N)   # Partial(Sum) -> Sharded(0): M x N in
         if self.mode == "nccl":
             full = torch.empty(M, N, dtype=torch.bfloat16, device=self.device)
             G.gemm(a, w, full, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=N, b_mn=b_mn)
@@ -159,14 +195,22 @@ class TensorParallel:
 
 
 # ---------------------------------------------------------------------------------------------------- autograd
+def _tags(tp_id: int | None, forward: TensorParallelCollective, backward: TensorParallelCollective):
+    """Plan tags of one parallel linear: its forward collective and the adjoint its backward pass runs."""
+    if tp_id is None:
+        return None, None
+    return tp_tag(2 * tp_id, forward), tp_tag(2 * tp_id + 1, backward)
+
+
 class _ColumnParallel(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x_shard, tp: TensorParallel, *weights):
+    def forward(ctx, x_shard, tp: TensorParallel, tp_id, *weights):
         x_shard = x_shard.contiguous()
         n_total = sum(w.shape[0] for w in weights)
         M = x_shard.shape[0] * tp.world
         out = torch.empty(M, n_total, dtype=torch.bfloat16, device=x_shard.device)
-        _, gathered = tp.gather_gemm(x_shard, weights[0], out=out, ldc=n_total, c_offset=0)
+        tag_f, ctx.tag_b = _tags(tp_id, TensorParallelCollective.COLUMN_OUTPUT_GATHER, TensorParallelCollective.ROW_OUTPUT_SCATTER)
+        _, gathered = tp.gather_gemm(x_shard, weights[0], out=out, ldc=n_total, c_offset=0, tag=tag_f)
         off = weights[0].shape[0]
         for w in weights[1:]:      # further weights reuse the gathered rows: plain local GEMMs
             G.gemm(gathered, w, out, M=M, N=w.shape[0], K=w.shape[1], lda=w.shape[1], ldb=w.shape[1], ldc=n_total,
@@ -192,47 +236,72 @@ class _ColumnParallel(torch.autograd.Function):
             off += n
         # dx = dy @ [W0; W1; ...]: partial over the output shards -> reduce-scatter over rows
         if len(weights) == 1:
-            dx = tp.gemm_scatter(dy, weights[0], b_mn=True)
+            dx = tp.gemm_scatter(dy, weights[0], b_mn=True, tag=ctx.tag_b)
         else:
             wcat = torch.cat(list(weights), dim=0)
-            dx = tp.gemm_scatter(dy, wcat, b_mn=True)
+            dx = tp.gemm_scatter(dy, wcat, b_mn=True, tag=ctx.tag_b)
         for w in weights:      # after the last enqueued reader of the weights (a ready callback may start their update)
             if w.requires_grad:
                 _ready(w)
-        return (dx, None) + (None,) * len(weights)
+        return (dx, None, None) + (None,) * len(weights)
 
 
 class _RowParallel(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, a, tp: TensorParallel, w, residual_shard):
+    def forward(ctx, a, tp: TensorParallel, tp_id, w, residual_shard):
         a = a.contiguous()
         ctx.save_for_backward(a, w)
         ctx.tp, ctx.has_res = tp, residual_shard is not None
-        return tp.gemm_scatter(a, w, residual=residual_shard.contiguous() if residual_shard is not None else None)
+        tag_f, ctx.tag_b = _tags(tp_id, TensorParallelCollective.ROW_OUTPUT_SCATTER, TensorParallelCollective.COLUMN_OUTPUT_GATHER)
+        return tp.gemm_scatter(a, w, residual=residual_shard.contiguous() if residual_shard is not None else None, tag=tag_f)
 
     @staticmethod
     def backward(ctx, dy_shard):
         a, w = ctx.saved_tensors
         tp, dy_shard = ctx.tp, dy_shard.contiguous()
         # da = all_gather(dy) @ W   (W is [N, Kd]: read MN-major);  dW += all_gather(dy)^T @ a
-        da, dy_full = tp.gather_gemm(dy_shard, w, b_mn=True)
+        da, dy_full = tp.gather_gemm(dy_shard, w, b_mn=True, tag=ctx.tag_b)
         if w.requires_grad:
             M, N = dy_full.shape
             Kd = a.shape[1]
             G.gemm(dy_full, a, main_grad(w), M=N, N=Kd, K=M, lda=N, ldb=Kd, ldc=Kd, a_mn=True, b_mn=True,
                    accumulate=True, splits=G.auto_splits(N, Kd, M))
             _ready(w)
-        return da, None, None, (dy_shard if ctx.has_res else None)
+        return da, None, None, None, (dy_shard if ctx.has_res else None)
 
 
-def column_parallel_linear(x_shard, tp: TensorParallel, *weights):
-    """``all_gather(x_shard) @ cat(weights)^T`` -> ``[M, sum(out_i)]`` (columns of this rank's weight shards)."""
-    return _ColumnParallel.apply(x_shard, tp, *weights)
+def parallel_linear(x, tp: TensorParallel, weights, *, src: Placement, dst: Placement, tp_id: int | None = None,
+                    residual_shard=None):
+    """A linear layer over the tensor-parallel group, LOWERED FROM THE PLACEMENTS of its activation: the transition
+    ``src -> dst`` that the layer has to realise decides the fused kernel, as the reference lowers its
+    ``TensorParallelCollective`` descriptors (crates/incin-backends/src/dist/nccl.rs:741-791):
+
+    * input ``Sharded(0)`` (token rows), needed ``Replicated``  -> all-gather -> GEMM (column-parallel weights);
+    * product ``Partial(Sum)``, wanted ``Sharded(0)``           -> GEMM -> reduce-scatter (row-parallel weight).
+
+    Anything else has no fused kernel and is refused with the reason.  ``tp_id`` names the layer in the step's plan."""
+    tr = validate_transition(src, dst)
+    weights = tuple(weights) if isinstance(weights, (tuple, list)) else (weights,)
+    if tr is PlacementTransition.ALL_GATHER:
+        if src.tensor_axis != 0 or residual_shard is not None:
+            raise PlacementError("the fused all-gather -> GEMM gathers token rows (Sharded(0)) and takes no residual")
+        return _ColumnParallel.apply(x, tp, tp_id, *weights)
+    if tr is PlacementTransition.REDUCE_SCATTER:
+        if dst.tensor_axis != 0 or src.reduction is not Reduction.SUM or len(weights) != 1:
+            raise PlacementError("the fused GEMM -> reduce-scatter sums partial products into token-row shards (one weight)")
+        return _RowParallel.apply(x, tp, tp_id, weights[0], residual_shard)
+    raise PlacementError(f"no fused tensor-parallel kernel realises {src.token()} -> {dst.token()} ({tr.value})")
 
 
-def row_parallel_linear(a, tp: TensorParallel, w, residual_shard=None):
-    """``reduce_scatter(a @ w^T) + residual_shard`` -> ``[M / tp, N]``."""
-    return _RowParallel.apply(a, tp, w, residual_shard)
+def column_parallel_linear(x_shard, tp: TensorParallel, *weights, tp_id: int | None = None):
+    """``all_gather(x_shard) @ cat(weights)^T`` -> ``[M, sum(out_i)]`` (columns of this rank's weight shards):
+    the ``Sharded(0) -> Replicated`` lowering of :func:`parallel_linear`."""
+    return parallel_linear(x_shard, tp, weights, src=Sharded(0), dst=Replicated(), tp_id=tp_id)
+
+
+def row_parallel_linear(a, tp: TensorParallel, w, residual_shard=None, tp_id: int | None = None):
+    """``reduce_scatter(a @ w^T) + residual_shard`` -> ``[M / tp, N]``: the ``Partial(Sum) -> Sharded(0)`` lowering."""
+    return parallel_linear(a, tp, (w,), src=Partial(Reduction.SUM), dst=Sharded(0), tp_id=tp_id, residual_shard=residual_shard)
 
 
 class PeerRangeSum:

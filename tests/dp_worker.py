@@ -14,7 +14,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def run(kind: str, use_graph: bool, steps: int = 5):
+def run(kind: str, use_graph: bool, steps: int = 5, session=None):
     from incin_b200.engine import TrainStep
     from incin_b200.models.gpt2 import GPT2, GPT2Config
     from incin_b200.optim import AdamW, ParamStore
@@ -23,7 +23,7 @@ def run(kind: str, use_graph: bool, steps: int = 5):
     device = torch.device("cuda", torch.cuda.current_device())
     cfg = GPT2Config.tiny()
     model = GPT2(cfg, seed=0).to(device)
-    reducer, allocator, desc = DP.make_reducer(kind, device)
+    reducer, allocator, desc = DP.make_reducer(kind, device, session=session)
     if isinstance(reducer, DP.FusedReducer):
         reducer.bucket_elems = 1 << 16  # several buckets even for the tiny model
     store = ParamStore(model.named_parameters(), allocator=allocator)
@@ -49,8 +49,16 @@ def main():
     out = {"world": world}
     ref, ref_losses, _ = run("nccl", False)
     ok = True
+    # the fused arms run under the repo's own control plane: plan agreed before the peer mappings exist, IPC handles
+    # over the rendezvous channel, every bucket launch checked against the plan cursor
+    from incin_b200.parallel.context import DistributedContext
+    from incin_b200.parallel.mesh import mesh
+    from incin_b200.parallel.session import bind_session
+    session = bind_session(DistributedContext.from_env(), mesh(dp=world))
     for kind, graph in (("fused-tail", False), ("fused", False), ("fused", True)):
-        w, losses, desc = run(kind, graph)
+        before = session.launches
+        w, losses, desc = run(kind, graph, session=session)
+        ok = ok and session.launches > before
         G.check_status()
         gathered = [torch.empty_like(w) for _ in range(world)]
         dist.all_gather(gathered, w)
@@ -59,6 +67,7 @@ def main():
         out[f"{kind}{'-graph' if graph else ''}"] = {"ranks_identical": same, "max_abs_diff_vs_nccl": err,
                                                      "loss_first": losses[0], "loss_last": losses[-1]}
         ok = ok and same and err < 2e-2 and losses[-1] < losses[0]
+    out["plan_validated_launches"] = session.launches
     out["ok"] = ok
     if rank == 0:
         print("DP_RESULT " + json.dumps(out), flush=True)

@@ -225,6 +225,36 @@ def _rank_main(rank, world, port, run_id, scenario, q):
                 q.put((rank, "agreed"))
             except PL.PreflightError:
                 q.put((rank, "rejected", ctx.state.name))
+        elif scenario in ("tp_plan", "tp_plan_same"):
+            # the tensor-parallel group under the plan contract: rank 1 plans a different model width.  The plan must
+            # be rejected before a single peer-mapped buffer is created or opened.
+            import incin_b200.parallel.tp as TP
+            from incin_b200.core import Cuda
+            from incin_b200.models.llama import LlamaConfig
+            from incin_b200.models.llama_tp import tensor_parallel_plan
+            from incin_b200.parallel import mesh as M, plan as PL
+            from incin_b200.parallel.session import CollectiveSession
+            class Probe:
+                def identity(self, d): return M.DeviceIdentity(f"GPU-{d.index}", "cuda", "sm_100")
+                def link(self, a, b): return M.LinkClass.HIGH_BANDWIDTH
+            m = M.DeviceMesh.bind(M.mesh(tp=world), [Cuda(i) for i in range(world)], Probe())
+            cfg = LlamaConfig.tiny()
+            if scenario == "tp_plan" and rank == 1:
+                cfg.d_model *= 2
+            opened = []
+            class RecordingBuffer:                       # stands in for the peer-mapped allocation
+                def __init__(self, nbytes, device): opened.append(("alloc", nbytes))
+                def exchange(self, *a, **k): opened.append(("exchange",)); return self
+            TP.SymmetricBuffer = RecordingBuffer
+            session = CollectiveSession(ctx, m)
+            try:
+                TP.TensorParallel("cpu", None, max_rows_per_rank=128, max_cols=cfg.d_model, session=session,
+                                  plan=tensor_parallel_plan(cfg, m, rank, 256), ranks=list(range(world)))
+                q.put((rank, "constructed", len(opened)))
+            except PL.PreflightError:
+                q.put((rank, "rejected", len(opened), ctx.state.name))
+            except Exception as e:      # past the preflight the CPU stand-in cannot go on (no device library): expected
+                q.put((rank, "agreed_then", type(e).__name__, len(opened) > 0))
         elif scenario == "vanish":
             if rank == 1:
                 import os
@@ -287,3 +317,56 @@ def test_vanished_peer_is_detected_on_the_host():
 def test_divergent_plan_rejected_before_any_communicator():
     out = _run(2, "plan")
     assert out[0][0] == "rejected" and out[1][0] == "rejected" and out[0][1] == "FAILED"
+
+
+def test_divergent_tensor_parallel_plan_is_rejected_before_any_peer_mapping():
+    out = _run(2, "tp_plan")
+    assert out[0] == ("rejected", 0, "FAILED") and out[1] == ("rejected", 0, "FAILED")     # nothing allocated or opened
+    same = _run(2, "tp_plan_same")
+    assert all(v[0] in ("constructed", "agreed_then") for v in same.values())              # equal plans pass the preflight
+
+
+def test_plan_lane_checks_every_launch_and_placements_pick_the_kernel():
+    from incin_b200.core import Cuda
+    from incin_b200.models.llama import LlamaConfig
+    from incin_b200.models.llama_tp import tensor_parallel_plan
+    from incin_b200.parallel import mesh as M, plan as PL
+    from incin_b200.parallel.dp import bucket_ranges, reducer_plan
+    from incin_b200.parallel.placement import Partial, PlacementError, Reduction, Replicated, Sharded
+    from incin_b200.parallel.session import CollectiveSession
+    from incin_b200.parallel.strategies import TensorParallelCollective as TC, tp_tag
+    from incin_b200.parallel.tp import parallel_linear
+
+    class Probe:
+        def identity(self, d): return M.DeviceIdentity(f"GPU-{d.index}", "cuda", "sm_100")
+        def link(self, a, b): return M.LinkClass.HIGH_BANDWIDTH
+    m = M.DeviceMesh.bind(M.mesh(tp=4), [Cuda(i) for i in range(4)], Probe())
+    cfg = LlamaConfig.tiny()
+    tokens = 512
+    plan = tensor_parallel_plan(cfg, m, 0, tokens)
+    assert len(plan.descriptors) == 8 * cfg.n_layer
+    lane = CollectiveSession(None, m).agree(plan)                 # single process: agreement is local
+    shard, full = tokens // 4 * cfg.d_model, tokens * cfg.d_model
+    lane.launch(tag=tp_tag(0, TC.COLUMN_OUTPUT_GATHER), kind=PL.CollectiveKind.all_gather(), elements=shard)
+    lane.launch(tag=tp_tag(2, TC.ROW_OUTPUT_SCATTER), kind=PL.CollectiveKind.reduce_scatter(Reduction.SUM), elements=full)
+    with pytest.raises(PL.PlanError):                              # out of order: the gate/up gather comes next
+        lane.launch(tag=tp_tag(6, TC.ROW_OUTPUT_SCATTER), kind=PL.CollectiveKind.reduce_scatter(Reduction.SUM), elements=full)
+    lane.begin_step()
+    with pytest.raises(PL.PlanError):                              # right tag, wrong element count
+        lane.launch(tag=tp_tag(0, TC.COLUMN_OUTPUT_GATHER), kind=PL.CollectiveKind.all_gather(), elements=shard + 1)
+    # the backward half is the adjoint sequence in reverse layer order
+    back = plan.descriptors[4 * cfg.n_layer]
+    assert back.tag == tp_tag(2 * (4 * (cfg.n_layer - 1) + 3) + 1, TC.COLUMN_OUTPUT_GATHER)
+    # data-parallel reducer plan: one chained all-reduce(mean) per bucket
+    entries = [("a", None, 0, 100), ("b", None, 128, 300), ("c", None, 448, 64)]
+    assert bucket_ranges(entries, 512, 0) == [(0, 512)] and bucket_ranges(entries, 512, 120) == [(0, 128), (128, 448), (448, 512)]
+    dpm = M.DeviceMesh.bind(M.mesh(dp=4), [Cuda(i) for i in range(4)], Probe())
+    rp = reducer_plan(dpm, 0, [(0, 128), (128, 448)])
+    assert [d.input_elements for d in rp.descriptors] == [128, 320] and rp.descriptors[1].depends_on == 0
+    # placements decide the kernel; illegal transitions are refused with the reason, before any tensor is touched
+    with pytest.raises(PlacementError):
+        parallel_linear(None, None, (None,), src=Replicated(), dst=Partial(Reduction.SUM))
+    with pytest.raises(PlacementError):
+        parallel_linear(None, None, (None,), src=Sharded(1), dst=Replicated())          # only token rows are gathered
+    with pytest.raises(PlacementError):
+        parallel_linear(None, None, (None, None), src=Partial(Reduction.SUM), dst=Sharded(0))

@@ -50,10 +50,20 @@ def main():
         out[f"gemm_rs_{it}"] = rel(ys, part[rank * Ml:(rank + 1) * Ml] + res.float())
 
     # ---- model level
+    # the first model runs under the repo's own control plane (plan agreed before any peer mapping, handles over the
+    # rendezvous channel, every fused launch checked against the plan cursor); the second on the torch.distributed plumbing
+    from incin_b200.models.llama_tp import tensor_parallel_plan
+    from incin_b200.parallel.context import DistributedContext
+    from incin_b200.parallel.mesh import mesh
+    from incin_b200.parallel.session import bind_session
+    session = bind_session(DistributedContext.from_env(), mesh(tp=world))
     for name, kvh in (("sharded_kv", 2), ("shared_kv", 1)):
         cfg = LlamaConfig(vocab_size=512, n_layer=2, d_model=256, n_head=4, n_kv_head=kvh, head_dim=64, d_ffn=512)
         B, T = 4, 128
-        tpm = TensorParallel(dev, max_rows_per_rank=B * T // world, max_cols=cfg.d_model)
+        sess = session if name == "sharded_kv" else None
+        tpm = TensorParallel(dev, max_rows_per_rank=B * T // world, max_cols=cfg.d_model, session=sess,
+                             plan=tensor_parallel_plan(cfg, session.mesh, rank, B * T) if sess else None,
+                             ranks=list(range(world)) if sess else None)
         gg = torch.Generator().manual_seed(3)
         tok = torch.randint(0, cfg.vocab_size, (B, T), generator=gg).to(dev)
         tgt = torch.randint(0, cfg.vocab_size, (B, T), generator=gg).to(dev)
@@ -62,7 +72,7 @@ def main():
         ref_step = TrainStep(ref, ref_opt, use_graph=False)
         m = LlamaTP.from_seed(cfg, world, rank, seed=0).to(dev)
         m.tp = tpm
-        opt = TPOptimizer(m, tpm, dev, lr=1e-3)
+        opt = TPOptimizer(m, tpm, dev, lr=1e-3, session=sess)
         step = TrainStep(m, opt, use_graph=False)
         lr_, lt_ = [], []
         for _ in range(4):
@@ -74,6 +84,9 @@ def main():
         full_q = dict(ref.named_parameters())["blocks.1.qkv_w"][: cfg.n_head * 64]
         mine = dict(m.named_parameters())["blocks.1.q_w"]
         hq = cfg.n_head // world * 64
+        if sess is not None:
+            out["plan_validated_launches"] = sess.launches
+            out["plan_completed_each_step"] = bool(tpm.lane.complete)
         out[name] = {"loss_ref": lr_, "loss_tp": lt_, "q_w_diff": rel(mine, full_q[rank * hq:(rank + 1) * hq]),
                      "embed_diff": rel(m.embed, ref.embed)}
     ok = all(v < 2e-2 for k, v in out.items() if k.startswith(("ag_", "gemm_")))
@@ -81,6 +94,7 @@ def main():
         r = out[name]
         ok = ok and all(abs(a - b) < 5e-2 for a, b in zip(r["loss_ref"], r["loss_tp"])) and r["loss_tp"][-1] < r["loss_tp"][0]
         ok = ok and r["q_w_diff"] < 5e-2 and r["embed_diff"] < 5e-2
+    ok = ok and out.get("plan_validated_launches", 0) >= 4 * 8 * 2 and out.get("plan_completed_each_step", False)
     out["ok"] = ok
     if rank == 0:
         print("TP_RESULT " + json.dumps(out), flush=True)
