@@ -252,6 +252,8 @@ def main() -> None:
         opt = AdamW(store, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
         if reducer is not None:
             reducer.attach(store, opt)
+            if hasattr(reducer, "describe"):
+                dp_kind = reducer.describe()
         use_graph = not args.no_graph and args.dp != "nccl"  # NCCL collectives stay outside graph capture
         step = TrainStep(model, opt, use_graph=use_graph, reducer=reducer)
 

@@ -19,8 +19,12 @@
 // host between them, and runs the optimiser as ~15 separate elementwise launches per tensor
 // (crates/incin-backends/src/dist/nccl.rs:606-632,896-975,1842).
 //
-// Only plain peer loads/stores are used (no multimem, no TMA from peer memory), so a rank that dies
-// between steps cannot fault its peers' GPUs.
+// Two variants of steps 2 and 4.  The default uses plain peer loads / stores only, so a rank that dies between steps
+// cannot fault its peers' GPUs.  The multicast variant (incin_dp_reduce_adamw_mc) sums the owned slice inside
+// NVSwitch (multimem.ld_reduce) and broadcasts the new weights with one multimem.st: per GPU and step 1/world of the
+// gradient bytes come in instead of (world-1)/world of them, and 1/world of the weights go out instead of
+// (world-1)/world.  It needs every rank alive while the buffers are bound to the multicast object.  Neither variant
+// issues a TMA load from peer memory.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -58,6 +62,22 @@ __device__ bool wait_flags(const uint32_t* flags, int world, uint32_t target, in
   return true;
 }
 
+// NVSwitch multicast ("multimem") accesses: a load that returns the sum over every GPU bound to the address, and a
+// store that lands in every bound GPU's memory.  16-byte aligned multicast addresses.
+__device__ __forceinline__ float4 mc_ld_reduce_f32x4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void mc_st_b128(void* mc, uint4 o) {   // 16 bytes, bit pattern unchanged
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(__uint_as_float(o.x)),
+               "f"(__uint_as_float(o.y)), "f"(__uint_as_float(o.z)), "f"(__uint_as_float(o.w))
+               : "memory");
+}
+
 struct DpParams {
   float* grads[INCIN_MAX_PEERS];           // every rank's flat fp32 gradient buffer (index = rank)
   __nv_bfloat16* shadows[INCIN_MAX_PEERS];  // every rank's flat bf16 parameter buffer
@@ -67,11 +87,14 @@ struct DpParams {
   long long lo, hi, n_decay;  // bucket range in elements (multiples of 8)
   int world, rank, slot;
   int* status;
+  const float* mc_grads;        // multicast view of the gradient buffers (MC kernels only)
+  __nv_bfloat16* mc_shadows;    // multicast view of the parameter buffers
 };
 
 // pad layout per slot: [ready: MAX_PEERS][done: MAX_PEERS][epoch][arrived][pad..] = 32 words
 constexpr int PAD_WORDS_PER_SLOT = 32;
 
+template <bool MC_G, bool MC_S>
 __global__ void __launch_bounds__(512)
 dp_reduce_adamw_kernel(const DpParams p) {
   uint32_t* mypad = p.pads[p.rank] + (size_t)p.slot * PAD_WORDS_PER_SLOT;
@@ -108,12 +131,19 @@ dp_reduce_adamw_kernel(const DpParams p) {
     const long long stride = (long long)gridDim.x * blockDim.x * 8;
     for (long long i = s0 + ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < s1; i += stride) {
       float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int r = 0; r < p.world; ++r) {
-        const int src = (p.rank + r) % p.world;  // stagger so peers are not all hit in the same order
-        const float4 a = *reinterpret_cast<const float4*>(p.grads[src] + i);
-        const float4 b = *reinterpret_cast<const float4*>(p.grads[src] + i + 4);
-        g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
-        g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+      if constexpr (MC_G) {   // the switch adds the world's gradients: one 16-byte response per 16 bytes of the slice
+        const float4 a = mc_ld_reduce_f32x4(p.mc_grads + i);
+        const float4 b = mc_ld_reduce_f32x4(p.mc_grads + i + 4);
+        g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
+        g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+      } else {
+        for (int r = 0; r < p.world; ++r) {
+          const int src = (p.rank + r) % p.world;  // stagger so peers are not all hit in the same order
+          const float4 a = *reinterpret_cast<const float4*>(p.grads[src] + i);
+          const float4 b = *reinterpret_cast<const float4*>(p.grads[src] + i + 4);
+          g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+          g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+        }
       }
       float w[8], mm[8], vv[8];
       *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(p.master + i);
@@ -142,9 +172,13 @@ dp_reduce_adamw_kernel(const DpParams p) {
       t = __floats2bfloat162_rn(w[2], w[3]); o.y = *reinterpret_cast<uint32_t*>(&t);
       t = __floats2bfloat162_rn(w[4], w[5]); o.z = *reinterpret_cast<uint32_t*>(&t);
       t = __floats2bfloat162_rn(w[6], w[7]); o.w = *reinterpret_cast<uint32_t*>(&t);
-      for (int r = 0; r < p.world; ++r) {
-        const int dst = (p.rank + r) % p.world;
-        *reinterpret_cast<uint4*>(p.shadows[dst] + i) = o;
+      if constexpr (MC_S) {
+        mc_st_b128(p.mc_shadows + i, o);   // one store, replicated by the switch into every rank's buffer
+      } else {
+        for (int r = 0; r < p.world; ++r) {
+          const int dst = (p.rank + r) % p.world;
+          *reinterpret_cast<uint4*>(p.shadows[dst] + i) = o;
+        }
       }
     }
   }
@@ -173,7 +207,17 @@ dp_reduce_adamw_kernel(const DpParams p) {
 
 using namespace incin;
 
-extern "C" int incin_dp_reduce_adamw(const incin_dp_desc* d, void* stream) {
+static int dp_launch(const incin_dp_desc* d, void* mc_grads, void* mc_shadows, void* stream);
+
+extern "C" int incin_dp_reduce_adamw(const incin_dp_desc* d, void* stream) { return dp_launch(d, nullptr, nullptr, stream); }
+
+extern "C" int incin_dp_reduce_adamw_mc(const incin_dp_desc* d, void* mc_grads, void* mc_shadows, void* stream) {
+  if ((!mc_grads && !mc_shadows) || (reinterpret_cast<uintptr_t>(mc_grads) & 15) || (reinterpret_cast<uintptr_t>(mc_shadows) & 15))
+    return INCIN_ERR_ARGUMENT;   // either may be null: that side then uses the plain peer pointers
+  return dp_launch(d, mc_grads, mc_shadows, stream);
+}
+
+static int dp_launch(const incin_dp_desc* d, void* mc_grads, void* mc_shadows, void* stream) {
   if (!d || d->world < 1 || d->world > INCIN_MAX_PEERS || d->rank < 0 || d->rank >= d->world) return INCIN_ERR_ARGUMENT;
   if ((d->lo & 7) || (d->hi & 7) || d->hi <= d->lo || d->slot < 0 || d->slot >= INCIN_DP_MAX_SLOTS)
     return INCIN_ERR_ARGUMENT;
@@ -195,11 +239,16 @@ extern "C" int incin_dp_reduce_adamw(const incin_dp_desc* d, void* stream) {
   p.rank = d->rank;
   p.slot = d->slot;
   p.status = (int*)d->status;
+  p.mc_grads = (const float*)mc_grads;
+  p.mc_shadows = (__nv_bfloat16*)mc_shadows;
   int ctas = d->ctas > 0 ? d->ctas : 32;
   const long long per = (d->hi - d->lo + d->world - 1) / d->world;
   const long long need = (per + 512 * 8 - 1) / (512 * 8);
   if (need < ctas) ctas = (int)(need > 0 ? need : 1);
-  dp_reduce_adamw_kernel<<<ctas, 512, 0, (cudaStream_t)stream>>>(p);
+  if (mc_grads && mc_shadows) dp_reduce_adamw_kernel<true, true><<<ctas, 512, 0, (cudaStream_t)stream>>>(p);
+  else if (mc_grads) dp_reduce_adamw_kernel<true, false><<<ctas, 512, 0, (cudaStream_t)stream>>>(p);
+  else if (mc_shadows) dp_reduce_adamw_kernel<false, true><<<ctas, 512, 0, (cudaStream_t)stream>>>(p);
+  else dp_reduce_adamw_kernel<false, false><<<ctas, 512, 0, (cudaStream_t)stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
 

@@ -40,6 +40,13 @@ typedef struct incin_dp_desc {
  * bf16 weights, in one kernel.  Every rank must launch it for the same buckets in the same order. */
 int incin_dp_reduce_adamw(const incin_dp_desc* desc, void* stream);
 int incin_dp_pad_bytes(void);
+/* The same kernel over NVSwitch multicast memory: `mc_grads` / `mc_shadows` are the MULTICAST addresses of the
+ * gradient and parameter buffers (every rank's buffer bound at the same offset of one multicast object; the unicast
+ * pointers in `desc` still name the same memory and carry the handshake pads).  The owned slice is summed inside the
+ * switch with multimem.ld_reduce (1/world of the bucket crosses this GPU's links instead of (world-1)/world of it)
+ * and the new bf16 weights leave once with multimem.st.  Only for groups whose ranks all stay alive while the
+ * buffers are bound: a rank that exits while bound can fault its peers. */
+int incin_dp_reduce_adamw_mc(const incin_dp_desc* desc, void* mc_grads, void* mc_shadows, void* stream);
 
 /* Barrier across the GPUs of a group, as one tiny kernel per GPU: every rank signals every peer's pad and waits
  * (bounded) for theirs.  When it has completed on a GPU, every peer has reached the same point of its stream, i.e.

@@ -31,6 +31,62 @@ class _DevMem:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
+class MulticastBuffer:
+    """A buffer that every rank of a group allocates at the same size, mapped into every peer AND bound to one
+    NVSwitch multicast object: ``ptrs[r]`` are the peers' unicast addresses (as with :class:`SymmetricBuffer`),
+    ``mc_ptr`` is the multicast address, through which ``multimem.ld_reduce`` returns the sum over all ranks and
+    ``multimem.st`` writes into all of them.  Allocation, handle exchange and the multicast binding are PyTorch's
+    symmetric-memory plumbing (``torch.distributed._symmetric_memory``: cuMem allocations shared by file descriptor);
+    the kernels that use the addresses are this library's.
+
+    Every rank must stay alive while such a buffer exists (a rank that exits while bound can fault its peers), so
+    jobs that test rank loss keep to :class:`SymmetricBuffer`; ``available()`` is False when NVLS is switched off
+    (``NCCL_NVLS_ENABLE=0``) or the platform has no multicast support."""
+
+    @staticmethod
+    def available() -> bool:
+        import os
+        if os.environ.get("NCCL_NVLS_ENABLE", "1") == "0" or os.environ.get("INCIN_MULTIMEM", "1") == "0":
+            return False
+        try:
+            import torch.distributed._symmetric_memory  # noqa: F401
+        except Exception:
+            return False
+        return dist.is_available() and dist.is_initialized() and torch.cuda.is_available()
+
+    def __init__(self, nbytes: int, device: torch.device):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.nbytes = (int(nbytes) + 15) // 16 * 16
+        self.device = device
+        self.local_bytes = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.local_bytes.zero_()
+        self.ptr = self.local_bytes.data_ptr()
+        self.ptrs: list[int] = [self.ptr]
+        self.mc_ptr = 0
+        self.rank, self.world = 0, 1
+        self._hdl = None
+
+    def typed(self, dtype: torch.dtype, numel: int | None = None) -> torch.Tensor:
+        t = self.local_bytes.view(dtype)
+        return t if numel is None else t[:numel]
+
+    def exchange(self, group=None, session=None, ranks=None) -> "MulticastBuffer":
+        import torch.distributed._symmetric_memory as symm_mem
+        g = group if group is not None else dist.group.WORLD
+        if session is not None:
+            session.ensure_active()
+        self._hdl = symm_mem.rendezvous(self.local_bytes, g)
+        self.world, self.rank = dist.get_world_size(g), dist.get_rank(g)
+        self.ptrs = [int(p) for p in self._hdl.buffer_ptrs]
+        self.mc_ptr = int(self._hdl.multicast_ptr or 0)
+        if self.ptrs[self.rank] != self.ptr or not self.mc_ptr:
+            raise nat.NativeError("symmetric-memory rendezvous returned no multicast mapping for this buffer")
+        return self
+
+    def close(self) -> None:
+        self._hdl = None
+
+
 class SymmetricBuffer:
     def __init__(self, nbytes: int, device: torch.device):
         self.nbytes = int(nbytes)

@@ -197,6 +197,7 @@ extern "C" {
     pub fn incin_digest_number(state: u64, v: u64) -> u64;
     pub fn incin_dp_pad_bytes() -> c_int;
     pub fn incin_dp_reduce_adamw(desc: *const incin_dp_desc, stream: *mut c_void) -> c_int;
+    pub fn incin_dp_reduce_adamw_mc(desc: *const incin_dp_desc, mc_grads: *mut c_void, mc_shadows: *mut c_void, stream: *mut c_void) -> c_int;
     pub fn incin_dropout_bf16(x: *const c_void, y: *mut c_void, n: c_longlong, p: f32, seed: u64, offset: u64, stream: *mut c_void) -> c_int;
     pub fn incin_embedding_bwd(dout: *const c_void, tokens: *const i64, dwte: *mut f32, dwpe: *mut f32, B: c_longlong, T: c_int, C: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_embedding_bwd_sorted(dout: *const c_void, order: *const c_longlong, seg_start: *const c_longlong, seg_token: *const c_longlong, n_segments: c_longlong, dwte: *mut f32, dwpe: *mut f32, B: c_longlong, T: c_int, C: c_int, vocab: c_longlong, stream: *mut c_void) -> c_int;

@@ -68,6 +68,10 @@ def main():
                                                      "loss_first": losses[0], "loss_last": losses[-1]}
         ok = ok and same and err < 2e-2 and losses[-1] < losses[0]
     out["plan_validated_launches"] = session.launches
+    out["multimem"] = bool(os.environ.get("INCIN_TEST_EXPECT_MULTIMEM") == "1")
+    if out["multimem"]:      # the launcher asked for the NVSwitch multicast variant: make sure that is what ran
+        from incin_b200.parallel.symm import MulticastBuffer
+        ok = ok and MulticastBuffer.available()
     out["ok"] = ok
     if rank == 0:
         print("DP_RESULT " + json.dumps(out), flush=True)
