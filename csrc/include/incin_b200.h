@@ -266,6 +266,12 @@ int incin_batchnorm_train_fwd(const void* x, const float* gamma, const float* be
                               int is_bf16, void* stream);
 int incin_batchnorm_eval(const void* x, const float* gamma, const float* beta, const float* mean, const float* var, void* y,
                          int N, int C, long long HW, float eps, int is_bf16, void* stream);
+/* adaptive average pooling over `planes` = N*C planes of H x W -> OH x OW (backward: in = dy, out = dx; a gather) */
+int incin_adaptive_avgpool2d(const void* in, void* out, long long planes, int H, int W, int OH, int OW, int backward,
+                             int is_bf16, void* stream);
+/* softmax over the last axis of [rows, C] (bf16 or fp32 io, fp32 arithmetic); backward: dx = y * (dy - sum(dy * y)) */
+int incin_softmax_lastdim_fwd(const void* x, void* y, long long rows, int C, int is_bf16, void* stream);
+int incin_softmax_lastdim_bwd(const void* dy, const void* y, void* dx, long long rows, int C, int is_bf16, void* stream);
 /* dgamma / dbeta are ACCUMULATED into (fp32) */
 int incin_batchnorm_bwd(const void* dy, const void* x, const float* gamma, const float* save_mean, const float* save_rstd,
                         void* dx, float* dgamma, float* dbeta, int N, int C, long long HW, int is_bf16, void* stream);

@@ -242,6 +242,53 @@ __global__ void __launch_bounds__(512) batchnorm_bwd_kernel(const T* __restrict_
   }
 }
 
+// ---- adaptive average pooling: output cell (oh, ow) averages rows [floor(oh*H/OH), ceil((oh+1)*H/OH)) x the same in w
+// (crates/incin-backends/src/cuda/ops/kernels/pool.cu adaptive_avg_pool2d_{fwd,bwd}; the backward there scatters with
+// atomics, here every input pixel gathers from the output cells whose window contains it)
+__device__ __forceinline__ int ad_start(int o, int in, int out) { return (int)(((long long)o * in) / out); }
+__device__ __forceinline__ int ad_end(int o, int in, int out) { return (int)((((long long)o + 1) * in + out - 1) / out); }
+
+template <typename T>
+__global__ void adaptive_avgpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int H, int W, int OH, int OW, long long total) {
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int ow = (int)(t % OW), oh = (int)((t / OW) % OH);
+    const long long plane = t / ((long long)OW * OH);
+    const int h0 = ad_start(oh, H, OH), h1 = ad_end(oh, H, OH), w0 = ad_start(ow, W, OW), w1 = ad_end(ow, W, OW);
+    const T* p = x + plane * H * W;
+    float acc = 0.0f;
+    for (int h = h0; h < h1; ++h)
+      for (int w = w0; w < w1; ++w) acc += ldf(p, (long long)h * W + w);
+    stf(y, t, acc / (float)((h1 - h0) * (w1 - w0)));
+  }
+}
+
+template <typename T>
+__global__ void adaptive_avgpool_bwd_kernel(const T* __restrict__ dy, T* __restrict__ dx, int H, int W, int OH, int OW, long long total) {
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int w = (int)(t % W), h = (int)((t / W) % H);
+    const long long plane = t / ((long long)W * H);
+    const T* p = dy + plane * OH * OW;
+    // output rows whose window [start, end) contains h: start(oh) <= h  and  end(oh) > h
+    int oh_lo = (int)(((long long)h * OH) / H), oh_hi = (int)((((long long)h + 1) * OH + H - 1) / H);
+    while (oh_lo > 0 && ad_end(oh_lo - 1, H, OH) > h) --oh_lo;
+    while (oh_hi < OH && ad_start(oh_hi, H, OH) <= h) ++oh_hi;
+    int ow_lo = (int)(((long long)w * OW) / W), ow_hi = (int)((((long long)w + 1) * OW + W - 1) / W);
+    while (ow_lo > 0 && ad_end(ow_lo - 1, W, OW) > w) --ow_lo;
+    while (ow_hi < OW && ad_start(ow_hi, W, OW) <= w) ++ow_hi;
+    float acc = 0.0f;
+    for (int oh = oh_lo; oh < oh_hi; ++oh) {
+      const int h0 = ad_start(oh, H, OH), h1 = ad_end(oh, H, OH);
+      if (h < h0 || h >= h1) continue;
+      for (int ow = ow_lo; ow < ow_hi; ++ow) {
+        const int w0 = ad_start(ow, W, OW), w1 = ad_end(ow, W, OW);
+        if (w < w0 || w >= w1) continue;
+        acc += ldf(p, (long long)oh * OW + ow) / (float)((h1 - h0) * (w1 - w0));
+      }
+    }
+    stf(dx, t, acc);
+  }
+}
+
 inline unsigned grid_for(long long n) {
   long long g = (n + 255) / 256;
   return (unsigned)(g < 1 ? 1 : (g > 148LL * 16 ? 148LL * 16 : g));
@@ -356,5 +403,21 @@ extern "C" int incin_batchnorm_bwd(const void* dy, const void* x, const float* g
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   DISPATCH(is_bf16, (batchnorm_bwd_kernel<__nv_bfloat16><<<C, 512, 0, s>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), gamma, save_mean, save_rstd, static_cast<__nv_bfloat16*>(dx), dgamma, dbeta, N, C, HW)),
            (batchnorm_bwd_kernel<float><<<C, 512, 0, s>>>(static_cast<const float*>(dy), static_cast<const float*>(x), gamma, save_mean, save_rstd, static_cast<float*>(dx), dgamma, dbeta, N, C, HW)));
+  return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
+}
+
+extern "C" int incin_adaptive_avgpool2d(const void* in, void* out, long long planes, int H, int W, int OH, int OW, int backward,
+                                        int is_bf16, void* stream) {
+  if (!in || !out || planes <= 0 || H <= 0 || W <= 0 || OH <= 0 || OW <= 0) return INCIN_ERR_ARGUMENT;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long total = planes * (backward ? (long long)H * W : (long long)OH * OW);
+  if (backward)
+    DISPATCH(is_bf16,
+             (adaptive_avgpool_bwd_kernel<<<grid_for(total), 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, H, W, OH, OW, total)),
+             (adaptive_avgpool_bwd_kernel<<<grid_for(total), 256, 0, s>>>((const float*)in, (float*)out, H, W, OH, OW, total)));
+  else
+    DISPATCH(is_bf16,
+             (adaptive_avgpool_fwd_kernel<<<grid_for(total), 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, H, W, OH, OW, total)),
+             (adaptive_avgpool_fwd_kernel<<<grid_for(total), 256, 0, s>>>((const float*)in, (float*)out, H, W, OH, OW, total)));
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }

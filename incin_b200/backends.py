@@ -34,14 +34,42 @@ class BackendUnavailable(RuntimeError):
     pass
 
 
+_FUSABLE = (torch.float32, torch.bfloat16, torch.float16)
+_UNARY_ALIASES = {"silu": "swish", "reciprocal": "recip"}
+
+
+def _binary(name: str, torch_fn: Callable) -> Callable:
+    """Elementwise binary op: on CUDA it is one kernel of the pointwise fuser (NVRTC, sm_100a; broadcasting through the
+    strided layout), on the CPU the PyTorch op."""
+    def run(a, b):
+        if isinstance(a, torch.Tensor) and isinstance(b, torch.Tensor) and a.is_cuda and b.is_cuda and \
+                a.dtype == b.dtype and a.dtype in _FUSABLE:
+            from .codegen import Arg, Binary, fused
+            return fused(Binary(name, Arg(0), Arg(1)), a, b)
+        return torch_fn(a, b)
+    return run
+
+
+def _unary(x, name: str):
+    from .codegen.pointwise import UNARY
+    op = _UNARY_ALIASES.get(name, name)
+    if x.is_cuda and x.dtype in _FUSABLE and op in UNARY:
+        from .codegen import Arg, Unary, fused
+        return fused(Unary(op, Arg(0)), x)
+    return F.activation(x, name) if name in ("gelu", "silu") else getattr(torch, name)(x)
+
+
 def _ops() -> dict[str, Callable]:
     """The op surface shared by the real backends (functional front end: CUDA kernels or their CPU twins)."""
     return {
         "matmul": lambda a, b: F.linear(a, b.t().contiguous()) if a.is_cuda else a @ b,
         "addmm": lambda x, w, b: F.linear(x, w, b),
-        "add": torch.add, "sub": torch.sub, "mul": torch.mul, "div": torch.div,
-        "unary": lambda x, name: F.activation(x, name) if name in ("gelu", "silu") else getattr(torch, name)(x),
-        "softmax": lambda x: torch.softmax(x.float(), -1).to(x.dtype),
+        "add": _binary("add", torch.add), "sub": _binary("sub", torch.sub), "mul": _binary("mul", torch.mul),
+        "div": _binary("div", torch.div), "maximum": _binary("max", torch.maximum), "minimum": _binary("min", torch.minimum),
+        "unary": _unary,
+        "softmax": lambda x, dim=-1: T.softmax(x, dim),
+        "conv1d": T.conv1d, "conv2d": T.conv2d, "conv_transpose2d": T.conv_transpose2d,
+        "adaptive_avg_pool2d": T.adaptive_avg_pool2d,
         "layer_norm": F.layer_norm, "rms_norm": F.rms_norm, "embedding": F.embedding,
         "cross_entropy": lambda logits, target: F.cross_entropy(logits, target, logits.shape[-1]),
         "sdpa": lambda qkv, heads: F.causal_attention(qkv, heads),

@@ -160,19 +160,42 @@ class Softmax(nn.Module):
         self.dim = dim
 
     def forward(self, x):
-        return torch.softmax(x, self.dim)
+        from ..ops.tensor_ops import softmax
+        return softmax(x, self.dim)
 
 
 class Conv2d(nn.Conv2d):
     """NCHW convolution (conv2d.rs); CPU and fp32 run ATen, the bf16 CUDA path lowers to im2col + tcgen05 GEMM."""
 
     def forward(self, x):
-        if x.is_cuda and x.dtype == torch.bfloat16 and self.groups == 1 and self.padding_mode == "zeros":
-            return F.conv2d_im2col(x, self.weight, self.bias, self.stride, self.padding, self.dilation)
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.groups == 1 and self.padding_mode == "zeros" and \
+                not isinstance(self.padding, str):
+            from ..ops.tensor_ops import conv2d
+            return conv2d(x, self.weight, self.bias, self.stride, self.padding, self.dilation)
         return super().forward(x)
 
 
-Conv1d = nn.Conv1d
+class Conv1d(nn.Conv1d):
+    """``[N, C, L]`` convolution; the bf16 CUDA path is the 2-D lowering over a height of 1 (conv1d in
+    crates/incin-backends/src/cuda/backend.rs:1576)."""
+
+    def forward(self, x):
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.groups == 1 and self.padding_mode == "zeros" and \
+                not isinstance(self.padding, str):
+            from ..ops.tensor_ops import conv1d
+            return conv1d(x, self.weight, self.bias, self.stride[0], self.padding[0], self.dilation[0])
+        return super().forward(x)
+
+
+class ConvTranspose2d(nn.ConvTranspose2d):
+    """Transposed NCHW convolution (crates/incin-backends/src/cuda/backend.rs:1604); bf16 CUDA tensors run GEMM + fold."""
+
+    def forward(self, x, output_size=None):
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.groups == 1 and output_size is None:
+            from ..ops.tensor_ops import conv_transpose2d
+            return conv_transpose2d(x, self.weight, self.bias, self.stride, self.padding, self.output_padding, self.dilation)
+        return super().forward(x, output_size)
+
 class BatchNorm2d(nn.Module):
     """Per-channel batch normalisation over ``[N, C, H, W]`` (crates/incin-core/src/nn/batch_norm.rs): fp32 affine
     parameters and running statistics, training forward + backward and the inference form on the native kernels."""
@@ -211,7 +234,14 @@ class AvgPool2d(nn.Module):
         return avg_pool2d(x, self.kernel_size, self.stride, self.padding)
 
 
-AdaptiveAvgPool2d = nn.AdaptiveAvgPool2d
+class AdaptiveAvgPool2d(nn.Module):
+    def __init__(self, output_size):
+        super().__init__()
+        self.output_size = output_size
+
+    def forward(self, x):
+        from ..ops.tensor_ops import adaptive_avg_pool2d
+        return adaptive_avg_pool2d(x, self.output_size)
 
 
 class RNNCell(nn.Module):

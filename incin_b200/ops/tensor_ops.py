@@ -39,6 +39,9 @@ nat.register_cuda_signatures({
     "incin_maxpool2d_fwd": (c_int, [c_void_p, c_void_p, c_void_p, C.POINTER(ConvGeom), c_int, c_void_p]),
     "incin_maxpool2d_bwd": (c_int, [c_void_p, c_void_p, c_void_p, C.POINTER(ConvGeom), c_int, c_void_p]),
     "incin_avgpool2d": (c_int, [c_void_p, c_void_p, C.POINTER(ConvGeom), c_int, c_int, c_void_p]),
+    "incin_adaptive_avgpool2d": (c_int, [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "incin_softmax_lastdim_fwd": (c_int, [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p]),
+    "incin_softmax_lastdim_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p]),
     "incin_batchnorm_train_fwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_ll, c_float, c_float, c_int, c_void_p]),
     "incin_batchnorm_eval": (c_int, [c_void_p] * 6 + [c_int, c_int, c_ll, c_float, c_int, c_void_p]),
     "incin_batchnorm_bwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_ll, c_int, c_void_p]),
@@ -392,6 +395,196 @@ def avg_pool2d(x, kernel, stride=None, padding=0):
     if not _native(x):
         return torch.nn.functional.avg_pool2d(x, kernel, stride, padding)
     return _AvgPool2d.apply(x, kernel, stride, padding)
+
+
+class _AdaptiveAvgPool2d(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, out_hw):
+        x = x.contiguous()
+        N, Cc, H, W = x.shape
+        oh, ow = out_hw
+        y = torch.empty(N, Cc, oh, ow, dtype=x.dtype, device=x.device)
+        nat.check(nat.cuda().incin_adaptive_avgpool2d(x.data_ptr(), y.data_ptr(), N * Cc, H, W, oh, ow, 0, _bf(x), _s()),
+                  "adaptive_avgpool_fwd")
+        ctx.dims = (N, Cc, H, W, oh, ow)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        N, Cc, H, W, oh, ow = ctx.dims
+        dy = dy.contiguous()
+        dx = torch.empty(N, Cc, H, W, dtype=dy.dtype, device=dy.device)
+        nat.check(nat.cuda().incin_adaptive_avgpool2d(dy.data_ptr(), dx.data_ptr(), N * Cc, H, W, oh, ow, 1, _bf(dy), _s()),
+                  "adaptive_avgpool_bwd")
+        return dx, None
+
+
+def adaptive_avg_pool2d(x, output_size):
+    """``[N, C, H, W] -> [N, C, OH, OW]``; cell (i, j) averages rows ``floor(i H / OH) .. ceil((i + 1) H / OH)`` and the
+    same in w (crates/incin-backends/src/cuda/backend.rs:1753).  ``None`` in ``output_size`` keeps that extent."""
+    oh, ow = _pair(output_size)
+    oh = x.shape[-2] if oh is None else oh
+    ow = x.shape[-1] if ow is None else ow
+    if not _native(x):
+        return torch.nn.functional.adaptive_avg_pool2d(x, (oh, ow))
+    return _AdaptiveAvgPool2d.apply(x, (oh, ow))
+
+
+class _SoftmaxLast(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        x = x.contiguous()
+        Cc = x.shape[-1]
+        y = torch.empty_like(x)
+        nat.check(nat.cuda().incin_softmax_lastdim_fwd(x.data_ptr(), y.data_ptr(), x.numel() // Cc, Cc, _bf(x), _s()), "softmax_fwd")
+        ctx.save_for_backward(y)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        dy = dy.contiguous()
+        Cc = y.shape[-1]
+        dx = torch.empty_like(y)
+        nat.check(nat.cuda().incin_softmax_lastdim_bwd(dy.data_ptr(), y.data_ptr(), dx.data_ptr(), y.numel() // Cc, Cc, _bf(y), _s()),
+                  "softmax_bwd")
+        return dx
+
+
+def softmax(x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    """Softmax over ``dim``: one native launch (forward) / one (backward) on bf16 / fp32 CUDA tensors; another axis is
+    moved to the end with the native strided copy and back."""
+    if not _native(x) or x.numel() == 0:
+        return torch.softmax(x, dim)
+    dim = dim % x.dim()
+    if dim == x.dim() - 1:
+        return _SoftmaxLast.apply(x)
+    return _SoftmaxLast.apply(x.transpose(dim, -1)).transpose(dim, -1)
+
+
+# ---------------------------------------------------------------------------------------------------- convolutions
+def _nchw_rows(x: torch.Tensor) -> torch.Tensor:
+    """``[N, C, H, W] -> [N*H*W, C]`` (channels last rows), native strided copy."""
+    N, Cc, H, W = x.shape
+    return materialize(x.permute(0, 2, 3, 1)).reshape(N * H * W, Cc)
+
+
+def _rows_nchw(rows: torch.Tensor, N: int, H: int, W: int) -> torch.Tensor:
+    return materialize(rows.reshape(N, H, W, rows.shape[-1]).permute(0, 3, 1, 2))
+
+
+def _conv_gemm_ok(*dims) -> bool:
+    return all(d % 8 == 0 for d in dims)      # 16-byte rows for the TMA-fed GEMM
+
+
+class _Conv2d(torch.autograd.Function):
+    """Convolution as unfold + tcgen05 GEMM, backward as GEMMs + fold: every step a kernel of this library
+    (crates/incin-backends/src/cuda/backend.rs:1604-1719 does the same with its SGEMM, per batch and group)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, stride, padding, dilation):
+        from . import gemm as G
+        N, Cin, H, W = x.shape
+        O, _, KH, KW = w.shape
+        cols = im2col(x, (KH, KW), stride, padding, dilation)                      # [N*L, Cin*KH*KW]
+        wk = w.reshape(O, Cin * KH * KW).contiguous()
+        y_rows = G.mm_nt(cols, wk, bias=b)                                         # [N*L, O]
+        g = _geom(x.shape, (KH, KW), stride, padding, dilation)
+        oh, ow = conv_out_hw(g)
+        ctx.save_for_backward(cols, wk)
+        ctx.meta = (x.shape, w.shape, stride, padding, dilation, oh, ow, b is not None)
+        return _rows_nchw(y_rows, N, oh, ow)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import gemm as G
+        from . import kernels as K
+        cols, wk = ctx.saved_tensors
+        x_shape, w_shape, stride, padding, dilation, oh, ow, has_b = ctx.meta
+        dy_rows = _nchw_rows(dy.contiguous())                                      # [N*L, O]
+        dx = dw = db = None
+        if ctx.needs_input_grad[1]:
+            dwf = torch.zeros(wk.shape, dtype=torch.float32, device=dy.device)
+            G.mm_tn_accum(dy_rows, cols, dwf)                                      # dy^T @ cols
+            dw = dwf.to(wk.dtype).reshape(w_shape)
+        if has_b and ctx.needs_input_grad[2]:
+            dbf = torch.zeros(w_shape[0], dtype=torch.float32, device=dy.device)
+            K.colsum_accum(dy_rows, dbf)
+            db = dbf.to(wk.dtype)
+        if ctx.needs_input_grad[0]:
+            dcols = G.mm_nn(dy_rows, wk)                                           # [N*L, Cin*KH*KW]
+            dx = col2im(dcols, x_shape, w_shape[2:], stride, padding, dilation)
+        return dx, dw, db, None, None, None
+
+
+def conv2d(x, w, b=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1)):
+    """NCHW convolution (groups = 1).  bf16 CUDA tensors whose GEMM dimensions are multiples of 8 run on the native
+    unfold / tcgen05 GEMM / fold kernels; everything else is evaluated by PyTorch."""
+    stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
+    O, Cin, KH, KW = w.shape
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and _conv_gemm_ok(O, Cin * KH * KW):
+        return _Conv2d.apply(x, w, b, stride, padding, dilation)
+    return torch.nn.functional.conv2d(x, w, b, stride, padding, dilation)
+
+
+def conv1d(x, w, b=None, stride: int = 1, padding: int = 0, dilation: int = 1):
+    """``[N, C, L]`` convolution as the 2-D one over a height of 1 (im2col_1d + GEMM in the reference:
+    crates/incin-backends/src/cuda/backend.rs:1576, kernels/conv.cu:106-181)."""
+    y = conv2d(x.unsqueeze(2), w.unsqueeze(2), b, (1, stride), (0, padding), (1, dilation))
+    return y.squeeze(2)
+
+
+class _ConvTranspose2d(torch.autograd.Function):
+    """Transposed convolution: one GEMM produces the column matrix, the fold kernel scatters it into the output
+    (gather form, no atomics); the backward is unfold + two GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, stride, padding, dilation, out_hw):
+        from . import gemm as G
+        N, Cin, H, W = x.shape
+        _, Cout, KH, KW = w.shape
+        x_rows = _nchw_rows(x)                                                     # [N*H*W, Cin]
+        wm = w.reshape(Cin, Cout * KH * KW).contiguous()
+        cols = G.mm_nn(x_rows, wm)                                                 # [N*H*W, Cout*KH*KW]
+        y_shape = (N, Cout, out_hw[0], out_hw[1])
+        y = col2im(cols, y_shape, (KH, KW), stride, padding, dilation)
+        if b is not None:
+            y = y + b.view(1, -1, 1, 1)
+        ctx.save_for_backward(x_rows, wm)
+        ctx.meta = (x.shape, w.shape, stride, padding, dilation, b is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import gemm as G
+        x_rows, wm = ctx.saved_tensors
+        x_shape, w_shape, stride, padding, dilation, has_b = ctx.meta
+        N, Cin, H, W = x_shape
+        dcols = im2col(dy.contiguous(), w_shape[2:], stride, padding, dilation)    # [N*H*W, Cout*KH*KW]
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = _rows_nchw(G.mm_nt(dcols, wm), N, H, W)                           # dcols @ wm^T -> [N*H*W, Cin]
+        if ctx.needs_input_grad[1]:
+            dwf = torch.zeros(wm.shape, dtype=torch.float32, device=dy.device)
+            G.mm_tn_accum(x_rows, dcols, dwf)                                      # x^T @ dcols
+            dw = dwf.to(wm.dtype).reshape(w_shape)
+        if has_b and ctx.needs_input_grad[2]:
+            db = reduce(reduce(reduce(dy.float(), "sum", 3), "sum", 2), "sum", 0).to(dy.dtype)
+        return dx, dw, db, None, None, None, None
+
+
+def conv_transpose2d(x, w, b=None, stride=(1, 1), padding=(0, 0), output_padding=(0, 0), dilation=(1, 1)):
+    """``x [N, Cin, H, W]``, ``w [Cin, Cout, KH, KW]`` -> ``[N, Cout, OH, OW]`` with
+    ``OH = (H - 1) stride - 2 padding + dilation (KH - 1) + output_padding + 1`` (groups = 1;
+    crates/incin-backends/src/cuda/backend.rs:1604)."""
+    stride, padding, dilation, opad = _pair(stride), _pair(padding), _pair(dilation), _pair(output_padding)
+    Cin, Cout, KH, KW = w.shape
+    H, W = x.shape[-2:]
+    oh = (H - 1) * stride[0] - 2 * padding[0] + dilation[0] * (KH - 1) + opad[0] + 1
+    ow = (W - 1) * stride[1] - 2 * padding[1] + dilation[1] * (KW - 1) + opad[1] + 1
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and _conv_gemm_ok(Cin, Cout * KH * KW):
+        return _ConvTranspose2d.apply(x, w, b, stride, padding, dilation, (oh, ow))
+    return torch.nn.functional.conv_transpose2d(x, w, b, stride, padding, opad, 1, dilation)
 
 
 class _BatchNormTrain(torch.autograd.Function):

@@ -1,0 +1,110 @@
+"""Native convolution family, adaptive pooling and softmax kernels against PyTorch fp32 math of the same ops."""
+import pytest
+import torch
+import torch.nn.functional as TF
+
+pytestmark = pytest.mark.gpu
+
+from _tol import check_close  # noqa: E402
+
+
+def _bf(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).cuda()
+
+
+def _grads(fn_ref, fn_ours, inputs, dy):
+    """Run both, return (y_ours, y_ref, grads_ours, grads_ref) with fp32 references."""
+    ref_in = [t.detach().float().clone().requires_grad_() for t in inputs]
+    y_ref = fn_ref(*ref_in)
+    y_ref.backward(dy.float())
+    our_in = [t.detach().clone().requires_grad_() for t in inputs]
+    y = fn_ours(*our_in)
+    y.backward(dy)
+    return y, y_ref, [t.grad for t in our_in], [t.grad for t in ref_in]
+
+
+@pytest.mark.parametrize("C,L,O,K,stride,pad,dil", [(8, 50, 16, 3, 1, 1, 1), (16, 64, 8, 5, 2, 2, 1), (8, 33, 24, 3, 1, 2, 2)])
+def test_conv1d_native_fwd_bwd(C, L, O, K, stride, pad, dil):
+    from incin_b200.ops import tensor_ops as T
+    x, w, b = _bf((3, C, L), 1), _bf((O, C, K), 2, 0.3), _bf((O,), 3)
+    lo = (L + 2 * pad - dil * (K - 1) - 1) // stride + 1
+    dy = _bf((3, O, lo), 4)
+    y, yr, g, gr = _grads(lambda x, w, b: TF.conv1d(x, w, b, stride, pad, dil), lambda x, w, b: T.conv1d(x, w, b, stride, pad, dil),
+                          [x, w, b], dy)
+    check_close(y, yr, what="conv1d y")
+    for name, a, r in zip(("dx", "dw", "db"), g, gr):
+        check_close(a, r, rtol=2e-2, atol_rms=2e-2, what=f"conv1d {name}")
+
+
+def test_conv2d_native_backward_needs_no_library_kernels():
+    from incin_b200.ops import tensor_ops as T
+    x, w, b = _bf((2, 8, 14, 12), 5), _bf((16, 8, 3, 3), 6, 0.2), _bf((16,), 7)
+    dy = _bf((2, 16, 7, 6), 8)
+    y, yr, g, gr = _grads(lambda x, w, b: TF.conv2d(x, w, b, 2, 1), lambda x, w, b: T.conv2d(x, w, b, (2, 2), (1, 1)), [x, w, b], dy)
+    check_close(y, yr, what="conv2d y")
+    for name, a, r in zip(("dx", "dw", "db"), g, gr):
+        check_close(a, r, rtol=2e-2, atol_rms=2e-2, what=f"conv2d {name}")
+
+
+@pytest.mark.parametrize("stride,pad,opad,dil", [(1, 0, 0, 1), (2, 1, 1, 1), (3, 2, 0, 2)])
+def test_conv_transpose2d_native_fwd_bwd(stride, pad, opad, dil):
+    from incin_b200.ops import tensor_ops as T
+    x, w, b = _bf((2, 8, 6, 5), 9), _bf((8, 8, 3, 3), 10, 0.2), _bf((8,), 11)
+    ref = lambda x, w, b: TF.conv_transpose2d(x, w, b, stride, pad, opad, 1, dil)
+    yshape = ref(x.float(), w.float(), b.float()).shape
+    dy = _bf(tuple(yshape), 12)
+    y, yr, g, gr = _grads(ref, lambda x, w, b: T.conv_transpose2d(x, w, b, stride, pad, opad, dil), [x, w, b], dy)
+    check_close(y, yr, what="conv_transpose2d y")
+    for name, a, r in zip(("dx", "dw", "db"), g, gr):
+        check_close(a, r, rtol=2e-2, atol_rms=2e-2, what=f"conv_transpose2d {name}")
+
+
+@pytest.mark.parametrize("H,W,OH,OW", [(10, 7, 4, 3), (8, 8, 1, 1), (5, 9, 5, 9), (6, 6, 4, 5), (3, 3, 7, 5)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_adaptive_avg_pool2d_fwd_bwd(H, W, OH, OW, dtype):
+    from incin_b200.ops import tensor_ops as T
+    x = _bf((2, 5, H, W), 13).to(dtype)
+    dy = _bf((2, 5, OH, OW), 14).to(dtype)
+    y, yr, g, gr = _grads(lambda x: TF.adaptive_avg_pool2d(x, (OH, OW)), lambda x: T.adaptive_avg_pool2d(x, (OH, OW)), [x], dy)
+    tol = dict(rtol=1.6e-2, atol_rms=1.5e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol_rms=1e-5)
+    check_close(y, yr, what="adaptive pool y", **tol)
+    check_close(g[0], gr[0], what="adaptive pool dx", **tol)
+
+
+@pytest.mark.parametrize("rows,C", [(64, 10), (33, 1000), (7, 2048), (5, 5000), (3, 50257)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_softmax_last_axis_fwd_bwd(rows, C, dtype):
+    from incin_b200.ops import tensor_ops as T
+    x = (_bf((rows, C), 15) * 3).to(dtype)
+    dy = _bf((rows, C), 16).to(dtype)
+    y, yr, g, gr = _grads(lambda x: torch.softmax(x, -1), lambda x: T.softmax(x, -1), [x], dy)
+    tol = dict(rtol=1.6e-2, atol_rms=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol_rms=1e-5)
+    check_close(y, yr, what="softmax y", **tol)
+    assert torch.allclose(y.float().sum(-1), torch.ones(rows, device="cuda"), atol=2e-2 if dtype == torch.bfloat16 else 1e-5)
+    # the reference of the backward uses OUR forward output rounded to the io type, as the kernel does
+    yy = y.detach().float()
+    ref_dx = yy * (dy.float() - (dy.float() * yy).sum(-1, keepdim=True))
+    check_close(g[0], ref_dx, what="softmax dx", **tol)
+    # softmax over an inner axis goes through the same kernel
+    x3 = _bf((4, 9, 6), 17).to(dtype)
+    check_close(T.softmax(x3, 1), torch.softmax(x3.float(), 1), what="softmax axis 1", **tol)
+
+
+def test_backend_elementwise_ops_run_fused_kernels():
+    """CudaBackend add / sub / mul / div / unary are kernels of the pointwise fuser, not library calls."""
+    from incin_b200 import _native as nat
+    from incin_b200.backends import CudaBackend
+    from incin_b200.codegen import runtime as RT
+    be = CudaBackend()
+    a, b = _bf((64, 48), 18), _bf((64, 48), 19) + 3
+    before = len(RT._cache) if hasattr(RT, "_cache") else None
+    for op, ref in (("add", torch.add), ("sub", torch.sub), ("mul", torch.mul), ("div", torch.div)):
+        check_close(be.run(op, a, b), ref(a.float(), b.float()), what=f"backend {op}")
+    check_close(be.run("add", a, b[:1]), a.float() + b[:1].float(), what="backend add broadcast")
+    for name, ref in (("exp", torch.exp), ("tanh", torch.tanh), ("silu", TF.silu), ("gelu", TF.gelu)):
+        check_close(be.run("unary", a, name), ref(a.float()), rtol=2e-2, atol_rms=2e-2, what=f"backend unary {name}")
+    check_close(be.run("softmax", a), torch.softmax(a.float(), -1), rtol=1.6e-2, atol_rms=2e-2, what="backend softmax")
+    if before is not None:
+        assert len(RT._cache) > before
+    assert nat.cuda_loaded()
