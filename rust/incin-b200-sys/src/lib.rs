@@ -159,6 +159,7 @@ extern "C" {
     pub fn incin_act_bwd(dy: *const c_void, pre: *const c_void, dx: *mut c_void, n: c_longlong, act: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_act_fwd(x: *const c_void, y: *mut c_void, n: c_longlong, act: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_adamw_flat(master: *mut f32, m: *mut f32, v: *mut f32, grad: *const f32, shadow_bf16: *mut c_void, n: c_longlong, n_decay: c_longlong, hyper: *const f32, stream: *mut c_void) -> c_int;
+    pub fn incin_adaptive_avgpool2d(r#in: *const c_void, out: *mut c_void, planes: c_longlong, H: c_int, W: c_int, OH: c_int, OW: c_int, backward: c_int, is_bf16: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_avgpool2d(r#in: *const c_void, out: *mut c_void, g: *const incin_conv_geom, backward: c_int, is_bf16: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_barrier_pad_bytes() -> c_int;
     pub fn incin_batchnorm_bwd(dy: *const c_void, x: *const c_void, gamma: *const f32, save_mean: *const f32, save_rstd: *const f32, dx: *mut c_void, dgamma: *mut f32, dbeta: *mut f32, N: c_int, C: c_int, HW: c_longlong, is_bf16: c_int, stream: *mut c_void) -> c_int;
@@ -260,6 +261,8 @@ extern "C" {
     pub fn incin_slot_reduce(slots: *const c_void, slot_stride: c_longlong, world: c_int, residual: *const c_void, out: *mut c_void, rows: c_longlong, N: c_int, ld: c_longlong, stream: *mut c_void) -> c_int;
     pub fn incin_sm100_num_sms() -> c_int;
     pub fn incin_sm100_version() -> *const c_char;
+    pub fn incin_softmax_lastdim_bwd(dy: *const c_void, y: *const c_void, dx: *mut c_void, rows: c_longlong, C: c_int, is_bf16: c_int, stream: *mut c_void) -> c_int;
+    pub fn incin_softmax_lastdim_fwd(x: *const c_void, y: *mut c_void, rows: c_longlong, C: c_int, is_bf16: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_strided_copy(src: *const c_void, dst: *mut c_void, rank: c_int, shape: *const c_longlong, src_strides: *const c_longlong, dst_strides: *const c_longlong, elem_bytes: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_sumsq_nonfinite_f32(x: *const f32, n: c_longlong, out: *mut f32, stream: *mut c_void) -> c_int;
     pub fn incin_swiglu_bwd(dy: *const c_void, gate_up: *const c_void, dgate_up: *mut c_void, rows: c_longlong, F: c_int, stream: *mut c_void) -> c_int;
