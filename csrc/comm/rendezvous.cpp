@@ -209,7 +209,14 @@ API int incin_rdv_connect(int rank, int world, const char* addr, const char* run
     if (!err) {
       uint8_t reply[160];
       startup_frame(reply, Accepted, 0, world, 0, local_device, run);
-      for (int r = 1; r < world && !err; ++r) err = write_all(c->fds[(size_t)r], reply, 160, deadline);
+      // the Accepted frame is followed by the device table (8 bytes per rank), so every rank knows where each peer's
+      // memory lives without a further exchange
+      std::vector<uint8_t> table((size_t)world * 8);
+      for (int r = 0; r < world; ++r) put64(table.data() + 8 * r, (uint64_t)c->peer_devices[(size_t)r]);
+      for (int r = 1; r < world && !err; ++r) {
+        err = write_all(c->fds[(size_t)r], reply, 160, deadline);
+        if (!err) err = write_all(c->fds[(size_t)r], table.data(), table.size(), deadline);
+      }
     }
   } else {
     c->fds.assign(1, -1);
@@ -237,7 +244,11 @@ API int incin_rdv_connect(int rank, int world, const char* addr, const char* run
         if (std::memcmp(f, MAGIC, 8) != 0) err = E_MAGIC;
         else if (f[8] == Reject) err = get16(f + 12) ? (int)get16(f + 12) : E_REJECTED;
         else if (f[8] != Accepted) err = E_MAGIC;
-        else c->peer_devices[0] = (int64_t)get64(f + 16);
+        else {
+          std::vector<uint8_t> table((size_t)world * 8);
+          err = read_all(fd, table.data(), table.size(), deadline);
+          for (int r = 0; r < world && !err; ++r) c->peer_devices[(size_t)r] = (int64_t)get64(table.data() + 8 * r);
+        }
       }
     }
   }

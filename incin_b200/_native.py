@@ -35,11 +35,14 @@ class NativeError(RuntimeError):
 
 
 LAUNCH_CALLS = 0  # number of native launch calls made by this process (each enqueues >= 1 kernel)
+LAUNCH_HOOK = None  # set by incin_b200.telemetry.trace while NVTX marks / the per-step device trace are switched on
 
 
 def check(rc: int, what: str = "") -> None:
     global LAUNCH_CALLS
     LAUNCH_CALLS += 1
+    if LAUNCH_HOOK is not None:
+        LAUNCH_HOOK(what)
     if rc != 0:
         raise NativeError(f"{what or 'native call'} failed: {STATUS_NAMES.get(rc, rc)}")
 

@@ -41,17 +41,22 @@ class TrainStep:
 
     # one full step, enqueued on the current stream
     def _enqueue(self, inputs: Sequence[torch.Tensor]) -> torch.Tensor:
-        self.store.zero_grad()
-        if self.reducer is not None:
-            self.reducer.begin_step()
-        loss = self.loss_fn(self.model, *inputs)
-        loss.backward()
-        if self.device.type != "cuda":
-            self.store.collect_autograd_grads()
-        if self.reducer is not None:
-            self.reducer.finish_step(self.opt)  # reduce-scatter + optimiser + all-gather, fused
-        else:
-            self.opt.launch()
+        from .telemetry import trace
+        with trace.op_range("zero_grad"):
+            self.store.zero_grad()
+            if self.reducer is not None:
+                self.reducer.begin_step()
+        with trace.op_range("forward"):
+            loss = self.loss_fn(self.model, *inputs)
+        with trace.op_range("backward"):
+            loss.backward()
+            if self.device.type != "cuda":
+                self.store.collect_autograd_grads()
+        with trace.op_range("optimizer"):
+            if self.reducer is not None:
+                self.reducer.finish_step(self.opt)  # reduce-scatter + optimiser + all-gather, fused
+            else:
+                self.opt.launch()
         return loss.detach()
 
     def _capture(self, inputs: Sequence[torch.Tensor], mode: str = "global") -> None:

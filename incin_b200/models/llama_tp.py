@@ -196,13 +196,14 @@ class TPOptimizer:
         else:
             self.sh_store = ParamStore(model.sharded_parameters(), allocator=alloc)
             if self.dp_reducer is not None and self.kv_share > 1:
-                self._grad_buf = next(b for b in self.dp_reducer._bufs if b.ptr == self.sh_store.grad.data_ptr())
+                # the reducer mapped the gradient buffer over the data axis; the K/V pair sum needs the mappings of the
+                # tensor-parallel neighbours, so the same memory is mapped a second time over that group
+                mine = next(b for b in self.dp_reducer._bufs if b.ptr == self.sh_store.grad.data_ptr())
+                self._grad_buf = mine.mapped_over(tp.group, session=session, ranks=tp.ranks)
         self.sh_opt = AdamW(self.sh_store, lr=lr, betas=betas, weight_decay=weight_decay)
         if self.dp_reducer is not None:
             self.dp_reducer.attach(self.sh_store, self.sh_opt)
         if self.kv_share > 1:
-            if self.dp_reducer is not None:
-                raise NotImplementedError("shared K/V heads together with a data axis: use n_kv_head >= tp")
             ranges = [(o, k) for n, p, o, k in self.sh_store.entries if n.endswith("kv_w")]
             base = (tp.rank // self.kv_share) * self.kv_share
             self._kv_sum = PeerRangeSum(self._grad_buf, ranges, list(range(base, base + self.kv_share)), tp.rank, tp,

@@ -138,6 +138,16 @@ class SymmetricBuffer:
             dist.barrier(group=group)
         return self
 
+    def mapped_over(self, group=None, session=None, ranks: list[int] | None = None) -> "SymmetricBuffer":
+        """Collective over ANOTHER group: a second view of the same local memory whose ``ptrs`` are the mappings of that
+        group's ranks (a gradient buffer that the data-parallel reducer mapped over its replicas is also summed over
+        the tensor-parallel neighbours that share a K/V head).  The view keeps this buffer alive."""
+        v = SymmetricBuffer.__new__(SymmetricBuffer)
+        v.nbytes, v.device, v._handle, v.ptr = self.nbytes, self.device, self._handle, self.ptr
+        v._owner, v.local_bytes, v._parent = self._owner, self.local_bytes, self
+        v.ptrs, v.rank, v.world, v._opened = [self.ptr], 0, 1, []
+        return v.exchange(group, session=session, ranks=ranks)
+
     def close(self) -> None:
         for p in self._opened:
             nat.cuda().incin_symm_close(p)

@@ -84,3 +84,60 @@ def test_step_pipeline_matches_sequential_steps():
     assert max(abs(a - b) for a, b in zip(got, ref)) < 2e-2, (got, ref)
     with pytest.raises(RuntimeError):
         pipe.pop()
+
+
+def test_steady_state_step_makes_no_device_allocation():
+    """After warm-up, neither an eager nor a graph-replayed training step asks the driver for memory: the caching
+    allocator's count of device allocations, its reserved bytes and the device's free memory do not move."""
+    from incin_b200.engine import TrainStep
+    from incin_b200.optim import AdamW, ParamStore
+    for use_graph in (False, True):
+        cfg, cpu, gpu, tok, tgt = _setup("auto")
+        step = TrainStep(gpu, AdamW(ParamStore(gpu.named_parameters()), lr=1e-3), use_graph=use_graph)
+        tok, tgt = tok.cuda(), tgt.cuda()
+        for _ in range(5):
+            step(tok, tgt)
+        torch.cuda.synchronize()
+        s0 = torch.cuda.memory_stats()
+        free0, _ = torch.cuda.mem_get_info()
+        for _ in range(6):
+            step(tok, tgt)
+        torch.cuda.synchronize()
+        s1 = torch.cuda.memory_stats()
+        free1, _ = torch.cuda.mem_get_info()
+        assert s1["num_device_alloc"] == s0["num_device_alloc"], (use_graph, s0["num_device_alloc"], s1["num_device_alloc"])
+        assert s1["reserved_bytes.all.current"] == s0["reserved_bytes.all.current"]
+        assert free1 == free0, (use_graph, free0, free1)
+
+
+def test_device_trace_rows_cover_the_eager_step():
+    """The per-step trace records one row per native launch call of an eager step; the rows' device times add up to
+    the step's own device time (events sit on the launching stream back to back)."""
+    from incin_b200 import _native
+    from incin_b200.engine import TrainStep
+    from incin_b200.optim import AdamW, ParamStore
+    from incin_b200.telemetry import trace
+    cfg, cpu, gpu, tok, tgt = _setup("auto")
+    step = TrainStep(gpu, AdamW(ParamStore(gpu.named_parameters()), lr=1e-3), use_graph=False)
+    tok, tgt = tok.cuda(), tgt.cuda()
+    for _ in range(3):
+        step(tok, tgt)
+    trace.enable(nvtx=True, events=True)
+    try:
+        calls0 = _native.LAUNCH_CALLS
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        trace.begin_step()
+        step(tok, tgt)
+        e1.record()
+        rows = trace.end_step()
+        calls = _native.LAUNCH_CALLS - calls0
+    finally:
+        trace.enable(nvtx=False, events=False)
+    assert _native.LAUNCH_HOOK is None
+    assert len(rows) == calls and calls > 10
+    total = sum(ms for _, ms in rows)
+    assert 0 < total <= e0.elapsed_time(e1) * 1.05
+    top = trace.summary(rows)
+    assert abs(sum(r["share"] for r in top) - 1.0) < 1e-2 and top[0]["ms"] >= top[-1]["ms"]
+    assert trace.end_step() == []      # tracing off again: free

@@ -408,3 +408,25 @@ def test_capability_document_matches_the_registries():
     doc = Path(__file__).resolve().parent.parent / "docs" / "capabilities.md"
     assert doc.read_text() == CAPABILITIES_HEADER + capability_report(), \
         "run `python -m incin_b200 capabilities --write` after changing incin_b200/core/spec.py"
+
+
+def test_trace_summary_and_hook_install(tmp_path):
+    """The launch hook is installed only while tracing is on; summaries group rows by launch name and the JSONL record
+    carries the totals."""
+    import json
+    from incin_b200 import _native
+    from incin_b200.telemetry import trace
+    assert _native.LAUNCH_HOOK is None
+    trace.enable(nvtx=False, events=True)
+    assert _native.LAUNCH_HOOK is trace.on_launch
+    trace.enable(events=False)
+    assert _native.LAUNCH_HOOK is None and not trace.active()
+    rows = [("gemm", 0.5), ("norm", 0.1), ("gemm", 0.25), ("adamw", 0.15)]
+    top = trace.summary(rows)
+    assert [r["name"] for r in top] == ["gemm", "adamw", "norm"]
+    assert top[0] == {"name": "gemm", "calls": 2, "ms": 0.75, "share": 0.75}
+    trace.to_jsonl(tmp_path / "t.jsonl", rows, step=3)
+    rec = json.loads((tmp_path / "t.jsonl").read_text())
+    assert rec["step"] == 3 and rec["launches"] == 4 and abs(rec["total_ms"] - 1.0) < 1e-9
+    with trace.op_range("anything"):   # off: a plain no-op, also without a GPU
+        pass
