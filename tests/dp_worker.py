@@ -40,6 +40,33 @@ def run(kind: str, use_graph: bool, steps: int = 5, session=None):
     return store.shadow.float().clone(), losses, desc
 
 
+def run_trainer(steps: int = 5, session=None):
+    """The same training through the public ``Trainer`` API on a plan of every GPU of the job."""
+    from incin_b200.core.device import DeviceSet
+    from incin_b200.models.gpt2 import GPT2, GPT2Config
+    from incin_b200.optim import AdamW, ParamStore
+    from incin_b200.parallel import dp as DP
+    from incin_b200.train import Trainer
+    rank, world = dist.get_rank(), dist.get_world_size()
+    device = torch.device("cuda", torch.cuda.current_device())
+    plan = Trainer.plan().devices(DeviceSet.cuda(range(world))).epochs(1).build()
+    assert plan.is_multi_device and "collectives-required" in [d.code for d in plan.decisions]
+    cfg = GPT2Config.tiny()
+    model = GPT2(cfg, seed=0).to(device)
+    reducer, allocator, _ = DP.make_reducer("auto", device, session=session)
+    store = ParamStore(model.named_parameters(), allocator=allocator)
+    opt = AdamW(store, lr=1e-3, weight_decay=0.1)
+    reducer.attach(store, opt)
+    g = torch.Generator().manual_seed(100 + rank)
+    tok = torch.randint(0, cfg.vocab_size, (2, 128), generator=g).pin_memory()
+    tgt = torch.randint(0, cfg.vocab_size, (2, 128), generator=g).pin_memory()
+    seen = []
+    losses = Trainer(plan).fit(model, opt, [(tok, tgt)] * steps, on_step=lambda n, v: seen.append(n))
+    torch.cuda.synchronize()
+    assert seen == list(range(1, steps + 1))
+    return store.shadow.float().clone(), list(losses)
+
+
 def main():
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -67,6 +94,10 @@ def main():
         out[f"{kind}{'-graph' if graph else ''}"] = {"ranks_identical": same, "max_abs_diff_vs_nccl": err,
                                                      "loss_first": losses[0], "loss_last": losses[-1]}
         ok = ok and same and err < 2e-2 and losses[-1] < losses[0]
+    w, losses = run_trainer(session=session)
+    err = (w - ref).abs().max().item()
+    out["trainer_fit"] = {"max_abs_diff_vs_nccl": err, "loss_first": losses[0], "loss_last": losses[-1]}
+    ok = ok and err < 2e-2 and len(losses) == 5 and max(abs(a - b) for a, b in zip(losses, ref_losses)) < 5e-2
     out["plan_validated_launches"] = session.launches
     out["multimem"] = bool(os.environ.get("INCIN_TEST_EXPECT_MULTIMEM") == "1")
     if out["multimem"]:      # the launcher asked for the NVSwitch multicast variant: make sure that is what ran

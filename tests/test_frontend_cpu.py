@@ -346,7 +346,8 @@ def test_telemetry_emitter_bounds_and_viewer(tmp_path):
     fut = T.Event.from_json('{"kind":"new_kind","name":"x","future_field":3}')
     assert fut.kind == "new_kind" and fut.payload["future_field"] == 3
     from incin_b200.telemetry.viz import render
-    assert "loss" in render(p) and "lr=0.0003" in render(p)
+    frame = render(p)
+    assert "loss" in frame and "0.0003" in frame and "events 21" in frame
     a, b = T.uuid7(), T.uuid7()
     assert a[14] == "7" and a[:8] <= b[:8]
 

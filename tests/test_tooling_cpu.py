@@ -430,3 +430,145 @@ def test_trace_summary_and_hook_install(tmp_path):
     assert rec["step"] == 3 and rec["launches"] == 4 and abs(rec["total_ms"] - 1.0) < 1e-9
     with trace.op_range("anything"):   # off: a plain no-op, also without a GPU
         pass
+
+
+def _viz_run(tmp_path):
+    from incin_b200 import telemetry as T
+    p = tmp_path / "run.jsonl"
+    evs = [T.Event("hyperparam", "lr", None, None, {"value": 3e-4}, ts=100.0)]
+    for i in range(40):
+        evs.append(T.Event("scalar", "loss", 4.0 / (i + 1), i + 1, ts=100.0 + i))
+        evs.append(T.Event("scalar", "tokens_per_s", 7e5 + i, i + 1, ts=100.0 + i))
+        evs.append(T.Event("gradient_norm", "wte", 2.0 - i * 0.01, i + 1, ts=100.0 + i))
+        evs.append(T.Event("weight_norm", "wte", 30.0, i + 1, ts=100.0 + i))
+    evs.append(T.Event("gradient_norm", "lm_head", float("inf"), 41, ts=141.0))
+    evs.append(T.Event("memory", "memory", None, 40, {"rss_bytes": 512 * 2**20, "cuda_allocated": 3 * 2**30}, ts=141.0))
+    evs.append(T.Event("graph_snapshot", "graph", None, 40, {"nodes": [
+        {"id": 0, "op": "input", "inputs": [], "shape": [4, 8], "dtype": "bf16"},
+        {"id": 1, "op": "matmul", "inputs": [0, 0], "shape": [4, 4], "dtype": "bf16"},
+        {"id": 2, "op": "relu", "inputs": [1], "shape": [4, 4], "dtype": "bf16"}]}, ts=141.0))
+    evs.append(T.Event("epoch", "epoch", 1.0, None, {"steps": 40}, ts=142.0))
+    p.write_text("".join(e.to_json() + "\n" for e in evs))
+    return p, evs
+
+
+def test_viz_panels_render_every_event_kind(tmp_path):
+    from incin_b200.telemetry import viz
+    p, evs = _viz_run(tmp_path)
+    frame = viz.render(p, 140, 48)
+    assert "step 40" in frame and "best 0.1" in frame                      # loss panel
+    assert "tokens_per_s" in frame                                          # scalars
+    assert "NON-FINITE" in frame and "wte" in frame                         # norms: the inf gradient is flagged
+    assert "3072.0 MiB" in frame and "epochs 1" in frame and "0.0003" in frame   # system
+    assert "3 nodes @ step 40" in frame and "matmul" in frame and "%0,%0" in frame  # graph
+    assert all(len(line) <= 140 for line in frame.splitlines()) and len(frame.splitlines()) <= 48
+    # the same panels fit a small terminal and a stacked layout without raising
+    app = viz.App()
+    app.feed(evs)
+    app.on_key("t")
+    small = app.render(60, 16).to_text()
+    assert not app.failed and "loss" in small
+    assert "\033[1m" in app.render(80, 24).to_ansi()
+
+
+def test_viz_focus_keymap_plugin_and_failure_isolation(tmp_path):
+    from incin_b200.telemetry import viz
+    p, evs = _viz_run(tmp_path)
+
+    class Counter(viz.Panel):
+        id, title = "counter", "event counter"
+        def __init__(self):
+            self.n, self.keys, self.explode = 0, [], False
+        def update(self, e):
+            self.n += 1
+        def render(self, canvas, area):
+            if self.explode:
+                raise RuntimeError("boom")
+            canvas.text(area, 0, 0, f"seen {self.n} events " + "x" * 500)       # clipped to the tile
+        def handle_key(self, key):
+            self.keys.append(key)
+            return True
+        def reset(self):
+            self.n, self.explode = 0, False
+
+    class Bundle(viz.Plugin):
+        def panels(self):
+            return [Counter()]
+
+    app = viz.App(plugins=[Bundle()])
+    assert [q.id for q in app.panels] == ["loss", "scalars", "norms", "system", "graph", "counter"]
+    with pytest.raises(ValueError):
+        viz.App(plugins=[Bundle(), Bundle()])                                # duplicate ids are refused
+    app.feed(evs)
+    counter = app.panels[-1]
+    assert counter.n == len(evs) and f"seen {len(evs)} events" in app.render(120, 40).to_text()
+    # focus: grid of two columns
+    assert app.focus == 0
+    app.on_key("l"); assert app.focus == 1
+    app.on_key("j"); assert app.focus == 3
+    app.on_key("h"); assert app.focus == 2
+    app.on_key("k"); assert app.focus == 0
+    app.on_key("k"); assert app.focus == 0                                   # no wrap at the edge
+    app.on_key("\x1b[Z"); assert app.focus == 5                              # Shift-Tab wraps
+    assert app.on_key("z") is viz.Action.PANEL_LOCAL and counter.keys == ["z"]
+    # a failing panel is fenced off, the others keep rendering, retry brings it back with the run replayed
+    counter.explode = True
+    frame = app.render(120, 40).to_text()
+    assert "[failed]" in frame and "RuntimeError: boom" in frame and "step 40" in frame and "xxxx" not in frame
+    app.feed(evs[:3])
+    assert counter.n == len(evs)                                             # fenced off: no more updates
+    app.on_key("r")
+    assert "counter" not in app.failed and counter.n == len(evs) + 3
+    assert f"seen {len(evs) + 3} events" in app.render(120, 40).to_text()
+    # graph panel keys scroll the node list
+    g = app.panels[4]
+    app.focus = 4
+    app.on_key("G"); assert g.scroll == 2
+    app.on_key("0"); assert g.scroll == 0
+    assert '"op": "matmul"' in g.hover_text(0, 3)
+    # keymap file: rebinding drops the default key of that action; unknown actions are an error
+    f = tmp_path / "incin-viz.toml"
+    f.write_text('[keymap]\nquit = ["x", "esc"]\ntoggle_layout = "space"\n')
+    km = viz.Keymap.from_toml(f)
+    assert km.resolve("x") is viz.Action.QUIT and km.resolve("\x1b") is viz.Action.QUIT
+    assert km.resolve("q") is viz.Action.PANEL_LOCAL and km.resolve(" ") is viz.Action.TOGGLE_LAYOUT
+    f.write_text('[keymap]\nquitt = "x"\n')
+    with pytest.raises(ValueError, match="unknown action"):
+        viz.Keymap.from_toml(f)
+    app2 = viz.App(keymap=km)
+    app2.on_key("x")
+    assert not app2.running
+
+
+def test_viz_tail_follows_a_growing_file_and_a_restart(tmp_path, monkeypatch):
+    import sys
+    import types
+    from incin_b200 import telemetry as T
+    from incin_b200.telemetry import viz
+    p = tmp_path / "live.jsonl"
+    tail = viz.RunTail(p)
+    assert tail.poll() == []                                                  # not there yet
+    a = T.Event("scalar", "loss", 2.0, 1).to_json()
+    b = T.Event("scalar", "loss", 1.0, 2).to_json()
+    p.write_text(a + "\n" + b[:10])
+    assert [e.value for e in tail.poll()] == [2.0]                            # the torn line waits
+    with open(p, "a") as f:
+        f.write(b[10:] + "\nnot json\n")
+    assert [e.value for e in tail.poll()] == [1.0] and tail.poll() == []
+    p.write_text(a + "\n")                                                    # a new run under the same name
+    assert [e.value for e in tail.poll()] == [2.0] and tail.restarted
+    # plug-ins named in the environment are loaded by the one-frame renderer
+    mod = types.ModuleType("viz_test_plugin")
+
+    class P(viz.Panel):
+        id, title = "extra", "extra panel"
+        def update(self, e): pass
+        def render(self, canvas, area): canvas.text(area, 0, 0, "hello from a plug-in")
+
+    class Pl(viz.Plugin):
+        def panels(self): return [P()]
+    mod.make = Pl
+    monkeypatch.setitem(sys.modules, "viz_test_plugin", mod)
+    monkeypatch.setenv("INCIN_VIZ_PLUGINS", "viz_test_plugin:make")
+    assert "hello from a plug-in" in viz.render(p)
+    viz.watch(p, interval=0.0, iterations=2)                                  # not a terminal: prints frames and returns

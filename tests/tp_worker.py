@@ -103,5 +103,72 @@ def main():
     sys.exit(0 if ok else 1)
 
 
+def mesh2d():
+    """dp x tp = 2 x 2 with ONE K/V head (both tensor-parallel ranks hold it): the sharded gradients are summed over the
+    K/V pair and then reduced over the data axis, through two mappings of the same buffer.  Compared with the same
+    model trained on one GPU on the concatenated batch."""
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    from incin_b200.engine import TrainStep
+    from incin_b200.models.llama import Llama, LlamaConfig
+    from incin_b200.models.llama_tp import LlamaTP, TPOptimizer, tensor_parallel_plan
+    from incin_b200.ops import gemm as G
+    from incin_b200.optim import AdamW, make_store
+    from incin_b200.parallel.context import DistributedContext
+    from incin_b200.parallel.mesh import mesh
+    from incin_b200.parallel.session import bind_session
+    from incin_b200.parallel.tp import TensorParallel
+    tp, dp = 2, world // 2
+    spec = mesh(dp=dp, tp=tp)
+    d, _, t = spec.coords(rank)
+    tp_groups = [dist.new_group([spec.rank_of(dd, 0, tt) for tt in range(tp)]) for dd in range(dp)]
+    dp_groups = [dist.new_group([spec.rank_of(dd, 0, tt) for dd in range(dp)]) for tt in range(tp)]
+    tp_ranks = [spec.rank_of(d, 0, tt) for tt in range(tp)]
+    dp_ranks = [spec.rank_of(dd, 0, t) for dd in range(dp)]
+    out = {"world": world}
+    for name, use_session in (("session", True), ("torch", False)):
+        session = bind_session(DistributedContext.from_env(), spec) if use_session else None
+        cfg = LlamaConfig(vocab_size=512, n_layer=2, d_model=256, n_head=4, n_kv_head=1, head_dim=64, d_ffn=512)
+        B, T = 4, 128
+        tpm = TensorParallel(dev, tp_groups[d], max_rows_per_rank=B * T // tp, max_cols=cfg.d_model, session=session,
+                             plan=tensor_parallel_plan(cfg, session.mesh, rank, B * T) if session else None,
+                             ranks=tp_ranks if session else None)
+        gg = torch.Generator().manual_seed(3)
+        tok_all = torch.randint(0, cfg.vocab_size, (dp * B, T), generator=gg).to(dev)
+        tgt_all = torch.randint(0, cfg.vocab_size, (dp * B, T), generator=gg).to(dev)
+        tok, tgt = tok_all[d * B:(d + 1) * B].contiguous(), tgt_all[d * B:(d + 1) * B].contiguous()
+        ref = Llama(cfg, seed=0).to(dev)
+        ref_step = TrainStep(ref, AdamW(make_store(ref), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1), use_graph=False)
+        m = LlamaTP.from_seed(cfg, tp, t, seed=0).to(dev)
+        m.tp = tpm
+        opt = TPOptimizer(m, tpm, dev, lr=1e-3, dp_group=dp_groups[t], world_group=None, session=session, dp_ranks=dp_ranks)
+        step = TrainStep(m, opt, use_graph=False)
+        lr_, lt_ = [], []
+        for _ in range(4):
+            lr_.append(float(ref_step(tok_all, tgt_all)))
+            l = step(tok, tgt).clone()
+            dist.all_reduce(l)
+            lt_.append(float(l) / dp)
+        G.check_status()
+        kv_ref = dict(ref.named_parameters())["blocks.1.qkv_w"][cfg.n_head * 64:]
+        out[name] = {"loss_ref": lr_, "loss_tp": lt_, "kv_w_diff": rel(dict(m.named_parameters())["blocks.1.kv_w"], kv_ref),
+                     "embed_diff": rel(m.embed, ref.embed)}
+        del step, opt, m, tpm, ref_step, ref
+    ok = True
+    for name in ("session", "torch"):
+        r = out[name]
+        ok = ok and all(abs(a - b) < 5e-2 for a, b in zip(r["loss_ref"], r["loss_tp"])) and r["loss_tp"][-1] < r["loss_tp"][0]
+        ok = ok and r["kv_w_diff"] < 5e-2 and r["embed_diff"] < 5e-2
+    out["ok"] = ok
+    if rank == 0:
+        print("TP_RESULT " + json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
 if __name__ == "__main__":
-    main()
+    mesh2d() if sys.argv[1:] == ["mesh2d"] else main()
