@@ -3,6 +3,7 @@ compile for sm_100a, no GPU needed), the tuning service and its cache, collectiv
 import json
 import subprocess
 import sys
+from pathlib import Path
 
 import pytest
 import torch
@@ -572,3 +573,95 @@ def test_viz_tail_follows_a_growing_file_and_a_restart(tmp_path, monkeypatch):
     monkeypatch.setenv("INCIN_VIZ_PLUGINS", "viz_test_plugin:make")
     assert "hello from a plug-in" in viz.render(p)
     viz.watch(p, interval=0.0, iterations=2)                                  # not a terminal: prints frames and returns
+
+
+def test_xtask_ledger_is_sound_and_detects_drift(tmp_path):
+    """The committed ledger passes; each kind of damage is reported."""
+    import copy
+    from incin_b200 import xtask
+    assert xtask.check_ledger() == []
+    assert xtask.docs(check=True) == []                                        # every generated document is current
+    good = xtask.load_ledger()
+    table = xtask.render_table(good)
+    assert "| K1 | core | kernel | complete |" in table and len(good) >= 60
+
+    def errors(mutate, tbl=None):
+        t = copy.deepcopy(good)
+        mutate(t)
+        return xtask.check_ledger(tasks=t, table=xtask.render_table(t) if tbl is None else tbl)
+
+    assert any("unknown component Z9" in e for e in errors(lambda t: t["K2"]["depends"].append("Z9")))
+    assert any("does not exist" in e for e in errors(lambda t: t["K2"]["files"].append("csrc/nope.cu")))
+    assert any("without evidence" in e for e in errors(lambda t: t["K5"].update(tests=[])))
+    assert any("unknown tier" in e for e in errors(lambda t: t["C1"].update(tier="stable")))
+    assert any("without a note" in e for e in errors(lambda t: t["B5"].pop("note")))
+    # a core component must not lean on a preview one
+    assert any("which is only preview" in e for e in errors(lambda t: t["C1"]["depends"].append("M4")))
+    # cycles: K1 -> K2 -> K1
+    cyc = errors(lambda t: t["K1"]["depends"].append("K2"))
+    assert any(e.startswith("dependency cycle") and "K1" in e and "K2" in e for e in cyc)
+    assert xtask.find_cycles({"a": {"depends": ["b"]}, "b": {"depends": ["c"]}, "c": {"depends": []}}) == []
+    # the markdown rendering is part of the contract
+    assert any("differs from the rendering" in e for e in errors(lambda t: None, tbl=table.replace("complete", "done", 1)))
+    assert xtask.main(["ledger"]) == 0 and xtask.main([]) == 2
+
+
+def test_lsp_proxy_frames_and_rewrites(tmp_path):
+    import io
+    import json
+    import subprocess
+    import sys
+    from incin_b200 import lsp
+    # framing: case-insensitive header, extra headers, back-to-back frames, truncated tail
+    buf = io.BytesIO()
+    lsp.write_frame(buf, b'{"a":1}')
+    buf.write(b"content-length: 2\r\nContent-Type: application/vscode-jsonrpc; charset=utf-8\r\n\r\n{}")
+    buf.write(b"Content-Length: 10\r\n\r\n{}")
+    buf.seek(0)
+    assert lsp.read_frame(buf) == b'{"a":1}' and lsp.read_frame(buf) == b"{}" and lsp.read_frame(buf) is None
+    with pytest.raises(ValueError):
+        lsp.read_frame(io.BytesIO(b"Content-Length: banana\r\n\r\n"))
+    with pytest.raises(ValueError):
+        lsp.read_frame(io.BytesIO(b"Content-Length: 99999999999\r\n\r\n"))
+    # diagnostics: the recognised message gains the explanation, the other entry and other messages pass through
+    err = "mat1 and mat2 shapes cannot be multiplied (4x8 and 16x2)"
+    pend = lsp.PendingRequests()
+    msg = {"jsonrpc": "2.0", "method": "textDocument/publishDiagnostics",
+           "params": {"uri": "file:///x.py", "diagnostics": [{"message": err, "severity": 1}, {"message": "unused import"}]}}
+    out = lsp.rewrite_from_server(msg, pend)
+    d0, d1 = out["params"]["diagnostics"]
+    assert d0["message"].startswith(err) and "hint:" in d0["message"] and "rule:" in d0["message"] and d0["severity"] == 1
+    assert d1 == {"message": "unused import"} and msg["params"]["diagnostics"][0]["message"] == err    # input untouched
+    assert lsp.rewrite_from_server(out, pend) is None                                # never explained twice
+    assert lsp.rewrite_from_server({"jsonrpc": "2.0", "method": "window/logMessage", "params": {"message": err}}, pend) is None
+    assert lsp.rewrite_from_server(msg, pend, hints=False) is None
+    # hovers: only answers to hover requests that went through the proxy are touched
+    answer = {"jsonrpc": "2.0", "id": 7, "result": {"contents": {"kind": "markdown", "value": err}}}
+    assert lsp.rewrite_from_server(answer, pend) is None
+    pend.observe_outgoing({"jsonrpc": "2.0", "id": 7, "method": "textDocument/hover", "params": {}})
+    new = lsp.rewrite_from_server(answer, pend)
+    assert "hint:" in new["result"]["contents"]["value"] and new["result"]["contents"]["kind"] == "markdown"
+    assert lsp.rewrite_from_server(answer, pend) is None                             # the id was consumed
+    # end to end through a child "server" that publishes one diagnostic per request and echoes the rest
+    server = tmp_path / "server.py"
+    server.write_text(
+        "import sys, json\n"
+        "sys.path.insert(0, %r)\n"
+        "from incin_b200.lsp import read_frame, write_frame\n"
+        "while (b := read_frame(sys.stdin.buffer)) is not None:\n"
+        "    m = json.loads(b)\n"
+        "    if m.get('method') == 'exit': break\n"
+        "    write_frame(sys.stdout.buffer, json.dumps({'jsonrpc': '2.0', 'method': 'textDocument/publishDiagnostics',\n"
+        "        'params': {'uri': 'u', 'diagnostics': [{'message': m['params']['text']}]}}).encode())\n"
+        % str(Path(__file__).resolve().parent.parent))
+    req = io.BytesIO()
+    lsp.write_frame(req, json.dumps({"jsonrpc": "2.0", "method": "x", "params": {"text": err}}).encode())
+    lsp.write_frame(req, json.dumps({"jsonrpc": "2.0", "method": "x", "params": {"text": "fine"}}).encode())
+    lsp.write_frame(req, json.dumps({"jsonrpc": "2.0", "method": "exit"}).encode())
+    p = subprocess.run([sys.executable, "-m", "incin_b200", "lsp", "--", sys.executable, str(server)], input=req.getvalue(),
+                       capture_output=True, timeout=120, cwd=str(Path(__file__).resolve().parent.parent))
+    assert p.returncode == 0, p.stderr.decode()[-2000:]
+    got = io.BytesIO(p.stdout)
+    first, second = json.loads(lsp.read_frame(got)), json.loads(lsp.read_frame(got))
+    assert "hint:" in first["params"]["diagnostics"][0]["message"]
+    assert second["params"]["diagnostics"][0]["message"] == "fine"
