@@ -292,6 +292,9 @@ def main() -> None:
             first_loss = l
             launches_per_step = _native.LAUNCH_CALLS - calls0 if args.impl == "ours" else 0
     G.check_status(device)
+    if os.environ.get("INCIN_TUNE_EXPLAIN") == "1" and rank == 0:   # what the autotune service timed during warm-up
+        from incin_b200.tuning import service
+        print(service().explain(), file=sys.stderr, flush=True)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:

@@ -70,7 +70,12 @@ typedef struct incin_gemm_desc {
    * shard [ag_rows_per_rank][K] (a peer-mapped pointer for r != ag_rank).  ag_copy_ctas CTAs of the same launch
    * pull the shards into the gathered buffer with bulk copies (each remote byte crosses NVLink once) and
    * publish one flag per 128-row tile in ag_flags (uint32[tiles_m], zeroed by the caller before the launch);
-   * the GEMM CTAs consume tiles in the order they arrive, own shard first.  ag_rows_per_rank % 128 == 0. */
+   * the GEMM CTAs consume tiles in the order they arrive, own shard first.  ag_rows_per_rank % 128 == 0.
+   * ag_src[ag_rank] == NULL: the caller has already written this rank's own rows into the gathered buffer; they are
+   * neither copied nor waited for.
+   * ag_copy_ctas = -n asks for copy warps instead: every compute CTA carries one more warp that moves its share of the
+   * shards in 8 KB bulk copies (no SM is taken from the GEMM; n operand stages of shared memory become the copy ring,
+   * at least three stay with the GEMM); ag_flags then count the completed chunks of a tile. */
   int ag_world, ag_rank, ag_rows_per_rank, ag_copy_ctas;
   const void* ag_src[8];
   void* ag_flags;
@@ -81,7 +86,8 @@ typedef struct incin_gemm_desc {
    * With rs_copy_ctas > 0 and rs_ready != NULL the transfer is done by copy CTAs instead: the epilogue writes
    * tiles owned by other ranks into the local staging buffer C ([M][ldc], ldc == N), counts finished epilogue
    * warps per 128-row block in rs_ready (uint32[tiles_m], zeroed by the caller), and rs_copy_ctas CTAs of the
-   * same launch push each completed block to its owner in 32 KB bulk copies while later blocks are computed. */
+   * same launch push each completed block to its owner in 32 KB bulk copies while later blocks are computed.
+   * rs_copy_ctas = -n: the blocks are pushed by one copy warp in every compute CTA instead (see ag_copy_ctas). */
   int rs_world, rs_rank, rs_rows_per_rank, rs_copy_ctas;
   void* rs_dst[8];
   long long rs_slot_stride;

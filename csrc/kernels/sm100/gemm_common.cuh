@@ -17,6 +17,10 @@ constexpr int SMEM_BUDGET = 224 * 1024;   // of the 227 KB a CTA may use; the re
 constexpr int EPI_WARPS = 8;
 constexpr int STG_WARP_BYTES = 32 * 128;
 constexpr int STG_BYTES = EPI_WARPS * STG_WARP_BYTES;   // 32 KB
+// Fused-collective launches of the single-CTA kernel may carry one more warp per CTA that moves the collective's data
+// (see the copy warp in gemm_tcgen05.cu); every other launch runs with GEMM_THREADS.
+constexpr int GEMM_COPY_WARP = 2 + EPI_WARPS;
+constexpr int GEMM_THREADS_COPY = GEMM_THREADS + 32;
 
 // STG: the variant with the 32 KB output staging area (one operand stage fewer for every tile but 128 x 256, whose
 // four 48 KB stages leave that much room anyway)
@@ -59,6 +63,11 @@ struct GemmKernelParams {
   __nv_bfloat16* rs_dst[8];
   long long rs_slot_stride;
   uint32_t* rs_ready;     // push mode: per 128-row block, epilogue warps that have finished writing it
+  // n > 0: the collective's data is moved by one extra warp in every compute CTA (chunks of 8 KB through a ring made
+  // of the last n operand stages) instead of by dedicated copy CTAs; ag_flags then count chunks per 128-row tile
+  int copy_warps;
+  uint32_t ag_flag_target;   // value of ag_flags[tile] at which the tile is complete
+  int ag_own_in_place;       // 1: this rank's own rows are already in the gathered buffer (nothing copies or waits for them)
   // 1: the epilogue stages its output in shared memory and writes C (and the pre-activation side output) with bulk
   // tensor stores / reduce-adds through the tensor maps passed beside the operands' (dense rows, aligned base)
   int tma_out;

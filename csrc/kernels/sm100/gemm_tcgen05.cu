@@ -37,7 +37,7 @@
 namespace incin {
 
 template <int BN, bool A_MN, bool B_MN, bool STG>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS_COPY, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux,
                     const GemmKernelParams p) {
@@ -51,12 +51,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* tempty_bar = tfull_bar + 2;           // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint64_t* copy_bar = bars;   // copy CTAs reuse the (otherwise idle) full/empty barriers, 2*STAGES >= NBUF of them
+  uint64_t* cw_bar = tempty_bar + 3;   // [2] barriers of the copy warp's two half rings (after tmem_slot and abort_flag)
+  // Copy-warp mode: the last p.copy_warps operand stages are the copy warp's ring; the operand ring is that much shorter.
+  constexpr int CW_CHUNK = 8 * 1024;
+  const int n_stages = Cfg::STAGES - p.copy_warps;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   // all-gather mode: the first CTAs of the grid (dispatched first) copy, the remaining gemm_ctas compute
-  const int n_compute = (p.ag_world > 1 || p.rs_push) ? p.gemm_ctas : (int)gridDim.x;
+  const int n_compute = ((p.ag_world > 1 || p.rs_push) && !p.copy_warps) ? p.gemm_ctas : (int)gridDim.x;
   const int n_copy = (int)gridDim.x - n_compute;
   const bool is_copier = (int)blockIdx.x < n_copy;
   const int cta = (int)blockIdx.x - n_copy;
@@ -70,6 +73,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mbar_init(&tfull_bar[a], 1);
       mbar_init(&tempty_bar[a], 8);
     }
+    for (int b = 0; b < 2; ++b) mbar_init(&cw_bar[b], 1);
     *abort_flag = 0;
     mbar_init_fence();
     tma_prefetch_desc(&tmA);
@@ -96,26 +100,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // Either way the data moves global -> shared -> global in 32 KB bulk copies, so every byte crosses NVLink
     // exactly once and in large transfers.
     if (threadIdx.x == 0) {
+      // 32 KB chunks through a ring that takes the whole operand memory.  What a copy CTA sustains is set by the bytes
+      // it has in flight (measured between two B200s, 16 CTAs, loads from the peer: 64 KB ring 14 GB/s per CTA,
+      // 192 KB ring 31-37 GB/s), so a buffer is recycled as soon as the store that drains it has read it; and by what
+      // the one issuing thread spends per chunk (with 8 KB chunks the loop itself capped a CTA at 10 GB/s), hence the
+      // large chunks.  The ring's barriers are the operand ring's (otherwise idle here), 2 * STAGES >= NBUF of them.
       constexpr int CHUNK = 32 * 1024;
-      constexpr int NBUF = Cfg::STAGES * Cfg::STAGE_BYTES / CHUNK;   // the whole operand ring is staging space here
-      constexpr int PENDING = 2;   // bulk stores whose shared-memory reads may still be outstanding
-      static_assert(NBUF > PENDING + 1, "staging ring too small");
+      constexpr int NBUF = Cfg::STAGES * Cfg::STAGE_BYTES / CHUNK;
+      constexpr int PENDING = NBUF / 2;   // bulk stores whose shared-memory reads may still be outstanding
+      constexpr int LAG = 2;              // stores after which an earlier store is checked for completion
+      static_assert(NBUF >= 4 && NBUF <= 2 * Cfg::STAGES, "staging ring");
+      uint64_t* cbar = bars;
       const bool pull = p.ag_world > 1;
       const int copier = (int)blockIdx.x, n_copiers = n_copy;
       const long long row_bytes = pull ? (long long)p.K * 2 : (long long)p.N * 2;
       const long long tile_bytes = (long long)BM * row_bytes;
       const int chunks_per_tile = (int)((tile_bytes + CHUNK - 1) / CHUNK);
       const int tiles_per_rank = (pull ? p.ag_rows_per_rank : p.rs_rows_per_rank) / BM;
-      const int list_len = pull ? p.tiles_m : p.tiles_m - tiles_per_rank;   // push: remote row blocks only
-      const int first = pull ? p.ag_rank * tiles_per_rank : (p.rs_rank + 1) * tiles_per_rank;
+      // the list of 128-row tiles to move, in consumption order: every rank's rows but (push, or pull with the own
+      // shard already in place) this rank's own, starting behind them
+      const bool skip_own = !pull || p.ag_own_in_place;
+      const int list_len = skip_own ? p.tiles_m - tiles_per_rank : p.tiles_m;
+      const int first = (pull ? p.ag_rank + (skip_own ? 1 : 0) : p.rs_rank + 1) * tiles_per_rank;
       const int my_tiles = copier < list_len ? (list_len - copier + n_copiers - 1) / n_copiers : 0;
       const long long my_chunks = (long long)my_tiles * chunks_per_tile;
       const uint32_t ready_target = (uint32_t)p.tiles_n * 8u;   // 8 epilogue warps per output tile
       // chunk g of this CTA: tile g / chunks_per_tile of its list (consumption order), piece g % chunks_per_tile
+      // (32-bit arithmetic: this thread is one serial instruction stream and 64-bit divisions cost it hundreds of cycles)
       auto locate = [&](long long g, int& m_blk, long long& off, uint32_t& bytes) {
-        const int mi = copier + (int)(g / chunks_per_tile) * n_copiers;
+        const uint32_t q = (uint32_t)g / (uint32_t)chunks_per_tile, r = (uint32_t)g - q * (uint32_t)chunks_per_tile;
+        const int mi = copier + (int)q * n_copiers;
         m_blk = (mi + first) % p.tiles_m;
-        off = (g % chunks_per_tile) * (long long)CHUNK;
+        off = (long long)r * CHUNK;
         bytes = (uint32_t)((tile_bytes - off) < CHUNK ? (tile_bytes - off) : CHUNK);
       };
       auto block_ready = [&](int m_blk) {
@@ -123,9 +139,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(p.rs_ready + m_blk) : "memory");
         return f >= ready_target;
       };
+      // pull: tile t of this CTA's list is complete in the gathered buffer -> its flag
+      auto publish_tile = [&](long long t) {
+        const int m_blk = (copier + (int)t * n_copiers + first) % p.tiles_m;
+        fence_proxy_async_global();
+        __threadfence();
+        asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p.ag_flags + m_blk), "r"(1u) : "memory");
+      };
       // Loads run ahead of the stores, across tile boundaries.  A staging buffer is free for the next load once
-      // the bulk store that drained it has READ it (wait_group.read), not once its writes have landed.
-      long long loaded = 0, stored = 0;
+      // the bulk store that drained it has READ it (wait_group.read), not once its writes have landed; whether a
+      // tile's stores have landed is looked at LAG stores later, so nothing is waited for right after it was issued.
+      long long loaded = 0, stored = 0, published = 0;
       long long ready_upto = pull ? my_chunks : 0;   // chunks below this index belong to blocks known to be complete
       bool ok = true;
       while (stored < my_chunks && ok) {
@@ -157,33 +181,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const char* src =
               pull ? reinterpret_cast<const char*>(p.ag_src[m_blk / tiles_per_rank]) + (long long)(m_blk % tiles_per_rank) * tile_bytes + off
                    : reinterpret_cast<const char*>(p.C) + (long long)m_blk * tile_bytes + off;
-          mbar_expect_tx(&copy_bar[buf], bytes);
-          bulk_load_1d(smem + buf * CHUNK, src, bytes, &copy_bar[buf]);
+          mbar_expect_tx(&cbar[buf], bytes);
+          bulk_load_1d(smem + buf * CHUNK, src, bytes, &cbar[buf]);
           ++loaded;
         }
         if (!ok || stored == loaded) continue;
         int m_blk; long long off; uint32_t bytes;
         locate(stored, m_blk, off, bytes);
         const int buf = (int)(stored % NBUF);
-        if (!mbar_wait(&copy_bar[buf], (uint32_t)((stored / NBUF) & 1), abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+        if (!mbar_wait(&cbar[buf], (uint32_t)((stored / NBUF) & 1), abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
         char* dst = pull ? reinterpret_cast<char*>(p.ag_gathered) + (long long)m_blk * tile_bytes + off
                          : reinterpret_cast<char*>(p.rs_dst[m_blk / tiles_per_rank]) + p.rs_rank * p.rs_slot_stride * 2 +
                                (long long)(m_blk % tiles_per_rank) * tile_bytes + off;
         bulk_store_1d(dst, smem + buf * CHUNK, bytes);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         ++stored;
-        if (pull && stored % chunks_per_tile == 0) {
-          // tile complete: its writes must have landed before the flag is published (loads stay in flight meanwhile)
-          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-          fence_proxy_async_global();
-          __threadfence();
-          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ag_flags + m_blk), "r"(1u) : "memory");
-        } else {
-          asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
+        asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
+        if (pull) {
+          // tiles whose last store is at least LAG stores old: those stores have landed after this wait
+          while ((published + 1) * chunks_per_tile + LAG <= stored) {
+            asm volatile("cp.async.bulk.wait_group %0;" ::"n"(LAG) : "memory");
+            publish_tile(published++);
+          }
         }
       }
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-      if (!pull) {
+      if (pull) {
+        while (ok && (published + 1) * chunks_per_tile <= stored) publish_tile(published++);
+      } else {
         fence_proxy_async_global();
         __threadfence_system();   // pushed blocks are visible to their owners before the cross-GPU barrier that follows
       }
@@ -200,13 +225,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int u = cta; u < p.total_units && ok; u += n_compute) {
         const Unit w = decode_unit(p, u);
         const int m0 = w.m_blk * BM, n0 = w.n_blk * BN;
-        if (p.ag_world > 1) {
+        if (p.ag_world > 1 && !(p.ag_own_in_place && w.m_blk / (p.ag_rows_per_rank / BM) == p.ag_rank)) {
           // the row block must have been gathered: bounded spin on its flag, then order the async proxy after it
           const long long t0 = clock64();
           uint32_t f = 0;
           for (;;) {
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(p.ag_flags + w.m_blk) : "memory");
-            if (f != 0) break;
+            if (f >= p.ag_flag_target) break;
             if (*abort_flag || clock64() - t0 > INCIN_WAIT_CLOCKS) {
               *abort_flag = 1;
               if (p.status) atomicCAS(p.status, 0, kStatusTimeoutPeer);
@@ -244,7 +269,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           }
           __syncwarp();
-          if (++stage == Cfg::STAGES) {
+          if (++stage == n_stages) {
             stage = 0;
             phase ^= 1;
           }
@@ -304,7 +329,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
             if (leader) umma_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
             __syncwarp();
-            if (++stage == Cfg::STAGES) {
+            if (++stage == n_stages) {
               stage = 0;
               phase ^= 1;
             }
@@ -315,6 +340,132 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (p.in_kind == 0) issue_all(std::integral_constant<int, 0>{});
       else if (p.in_kind == 1) issue_all(std::integral_constant<int, 1>{});
       else issue_all(std::integral_constant<int, 2>{});
+    }
+  } else if (warp == GEMM_COPY_WARP) {
+    // ------------------------------------------------------------- copy warp (fused collectives, copy-warp mode)
+    // One lane of one extra warp in EVERY compute CTA moves a share of the collective's data in 8 KB bulk copies
+    // global -> shared -> global.  What one SM can have in flight towards a peer is small (a dedicated copy CTA with
+    // a 200 KB ring moves about 26 GB/s); spread over all SMs the same transfers need only a few operand stages of
+    // shared memory per SM and take no SM away from the tensor-core work, and each byte still crosses NVLink once.
+    //   all-gather:     chunk g of the tile list (consumption order) is pulled by CTA g % grid; a tile's flag counts
+    //                   its completed chunks and the producer warps wait for ag_flag_target of them;
+    //   reduce-scatter: chunk g of the list of remote row blocks is pushed by CTA g % grid once the block is complete
+    //                   in the local staging buffer (rs_ready).
+    // The ring is two halves: while the stores of one batch drain one half, the loads of the next batch fill the
+    // other; completion (and the flags of a batch) is checked one batch late, so no copy is waited for right after it
+    // was issued.  The warp waits only for its own copies and for epilogue counters, never for another copy warp, and
+    // nothing but the producers' flag wait depends on it.
+    if (p.copy_warps && lane == 0) {
+      uint8_t* ring = smem + n_stages * Cfg::STAGE_BYTES;
+      const int half_chunks = (Cfg::STAGES - n_stages) * Cfg::STAGE_BYTES / (2 * CW_CHUNK);
+      const bool pull = p.ag_world > 1;
+      const long long row_bytes = pull ? (long long)p.K * 2 : (long long)p.N * 2;
+      const long long tile_bytes = (long long)BM * row_bytes;
+      const int chunks_per_tile = (int)((tile_bytes + CW_CHUNK - 1) / CW_CHUNK);
+      const int tiles_per_rank = (pull ? p.ag_rows_per_rank : p.rs_rows_per_rank) / BM;
+      const bool skip_own = !pull || p.ag_own_in_place;     // push, or pull with the own shard already in place
+      const int list_len = skip_own ? p.tiles_m - tiles_per_rank : p.tiles_m;
+      const int first = (pull ? p.ag_rank + (skip_own ? 1 : 0) : p.rs_rank + 1) * tiles_per_rank;
+      const long long total = (long long)list_len * chunks_per_tile;
+      const long long n_mine = cta < total ? (total - cta + n_compute - 1) / n_compute : 0;
+      const long long n_batches = (n_mine + half_chunks - 1) / half_chunks;
+      const uint32_t ready_target = (uint32_t)p.tiles_n * 8u;   // 8 epilogue warps per output tile
+      // 32-bit arithmetic on purpose: this lane is one serial instruction stream and a 64-bit division costs it
+      // hundreds of cycles (total < 2^31 is checked on the host)
+      auto locate = [&](long long i, int& m_blk, long long& off, uint32_t& bytes) {
+        const uint32_t g = (uint32_t)cta + (uint32_t)i * (uint32_t)n_compute;
+        const uint32_t q = g / (uint32_t)chunks_per_tile, r = g - q * (uint32_t)chunks_per_tile;
+        uint32_t m = q + (uint32_t)first;
+        if (m >= (uint32_t)p.tiles_m) m -= (uint32_t)p.tiles_m;
+        m_blk = (int)m;
+        off = (long long)r * CW_CHUNK;
+        bytes = (uint32_t)((tile_bytes - off) < CW_CHUNK ? (tile_bytes - off) : CW_CHUNK);
+      };
+      int ready_blk = -1;       // push: the last block seen complete
+      // loads of batch k into half k & 1 (push: once every block the batch touches is complete in the staging buffer)
+      auto issue_loads = [&](long long k) -> bool {
+        const long long i0 = k * half_chunks, i1 = (i0 + half_chunks < n_mine) ? i0 + half_chunks : n_mine;
+        uint32_t sum = 0;
+        for (long long i = i0; i < i1; ++i) {
+          int m_blk; long long off; uint32_t bytes;
+          locate(i, m_blk, off, bytes);
+          sum += bytes;
+          if (!pull && m_blk != ready_blk) {
+            const long long t0 = clock64();
+            for (;;) {
+              uint32_t f;
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(f) : "l"(p.rs_ready + m_blk) : "memory");
+              if (f >= ready_target) break;
+              if (*abort_flag || clock64() - t0 > INCIN_WAIT_CLOCKS) {
+                *abort_flag = 1;
+                if (p.status) atomicCAS(p.status, 0, kStatusTimeoutPeer);
+                return false;
+              }
+              __nanosleep(200);
+            }
+            ready_blk = m_blk;
+          }
+        }
+        if (!pull) fence_proxy_async_global();   // the blocks were written with ordinary stores; the bulk loads come after
+        uint64_t* bar = &cw_bar[k & 1];
+        uint8_t* half = ring + (k & 1) * half_chunks * CW_CHUNK;
+        mbar_expect_tx(bar, sum);
+        for (long long i = i0; i < i1; ++i) {
+          int m_blk; long long off; uint32_t bytes;
+          locate(i, m_blk, off, bytes);
+          const char* src =
+              pull ? reinterpret_cast<const char*>(p.ag_src[m_blk / tiles_per_rank]) + (long long)(m_blk % tiles_per_rank) * tile_bytes + off
+                   : reinterpret_cast<const char*>(p.C) + (long long)m_blk * tile_bytes + off;
+          bulk_load_1d(half + (i - i0) * CW_CHUNK, src, bytes, bar);
+        }
+        return true;
+      };
+      // all-gather: the chunks of batch k have landed in the gathered buffer.  One fence orders all of them before
+      // the counts (a fence costs this thread more than a microsecond while the epilogue warps of its SM are storing,
+      // so there is exactly one per batch and the counts themselves are relaxed).
+      auto publish = [&](long long k) {
+        const long long i0 = k * half_chunks, i1 = (i0 + half_chunks < n_mine) ? i0 + half_chunks : n_mine;
+        fence_proxy_async_global();
+        __threadfence();
+        for (long long i = i0; i < i1; ++i) {
+          int m_blk; long long off; uint32_t bytes;
+          locate(i, m_blk, off, bytes);
+          asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(p.ag_flags + m_blk), "r"(1u) : "memory");
+        }
+      };
+      bool ok = n_batches > 0 ? issue_loads(0) : true;
+      long long done = 0;       // batches whose stores have been issued
+      for (long long k = 0; k < n_batches && ok; ++k) {
+        if (!mbar_wait(&cw_bar[k & 1], (uint32_t)((k >> 1) & 1), abort_flag, p.status, kStatusTimeoutFull)) { ok = false; break; }
+        const long long i0 = k * half_chunks, i1 = (i0 + half_chunks < n_mine) ? i0 + half_chunks : n_mine;
+        uint8_t* half = ring + (k & 1) * half_chunks * CW_CHUNK;
+        for (long long i = i0; i < i1; ++i) {
+          int m_blk; long long off; uint32_t bytes;
+          locate(i, m_blk, off, bytes);
+          char* dst = pull ? reinterpret_cast<char*>(p.ag_gathered) + (long long)m_blk * tile_bytes + off
+                           : reinterpret_cast<char*>(p.rs_dst[m_blk / tiles_per_rank]) + p.rs_rank * p.rs_slot_stride * 2 +
+                                 (long long)(m_blk % tiles_per_rank) * tile_bytes + off;
+          bulk_store_1d(dst, half + (i - i0) * CW_CHUNK, bytes);
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        done = k + 1;
+        if (k + 1 < n_batches) {
+          // the other half is free once the stores of batch k - 1 have read it
+          if (k >= 1) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          ok = issue_loads(k + 1);
+        }
+        if (pull && k >= 1) {
+          asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");   // batch k - 1 has landed (batch k stays in flight)
+          publish(k - 1);
+        }
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      if (pull) {
+        if (done >= 1) publish(done - 1);
+      } else {
+        fence_proxy_async_global();
+        __threadfence_system();   // pushed blocks are visible to their owners before the cross-GPU barrier that follows
+      }
     }
   } else {
     // ------------------------------------------------------------- epilogue (8 warps: 4 lane quarters x 2 column halves)
@@ -481,7 +632,7 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtens
   if (!ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, attr_set)) return INCIN_ERR_LAUNCH;
   int grid = p.total_units < max_ctas ? p.total_units : max_ctas;
   GemmKernelParams q = p;
-  if (p.ag_world > 1 || p.rs_push) {
+  if ((p.ag_world > 1 || p.rs_push) && !p.copy_warps) {
     int copy = p.gemm_ctas;   // the caller's request for copy CTAs travels in gemm_ctas until here
     if (copy < 1) copy = 8;
     if (copy > max_ctas / 2) copy = max_ctas / 2;
@@ -492,7 +643,7 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const CUtens
   }
   // fused-collective launches wait on other GPUs: those stay ordinary launches
   if (q.ag_world > 1 || q.rs_world > 1) {
-    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, tc, tx, q);
+    kern<<<grid, q.copy_warps ? GEMM_THREADS_COPY : GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, tc, tx, q);
     return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
   }
   return launch_pdl<true>(kern, dim3(grid), dim3(GEMM_THREADS), Cfg::SMEM_BYTES, stream, ta, tb, tc, tx, q) == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
@@ -710,6 +861,7 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   p.status = reinterpret_cast<int*>(d->status);
   p.in_kind = in_kind;
   p.ag_world = d->ag_world > 1 ? d->ag_world : 0;
+  p.ag_own_in_place = 0;
   p.ag_rank = d->ag_rank;
   p.ag_rows_per_rank = d->ag_rows_per_rank;
   p.gemm_ctas = d->ag_world > 1 ? d->ag_copy_ctas : d->rs_copy_ctas;
@@ -720,7 +872,12 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   p.rs_rows_per_rank = d->rs_rows_per_rank;
   p.rs_slot_stride = d->rs_slot_stride;
   p.rs_ready = reinterpret_cast<uint32_t*>(d->rs_ready);
-  p.rs_push = (p.rs_world && d->rs_copy_ctas > 0 && d->rs_ready) ? 1 : 0;
+  p.rs_push = (p.rs_world && d->rs_copy_ctas != 0 && d->rs_ready) ? 1 : 0;
+  // a negative count of copy CTAs asks for copy warps: one extra warp in every compute CTA moves the data
+  // (-n: n operand stages of shared memory become the copy ring; at least three stages stay with the GEMM)
+  p.copy_warps = p.ag_world ? (d->ag_copy_ctas < 0 ? -d->ag_copy_ctas : 0) : ((p.rs_push && d->rs_copy_ctas < 0) ? -d->rs_copy_ctas : 0);
+  p.ag_flag_target = 1;
+  if (p.ag_world && p.copy_warps) p.ag_flag_target = (uint32_t)(((long long)BM * d->K * 2 + 8 * 1024 - 1) / (8 * 1024));
   for (int r = 0; r < 8; ++r) {
     p.ag_src[r] = reinterpret_cast<const __nv_bfloat16*>(d->ag_src[r]);
     p.rs_dst[r] = reinterpret_cast<__nv_bfloat16*>(d->rs_dst[r]);
@@ -729,8 +886,10 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
     if (p.ag_world > 8 || d->a_mn_major || d->lda != d->K || (d->K % 8) || p.ag_rows_per_rank % BM ||
         d->M != p.ag_world * p.ag_rows_per_rank || !p.ag_flags || splits != 1 || blo * bhi != 1)
       return INCIN_ERR_ARGUMENT;
+    // a NULL source for this rank's own shard: the caller has already placed those rows in the gathered buffer
+    p.ag_own_in_place = p.ag_src[p.ag_rank] ? 0 : 1;
     for (int r = 0; r < p.ag_world; ++r)
-      if (!p.ag_src[r]) return INCIN_ERR_ARGUMENT;
+      if (!p.ag_src[r] && r != p.ag_rank) return INCIN_ERR_ARGUMENT;
   }
   if (p.rs_world) {
     if (p.rs_world > 8 || d->out_fp32 || p.rs_rows_per_rank % BM || d->M != p.rs_world * p.rs_rows_per_rank ||
@@ -773,6 +932,13 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
     }
   }
 
+  if (p.copy_warps) {
+    // the copy warps index chunks with 32-bit arithmetic
+    if ((long long)p.tiles_m * (((long long)BM * (p.ag_world ? d->K : d->N) * 2 + 8191) / 8192) > 0x3fffffffLL) return INCIN_ERR_ARGUMENT;
+    const int stages = (224 * 1024 - ((p.tma_out || bn == 256) ? 32 * 1024 : 0)) / ((BM + bn) * BK * 2);
+    if (p.copy_warps > stages - 3) p.copy_warps = stages - 3;
+    if (p.copy_warps < 1) return INCIN_ERR_ARGUMENT;
+  }
   const bool amn = d->a_mn_major != 0, bmn = d->b_mn_major != 0;
   if (pair) return incin::launch_pair(amn, bmn, ta, tb, tc, tx, p, tiles_m2, sms, stream);
   int rc2;

@@ -128,10 +128,11 @@ def _tuned_tile_n(kw: dict) -> int:
     svc = service()
     if svc.policy in (TuningPolicy.DISABLED, TuningPolicy.HEURISTIC) and not svc.lru:
         return 0
-    if torch.cuda.is_current_stream_capturing():
-        return 0
     key = (f"gemm/{kw['M']}x{kw['N']}x{kw['K']}/{int(kw['a_mn'])}{int(kw['b_mn'])}/b{kw['batch'][0] * kw['batch'][1]}"
            f"/e{kw['act']}{int(kw['bias'] is not None)}{int(kw['residual'] is not None)}")
+    if torch.cuda.is_current_stream_capturing():   # nothing can be timed inside a capture: use what warm-up found
+        rec = svc.lookup(key)
+        return rec.best["tile_n"] if rec is not None else 0
 
     def measure(params):
         args = {k: kw[k] for k in ("M", "N", "K", "lda", "ldb", "ldc", "a_mn", "b_mn", "batch", "a_strides", "b_strides",

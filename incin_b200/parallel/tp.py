@@ -22,6 +22,8 @@ ncclAllGather / ncclAllReduce plus separate SGEMMs and reshapes (crates/incin-ba
 """
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 
 import torch
@@ -107,10 +109,17 @@ class TensorParallel:
     GEMM_TFLOPS = 1200.0
 
     def _copy_ctas(self, copy_bytes: float, link_bytes: float, flops: float) -> int:
-        """Number of CTAs of the fused launch that copy instead of computing: the count that minimises
-        ``max(copy time, link time, GEMM time on the remaining SMs)``."""
+        """Who moves the data of a fused launch.  By default the number of CTAs of the launch that copy instead of
+        computing: the count that minimises ``max(copy time, link time, GEMM time on the remaining SMs)``.  Negative
+        (``INCIN_TP_COPY=warps``): one extra warp in every compute CTA moves the data and no SM is taken from the
+        tensor-core work; the value is minus the number of operand stages of shared memory that become the copy ring.
+        Measured between two B200s the copy warps lose: a bulk store to a peer that waits for link credits holds up
+        the operand loads of its own SM behind it (GEMM -> reduce-scatter 0.53 ms against 0.17 ms with copy CTAs),
+        so dedicated CTAs, which keep that back-pressure on SMs that do nothing else, stay the default."""
         if self.copy_ctas:
             return self.copy_ctas
+        if os.environ.get("INCIN_TP_COPY", "ctas") == "warps":
+            return -max(1, int(os.environ.get("INCIN_TP_COPY_STAGES", "2")))   # operand stages that become the copy ring
         best, best_t = 8, float("inf")
         for c in range(4, 73, 4):
             t = max(copy_bytes / (c * self.COPY_CTA_GBS * 1e9), link_bytes / (self.LINK_GBS * 1e9),
@@ -150,13 +159,18 @@ class TensorParallel:
         M = Ml * self.world
         N = w.shape[1] if b_mn else w.shape[0]
         gathered = torch.empty(M, Kd, dtype=torch.bfloat16, device=self.device)
+        # this rank's own rows go into place with one local copy; the fused launch moves only the peers' shards
+        gathered[self.rank * Ml:(self.rank + 1) * Ml].copy_(x_shard)
+        src = list(buf.ptrs)
+        src[self.rank] = 0
         flags = torch.zeros(M // 128, dtype=torch.int32, device=self.device)
         if out is None:
             out = torch.empty(M, N, dtype=torch.bfloat16, device=self.device)
             ldc = N
         G.gemm(gathered, w, out, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=ldc, b_mn=b_mn, c_offset=c_offset,
-               gather={"world": self.world, "rank": self.rank, "rows_per_rank": Ml, "src": buf.ptrs, "flags": flags,
-                       "copy_ctas": self._copy_ctas(M * Kd * 2, (self.world - 1) * Ml * Kd * 2, 2.0 * M * N * Kd)})
+               gather={"world": self.world, "rank": self.rank, "rows_per_rank": Ml, "src": src, "flags": flags,
+                       "copy_ctas": self._copy_ctas((self.world - 1) * Ml * Kd * 2, (self.world - 1) * Ml * Kd * 2,
+                                                    2.0 * M * N * Kd)})
         return out, gathered
 
     def gemm_scatter(self, a: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False,

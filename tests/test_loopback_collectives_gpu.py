@@ -23,7 +23,8 @@ def _bf16(shape, seed, scale=1.0):
 
 @pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 3), (8, 5)])
 @pytest.mark.parametrize("b_mn", [False, True])
-def test_all_gather_gemm_with_local_peers(world, rank, b_mn):
+@pytest.mark.parametrize("copy_ctas", [6, -1, -2])  # > 0: dedicated copy CTAs; -n: one copy warp in every compute CTA, n stages as ring
+def test_all_gather_gemm_with_local_peers(world, rank, b_mn, copy_ctas):
     from incin_b200.ops import gemm as G
     Ml, Kd, N = 256, 512, 384
     shards = [_bf16((Ml, Kd), 10 + r) for r in range(world)]
@@ -32,19 +33,31 @@ def test_all_gather_gemm_with_local_peers(world, rank, b_mn):
     gathered = torch.zeros(M, Kd, dtype=torch.bfloat16, device="cuda")
     flags = torch.zeros(M // 128, dtype=torch.int32, device="cuda")
     out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    src = [s.data_ptr() for s in shards]
+    own_in_place = b_mn          # half of the cases: the caller has put this rank's own rows into place (NULL source)
+    if own_in_place:
+        gathered[rank * Ml:(rank + 1) * Ml].copy_(shards[rank])
+        src[rank] = 0
     G.gemm(gathered, w, out, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=N, b_mn=b_mn,
-           gather={"world": world, "rank": rank, "rows_per_rank": Ml, "src": [s.data_ptr() for s in shards],
-                   "flags": flags, "copy_ctas": 6})
+           gather={"world": world, "rank": rank, "rows_per_rank": Ml, "src": src,
+                   "flags": flags, "copy_ctas": copy_ctas})
     G.check_status()
     full = torch.cat(shards, 0)
-    assert torch.equal(gathered, full)                       # the copy CTAs assembled every shard
-    assert int(flags.min()) == 1                             # and published every 128-row tile
+    assert torch.equal(gathered, full)                       # the copiers assembled every shard
+    # and published every 128-row tile: one flag per tile, or (copy warps) one count per 8 KB chunk of it
+    done = 1 if copy_ctas > 0 else (128 * Kd * 2 + 8191) // 8192
+    peers = torch.ones(M // 128, dtype=torch.bool)
+    if own_in_place:
+        peers[rank * Ml // 128:(rank + 1) * Ml // 128] = False          # own tiles are neither copied nor flagged
+        assert int(flags.cpu()[~peers].max()) == 0
+    assert int(flags.cpu()[peers].min()) == done and int(flags.cpu()[peers].max()) == done
     ref = full.float() @ (w.float() if b_mn else w.float().t())
     check_close(out, ref, rtol=1.6e-2, atol_rms=1.5e-2, what=f"all-gather gemm world {world}")
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("copy_ctas", [0, 6])     # 0: epilogue stores straight into the owners' slots; >0: pushed by copy CTAs
+@pytest.mark.parametrize("copy_ctas", [0, 6, -1, -2])  # 0: epilogue stores straight into the owners' slots; > 0: pushed by
+                                                       # copy CTAs; -n: pushed by one copy warp in every compute CTA
 def test_gemm_reduce_scatter_with_local_owners(world, copy_ctas):
     from incin_b200 import _native as nat
     from incin_b200.ops import gemm as G
