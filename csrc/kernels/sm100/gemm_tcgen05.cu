@@ -519,8 +519,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&tempty_bar[acc]);
-        if (p.rs_push) {   // this warp's part of the tile is in the staging buffer: count it for the copy CTAs
-          __threadfence();
+        if (p.rs_push) {
+          // this warp's part of the tile is in the staging buffer: count it for the copiers.  The release of the
+          // count orders the warp's stores (made visible to this lane by the __syncwarp above) before it; a separate
+          // fence in front of it showed up as a fifth of all warp stalls of this launch.
           asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.rs_ready + w.m_blk), "r"(1u) : "memory");
         }
       }

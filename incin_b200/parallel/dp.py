@@ -110,7 +110,9 @@ class FusedReducer:
         """What this reducer does, for benchmark records (valid once the buffers have been allocated)."""
         mc_g = getattr(getattr(self, "grad_buf", None), "mc_ptr", 0)
         mc_s = getattr(getattr(self, "shadow_buf", None), "mc_ptr", 0)
-        how = (("in-switch multimem.ld_reduce of the owned gradient slice" if mc_g else "P2P loads of the owned gradient slice") + " + " +
+        staged = getattr(self, "grad_stage", None) is not None
+        how = (("in-switch multimem.ld_reduce of the owned gradient slice" + (" from a multicast-bound copy of the gradients" if staged else "")
+                if (mc_g or staged) else "P2P loads of the owned gradient slice") + " + " +
                ("one multimem.st of the new weights through NVSwitch" if mc_s else "P2P stores of the new weights"))
         when = "overlapped with backward" if self.overlap else "after backward"
         return f"fused reduce-scatter + AdamW + all-gather, one kernel per bucket ({how}), {when}"
@@ -124,7 +126,9 @@ class FusedReducer:
         # kernels' fp32 accumulation into multicast-bound memory (split-K reduce-adds, norm and bias gradients) runs
         # markedly slower than into ordinary device memory, which costs far more than the in-switch reduction of
         # 1/world of the gradients saves.  So only the parameter buffer is bound by default (one multimem.st instead
-        # of world - 1 peer stores per 16 bytes); INCIN_MULTIMEM_BUFFERS=grad,shadow binds both.
+        # of world - 1 peer stores per 16 bytes); INCIN_MULTIMEM_BUFFERS=grad,shadow binds both.  "stage" keeps the
+        # gradients in ordinary memory and copies each bucket into a multicast-bound buffer right before its reduction
+        # (one extra local pass over the gradients buys the in-switch reduction: world - 1 times fewer inbound bytes).
         which = os.environ.get("INCIN_MULTIMEM_BUFFERS", "shadow")
         if self.multimem and (("grad" in which) if dtype == torch.float32 else ("shadow" in which)):
             from .symm import MulticastBuffer
@@ -159,6 +163,12 @@ class FusedReducer:
         for b in (shadow_buf, grad_buf, self.pad):
             b.exchange(self.group, session=self.session, ranks=self.ranks)
         self.shadow_buf, self.grad_buf = shadow_buf, grad_buf
+        self.grad_stage = None
+        import os
+        if self.multimem and "stage" in os.environ.get("INCIN_MULTIMEM_BUFFERS", "shadow") and not getattr(grad_buf, "mc_ptr", 0):
+            from .symm import MulticastBuffer
+            self.grad_stage = MulticastBuffer(store.grad.numel() * 4, self.device).exchange(self.group, session=self.session)
+            self._stage_view = self.grad_stage.typed(torch.float32, store.grad.numel())
         self._descs = [self._make_desc(i, lo, hi) for i, (lo, hi) in enumerate(self.buckets)]
         # readiness bookkeeping: a bucket is ready when every parameter overlapping it is complete
         self._entry_buckets: dict[int, list[int]] = {}
@@ -204,7 +214,13 @@ class FusedReducer:
             lo, hi = self.buckets[i]
             self.lane.launch(tag=i, kind=CollectiveKind.all_reduce(Reduction.MEAN), elements=hi - lo, dtype=DTypeId.F32)
         if self.multimem:
-            nat.check(nat.cuda().incin_dp_reduce_adamw_mc(C.byref(self._descs[i]), getattr(self.grad_buf, "mc_ptr", None),
+            mc_g = getattr(self.grad_buf, "mc_ptr", None)
+            if self.grad_stage is not None:
+                lo, hi = self.buckets[i]
+                with torch.cuda.stream(stream):
+                    self._stage_view[lo:hi].copy_(self.store.grad[lo:hi])
+                mc_g = self.grad_stage.mc_ptr
+            nat.check(nat.cuda().incin_dp_reduce_adamw_mc(C.byref(self._descs[i]), mc_g,
                                                           getattr(self.shadow_buf, "mc_ptr", None), stream.cuda_stream),
                       "dp_reduce_adamw_mc")
         else:

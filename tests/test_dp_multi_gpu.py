@@ -26,12 +26,15 @@ def test_fused_dp_matches_nccl_baseline():
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
-def test_fused_dp_over_nvswitch_multicast_matches_nccl_baseline():
-    """The same worker with NVLS left on: gradient / parameter buffers are bound to a multicast object and the kernel
-    reduces with multimem.ld_reduce and broadcasts with multimem.st.  No rank leaves in this test."""
+@pytest.mark.parametrize("buffers", ["shadow", "shadow,stage", "grad,shadow"])
+def test_fused_dp_over_nvswitch_multicast_matches_nccl_baseline(buffers):
+    """The same worker with NVLS left on.  ``shadow``: the parameter buffer is bound to a multicast object and the new
+    weights leave through multimem.st; ``stage``: each gradient bucket is also copied into a multicast-bound buffer and
+    reduced in the switch with multimem.ld_reduce; ``grad``: the gradient buffer itself is bound.  No rank leaves."""
     n = min(torch.cuda.device_count(), 4)
     env = {k: v for k, v in os.environ.items() if k != "NCCL_NVLS_ENABLE"}
     env["INCIN_TEST_EXPECT_MULTIMEM"] = "1"
+    env["INCIN_MULTIMEM_BUFFERS"] = buffers
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", "29641", os.path.join(HERE, "dp_worker.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
