@@ -125,6 +125,56 @@ class CudaBackend(Backend):
         return torch.device("cuda", self.index)
 
 
+class NumpyBackend(Backend):
+    """An EXTERNAL library held to the same contract: the op table mapped onto NumPy, with a capability table of its
+    own (fp32 only, a subset of the ops).  This is the role of the reference's Candle adapter
+    (crates/incin-backends/src/external/: a third-party tensor library behind the backend traits, admitted through the
+    conformance suite): what it does not claim is skipped, what it claims must match the fp32 CPU reference."""
+    kind, name = DeviceKind.CPU, "numpy"
+
+    def __init__(self):
+        import numpy as np
+        from .core.spec import CapabilityRegistry, CapabilityRule
+        f32 = (DTypeId.F32,)
+        claimed = ("matmul", "addmm", "add", "sub", "mul", "div", "unary", "softmax", "layer_norm", "rms_norm", "sum",
+                   "mean", "max", "min", "argmax", "cumsum", "concat", "transpose", "index_select", "embedding")
+        self.registry = CapabilityRegistry(DeviceKind.CPU, [CapabilityRule(op, f32, SupportLevel.NATIVE, "numpy") for op in claimed])
+        n = lambda t: t.detach().cpu().numpy() if isinstance(t, torch.Tensor) else t
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a)) if isinstance(a, np.ndarray) else torch.as_tensor(a)
+
+        def softmax(x, dim=-1):
+            e = np.exp(x - x.max(axis=dim, keepdims=True))
+            return e / e.sum(axis=dim, keepdims=True)
+
+        def layer_norm(x, g, b=None, eps=1e-5):
+            mu, var = x.mean(-1, keepdims=True), x.var(-1, keepdims=True)
+            y = (x - mu) / np.sqrt(var + eps) * g
+            return y if b is None else y + b
+
+        erf = np.vectorize(__import__("math").erf, otypes=[np.float32])
+        unary = {"relu": lambda x: np.maximum(x, 0), "exp": np.exp, "log": np.log, "tanh": np.tanh, "sqrt": np.sqrt,
+                 "abs": np.abs, "neg": np.negative, "sigmoid": lambda x: 1 / (1 + np.exp(-x)),
+                 "gelu": lambda x: 0.5 * x * (1 + erf(x * 0.70710678)), "silu": lambda x: x / (1 + np.exp(-x))}
+        table = {
+            "matmul": lambda a, b: a @ b, "addmm": lambda x, w, b: x @ w.T + b,
+            "add": np.add, "sub": np.subtract, "mul": np.multiply, "div": np.divide,
+            "unary": lambda x, name: unary[name](x), "softmax": softmax, "layer_norm": layer_norm,
+            "rms_norm": lambda x, g, eps=1e-5: x / np.sqrt((x * x).mean(-1, keepdims=True) + eps) * g,
+            "sum": lambda x, dim=None: x.sum(axis=dim), "mean": lambda x, dim=None: x.mean(axis=dim),
+            "max": lambda x, dim=None: x.max(axis=dim), "min": lambda x, dim=None: x.min(axis=dim),
+            "argmax": lambda x, dim=None: x.argmax(axis=dim), "cumsum": lambda x, dim: np.cumsum(x, axis=dim),
+            "concat": lambda ts, dim=0: np.concatenate(ts, axis=dim), "transpose": lambda x, a, b: np.swapaxes(x, a, b),
+            "index_select": lambda x, dim, idx: np.take(x, idx, axis=dim),
+            "embedding": lambda idx, w, pos=None: w[idx] if pos is None else w[idx] + pos[: idx.shape[-1]],
+        }
+        self.ops = {name: (lambda *a, _f=fn, **kw: t(_f(*[[n(u) for u in v] if isinstance(v, (list, tuple)) and v and
+                                                           isinstance(v[0], torch.Tensor) else n(v) for v in a], **kw)))
+                    for name, fn in table.items()}
+
+    def device(self):
+        return torch.device("cpu")
+
+
 class DummyBackend(Backend):
     """Shape-only execution on meta tensors: no storage, no kernels."""
     kind, name = DeviceKind.CPU, "dummy"
@@ -228,6 +278,31 @@ def _cases() -> list[Case]:
                  lambda x, k: torch.nn.functional.max_pool2d(x, k)),
             Case("concat", dt, lambda dev, d, a=g(4, 8), b=g(4, 3): ([a.to(dev, d), b.to(dev, d)], 1), Tolerance.EXACT,
                  lambda ts, dim: torch.cat(ts, dim)),
+            Case("add", dt, mk(g(32, 48), g(32, 48)), tol, torch.add),
+            Case("sub", dt, mk(g(32, 48), g(1, 48)), tol, torch.sub),                      # broadcast over rows
+            Case("mul", dt, mk(g(32, 48), g(32, 1)), tol, torch.mul),                      # broadcast over columns
+            Case("div", dt, lambda dev, d, a=g(32, 48), b=g(32, 48).abs() + 0.5: (a.to(dev, d), b.to(dev, d)), tol, torch.div),
+            Case("unary", dt, lambda dev, d, x=g(40, 72): (x.to(dev, d), "gelu"), tol, lambda x, n: torch.nn.functional.gelu(x)),
+            Case("unary", dt, lambda dev, d, x=g(40, 72): (x.to(dev, d), "tanh"), tol, lambda x, n: torch.tanh(x)),
+            Case("unary", dt, lambda dev, d, x=g(40, 72) * 0.5: (x.to(dev, d), "exp"), tol, lambda x, n: torch.exp(x)),
+            Case("softmax", dt, lambda dev, d, x=g(24, 200): (x.to(dev, d), -1), tol, lambda x, dim: torch.softmax(x, dim)),
+            Case("mean", dt, lambda dev, d, x=g(17, 130): (x.to(dev, d), 1), tol, lambda x, dim: x.mean(dim)),
+            Case("min", dt, mk(g(33, 257)), Tolerance.EXACT if dt is DTypeId.F32 else tol, lambda x: x.min()),
+            Case("argmax", dt, lambda dev, d, x=g(9, 120): (x.to(dev, d), 1), Tolerance.EXACT, lambda x, dim: x.argmax(dim)),
+            Case("avg_pool2d", dt, lambda dev, d, x=g(2, 3, 16, 16): (x.to(dev, d), 2), tol,
+                 lambda x, k: torch.nn.functional.avg_pool2d(x, k)),
+            Case("adaptive_avg_pool2d", dt, lambda dev, d, x=g(2, 3, 15, 10): (x.to(dev, d), (4, 3)), tol,
+                 lambda x, o: torch.nn.functional.adaptive_avg_pool2d(x, o)),
+            Case("conv2d", dt, mk(g(2, 8, 12, 12), g(16, 8, 3, 3) * 0.2, g(16)), tol,
+                 lambda x, w, b: torch.nn.functional.conv2d(x, w, b)),
+            Case("conv1d", dt, mk(g(2, 8, 40), g(16, 8, 3) * 0.2, g(16)), tol, lambda x, w, b: torch.nn.functional.conv1d(x, w, b)),
+            Case("conv_transpose2d", dt, mk(g(2, 8, 6, 6), g(8, 16, 3, 3) * 0.2, g(16)), tol,
+                 lambda x, w, b: torch.nn.functional.conv_transpose2d(x, w, b)),
+            Case("transpose", dt, lambda dev, d, x=g(6, 10): (x.to(dev, d), 0, 1), Tolerance.EXACT, lambda x, a, b: x.transpose(a, b)),
+            Case("index_select", dt, lambda dev, d, x=g(12, 16): (x.to(dev, d), 0, torch.tensor([3, 0, 11, 3]).to(dev)),
+                 Tolerance.EXACT, lambda x, dim, idx: x.index_select(dim, idx)),
+            Case("embedding", dt, lambda dev, d, w=g(50, 32): (torch.tensor([[1, 4, 49], [0, 0, 7]]).to(dev), w.to(dev, d)),
+                 Tolerance.EXACT if dt is DTypeId.F32 else tol, lambda idx, w: w[idx]),
         ]
     return out
 

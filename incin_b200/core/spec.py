@@ -241,7 +241,8 @@ CPU_CAPABILITIES: tuple[CapabilityRule, ...] = tuple(
     CapabilityRule(op, _ALL if op in ("reshape", "transpose", "concat", "gather", "index_select") else _F,
                    SupportLevel.NATIVE, "torch-cpu / libincin_host oracle")
     for op in ("matmul", "bmm", "addmm", "add", "sub", "mul", "div", "unary", "softmax", "layer_norm", "rms_norm",
-               "embedding", "cross_entropy", "sdpa", "conv2d", "max_pool2d", "avg_pool2d", "batch_norm", "sum", "mean",
+               "embedding", "cross_entropy", "sdpa", "conv1d", "conv2d", "conv_transpose2d", "max_pool2d", "avg_pool2d",
+               "adaptive_avg_pool2d", "batch_norm", "sum", "mean",
                "max", "min", "argmax", "topk", "argsort", "cumsum", "reshape", "transpose", "concat", "gather",
                "index_select", "adamw", "sgd", "rope", "swiglu", "dropout")
 ) + (CapabilityRule("quantize_q8_0", (DTypeId.F32,), SupportLevel.NATIVE, "libincin_host oracle"),
@@ -277,6 +278,9 @@ CUDA_CAPABILITIES: tuple[CapabilityRule, ...] = (
     CapabilityRule("dropout", _BF, SupportLevel.NATIVE, "philox dropout"),
     CapabilityRule("quantize_q8_0", (DTypeId.F32,), SupportLevel.NATIVE, "q8_0 quantize/dequantize"),
     CapabilityRule("conv2d", _BF, SupportLevel.COMPOSED, "im2col + gemm_tcgen05"),
+    CapabilityRule("conv1d", _BF, SupportLevel.COMPOSED, "im2col (height 1) + gemm_tcgen05"),
+    CapabilityRule("conv_transpose2d", _BF, SupportLevel.COMPOSED, "gemm_tcgen05 + col2im (gather, no atomics)"),
+    CapabilityRule("adaptive_avg_pool2d", _BF + (DTypeId.F32,), SupportLevel.NATIVE, "adaptive_avgpool2d fwd/bwd"),
     CapabilityRule("argmax", _BF + (DTypeId.F32,), SupportLevel.NATIVE, "reduce kernels (index output)"),
     CapabilityRule("cumsum", _BF + (DTypeId.F32,), SupportLevel.NATIVE, "block scan"),
     CapabilityRule("max_pool2d", _BF + (DTypeId.F32,), SupportLevel.NATIVE, "maxpool2d fwd (argmax kept) / gather bwd"),

@@ -202,6 +202,102 @@ def lower_group(g: Graph, group: FusionGroup):
     return expr(group.nodes[-1]), ext
 
 
+# ------------------------------------------------------------------------------------------------ row chains
+ROW_OPS = {"_softmax": "softmax", "softmax": "softmax", "_log_softmax": "log_softmax", "log_softmax": "log_softmax"}
+
+
+@dataclass
+class RowFusionGroup:
+    """A last-axis softmax / log-softmax with the pointwise nodes that feed it and follow it."""
+    pre: list[int]        # pointwise nodes before the row op (may be empty), topological order
+    row: int              # the row op's node id
+    post: list[int]       # pointwise nodes after it (may be empty)
+
+    @property
+    def nodes(self) -> list[int]:
+        return self.pre + [self.row] + self.post
+
+
+def row_fusion_pass(g: Graph) -> list[RowFusionGroup]:
+    """Around every last-axis softmax: the pointwise nodes whose only consumer lies inside the group (walking up from
+    the row op), and the single-consumer pointwise chain that follows it.  Every member has the row tensor's shape;
+    tensors entering from outside may also be ``[C]`` vectors (lowered to per-column operands)."""
+    cons = g.consumers()
+    out, taken = [], set()
+    for n in g.nodes:
+        kind = ROW_OPS.get(n.op)
+        if kind is None or not n.inputs or not n.shape:
+            continue
+        dim = (n.attrs.get("scalars") or [-1])[0]
+        if int(dim) not in (-1, len(n.shape) - 1):
+            continue
+        pre: list[int] = []
+        frontier = [n.inputs[0]]
+        while frontier:
+            nid = frontier.pop()
+            m = g.nodes[nid]
+            if m.op not in POINTWISE or m.shape != n.shape or nid in taken or nid in pre:
+                continue
+            if nid in g.outputs or any(c != n.id and c not in pre for c in cons[nid]):
+                continue                      # somebody outside the group needs this value: it stays materialised
+            pre.append(nid)
+            frontier.extend(m.inputs)
+        post, cur = [], n
+        while len(cons[cur.id]) == 1 and cur.id not in g.outputs:
+            c = g.nodes[cons[cur.id][0]]
+            if c.op not in POINTWISE or c.shape != n.shape or c.id in taken:
+                break
+            post.append(c.id)
+            cur = c
+        if pre or post:
+            grp = RowFusionGroup(sorted(pre), n.id, post)
+            taken.update(grp.nodes)
+            out.append(grp)
+    return out
+
+
+def lower_row_group(g: Graph, group: RowFusionGroup):
+    """-> ``(kind, pre expression, post expression, row-tensor node ids, column-vector node ids)`` for
+    :func:`incin_b200.codegen.fused_rows` (``Arg(i)`` = i-th row tensor, ``Col(i)`` = i-th vector)."""
+    from .codegen.pointwise import Arg, Binary, Const, Unary
+    from .codegen.rows import Col, Norm
+    row = g.nodes[group.row]
+    C = row.shape[-1]
+    rows_ext: list[int] = []
+    cols_ext: list[int] = []
+
+    def leaf(nid: int):
+        shape = tuple(g.nodes[nid].shape)
+        if shape == tuple(row.shape):
+            if nid not in rows_ext:
+                rows_ext.append(nid)
+            return Arg(rows_ext.index(nid))
+        if shape == (C,):
+            if nid not in cols_ext:
+                cols_ext.append(nid)
+            return Col(cols_ext.index(nid))
+        raise ValueError(f"operand %{nid} of shape {shape} is neither a row tensor {tuple(row.shape)} nor a [{C}] vector")
+
+    def build(nid: int, inside: set[int], norm_of: int | None):
+        if nid == norm_of:
+            return Norm()
+        if nid not in inside:
+            return leaf(nid)
+        n = g.nodes[nid]
+        ops = [build(i, inside, norm_of) for i in n.inputs] + [Const(float(s)) for s in n.attrs.get("scalars", [])]
+        if n.op in _UNARY and len(ops) == 1:
+            return Unary(_UNARY[n.op], ops[0])
+        if n.op in _BINARY and len(ops) == 2:
+            return Binary(_BINARY[n.op], ops[0], ops[1])
+        raise ValueError(f"cannot lower {n.op} with {len(ops)} operands")
+
+    pre = build(row.inputs[0], set(group.pre), None)
+    post = build(group.post[-1], set(group.post), group.row) if group.post else None
+    if not rows_ext:
+        raise ValueError("the chain reads no row tensor")
+    return ROW_OPS[row.op], pre, post, rows_ext, cols_ext
+
+
 # ------------------------------------------------------------------------------------------------ memory planning
 @dataclass
 class MemoryPlan:

@@ -115,3 +115,27 @@ def test_llama_single_gpu_matches_fp32_reference_and_trains():
     assert losses[-1] < losses[0] - 0.5, losses
     assert step.graph is not None, step.capture_error
     G.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_row_chain_fuser_matches_fp32_math(dtype):
+    """softmax / log-softmax / layer norm / rms norm with pointwise prologues and epilogues, one kernel each, against
+    the fp32 evaluation of the same chain; odd widths and more rows than warps in flight."""
+    from _tol import check_close
+    from incin_b200.codegen import Arg, Col, Norm, Scalar, Unary, fused_rows, reference_rows
+    g = torch.Generator().manual_seed(5)
+    for rows, C in ((37, 100), (4096, 768), (3, 2049)):
+        x = torch.randn(rows, C, generator=g).to(dtype).cuda()
+        r = torch.randn(rows, C, generator=g).to(dtype).cuda()
+        gain = (torch.rand(C, generator=g) + 0.5).to(dtype).cuda()
+        bias = torch.randn(C, generator=g).to(dtype).cuda()
+        chains = [("softmax", Arg(0) * Scalar(0) + Col(0), None, [x], [bias], [0.125]),
+                  ("log_softmax", Arg(0) + Arg(1), None, [x, r], [], []),
+                  ("layer_norm", Arg(0) + Arg(1), Norm() * Col(0) + Col(1), [x, r], [gain, bias], []),
+                  ("rms_norm", Arg(0), Unary("gelu", Norm() * Col(0)), [x], [gain], [])]
+        for kind, pre, post, rin, cols, sc in chains:
+            got = fused_rows(kind, pre, rin, post=post, cols=cols, scalars=sc)
+            want = reference_rows(kind, pre, rin, post=post, cols=cols, scalars=sc)
+            assert got.dtype == dtype and got.shape == x.shape
+            tol = dict(rtol=2e-2, atol_rms=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-3, atol_rms=1e-3)
+            check_close(got, want, what=f"{kind} {rows}x{C} {dtype}", **tol)

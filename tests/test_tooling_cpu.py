@@ -299,6 +299,14 @@ def test_backends_dispatch_dummy_and_conformance():
             from incin_b200.core.spec import SupportLevel
             return SupportLevel.UNSUPPORTED
     assert all(r.status == "skipped" for r in run_conformance(Claimless()))
+    # an external library behind the same contract: what it claims must pass, what it does not claim is skipped
+    from incin_b200.backends import NumpyBackend
+    ext = run_conformance(NumpyBackend())
+    by = {s: [r for r in ext if r.status == s] for s in ("passed", "failed", "skipped")}
+    assert not by["failed"], by["failed"]
+    assert len(by["passed"]) >= 20 and all(r.dtype == "f32" for r in by["passed"])
+    assert {r.op for r in by["skipped"]} >= {"conv2d", "max_pool2d"} and any(r.dtype == "bf16" for r in by["skipped"])
+    assert len({r.op for r in res}) >= 25                                      # case families of the suite
 
 
 def test_iteration_plans_collapse_broadcast_and_bounds():
@@ -665,3 +673,62 @@ def test_lsp_proxy_frames_and_rewrites(tmp_path):
     first, second = json.loads(lsp.read_frame(got)), json.loads(lsp.read_frame(got))
     assert "hint:" in first["params"]["diagnostics"][0]["message"]
     assert second["params"]["diagnostics"][0]["message"] == "fine"
+
+
+def test_row_chain_fuser_renders_and_compiles_without_a_gpu():
+    """pointwise -> row normalisation -> pointwise as ONE kernel: the source carries the whole chain, compiles for
+    sm_100a with NVRTC, and malformed chains are refused at render time."""
+    from incin_b200.codegen import Col, Norm, reference_rows, render_row_cuda
+    from incin_b200.codegen.runtime import nvrtc_compile
+    chains = {
+        "masked scaled softmax": ("softmax", Arg(0) * Scalar(0) + Col(0), None),
+        "log-softmax of a sum": ("log_softmax", Arg(0) + Arg(1), None),
+        "residual layer norm with gain and bias": ("layer_norm", Arg(0) + Arg(1), Norm() * Col(0) + Col(1)),
+        "gelu of a gained rms norm": ("rms_norm", Arg(0), Unary("gelu", Norm() * Col(0))),
+    }
+    for name, (kind, pre, post) in chains.items():
+        for dt in ("bf16", "f32"):
+            src, key = render_row_cuda(kind, pre, post, dt)
+            assert key.entry in src and src.count("__global__") == 1, name
+            assert len(nvrtc_compile(src, key.entry + ".cu")) > 1000, name
+    src, key = render_row_cuda("layer_norm", Arg(0) + Arg(1), Norm() * Col(0) + Col(1), "bf16")
+    assert "in1 + base + c" in src and "col1 + c" in src and "rsqrtf" in src and (key.n_args, key.n_cols, key.n_scalars) == (2, 2, 0)
+    assert render_row_cuda("softmax", Arg(0) * Scalar(0), None, "bf16")[1] != render_row_cuda("softmax", Arg(0) * Scalar(1), None, "bf16")[1]
+    with pytest.raises(ValueError):
+        render_row_cuda("softmax", Norm() + Arg(0))                    # the prologue has nothing normalised yet
+    with pytest.raises(ValueError):
+        render_row_cuda("median", Arg(0))
+    with pytest.raises(ValueError):
+        render_row_cuda("softmax", Col(0))                             # no row tensor
+    # the fp32 oracle of a chain (also the CPU path) agrees with plain PyTorch
+    x, r = torch.randn(5, 33), torch.randn(5, 33)
+    g, b = torch.rand(33) + 0.5, torch.randn(33)
+    got = reference_rows("layer_norm", Arg(0) + Arg(1), [x, r], post=Norm() * Col(0) + Col(1), cols=[g, b])
+    assert torch.allclose(got, torch.nn.functional.layer_norm(x + r, (33,), g, b), atol=1e-5)
+    got = reference_rows("softmax", Arg(0) * Scalar(0) + Col(0), [x], cols=[b], scalars=[0.25])
+    assert torch.allclose(got, torch.softmax(x * 0.25 + b, -1), atol=1e-6)
+
+
+def test_row_fusion_pass_finds_and_lowers_softmax_chains():
+    from incin_b200.codegen import reference_rows
+
+    def f(x, mask, y):
+        return torch.softmax(x * 0.5 + mask, -1) * y
+
+    x, mask, y = torch.randn(6, 40), torch.randn(40), torch.randn(6, 40)
+    g = G.trace(f, x, mask, y)
+    groups = G.row_fusion_pass(g)
+    assert len(groups) == 1 and len(groups[0].pre) == 2 and len(groups[0].post) == 1
+    kind, pre, post, rows_ext, cols_ext = G.lower_row_group(g, groups[0])
+    assert kind == "softmax" and len(rows_ext) == 2 and len(cols_ext) == 1
+    by_id = {nid: t for nid, t in zip(g.inputs, (x, mask, y))}
+    got = reference_rows(kind, pre, [by_id[i] for i in rows_ext], post=post, cols=[by_id[i] for i in cols_ext])
+    assert torch.allclose(got, f(x, mask, y), atol=1e-6)
+    # a value that something outside the group also reads stays out of the prologue
+    def h(x):
+        t = x * 2.0
+        return torch.log_softmax(t, -1), t
+    g2 = G.trace(h, x)
+    assert G.row_fusion_pass(g2) == []
+    # a softmax over another axis is not a row op of this pass
+    assert G.row_fusion_pass(G.trace(lambda a: torch.softmax(a + 1.0, 0), x)) == []
