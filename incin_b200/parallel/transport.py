@@ -131,6 +131,68 @@ class NcclTransport:
         self.context = context
         self.cursor = PlanCursor(agreed_plan) if agreed_plan is not None else None
 
+    @classmethod
+    def connect_context(cls, context, plan, *, backend: str | None = None, device: torch.device | None = None,
+                        timeout_s: float = 60.0) -> "NcclTransport":
+        """Bring up the communicator from a rendezvous context, in the reference's order
+        (crates/incin-backends/src/dist/nccl.rs:454-512 ``connect_context``, :1539-1587 ``exchange_bootstrap``):
+
+        1. topology: every rank publishes where it runs (host, device kind, device identity) over the context's control
+           channel; two ranks on one physical device, or ranks of different device kinds, are refused;
+        2. preflight: the hash of ``plan`` must agree on every rank (``context.preflight``) BEFORE any communicator exists;
+        3. bootstrap: rank 0 picks the address the library communicator will use and publishes it over the control
+           channel (the role of the NCCL unique id); only then is the ``torch.distributed`` process group created.
+        A failure in 1 or 2 invalidates the context and leaves ``torch.distributed`` untouched."""
+        import datetime
+        import json
+        import os
+        import socket
+        import torch.distributed as dist
+        from .context import ContextFailure
+        context.ensure_active()
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        if device.type == "cuda":
+            props = torch.cuda.get_device_properties(device)
+            ident = str(getattr(props, "uuid", "")) or f"cuda:{device.index}"
+        else:
+            ident = f"cpu:{os.getpid()}"
+        me = {"rank": context.rank, "host": socket.gethostname(), "kind": device.type, "device": ident}
+        # (the control channel gathers equal-size blobs: identities and the address travel zero-padded)
+        peers = [json.loads(b.rstrip(b"\0").decode()) for b in context.allgather_bytes(json.dumps(me).encode().ljust(512, b"\0"))]
+        kinds = {p["kind"] for p in peers}
+        seen: dict[tuple, int] = {}
+        problem = None
+        if len(kinds) != 1:
+            problem = f"ranks run on different device kinds: {sorted(kinds)}"
+        for p in peers:
+            key = (p["host"], p["device"])
+            if key in seen and p["kind"] == "cuda":
+                problem = f"ranks {seen[key]} and {p['rank']} share device {p['device']} on {p['host']}"
+            seen[key] = p["rank"]
+        if problem:
+            context.invalidate(ContextFailure.PLAN_MISMATCH)
+            raise TransportError("topology rejected: " + problem)
+        agreed = context.preflight(plan)              # raises PreflightError and invalidates the context on divergence
+        if context.rank == 0:
+            s = socket.socket()
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+            s.close()
+            boot = f"tcp://127.0.0.1:{port}".encode()
+        else:
+            boot = b""
+        boot = context.allgather_bytes(boot.ljust(64, b"\0"))[0].rstrip(b"\0").decode()
+        if dist.is_initialized():
+            raise TransportError("torch.distributed is already initialised: connect_context owns the communicator bootstrap")
+        backend = backend or ("nccl" if device.type == "cuda" else "gloo")
+        kw = {"device_id": device} if device.type == "cuda" else {}
+        dist.init_process_group(backend, init_method=boot, rank=context.rank, world_size=context.world,
+                                timeout=datetime.timedelta(seconds=timeout_s), **kw)
+        tr = cls(None, context=context, agreed_plan=agreed)
+        tr.topology = peers
+        return tr
+
     def _guard(self, tag, kind: CollectiveKind, t: torch.Tensor):
         if self.context is not None:
             self.context.ensure_active()

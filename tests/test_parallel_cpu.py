@@ -255,6 +255,33 @@ def _rank_main(rank, world, port, run_id, scenario, q):
                 q.put((rank, "rejected", len(opened), ctx.state.name))
             except Exception as e:      # past the preflight the CPU stand-in cannot go on (no device library): expected
                 q.put((rank, "agreed_then", type(e).__name__, len(opened) > 0))
+        elif scenario in ("nccl_connect", "nccl_connect_diverge"):
+            # the library communicator comes up from the context: topology, preflight, then the bootstrap address
+            import torch
+            import torch.distributed as dist
+            from incin_b200.core import Cuda
+            from incin_b200.parallel import mesh as M, plan as PL, strategies as S
+            from incin_b200.parallel.transport import NcclTransport
+            class Probe:
+                def identity(self, d): return M.DeviceIdentity(f"GPU-{d.index}", "cuda", "sm_100")
+                def link(self, a, b): return M.LinkClass.HIGH_BANDWIDTH
+            m = M.DeviceMesh.bind(M.mesh(dp=world), [Cuda(i) for i in range(world)], Probe())
+            b = S.DataParallelPlanBuilder(m, rank)
+            b.push(0, 8 + (scenario == "nccl_connect_diverge" and rank == 1))
+            try:
+                tr = NcclTransport.connect_context(ctx, b.finish(), device=torch.device("cpu"))
+            except PL.PreflightError:
+                q.put((rank, "rejected", dist.is_initialized(), ctx.state.name))
+            else:
+                t = tr.all_reduce(torch.full((8,), float(rank + 1)), PL.Reduction.MEAN, tag=0)    # the planned gradient mean
+                ok_plan = True
+                try:
+                    tr.all_reduce(torch.zeros(8), PL.Reduction.MEAN, tag=1)     # not in the agreed plan
+                    ok_plan = False
+                except PL.PlanError:
+                    pass
+                q.put((rank, "connected", t.tolist()[0], ok_plan, len(tr.topology), ctx.state.name))
+                dist.destroy_process_group()
         elif scenario == "vanish":
             if rank == 1:
                 import os
@@ -324,6 +351,14 @@ def test_divergent_tensor_parallel_plan_is_rejected_before_any_peer_mapping():
     assert out[0] == ("rejected", 0, "FAILED") and out[1] == ("rejected", 0, "FAILED")     # nothing allocated or opened
     same = _run(2, "tp_plan_same")
     assert all(v[0] in ("constructed", "agreed_then") for v in same.values())              # equal plans pass the preflight
+
+
+def test_library_communicator_is_bootstrapped_from_the_context():
+    out = _run(2, "nccl_connect")
+    # mean of (rank + 1) over two ranks; the launch outside the plan is refused and fails the context
+    assert out[0] == ("connected", 1.5, True, 2, "FAILED") and out[1] == ("connected", 1.5, True, 2, "FAILED")
+    bad = _run(2, "nccl_connect_diverge")
+    assert all(v == ("rejected", False, "FAILED") for v in bad.values())      # no communicator was ever created
 
 
 def test_plan_lane_checks_every_launch_and_placements_pick_the_kernel():
