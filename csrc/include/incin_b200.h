@@ -120,6 +120,13 @@ int incin_layernorm_bwd(const void* dy, const void* x, const void* gamma, const 
 /* RMSNorm: y = x * rsqrt(mean(x^2) + eps) * gamma */
 int incin_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd, long long rows, int C, float eps,
                       void* stream);
+/* LayerNorm backward that also adds the column sums of the dx it writes (dx_add included) into dxsum[C] (fp32): the
+ * bias gradient of the linear layer whose output entered the residual stream in front of this norm.  One-pass kernel
+ * only: C % 8 == 0 and C <= 1024, dgamma required; scratch of incin_layernorm_bwd_colsum_scratch_floats(rows, C) floats. */
+long long incin_layernorm_bwd_colsum_scratch_floats(long long rows, int C);
+int incin_layernorm_bwd_colsum(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                               const void* dx_add, void* dx, float* dgamma, float* dbeta, float* dxsum, float* scratch,
+                               long long rows, int C, void* stream);
 int incin_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rstd, const void* dx_add,
                       void* dx, float* dgamma, float* scratch, long long rows, int C, void* stream);
 

@@ -410,44 +410,53 @@ norm_bwd_param_partial_vec(const __nv_bfloat16* __restrict__ dy, const __nv_bflo
 constexpr int PF_LANES = 32;
 __global__ void __launch_bounds__(32 * PF_LANES)
 norm_bwd_param_final(const float* __restrict__ scratch, float* __restrict__ dgamma, float* __restrict__ dbeta, int C,
-                     int chunks) {
+                     int chunks, int na, float* __restrict__ dxsum) {
+  // scratch[chunk][na][C]: na = 2 partial sums per column (dgamma, dbeta), or 3 with the column sums of dx behind them
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float sa[PF_LANES][33], sb[PF_LANES][33];
+  __shared__ float sa[PF_LANES][33], sb[PF_LANES][33], sc[PF_LANES][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + tx;
-  float a = 0.f, b = 0.f;
+  float a = 0.f, b = 0.f, d = 0.f;
   if (c < C) {
     int k = ty;
     for (; k + 3 * PF_LANES < chunks; k += 4 * PF_LANES) {
       float va[4], vb[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        va[u] = scratch[((long long)(k + u * PF_LANES) * 2 + 0) * C + c];
-        vb[u] = scratch[((long long)(k + u * PF_LANES) * 2 + 1) * C + c];
+        va[u] = scratch[((long long)(k + u * PF_LANES) * na + 0) * C + c];
+        vb[u] = scratch[((long long)(k + u * PF_LANES) * na + 1) * C + c];
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         a += va[u];
         b += vb[u];
       }
+      if (dxsum) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) d += scratch[((long long)(k + u * PF_LANES) * na + 2) * C + c];
+      }
     }
     for (; k < chunks; k += PF_LANES) {
-      a += scratch[((long long)k * 2 + 0) * C + c];
-      b += scratch[((long long)k * 2 + 1) * C + c];
+      a += scratch[((long long)k * na + 0) * C + c];
+      b += scratch[((long long)k * na + 1) * C + c];
+      if (dxsum) d += scratch[((long long)k * na + 2) * C + c];
     }
   }
   sa[ty][tx] = a;
   sb[ty][tx] = b;
+  sc[ty][tx] = d;
   __syncthreads();
   if (ty == 0 && c < C) {
 #pragma unroll
     for (int t = 1; t < PF_LANES; ++t) {
       a += sa[t][tx];
       b += sb[t][tx];
+      d += sc[t][tx];
     }
     dgamma[c] += a;
     if (dbeta) dbeta[c] += b;
+    if (dxsum) dxsum[c] += d;
   }
 }
 
@@ -459,7 +468,10 @@ norm_bwd_param_final(const float* __restrict__ scratch, float* __restrict__ dgam
 // The row is held as the raw 16-byte loads (bf16) and unpacked where it is used; the per-column accumulators of each
 // warp live in shared memory (element (it, i, lane) at it*256 + i*32 + lane: a warp touches 32 different banks), which
 // keeps the kernel under 85 registers so that three blocks (24 warps) per SM have loads in flight.
-template <bool RMS, int ITER>
+// CSUM: a third accumulator takes the column sums of the dx this kernel writes (the incoming residual gradient
+// included): that is the bias gradient of the linear layer whose output entered the residual stream in front of this
+// norm, which then needs no column-sum launch of its own.
+template <bool RMS, int ITER, bool CSUM = false>
 __global__ void __launch_bounds__(NORM_WARPS * 32, 3)
 norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                       const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
@@ -468,15 +480,18 @@ norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
                       long long rows_per) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float acc_smem[];                     // [NORM_WARPS][2][ITER * 256]
+  extern __shared__ float acc_smem[];                     // [NORM_WARPS][NA][ITER * 256]
   constexpr int W = ITER * 256;
+  constexpr int NA = CSUM ? 3 : 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float* gacc = acc_smem + (warp * 2 + 0) * W;
-  float* bacc = acc_smem + (warp * 2 + 1) * W;
+  float* gacc = acc_smem + (warp * NA + 0) * W;
+  float* bacc = acc_smem + (warp * NA + 1) * W;
+  float* cacc = acc_smem + (warp * NA + (CSUM ? 2 : 0)) * W;   // only touched when CSUM
 #pragma unroll
   for (int j = lane; j < W; j += 32) {
     gacc[j] = 0.f;
     bacc[j] = 0.f;
+    if (CSUM) cacc[j] = 0.f;
   }
   __syncwarp();
   const long long r0 = (long long)blockIdx.x * rows_per;
@@ -535,6 +550,10 @@ norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
           for (int i = 0; i < 8; ++i) o[i] += a[i];
         }
         store8(dx + r * C + c, o);
+        if (CSUM) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) cacc[it * 256 + i * 32 + lane] += o[i];
+        }
       }
     }
   }
@@ -543,14 +562,16 @@ norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
   for (int j = threadIdx.x; j < W; j += NORM_WARPS * 32) {
     const int c = (j & ~255) + (j & 31) * 8 + ((j >> 5) & 7);
     if (c < C) {
-      float a = 0.f, bsum = 0.f;
+      float a = 0.f, bsum = 0.f, csum = 0.f;
 #pragma unroll
       for (int w = 0; w < NORM_WARPS; ++w) {
-        a += acc_smem[(w * 2 + 0) * W + j];
-        bsum += acc_smem[(w * 2 + 1) * W + j];
+        a += acc_smem[(w * NA + 0) * W + j];
+        bsum += acc_smem[(w * NA + 1) * W + j];
+        if (CSUM) csum += acc_smem[(w * NA + 2) * W + j];
       }
-      scratch[((long long)blockIdx.x * 2 + 0) * C + c] = a;
-      scratch[((long long)blockIdx.x * 2 + 1) * C + c] = bsum;
+      scratch[((long long)blockIdx.x * NA + 0) * C + c] = a;
+      scratch[((long long)blockIdx.x * NA + 1) * C + c] = bsum;
+      if (CSUM) scratch[((long long)blockIdx.x * NA + 2) * C + c] = csum;
     }
   }
 }
@@ -581,30 +602,37 @@ static int param_chunks(long long rows, int C) {
 template <bool RMS>
 static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
                            const void* dx_add, void* dx, float* dgamma, float* dbeta, float* scratch, long long rows,
-                           int C, cudaStream_t s) {
+                           int C, cudaStream_t s, float* dxsum = nullptr) {
   if (rows <= 0 || C <= 0) return INCIN_ERR_ARGUMENT;
+  if (dxsum && !(dgamma && fused_bwd_ok(C))) return INCIN_ERR_ARGUMENT;   // column sums of dx: one-pass kernel only
   if (dgamma && fused_bwd_ok(C)) {
     if (!scratch) return INCIN_ERR_ARGUMENT;
     const long long rp = fused_rows_per(rows, C);
     const int chunks = param_chunks(rows, C);
     const int iters = (C + 255) / 256;
-    const size_t acc_bytes = (size_t)NORM_WARPS * 2 * iters * 256 * sizeof(float);   // 16 KB per 256 columns
-    static PerDeviceFlags attr_set[5];   // per kernel (RMS is a template argument here) and per device
+    const int na = dxsum ? 3 : 2;
+    const size_t acc_bytes = (size_t)NORM_WARPS * na * iters * 256 * sizeof(float);   // 8 KB per 256 columns and sum
+    static PerDeviceFlags attr_set[10];   // per kernel (RMS is a template argument here) and per device
     bool attr_ok = true;
     auto go = [&](auto kern) {
-      if (!ensure_dynamic_smem(kern, (int)acc_bytes, attr_set[iters])) {
+      if (!ensure_dynamic_smem(kern, (int)acc_bytes, attr_set[iters + (dxsum ? 5 : 0)])) {
         attr_ok = false;   // nothing was launched: the partial sums must not be reduced either
         return;
       }
       launch_pdl(kern, dim3((unsigned)chunks), dim3(NORM_WARPS * 32), acc_bytes, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                  (const __nv_bfloat16*)gamma, mean, rstd, (const __nv_bfloat16*)dx_add, (__nv_bfloat16*)dx, scratch, rows, C, rp);
     };
-    if (iters == 1) go(norm_bwd_fused_kernel<RMS, 1>);
+    if (dxsum) {
+      if (iters == 1) go(norm_bwd_fused_kernel<RMS, 1, true>);
+      else if (iters == 2) go(norm_bwd_fused_kernel<RMS, 2, true>);
+      else if (iters == 3) go(norm_bwd_fused_kernel<RMS, 3, true>);
+      else go(norm_bwd_fused_kernel<RMS, 4, true>);
+    } else if (iters == 1) go(norm_bwd_fused_kernel<RMS, 1>);
     else if (iters == 2) go(norm_bwd_fused_kernel<RMS, 2>);
     else if (iters == 3) go(norm_bwd_fused_kernel<RMS, 3>);
     else go(norm_bwd_fused_kernel<RMS, 4>);
     if (!attr_ok) return INCIN_ERR_DRIVER;
-    launch_pdl(norm_bwd_param_final, dim3((C + 31) / 32), dim3(32 * PF_LANES), 0, s, scratch, dgamma, dbeta, C, chunks);
+    launch_pdl(norm_bwd_param_final, dim3((C + 31) / 32), dim3(32 * PF_LANES), 0, s, scratch, dgamma, dbeta, C, chunks, na, dxsum);
     return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
   }
   const unsigned blocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
@@ -623,7 +651,7 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, con
       launch_pdl(norm_bwd_param_partial<RMS>, dim3(grid), dim3(32 * PG_TY), 0, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                                mean, rstd, scratch, rows, C, chunks);
     }
-    launch_pdl(norm_bwd_param_final, dim3((C + 31) / 32), dim3(32 * PF_LANES), 0, s, scratch, dgamma, dbeta, C, chunks);
+    launch_pdl(norm_bwd_param_final, dim3((C + 31) / 32), dim3(32 * PF_LANES), 0, s, scratch, dgamma, dbeta, C, chunks, 2, (float*)nullptr);
   }
   return cudaGetLastError() == cudaSuccess ? INCIN_OK : INCIN_ERR_LAUNCH;
 }
@@ -655,6 +683,21 @@ extern "C" int incin_layernorm_bwd(const void* dy, const void* x, const void* ga
                                    float* scratch, long long rows, int C, void* stream) {
   return norm_bwd_launch<false>(dy, x, gamma, mean, rstd, dx_add, dx, dgamma, dbeta, scratch, rows, C,
                                 (cudaStream_t)stream);
+}
+
+// LayerNorm backward that also accumulates the column sums of the dx it writes into dxsum[C] (fp32, +=): the bias
+// gradient of the linear layer in front of this norm on the residual stream.  C % 8 == 0 and C <= 1024 (the one-pass
+// kernel); scratch holds incin_layernorm_bwd_colsum_scratch_floats(rows, C) floats.
+extern "C" long long incin_layernorm_bwd_colsum_scratch_floats(long long rows, int C) {
+  return (long long)param_chunks(rows, C) * 3 * C;
+}
+
+extern "C" int incin_layernorm_bwd_colsum(const void* dy, const void* x, const void* gamma, const float* mean,
+                                          const float* rstd, const void* dx_add, void* dx, float* dgamma, float* dbeta,
+                                          float* dxsum, float* scratch, long long rows, int C, void* stream) {
+  if (!dxsum) return INCIN_ERR_ARGUMENT;
+  return norm_bwd_launch<false>(dy, x, gamma, mean, rstd, dx_add, dx, dgamma, dbeta, scratch, rows, C,
+                                (cudaStream_t)stream, dxsum);
 }
 
 extern "C" int incin_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rstd,

@@ -74,6 +74,8 @@ _CUDA_SIGS = {
     "incin_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_ll, c_int, c_float, c_void_p]),
     "incin_layernorm_bwd_scratch_floats": (c_ll, [c_ll, c_int]),
     "incin_layernorm_bwd": (c_int, [c_void_p] * 10 + [c_ll, c_int, c_void_p]),
+    "incin_layernorm_bwd_colsum_scratch_floats": (c_ll, [c_ll, c_int]),
+    "incin_layernorm_bwd_colsum": (c_int, [c_void_p] * 11 + [c_ll, c_int, c_void_p]),
     "incin_rmsnorm_fwd": (c_int, [c_void_p] * 4 + [c_ll, c_int, c_float, c_void_p]),
     "incin_rmsnorm_bwd": (c_int, [c_void_p] * 8 + [c_ll, c_int, c_void_p]),
     "incin_embedding_fwd": (c_int, [c_void_p] * 4 + [c_ll, c_int, c_int, c_void_p]),

@@ -75,14 +75,20 @@ class Block(nn.Module):
         self.out_b = nn.Parameter(torch.zeros(c))
         self.cfg = cfg
 
-    def forward(self, x):
+    def forward(self, x, bias_of_input=None, defer_out_bias: bool = False):
+        """``bias_of_input``: the bias of the linear layer that produced ``x`` (the previous block's ``out_b``) when that
+        layer left its bias gradient to the norm that consumes its output; ``defer_out_bias``: this block's ``out_b``
+        gradient is left to whoever normalises the block's output.  The gradient that a norm's backward returns IS the
+        output gradient of the linear in front of it, so its column sums cost no extra pass there, where the linear
+        would need a launch that reads the whole gradient again."""
         cfg = self.cfg
-        res, h = F.layernorm_fork(x, self.ln1_g, self.ln1_b, cfg.ln_eps)
+        res, h = F.layernorm_fork(x, self.ln1_g, self.ln1_b, cfg.ln_eps, bias_of_input=bias_of_input)
         qkv = F.linear(h, self.qkv_w, self.qkv_b)
         a = F.causal_attention(qkv, cfg.n_head, cfg.d_model // cfg.n_head)
-        x = F.linear(a, self.proj_w, self.proj_b, residual=res)
-        res, h = F.layernorm_fork(x, self.ln2_g, self.ln2_b, cfg.ln_eps)
-        return F.mlp(h, self.fc_w, self.fc_b, self.out_w, self.out_b, act="gelu", residual=res)
+        x = F.linear(a, self.proj_w, self.proj_b, residual=res, defer_bias_grad=True)
+        res, h = F.layernorm_fork(x, self.ln2_g, self.ln2_b, cfg.ln_eps, bias_of_input=self.proj_b)
+        return F.mlp(h, self.fc_w, self.fc_b, self.out_w, self.out_b, act="gelu", residual=res,
+                     defer_b2_grad=defer_out_bias)
 
 
 class GPT2(nn.Module):
@@ -114,9 +120,11 @@ class GPT2(nn.Module):
         T = tokens.shape[1]
         assert T <= cfg.max_seq
         x = F.embedding(tokens, self.wte, self.wpe)
-        for b in self.blocks:
-            x = b(x)
-        h = F.layer_norm(x, self.lnf_g, self.lnf_b, cfg.ln_eps)
+        prev_bias = None
+        for b in self.blocks:       # every block's output is normalised next (by the next block or by the final norm)
+            x = b(x, prev_bias, True)
+            prev_bias = b.out_b
+        h = F.layer_norm(x, self.lnf_g, self.lnf_b, cfg.ln_eps, bias_of_input=prev_bias)
         if targets is None:
             return F.linear(h, self.wte)[..., : cfg.vocab_size]   # tied LM head over the padded vocabulary
         return F.linear_cross_entropy(h, self.wte, targets, cfg.vocab_size)

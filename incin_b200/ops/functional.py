@@ -66,8 +66,9 @@ def _c(t: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------------------------- linear
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, b, residual, act):
+    def forward(ctx, x, w, b, residual, act, defer_bias_grad=False):
         x = _c(x)
+        ctx.defer_bias = defer_bias_grad
         aux = None
         if act != nat.ACT_NONE:
             aux = torch.empty(*x.shape[:-1], w.shape[0], dtype=torch.bfloat16, device=x.device)
@@ -87,16 +88,17 @@ class _Linear(torch.autograd.Function):
         dpre = K.act_bwd(dy, aux, ctx.act) if ctx.act != nat.ACT_NONE else dy
         if w.requires_grad:
             G.mm_tn_accum(dpre, x, main_grad(w), max_ctas=_max_ctas)
-        if ctx.has_bias and ctx.bias.requires_grad:
+        own_bias = ctx.has_bias and ctx.bias.requires_grad and not ctx.defer_bias
+        if own_bias:
             K.colsum_accum(dpre, main_grad(ctx.bias))
         dx = G.mm_nn(dpre, w, max_ctas=_max_ctas) if ctx.needs_input_grad[0] else None
         # A ready callback may launch the data-parallel update, which overwrites w on another stream: it is
         # called only after the last kernel that reads w (the data-gradient product above) has been enqueued.
         if w.requires_grad:
             _ready(w)
-        if ctx.has_bias and ctx.bias.requires_grad:
+        if own_bias:
             _ready(ctx.bias)
-        return dx, None, None, (dy if ctx.has_res else None), None
+        return dx, None, None, (dy if ctx.has_res else None), None, None
 
 
 class _LinearF32Acc(torch.autograd.Function):
@@ -150,10 +152,12 @@ def _f32acc_native(x: torch.Tensor, w: torch.Tensor) -> bool:
     return False
 
 
-def linear(x, w, b=None, *, act=None, residual=None):
-    """``act(x @ w^T + b) + residual`` with everything fused into the GEMM epilogue on CUDA."""
+def linear(x, w, b=None, *, act=None, residual=None, defer_bias_grad: bool = False):
+    """``act(x @ w^T + b) + residual`` with everything fused into the GEMM epilogue on CUDA.
+    ``defer_bias_grad``: the bias gradient (column sums of this op's output gradient) is produced by the norm that
+    consumes the output (``layernorm_fork(..., bias_of_input=b)``) instead of by a launch of its own."""
     if _nat(x):
-        return _Linear.apply(x, w, b, residual, ACT[act])
+        return _Linear.apply(x, w, b, residual, ACT[act], defer_bias_grad and act is None)
     y = _LinearF32Acc.apply(x, w, b) if _f32acc_native(x, w) else TF.linear(x, w, b)
     if act == "gelu":
         y = TF.gelu(y)
@@ -166,8 +170,9 @@ class _MLP(torch.autograd.Function):
     """y = act(x W1^T + b1) W2^T + b2 + residual; the activation backward rides in the dgrad GEMM epilogue."""
 
     @staticmethod
-    def forward(ctx, x, w1, b1, w2, b2, residual, act):
+    def forward(ctx, x, w1, b1, w2, b2, residual, act, defer_b2_grad=False):
         x = _c(x)
+        ctx.defer_b2 = defer_b2_grad
         pre = torch.empty(*x.shape[:-1], w1.shape[0], dtype=torch.bfloat16, device=x.device)
         h = G.mm_nt(x, w1, bias=b1, act=act, aux=pre, max_ctas=_max_ctas)
         y = G.mm_nt(h, w2, bias=b2, residual=_c(residual) if residual is not None else None, max_ctas=_max_ctas)
@@ -180,12 +185,13 @@ class _MLP(torch.autograd.Function):
         x, w1, w2, pre, h = ctx.saved_tensors
         dy = _c(dy)
         G.mm_tn_accum(dy, h, main_grad(w2), max_ctas=_max_ctas)
-        if ctx.b2 is not None:
+        own_b2 = ctx.b2 is not None and not ctx.defer_b2
+        if own_b2:
             K.colsum_accum(dy, main_grad(ctx.b2))
         dpre = G.mm_nn(dy, w2, act=_DACT[ctx.act], aux=pre, max_ctas=_max_ctas)
         # ready callbacks come after the last enqueued reader of each weight (they may start its update)
         _ready(w2)
-        if ctx.b2 is not None:
+        if own_b2:
             _ready(ctx.b2)
         G.mm_tn_accum(dpre, x, main_grad(w1), max_ctas=_max_ctas)
         if ctx.b1 is not None:
@@ -194,12 +200,13 @@ class _MLP(torch.autograd.Function):
         _ready(w1)
         if ctx.b1 is not None:
             _ready(ctx.b1)
-        return dx, None, None, None, None, (dy if ctx.has_res else None), None
+        return dx, None, None, None, None, (dy if ctx.has_res else None), None, None
 
 
-def mlp(x, w1, b1, w2, b2, *, act="gelu", residual=None):
+def mlp(x, w1, b1, w2, b2, *, act="gelu", residual=None, defer_b2_grad: bool = False):
+    """``defer_b2_grad``: the gradient of ``b2`` is produced by the norm that consumes the output (see :func:`linear`)."""
     if _nat(x):
-        return _MLP.apply(x, w1, b1, w2, b2, residual, ACT[act])
+        return _MLP.apply(x, w1, b1, w2, b2, residual, ACT[act], defer_b2_grad and b2 is not None)
     h = TF.linear(x, w1, b1)
     h = TF.gelu(h) if act == "gelu" else TF.silu(h)
     y = TF.linear(h, w2, b2)
@@ -209,11 +216,12 @@ def mlp(x, w1, b1, w2, b2, *, act="gelu", residual=None):
 # --------------------------------------------------------------------------------------------- norms
 class _LayerNorm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, g, b, eps, fork):
+    def forward(ctx, x, g, b, eps, fork, bias_of_input=None):
         x = _c(x)
         y, mean, rstd = K.layernorm_fwd(x, g, b, eps)
         ctx.save_for_backward(x, g, mean, rstd)
         ctx.b, ctx.fork = b, fork
+        ctx.in_bias = bias_of_input if (bias_of_input is not None and bias_of_input.requires_grad) else None
         if fork:
             return x.view_as(x), y
         return y
@@ -226,27 +234,38 @@ class _LayerNorm(torch.autograd.Function):
         else:
             dxid, dy = None, grads[0]
         if dy is None:  # normalised branch unused: only the identity gradient flows
-            return dxid, None, None, None, None
+            if ctx.in_bias is not None and dxid is not None:
+                K.colsum_accum(_c(dxid), main_grad(ctx.in_bias))
+                _ready(ctx.in_bias)
+            return dxid, None, None, None, None, None
         dg = main_grad(g) if g.requires_grad else None
         db = main_grad(ctx.b) if (ctx.b is not None and ctx.b.requires_grad) else None
-        dx = K.layernorm_bwd(_c(dy), x, g, mean, rstd, _c(dxid) if dxid is not None else None, dg, db)
+        # the gradient this op returns is the output gradient of the linear layer in front of it: its column sums are
+        # that layer's bias gradient and come out of the same pass
+        dx = K.layernorm_bwd(_c(dy), x, g, mean, rstd, _c(dxid) if dxid is not None else None, dg, db,
+                             main_grad(ctx.in_bias) if ctx.in_bias is not None else None)
         if dg is not None:
             _ready(g)
         if db is not None:
             _ready(ctx.b)
-        return dx, None, None, None, None
+        if ctx.in_bias is not None:
+            _ready(ctx.in_bias)
+        return dx, None, None, None, None, None
 
 
-def layer_norm(x, g, b=None, eps: float = 1e-5):
+def layer_norm(x, g, b=None, eps: float = 1e-5, *, bias_of_input=None):
+    """``bias_of_input``: the bias of the linear layer that produced ``x`` (called with ``defer_bias_grad``); its
+    gradient is accumulated by this op's backward."""
     if _nat(x):
-        return _LayerNorm.apply(x, g, b, eps, False)
+        return _LayerNorm.apply(x, g, b, eps, False, bias_of_input)
     return TF.layer_norm(x, (x.shape[-1],), g, b, eps)
 
 
-def layernorm_fork(x, g, b=None, eps: float = 1e-5):
-    """Returns ``(x, layer_norm(x))``; the backward adds both incoming gradients in the LN kernel."""
+def layernorm_fork(x, g, b=None, eps: float = 1e-5, *, bias_of_input=None):
+    """Returns ``(x, layer_norm(x))``; the backward adds both incoming gradients in the LN kernel (and accumulates the
+    gradient of ``bias_of_input``, see :func:`layer_norm`)."""
     if _nat(x):
-        return _LayerNorm.apply(x, g, b, eps, True)
+        return _LayerNorm.apply(x, g, b, eps, True, bias_of_input)
     return x, TF.layer_norm(x, (x.shape[-1],), g, b, eps)
 
 

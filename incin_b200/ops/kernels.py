@@ -36,10 +36,25 @@ def norm_bwd_scratch(rows: int, C: int, device) -> torch.Tensor:
     return torch.empty(n, dtype=F32, device=device)
 
 
-def layernorm_bwd(dy, x, gamma, mean, rstd, dx_add, dgamma, dbeta):
+def layernorm_bwd(dy, x, gamma, mean, rstd, dx_add, dgamma, dbeta, dx_colsum=None):
+    """``dx_colsum`` (fp32 ``[C]``, accumulated into): the column sums of the returned dx, i.e. the bias gradient of the
+    linear layer in front of this norm on the residual stream.  They come out of the one-pass kernel for free
+    (C % 8 == 0, C <= 1024, parameter gradients requested); otherwise one column-sum launch follows."""
     C = x.shape[-1]
     rows = x.numel() // C
     dx = torch.empty_like(x)
+    if dx_colsum is not None:
+        if dgamma is not None and C % 8 == 0 and C <= 1024:
+            n = nat.cuda().incin_layernorm_bwd_colsum_scratch_floats(rows, C)
+            scratch = torch.empty(n, dtype=F32, device=x.device)
+            nat.check(nat.cuda().incin_layernorm_bwd_colsum(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr(),
+                                                           rstd.data_ptr(), nat.ptr(dx_add), dx.data_ptr(), nat.ptr(dgamma),
+                                                           nat.ptr(dbeta), dx_colsum.data_ptr(), scratch.data_ptr(), rows, C,
+                                                           _s()), "layernorm_bwd_colsum")
+            return dx
+        dx = layernorm_bwd(dy, x, gamma, mean, rstd, dx_add, dgamma, dbeta)
+        colsum_accum(dx, dx_colsum)
+        return dx
     scratch = norm_bwd_scratch(rows, C, x.device) if dgamma is not None else None
     nat.check(nat.cuda().incin_layernorm_bwd(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr(),
                                             rstd.data_ptr(), nat.ptr(dx_add), dx.data_ptr(), nat.ptr(dgamma),

@@ -213,6 +213,8 @@ extern "C" {
     pub fn incin_gemm_bf16(desc: *const incin_gemm_desc, stream: *mut c_void) -> c_int;
     pub fn incin_im2col(x: *const c_void, cols: *mut c_void, g: *const incin_conv_geom, is_bf16: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_layernorm_bwd(dy: *const c_void, x: *const c_void, gamma: *const c_void, mean: *const f32, rstd: *const f32, dx_add: *const c_void, dx: *mut c_void, dgamma: *mut f32, dbeta: *mut f32, scratch: *mut f32, rows: c_longlong, C: c_int, stream: *mut c_void) -> c_int;
+    pub fn incin_layernorm_bwd_colsum(dy: *const c_void, x: *const c_void, gamma: *const c_void, mean: *const f32, rstd: *const f32, dx_add: *const c_void, dx: *mut c_void, dgamma: *mut f32, dbeta: *mut f32, dxsum: *mut f32, scratch: *mut f32, rows: c_longlong, C: c_int, stream: *mut c_void) -> c_int;
+    pub fn incin_layernorm_bwd_colsum_scratch_floats(rows: c_longlong, C: c_int) -> c_longlong;
     pub fn incin_layernorm_bwd_noalloc(dy: *const c_void, x: *const c_void, gamma: *const c_void, mean: *const f32, rstd: *const f32, dx_add: *const c_void, dx: *mut c_void, dgamma: *mut f32, dbeta: *mut f32, rows: c_longlong, C: c_int, stream: *mut c_void) -> c_int;
     pub fn incin_layernorm_bwd_scratch_floats(rows: c_longlong, C: c_int) -> c_longlong;
     pub fn incin_layernorm_fwd(x: *const c_void, gamma: *const c_void, beta: *const c_void, y: *mut c_void, mean: *mut f32, rstd: *mut f32, rows: c_longlong, C: c_int, eps: f32, stream: *mut c_void) -> c_int;

@@ -199,3 +199,28 @@ def test_linear_cross_entropy_fused():
     close(x.grad, xf.grad, tol=3e-2)
     close(w.main_grad, wf.grad, tol=3e-2)
     assert w.main_grad[V:].abs().max().item() == 0.0      # padded vocabulary rows get no gradient
+
+
+@pytest.mark.parametrize("C", [768, 1024, 2048, 100])
+def test_layernorm_backward_also_returns_the_column_sums_of_dx(C):
+    """The bias gradient of the linear in front of a norm is the column sum of the norm's input gradient: it comes out
+    of the one-pass backward kernel (C <= 1024, C % 8 == 0) or from one column-sum launch behind it; either way it
+    equals the fp32 column sums of the dx that the plain backward returns, and it accumulates."""
+    from _tol import check_close
+    from incin_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(C)
+    rows = 1000
+    x = torch.randn(rows, C, generator=g).bfloat16().cuda()
+    dy = torch.randn(rows, C, generator=g).bfloat16().cuda()
+    res = torch.randn(rows, C, generator=g).bfloat16().cuda()
+    gamma = (torch.rand(C, generator=g) + 0.5).bfloat16().cuda()
+    beta = torch.zeros(C).bfloat16().cuda()
+    _, mean, rstd = K.layernorm_fwd(x, gamma, beta, 1e-5)
+    dg0, db0 = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+    dx0 = K.layernorm_bwd(dy, x, gamma, mean, rstd, res, dg0, db0)
+    dg1, db1 = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+    cs = torch.full((C,), 3.0, device="cuda")                       # accumulates on top of what is there
+    dx1 = K.layernorm_bwd(dy, x, gamma, mean, rstd, res, dg1, db1, cs)
+    assert torch.equal(dx0, dx1) and torch.equal(dg0, dg1) and torch.equal(db0, db1)
+    want = dx0.float().sum(0) + 3.0
+    check_close(cs, want, rtol=1e-2, atol_rms=1e-2, what=f"column sums of dx, C={C}")
