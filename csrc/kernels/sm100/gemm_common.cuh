@@ -65,6 +65,7 @@ struct GemmKernelParams {
   uint32_t* rs_ready;     // push mode: per 128-row block, epilogue warps that have finished writing it
   // n > 0: the collective's data is moved by one extra warp in every compute CTA (chunks of 8 KB through a ring made
   // of the last n operand stages) instead of by dedicated copy CTAs; ag_flags then count chunks per 128-row tile
+  int wide_io;   // 1: 256-bit global loads / stores in the epilogue where the address allows (INCIN_GEMM_B256, default 1)
   int copy_warps;
   uint32_t ag_flag_target;   // value of ag_flags[tile] at which the tile is complete
   int ag_own_in_place;       // 1: this rank's own rows are already in the gathered buffer (nothing copies or waits for them)
@@ -112,6 +113,20 @@ __device__ __forceinline__ Unit decode_unit(const GemmKernelParams& p, int u) {
   return w;
 }
 
+// 256-bit global accesses (sm_100): one instruction moves 32 bytes per thread, so a row-per-lane store writes whole 32-byte
+// sectors (two 16-byte stores of different instructions would each write half a sector) in half the instructions.
+__device__ __forceinline__ void st_global_b256(void* ptr, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+               "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+__device__ __forceinline__ void ld_global_b256(const void* ptr, uint32_t (&w)[8]) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+               : "l"(ptr));
+}
+__device__ __forceinline__ bool aligned32(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 31) == 0; }
+
 // Values of one accumulator chunk: thread = one output row, r = its 32 consecutive fp32 accumulator columns starting
 // at column nc.  alpha, bias, GELU / SiLU, activation-gradient masks, residual.  With STAGE_PRE the pre-activation
 // (the side output kept for the backward pass) is returned in pre[] for the caller to store; otherwise it is written
@@ -147,7 +162,15 @@ __device__ __forceinline__ void epilogue_values(const GemmKernelParams& p, const
             for (int j = 0; j < 32; ++j) pre[j] = v[j];
           } else if (p.aux && row_ok) {  // keep the pre-activation for the backward pass
             __nv_bfloat16* ax = p.aux + cbase + nc;
-            if (full) {
+            if (full && p.wide_io && aligned32(ax)) {
+#pragma unroll
+              for (int q = 0; q < 2; ++q) {
+                uint32_t o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = pack_bf16x2(v[q * 16 + e * 2], v[q * 16 + e * 2 + 1]);
+                st_global_b256(ax + q * 16, o);
+              }
+            } else if (full) {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 uint4 o;
@@ -173,7 +196,24 @@ __device__ __forceinline__ void epilogue_values(const GemmKernelParams& p, const
         } else if ((p.act == INCIN_ACT_DGELU || p.act == INCIN_ACT_DSILU) && row_ok) {
           // multiply by act'(pre-activation): fuses the activation backward into the data-gradient GEMM
           const __nv_bfloat16* ax = p.aux + cbase + nc;
-          if (full) {
+          if (full && p.wide_io && aligned32(ax)) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              uint32_t bw[8];
+              ld_global_b256(ax + q * 16, bw);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float2 f = unpack_bf16x2(bw[e]);
+                if (p.act == INCIN_ACT_DGELU) {
+                  v[q * 16 + e * 2] *= gelu_erf_grad(f.x);
+                  v[q * 16 + e * 2 + 1] *= gelu_erf_grad(f.y);
+                } else {
+                  v[q * 16 + e * 2] *= silu_grad(f.x);
+                  v[q * 16 + e * 2 + 1] *= silu_grad(f.y);
+                }
+              }
+            }
+          } else if (full) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const uint4 bb = *reinterpret_cast<const uint4*>(ax + q * 8);
@@ -202,7 +242,19 @@ __device__ __forceinline__ void epilogue_values(const GemmKernelParams& p, const
         }
         if (p.residual && row_ok) {
           const __nv_bfloat16* rs = p.residual + cbase + nc;
-          if (full) {
+          if (full && p.wide_io && aligned32(rs)) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              uint32_t bw[8];
+              ld_global_b256(rs + q * 16, bw);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float2 f = unpack_bf16x2(bw[e]);
+                v[q * 16 + e * 2] += f.x;
+                v[q * 16 + e * 2 + 1] += f.y;
+              }
+            }
+          } else if (full) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const uint4 bb = *reinterpret_cast<const uint4*>(rs + q * 8);
@@ -244,7 +296,15 @@ __device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, const 
                 if (nc + j < p.N) atomicAdd(out + j, v[j]);
             }
           } else {
-            if (full) {
+            if (full && p.wide_io && aligned32(out)) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint32_t o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(v[q * 8 + e]);
+                st_global_b256(out + q * 8, o);
+              }
+            } else if (full) {
 #pragma unroll
               for (int q = 0; q < 8; ++q)
                 *reinterpret_cast<float4*>(out + q * 4) =
@@ -257,7 +317,15 @@ __device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, const 
           }
         } else {
           __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(c_ptr) + cbase + nc;
-          if (full) {
+          if (full && p.wide_io && aligned32(out)) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              uint32_t o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o[e] = pack_bf16x2(v[q * 16 + e * 2], v[q * 16 + e * 2 + 1]);
+              st_global_b256(out + q * 16, o);
+            }
+          } else if (full) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               uint4 o;

@@ -862,6 +862,11 @@ extern "C" int incin_gemm_bf16(const incin_gemm_desc* d, void* stream_) {
   p.aux = reinterpret_cast<__nv_bfloat16*>(d->aux);
   p.status = reinterpret_cast<int*>(d->status);
   p.in_kind = in_kind;
+  static const int wide_io = [] {
+    const char* e = std::getenv("INCIN_GEMM_B256");
+    return e ? std::atoi(e) : 1;
+  }();
+  p.wide_io = wide_io;
   p.ag_world = d->ag_world > 1 ? d->ag_world : 0;
   p.ag_own_in_place = 0;
   p.ag_rank = d->ag_rank;
