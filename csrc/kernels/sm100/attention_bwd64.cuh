@@ -455,19 +455,22 @@ flash_bwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(dkv_drained);   // the next item's products may overwrite dV / dK now
       if (kv_live) {
+        // this thread's 16 columns of the row are 32 contiguous bytes: one 256-bit store each where the address allows
+        uint32_t ka[8], va[8];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          uint4 a, bb;
-          a.x = pack_bf16x2(__uint_as_float(rk[u * 8 + 0]) * p.scale, __uint_as_float(rk[u * 8 + 1]) * p.scale);
-          a.y = pack_bf16x2(__uint_as_float(rk[u * 8 + 2]) * p.scale, __uint_as_float(rk[u * 8 + 3]) * p.scale);
-          a.z = pack_bf16x2(__uint_as_float(rk[u * 8 + 4]) * p.scale, __uint_as_float(rk[u * 8 + 5]) * p.scale);
-          a.w = pack_bf16x2(__uint_as_float(rk[u * 8 + 6]) * p.scale, __uint_as_float(rk[u * 8 + 7]) * p.scale);
-          bb.x = pack_bf16x2(__uint_as_float(rv[u * 8 + 0]), __uint_as_float(rv[u * 8 + 1]));
-          bb.y = pack_bf16x2(__uint_as_float(rv[u * 8 + 2]), __uint_as_float(rv[u * 8 + 3]));
-          bb.z = pack_bf16x2(__uint_as_float(rv[u * 8 + 4]), __uint_as_float(rv[u * 8 + 5]));
-          bb.w = pack_bf16x2(__uint_as_float(rv[u * 8 + 6]), __uint_as_float(rv[u * 8 + 7]));
-          *reinterpret_cast<uint4*>(dk_row + u * 8) = a;
-          *reinterpret_cast<uint4*>(dv_row + u * 8) = bb;
+        for (int e = 0; e < 8; ++e) {
+          ka[e] = pack_bf16x2(__uint_as_float(rk[e * 2]) * p.scale, __uint_as_float(rk[e * 2 + 1]) * p.scale);
+          va[e] = pack_bf16x2(__uint_as_float(rv[e * 2]), __uint_as_float(rv[e * 2 + 1]));
+        }
+        if (aligned32(dk_row) && aligned32(dv_row)) {
+          st_global_b256(dk_row, ka);
+          st_global_b256(dv_row, va);
+        } else {
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            *reinterpret_cast<uint4*>(dk_row + u * 8) = make_uint4(ka[u * 4], ka[u * 4 + 1], ka[u * 4 + 2], ka[u * 4 + 3]);
+            *reinterpret_cast<uint4*>(dv_row + u * 8) = make_uint4(va[u * 4], va[u * 4 + 1], va[u * 4 + 2], va[u * 4 + 3]);
+          }
         }
       }
       base += n_iters;

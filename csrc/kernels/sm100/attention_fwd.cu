@@ -293,7 +293,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t r[32];
         tmem_ld_32x32(tmem_O + lane_addr + c * 32, r);
         tmem_ld_wait();
-        if (live_row) {
+        if (live_row && aligned32(orow)) {   // 32 bytes per store: whole sectors of the row
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            uint32_t o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              o[e] = pack_bf16x2(__uint_as_float(r[u * 16 + e * 2]) * inv, __uint_as_float(r[u * 16 + e * 2 + 1]) * inv);
+            st_global_b256(orow + c * 32 + u * 16, o);
+          }
+        } else if (live_row) {
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             uint4 o;

@@ -113,20 +113,6 @@ __device__ __forceinline__ Unit decode_unit(const GemmKernelParams& p, int u) {
   return w;
 }
 
-// 256-bit global accesses (sm_100): one instruction moves 32 bytes per thread, so a row-per-lane store writes whole 32-byte
-// sectors (two 16-byte stores of different instructions would each write half a sector) in half the instructions.
-__device__ __forceinline__ void st_global_b256(void* ptr, const uint32_t (&w)[8]) {
-  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
-               "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
-               : "memory");
-}
-__device__ __forceinline__ void ld_global_b256(const void* ptr, uint32_t (&w)[8]) {
-  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
-               : "l"(ptr));
-}
-__device__ __forceinline__ bool aligned32(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 31) == 0; }
-
 // Values of one accumulator chunk: thread = one output row, r = its 32 consecutive fp32 accumulator columns starting
 // at column nc.  alpha, bias, GELU / SiLU, activation-gradient masks, residual.  With STAGE_PRE the pre-activation
 // (the side output kept for the backward pass) is returned in pre[] for the caller to store; otherwise it is written
