@@ -21,6 +21,9 @@ from .core.dtype import DTypeId, to_torch
 _seed = [0x1234ABCD, 0]      # seed, running offset (advanced by the number of values drawn)
 
 
+builtins_slice = slice      # the module defines its own ``slice`` further down (the reference's name for the op)
+
+
 def manual_seed(seed: int) -> None:
     _seed[0], _seed[1] = int(seed), 0
 
@@ -30,6 +33,8 @@ def _dev(device):
 
 
 def _dt(dtype):
+    if isinstance(dtype, str):      # "bf16", "f32", ... : the ids' short names
+        dtype = DTypeId(dtype)
     return to_torch(dtype) if isinstance(dtype, DTypeId) else (dtype or torch.float32)
 
 
@@ -97,6 +102,32 @@ def randn(*shape, dtype=None, device=None, mean: float = 0.0, std: float = 1.0):
     return _philox(n, True, _dev(device), mean, std).reshape(shape).to(_dt(dtype))
 
 
+def from_raw(ptr: int, shape, dtype=None, device=None, owner=None):
+    """A tensor over memory this process already owns (crates/incin-core/src/tensor/base.rs ``from_raw``): ``ptr`` is
+    a host address (``device`` = cpu) or a device address of the given CUDA device.  Nothing is copied and nothing is
+    freed: ``owner`` (any object) is kept alive with the tensor, the caller keeps the allocation alive otherwise."""
+    import ctypes
+    dt = _dt(dtype)
+    shape = tuple(int(s) for s in shape)
+    n = 1
+    for s in shape:
+        n *= s
+    nbytes = n * torch.empty((), dtype=dt).element_size()
+    dev = _dev(device)
+    if dev.type == "cuda":
+        class _Mem:
+            pass
+        m = _Mem()
+        m.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (int(ptr), False), "version": 3}
+        m._owner = owner
+        flat = torch.as_tensor(m, device=dev)
+    else:
+        buf = (ctypes.c_ubyte * nbytes).from_address(int(ptr))
+        buf._owner = owner
+        flat = torch.frombuffer(buf, dtype=torch.uint8)
+    return flat.view(dt).reshape(shape)
+
+
 def sample(distribution, shape, device=None):
     """Draw from a :mod:`incin_b200.distributions` object."""
     return distribution.sample(tuple(shape)).to(_dev(device))
@@ -116,6 +147,53 @@ def to_vec1(t: torch.Tensor) -> list:
 
 # ---- thin compositions (views or one or two kernels) -----------------------------------------------------------
 chunk, split, stack, expand = torch.chunk, torch.split, torch.stack, lambda t, *shape: t.expand(*shape)
+
+
+def flatten(t, start_dim: int = 0, end_dim: int = -1):
+    return t.flatten(start_dim, end_dim)
+
+
+def slice(t, dim: int, start: int, end: int, step: int = 1):      # noqa: A001 - the reference's name
+    """``t[..., start:end:step, ...]`` along ``dim`` (a view)."""
+    idx = [builtins_slice(None)] * t.dim()
+    idx[dim] = builtins_slice(start, end, step)
+    return t[tuple(idx)]
+
+
+def to_dtype(t, dtype):
+    return t.to(_dt(dtype))
+
+
+def where_cond(cond, a, b):
+    from .ops import tensor_ops as TO
+    return TO.where(cond, a, b)
+
+
+def gather(t, dim: int, index):
+    """Last-axis gathers of CUDA tensors run on the native kernel, every other case on the PyTorch op."""
+    from .ops import tensor_ops as TO
+    if dim in (-1, t.dim() - 1):
+        return TO.gather_last(t, index)
+    return torch.gather(t, dim, index)
+
+
+def scatter(t, dim: int, index, src):
+    from .ops import tensor_ops as TO
+    if dim in (-1, t.dim() - 1):
+        return TO.scatter_last(t.clone(), index, src)
+    return torch.scatter(t, dim, index, src)
+
+
+def _reduction(name):
+    def run(t, dim=None, keepdim: bool = False):
+        from .ops import tensor_ops as TO
+        return TO.reduce(t, name, dim, keepdim)
+    run.__name__ = name
+    run.__doc__ = f"``{name}`` over all elements or over ``dim`` (native reduction kernels on CUDA)."
+    return run
+
+
+sum, mean, max, min, argmax, argmin = (_reduction(n) for n in ("sum", "mean", "max", "min", "argmax", "argmin"))  # noqa: A001
 
 
 def unfold(t, dim, size, step):

@@ -529,3 +529,28 @@ def test_shape_algebra_fuzz_against_torch():
         except ShapeError:
             got = None
         assert got == ref, (a, b, got, ref)
+
+
+def test_tensor_api_names_of_the_reference_surface():
+    """Creation, reductions and manipulation under the reference's names (crates/incin-core/src/tensor/base.rs,
+    tensor/ops/{reduce,manipulation}.rs): thin front ends over the native ops and their PyTorch twins."""
+    import ctypes
+    import incin_b200.tensor as T
+    x = torch.arange(24.0).reshape(2, 3, 4)
+    assert T.flatten(x, 1).shape == (2, 12)
+    assert torch.equal(T.slice(x, 2, 1, 4, 2), x[:, :, 1:4:2]) and torch.equal(T.slice(x, 0, 1, 2), x[1:2])
+    assert T.to_dtype(x, "bf16").dtype == torch.bfloat16 and T.to_dtype(x, torch.float64).dtype == torch.float64
+    assert torch.equal(T.where_cond(x > 5, x, -x), torch.where(x > 5, x, -x))
+    idx = torch.tensor([[[0, 3], [1, 1], [2, 0]], [[3, 3], [0, 1], [2, 2]]])
+    assert torch.equal(T.gather(x, -1, idx), torch.gather(x, -1, idx))
+    assert torch.equal(T.gather(x, 1, idx[:, :, :1].expand(2, 3, 4) % 3), torch.gather(x, 1, idx[:, :, :1].expand(2, 3, 4) % 3))
+    z = torch.zeros(2, 3, 4)
+    assert torch.equal(T.scatter(z, -1, idx, torch.ones(2, 3, 2)), torch.scatter(z, -1, idx, torch.ones(2, 3, 2)))
+    assert float(T.sum(x)) == 276 and float(T.mean(x)) == 11.5 and float(T.max(x)) == 23 and float(T.min(x)) == 0
+    assert T.argmin(x.flatten()).item() == 0 and torch.equal(T.argmax(x, 2), x.argmax(2))
+    assert torch.equal(T.sum(x, 1, keepdim=True), x.sum(1, keepdim=True))
+    a = (ctypes.c_float * 6)(1, 2, 3, 4, 5, 6)
+    t = T.from_raw(ctypes.addressof(a), (2, 3), "f32", owner=a)
+    assert t.tolist() == [[1, 2, 3], [4, 5, 6]]
+    a[0] = 9                                                  # a view of the caller's memory, not a copy
+    assert t[0, 0].item() == 9
