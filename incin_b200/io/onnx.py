@@ -394,3 +394,6 @@ def import_model(path, limits: ResourceLimits = DEFAULT_LIMITS) -> OnnxGraph:
     limits.check("tensor count", len(g.initializers), limits.max_tensor_count)
     g.inputs = [(n, s) for n, s in g.inputs if n not in g.initializers]
     return g
+
+
+export_onnx, import_onnx = export_module, import_model      # the exporter / importer under the reference's names

@@ -149,3 +149,6 @@ def matmul_placement(a: Placement, b: Placement) -> Placement:
     if a.kind is K.SHARDED and b.kind is K.SHARDED and b.tensor_axis == 0 and a.mesh_axis is b.mesh_axis:
         return Partial(Reduction.SUM, a.mesh_axis)
     raise PlacementError(f"matmul of {a.token()} and {b.token()} has no distributed rule")
+
+
+LegalTransition = PlacementTransition      # the reference's name (crates/incin-core/src/dist/placement.rs)
