@@ -129,7 +129,7 @@ def main():
         for mode, cc in arms:
             tp = TensorParallel(dev, None, max_rows_per_rank=Ml, max_cols=max(H, cols), mode=mode, copy_ctas=cc)
             ag = _time(lambda: tp.gather_gemm(x, w_col), args.iters, dev)
-            rs = _time(lambda: tp.gemm_scatter(a, w_row), args.iters, dev) if cc == arms[1][1] or mode == "nccl" else None
+            rs = _time(lambda: tp.gemm_scatter(a, w_row), args.iters, dev)
             G.check_status(dev)
             # the fused kernels must reproduce the collective + GEMM pair (same bf16 inputs, fp32 accumulation)
             o_ag = tp.gather_gemm(x, w_col)[0].float()
