@@ -104,11 +104,17 @@ class TensorParallel:
             self.lane.launch(tag=tag, kind=kind, elements=elements, dtype=DTypeId.BF16)
 
     # ------------------------------------------------------------------------------------------------ primitives
-    COPY_CTA_GBS = 26.0      # measured: bytes one copy CTA moves through its shared-memory staging ring per second
+    # What one copy CTA of a fused launch sustains over NVLink while the rest of the GPU computes.  A copy-only kernel
+    # reaches 26-37 GB/s per CTA; inside the fused launches the best CTA counts of a tp = 4 sweep (12 / 20 / 32 / 44
+    # copy CTAs: all-gather 0.352 / 0.256 / 0.218 / 0.227 ms at shard width 384, 0.366 / 0.264 / 0.237 / 0.245 ms at
+    # 1408) correspond to about 18 GB/s for the pulling all-gather; the pushing reduce-scatter, whose GEMM is the
+    # heavier one at the same shard width, does best with fewer (0.228 / 0.230 / 0.235 ms with 20 / 32 / 44 at 1408).
+    COPY_CTA_GBS = 18.0
+    COPY_CTA_GBS_PUSH = 24.0
     LINK_GBS = 650.0
     GEMM_TFLOPS = 1200.0
 
-    def _copy_ctas(self, copy_bytes: float, link_bytes: float, flops: float) -> int:
+    def _copy_ctas(self, copy_bytes: float, link_bytes: float, flops: float, push: bool = False) -> int:
         """Who moves the data of a fused launch.  By default the number of CTAs of the launch that copy instead of
         computing: the count that minimises ``max(copy time, link time, GEMM time on the remaining SMs)``.  Negative
         (``INCIN_TP_COPY=warps``): one extra warp in every compute CTA moves the data and no SM is taken from the
@@ -122,7 +128,7 @@ class TensorParallel:
             return -max(1, int(os.environ.get("INCIN_TP_COPY_STAGES", "2")))   # operand stages that become the copy ring
         best, best_t = 8, float("inf")
         for c in range(4, 73, 4):
-            t = max(copy_bytes / (c * self.COPY_CTA_GBS * 1e9), link_bytes / (self.LINK_GBS * 1e9),
+            t = max(copy_bytes / (c * (self.COPY_CTA_GBS_PUSH if push else self.COPY_CTA_GBS) * 1e9), link_bytes / (self.LINK_GBS * 1e9),
                     flops / (self.GEMM_TFLOPS * 1e12 * (148 - c) / 148))
             if t < best_t * 0.97:      # prefer fewer copy CTAs unless more of them buy at least 3 %
                 best, best_t = c, t
@@ -200,7 +206,7 @@ class TensorParallel:
         G.gemm(a, w, stage, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=N, b_mn=b_mn,
                scatter={"world": self.world, "rank": self.rank, "rows_per_rank": Ml, "dst": buf.ptrs,
                         "slot_stride": Ml * N, "ready": ready,
-                        "copy_ctas": self._copy_ctas(remote, remote, 2.0 * M * N * Kd)})
+                        "copy_ctas": self._copy_ctas(remote, remote, 2.0 * M * N * Kd, push=True)})
         self.barrier()   # every peer's tiles for my rows have landed in my slot buffer
         out = torch.empty(Ml, N, dtype=torch.bfloat16, device=self.device)
         nat.check(nat.cuda().incin_slot_reduce(buf.ptr, Ml * N, self.world, nat.ptr(residual), out.data_ptr(), Ml, N, N,
