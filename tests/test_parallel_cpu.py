@@ -405,3 +405,35 @@ def test_plan_lane_checks_every_launch_and_placements_pick_the_kernel():
         parallel_linear(None, None, (None,), src=Sharded(1), dst=Replicated())          # only token rows are gathered
     with pytest.raises(PlacementError):
         parallel_linear(None, None, (None, None), src=Partial(Reduction.SUM), dst=Sharded(0))
+
+
+def test_copy_cta_heuristic_balances_copy_link_and_gemm():
+    """The number of copy CTAs of a fused launch: enough of them to keep up with the link when the GEMM is light, fewer
+    when the GEMM needs the SMs, fewer for the pushing reduce-scatter than for the pulling all-gather, and the explicit
+    settings win over the model."""
+    import incin_b200.parallel.tp as TP
+    pick = TP.TensorParallel._copy_ctas
+    class Stub:
+        copy_ctas = 0
+        COPY_CTA_GBS, COPY_CTA_GBS_PUSH = TP.TensorParallel.COPY_CTA_GBS, TP.TensorParallel.COPY_CTA_GBS_PUSH
+        LINK_GBS, GEMM_TFLOPS = TP.TensorParallel.LINK_GBS, TP.TensorParallel.GEMM_TFLOPS
+    s = Stub()
+    link = 112e6                                        # tp = 8, 32768 tokens, hidden 2048: bytes in per GPU
+    light, heavy = 2.0 * 32768 * 384 * 2048, 2.0 * 32768 * 1408 * 2048 * 4
+    c_light, c_heavy = pick(s, link, link, light), pick(s, link, link, heavy)
+    assert 24 <= c_light <= 48 and c_heavy < c_light and c_heavy >= 4
+    assert pick(s, link, link, light, push=True) < c_light
+    assert pick(s, link / 8, link / 8, light) <= c_light          # fewer bytes never ask for more copy CTAs
+    s.copy_ctas = 12
+    assert pick(s, link, link, light) == 12
+    s.copy_ctas = 0
+    import os
+    old = os.environ.get("INCIN_TP_COPY")
+    os.environ["INCIN_TP_COPY"] = "warps"
+    try:
+        assert pick(s, link, link, light) < 0                      # copy warps: minus the ring's operand stages
+    finally:
+        if old is None:
+            del os.environ["INCIN_TP_COPY"]
+        else:
+            os.environ["INCIN_TP_COPY"] = old
