@@ -309,14 +309,64 @@ class MemoryPlan:
 _ESZ = {"float32": 4, "bfloat16": 2, "float16": 2, "int64": 8, "int32": 4, "uint8": 1, "bool": 1, "float64": 8}
 
 
-def liveness(g: Graph) -> dict[int, tuple[int, int]]:
-    """node id -> (first, last) position it is alive; graph outputs live to the end."""
+@dataclass
+class SavedTensorSet:
+    """Values that forward ops stash for their backward recipes (crates/incin-core/src/compiled/alloc.rs:129-160): the
+    memory plan keeps them alive to the end of the backward pass instead of to their last forward use."""
+    values: set = field(default_factory=set)
+
+    def save(self, value_id: int) -> None:
+        self.values.add(value_id)
+
+    def __contains__(self, value_id: int) -> bool:
+        return value_id in self.values
+
+    def __len__(self) -> int:
+        return len(self.values)
+
+
+# what each op's backward reads: "in" = its inputs, "out" = its own output, "in0" = the first input only
+_SAVES = {"mm": "in", "bmm": "in", "addmm": "in", "linear": "in", "matmul": "in", "mul": "in", "div": "in", "pow": "in",
+          "maximum": "in", "minimum": "in", "where": "in", "relu": "out", "sigmoid": "out", "tanh": "out", "exp": "out",
+          "sqrt": "out", "rsqrt": "out", "_softmax": "out", "softmax": "out", "_log_softmax": "out",
+          "log_softmax": "out", "gelu": "in", "silu": "in", "log": "in", "abs": "in", "reciprocal": "out", "mish": "in",
+          "elu": "in", "softplus": "in", "native_layer_norm": "in", "layer_norm": "in", "convolution": "in",
+          "max_pool2d_with_indices": "in", "embedding": "in0", "nll_loss_forward": "in"}
+
+
+def saved_for_backward(g: Graph) -> SavedTensorSet:
+    """The values a backward pass over ``g`` will read again, by the rule table above (ops it does not know keep
+    their inputs: the safe side for a memory plan)."""
+    saved = SavedTensorSet()
+    for n in g.nodes:
+        if n.op == "input":
+            continue
+        rule = _SAVES.get(n.op, "in" if n.op not in ("add", "sub", "neg", "sum", "mean", "view", "reshape", "t",
+                                                     "transpose", "permute", "expand", "clone", "detach") else None)
+        if rule == "out":
+            saved.save(n.id)
+        elif rule == "in":
+            for i in n.inputs:
+                saved.save(i)
+        elif rule == "in0" and n.inputs:
+            saved.save(n.inputs[0])
+    return saved
+
+
+def liveness(g: Graph, saved: SavedTensorSet | None = None, backward_end: int | None = None) -> dict[int, tuple[int, int]]:
+    """node id -> (first, last) position it is alive; graph outputs live to the end.  With ``saved`` the saved values
+    stay alive until ``backward_end`` (default: the end of the graph), as ``extend_for_saved_tensors`` does."""
     last = {n.id: n.id for n in g.nodes}
     for n in g.nodes:
         for i in n.inputs:
             last[i] = max(last[i], n.id)
     for o in g.outputs:
         last[o] = len(g.nodes)
+    if saved is not None:
+        end = len(g.nodes) if backward_end is None else backward_end
+        for v in saved.values:
+            if v in last and last[v] < end:
+                last[v] = end
     return {n.id: (n.id, last[n.id]) for n in g.nodes}
 
 
@@ -337,9 +387,10 @@ def _plan_memory_native(g: Graph, live, size) -> "MemoryPlan | None":
     return MemoryPlan(offsets, peak, sum(size[n.id] for n in nodes if n.op != "input"))
 
 
-def plan_memory(g: Graph, align: int = 256) -> MemoryPlan:
-    """Greedy first-fit reuse of a single arena by liveness (``AllocationPlanner``)."""
-    live = liveness(g)
+def plan_memory(g: Graph, align: int = 256, saved: SavedTensorSet | None = None) -> MemoryPlan:
+    """Greedy first-fit reuse of a single arena by liveness (``AllocationPlanner``); ``saved`` keeps the values a
+    backward pass needs alive to the end."""
+    live = liveness(g, saved)
     size = {}
     for n in g.nodes:
         numel = 1
@@ -365,6 +416,74 @@ def plan_memory(g: Graph, align: int = 256) -> MemoryPlan:
         placed.append((off, size[n.id], f, l))
         peak = max(peak, off + size[n.id])
     return MemoryPlan(offsets, peak, sum(size[n.id] for n in g.nodes if n.op != "input"))
+
+
+# ------------------------------------------------------------------------------------------------ bounded plan tuning
+@dataclass
+class PlanTuningReport:
+    baseline_latency_us: float
+    tuned_latency_us: float
+    speedup_ratio: float
+    iterations_evaluated: int
+    is_bounded: bool
+    best: str = "baseline"
+    met_target: bool = False
+
+
+class BoundedPlanTuner:
+    """Scores a bounded number of execution variants of a traced graph and reports the best one against the unfused
+    single-launch-per-node baseline (crates/incin-core/src/compiled/tuning.rs:24-64, where the sweep is simulated).
+    Here the variants are real plan choices (no fusion, pointwise chains fused, row chains fused as well, and arena
+    alignments for the memory plan) and the score is an analytical latency: every launch costs ``launch_us`` and every
+    materialised tensor is written once and read once per consumer at ``gbs``; a fused group launches once and
+    materialises only its last value."""
+
+    def __init__(self, max_iterations: int = 8, min_speedup_target: float = 1.0, launch_us: float = 3.0, gbs: float = 6500.0):
+        if max_iterations < 1:
+            raise ValueError("max_iterations must be >= 1")
+        self.max_iterations, self.min_speedup_target = max_iterations, min_speedup_target
+        self.launch_us, self.gbs = launch_us, gbs
+
+    def _latency(self, g: Graph, groups: list[list[int]]) -> float:
+        cons = g.consumers()
+        member = {}
+        for k, grp in enumerate(groups):
+            for nid in grp:
+                member[nid] = k
+        launches = sum(1 for n in g.nodes if n.op != "input" and n.id not in member) + len(groups)
+        traffic = 0
+        for n in g.nodes:
+            numel = 1
+            for d in n.shape:
+                numel *= d
+            nbytes = numel * _ESZ.get(n.dtype, 4)
+            k = member.get(n.id)
+            internal = k is not None and n.id != groups[k][-1] and all(member.get(c) == k for c in cons[n.id])
+            if internal:
+                continue                                  # lives in registers inside the fused kernel
+            readers = len({member.get(c, ("n", c)) for c in cons[n.id]})   # a fused group reads an operand once
+            traffic += nbytes * ((0 if n.op == "input" else 1) + readers)
+        return launches * self.launch_us + traffic / (self.gbs * 1e3)
+
+    def tune_plan(self, g: Graph) -> PlanTuningReport:
+        variants = [("baseline", [])]
+        pw = [grp.nodes for grp in fusion_pass(g)]
+        if pw:
+            variants.append(("pointwise chains fused", pw))
+        rows = row_fusion_pass(g)
+        if rows:
+            taken = {nid for r in rows for nid in r.nodes}
+            variants.append(("pointwise and row chains fused", [r.nodes for r in rows] + [grp for grp in pw if not taken & set(grp)]))
+        baseline = self._latency(g, [])
+        best_name, best = "baseline", baseline
+        it = 0
+        for name, groups in variants[: self.max_iterations]:
+            it += 1
+            t = self._latency(g, groups)
+            if t < best:
+                best_name, best = name, t
+        speed = baseline / best if best > 0 else 1.0
+        return PlanTuningReport(baseline, best, speed, it, it <= self.max_iterations, best_name, speed >= self.min_speedup_target)
 
 
 # ------------------------------------------------------------------------------------------------ plans / artifacts

@@ -733,3 +733,29 @@ def test_row_fusion_pass_finds_and_lowers_softmax_chains():
     assert G.row_fusion_pass(g2) == []
     # a softmax over another axis is not a row op of this pass
     assert G.row_fusion_pass(G.trace(lambda a: torch.softmax(a + 1.0, 0), x)) == []
+
+
+def test_saved_tensors_extend_liveness_and_bounded_plan_tuner():
+    def f(x, w, m):
+        h = torch.relu(x @ w)
+        p = torch.softmax(h * 0.5 + m, -1)
+        return (p * h).sum()
+
+    x, w, m = torch.randn(16, 32), torch.randn(32, 64), torch.randn(64)
+    g = G.trace(f, x, w, m)
+    saved = G.saved_for_backward(g)
+    ops = {n.id: n.op for n in g.nodes}
+    relu_id = next(i for i, o in ops.items() if o == "relu")
+    sm_id = next(i for i, o in ops.items() if o in ("_softmax", "softmax"))
+    assert relu_id in saved and sm_id in saved and g.inputs[0] in saved          # relu / softmax outputs, matmul operands
+    plain, kept = G.liveness(g), G.liveness(g, saved)
+    assert kept[relu_id][1] == len(g.nodes) >= plain[relu_id][1]
+    assert all(kept[i][1] >= plain[i][1] for i in plain)
+    assert G.plan_memory(g, saved=saved).peak_bytes >= G.plan_memory(g).peak_bytes   # saved values cannot be reused
+    rep = G.BoundedPlanTuner(max_iterations=8, min_speedup_target=1.05).tune_plan(g)
+    assert rep.is_bounded and rep.iterations_evaluated <= 8 and rep.tuned_latency_us < rep.baseline_latency_us
+    assert rep.best != "baseline" and rep.met_target and abs(rep.speedup_ratio - rep.baseline_latency_us / rep.tuned_latency_us) < 1e-9
+    one = G.BoundedPlanTuner(max_iterations=1).tune_plan(g)                          # bound reached before any variant
+    assert one.iterations_evaluated == 1 and one.best == "baseline" and one.speedup_ratio == 1.0
+    with pytest.raises(ValueError):
+        G.BoundedPlanTuner(max_iterations=0)
