@@ -105,10 +105,20 @@ def plan(inputs: Sequence[TensorMeta], output: TensorMeta) -> IterationPlan:
     return IterationPlan(tuple(shape), operands, numel)
 
 
+@dataclass(frozen=True)
+class UnaryIterationPlan(IterationPlan):
+    """The plan of a one-input elementwise op (what :func:`unary_plan` returns)."""
+
+    @property
+    def input(self) -> "OperandLayout":
+        return self.operands[0]
+
+
 def unary_plan(x: TensorMeta, out: TensorMeta) -> IterationPlan:
     if tuple(x.shape) != tuple(out.shape):
         raise IterationError("a unary op keeps the shape")
-    return plan([x], out)
+    p = plan([x], out)
+    return UnaryIterationPlan(p.shape, p.operands, p.numel)
 
 
 def check_bounds(p: IterationPlan, allocation_elems: Sequence[int]) -> None:

@@ -241,6 +241,7 @@ class _Idx:
 
     def __getitem__(self, item):
         items = item if isinstance(item, tuple) else (item,)
+        items = tuple(i.to_python() if hasattr(i, "to_python") else i for i in items)      # Slice objects
         if sum(1 for i in items if i is Ellipsis) > 1:
             raise ShapeError(OperationKind.SLICE, "only one ellipsis is allowed")
         return IndexSpec(items)
@@ -279,3 +280,55 @@ class IndexSpec:
 
 
 idx = _Idx()
+
+
+# ---- the reference's typed index / shape-rule vocabulary as run-time objects (shapes/idx.rs, broadcast.rs, reshape.rs)
+@dataclass(frozen=True)
+class Slice:
+    """``start..end`` (optionally stepped) along one axis; ``idx[...]`` accepts it next to Python slices."""
+    start: int | None = None
+    end: int | None = None
+    step: int = 1
+
+    def to_python(self):
+        return slice(self.start, self.end, self.step if self.step != 1 else None)
+
+
+class _InferDim:
+    """The ``-1`` of a reshape target: the extent that the element count determines."""
+
+    def __index__(self):
+        return -1
+
+    def __repr__(self):
+        return "InferDim"
+
+
+InferDim = _InferDim()
+EllipsisDim = Ellipsis      # the reference's ``Ellipsis`` index: every axis not named otherwise
+
+
+@dataclass(frozen=True)
+class BroadcastShape:
+    """Two operand shapes and the shape their elementwise result has (ShapeError when they do not broadcast)."""
+    lhs: tuple
+    rhs: tuple
+
+    @property
+    def result(self) -> Shape:
+        return broadcast_shapes(self.lhs, self.rhs)
+
+
+@dataclass(frozen=True)
+class ReshapeShape:
+    """A source shape viewed as ``target`` (one extent may be ``InferDim`` / ``-1``)."""
+    source: tuple
+    target: tuple
+
+    @property
+    def result(self) -> tuple[int, ...]:
+        numel = 1
+        for d in self.source:
+            numel *= int(d)
+        return reshape_infer(numel, [int(d.__index__()) if hasattr(d, "__index__") else int(d) for d in self.target])
+

@@ -72,6 +72,99 @@ class TensorMeta:
         return self.offset + sum((d - 1) * abs(s) for d, s in zip(self.shape, self.strides) if d > 0)
 
 
+class Alignment(enum.IntEnum):
+    """Alignment classes of a tensor's first element (crates/incin-core/src/exec/meta.rs): what decides whether the
+    vector paths (16-byte accesses, TMA, 32-byte accesses of sm_100) may be used."""
+    BYTE = 1
+    WORD = 4
+    VEC16 = 16
+    VEC32 = 32
+    LINE = 128
+
+    @staticmethod
+    def of_address(addr: int) -> "Alignment":
+        for a in (Alignment.LINE, Alignment.VEC32, Alignment.VEC16, Alignment.WORD):
+            if addr % int(a) == 0:
+                return a
+        return Alignment.BYTE
+
+
+@dataclass(frozen=True)
+class AxisMask:
+    """The axes a reduction removes, as a bit mask over at most MAX_RANK axes (exec/spec.rs ``AxisMask``)."""
+    bits: int
+    rank: int
+
+    @staticmethod
+    def from_axes(axes: Sequence[int], rank: int) -> "AxisMask":
+        if not 0 < rank <= 8:
+            raise ShapeError(OperationKind.REDUCE, f"rank {rank} out of range")
+        bits = 0
+        for a in axes:
+            if not -rank <= a < rank:
+                raise ShapeError(OperationKind.REDUCE, f"axis {a} out of range for rank {rank}")
+            a %= rank
+            if bits >> a & 1:
+                raise ShapeError(OperationKind.REDUCE, f"axis {a} named twice")
+            bits |= 1 << a
+        return AxisMask(bits, rank)
+
+    @staticmethod
+    def all(rank: int) -> "AxisMask":
+        return AxisMask((1 << rank) - 1, rank)
+
+    def contains(self, axis: int) -> bool:
+        return bool(self.bits >> (axis % self.rank) & 1)
+
+    def axes(self) -> tuple[int, ...]:
+        return tuple(a for a in range(self.rank) if self.bits >> a & 1)
+
+    def __len__(self) -> int:
+        return bin(self.bits).count("1")
+
+    def reduced_shape(self, shape: Sequence[int], keepdim: bool = False) -> tuple[int, ...]:
+        if len(shape) != self.rank:
+            raise ShapeError(OperationKind.REDUCE, f"mask of rank {self.rank} applied to shape {tuple(shape)}")
+        return tuple(1 if self.contains(a) else d for a, d in enumerate(shape) if keepdim or not self.contains(a))
+
+
+@dataclass(frozen=True)
+class TensorHandle:
+    """What a backend needs to launch on a tensor without owning it: metadata, address, alignment class
+    (exec/request.rs ``TensorHandle``)."""
+    meta: TensorMeta
+    address: int
+    alignment: Alignment
+
+    @staticmethod
+    def of(t) -> "TensorHandle":
+        return TensorHandle(TensorMeta.of(t), int(t.data_ptr()), Alignment.of_address(int(t.data_ptr())))
+
+
+@dataclass(frozen=True)
+class ExecutionContext:
+    """Where and how a validated op runs: device, stream, and the execution / precision policies in force
+    (exec/context.rs:24).  ``current()`` snapshots the ambient state."""
+    device: DeviceId
+    stream: int
+    policy: object
+    precision: object
+
+    @staticmethod
+    def current(device=None) -> "ExecutionContext":
+        import torch
+        from .policy import current_policy
+        try:
+            from .policy import current_precision
+            precision = current_precision()
+        except ImportError:
+            precision = None
+        if device is None:
+            device = DeviceId(DeviceKind.CUDA, torch.cuda.current_device()) if torch.cuda.is_available() else DeviceId(DeviceKind.CPU)
+        stream = torch.cuda.current_stream().cuda_stream if device.kind is DeviceKind.CUDA and torch.cuda.is_available() else 0
+        return ExecutionContext(device, int(stream), current_policy(), precision)
+
+
 class ProofLevel(enum.Enum):
     STATIC = "static"          # every extent was known when the descriptor was built
     RANKED = "ranked"          # rank known, some extents runtime

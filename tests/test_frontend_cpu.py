@@ -554,3 +554,38 @@ def test_tensor_api_names_of_the_reference_surface():
     assert t.tolist() == [[1, 2, 3], [4, 5, 6]]
     a[0] = 9                                                  # a view of the caller's memory, not a copy
     assert t[0, 0].item() == 9
+
+
+def test_descriptor_vocabulary_axis_mask_alignment_handles_and_index_objects():
+    from incin_b200.core.iteration import UnaryIterationPlan, unary_plan
+    from incin_b200.core.shapes import BroadcastShape, InferDim, ReshapeShape, ShapeError, Slice, idx, s
+    from incin_b200.core.spec import Alignment, AxisMask, ExecutionContext, TensorHandle, TensorMeta
+    m = AxisMask.from_axes([-1, 0], 3)
+    assert m.axes() == (0, 2) and m.contains(2) and not m.contains(1) and len(m) == 2
+    assert m.reduced_shape((4, 5, 6)) == (5,) and m.reduced_shape((4, 5, 6), keepdim=True) == (1, 5, 1)
+    assert AxisMask.all(4).axes() == (0, 1, 2, 3)
+    for bad in ([1, 1], [3], [-4]):
+        with pytest.raises(ShapeError):
+            AxisMask.from_axes(bad, 3)
+    with pytest.raises(ShapeError):
+        m.reduced_shape((4, 5))
+    assert Alignment.of_address(256) is Alignment.LINE and Alignment.of_address(96) is Alignment.VEC32
+    assert Alignment.of_address(48) is Alignment.VEC16 and Alignment.of_address(12) is Alignment.WORD
+    assert Alignment.of_address(6) is Alignment.BYTE and Alignment.VEC32 > Alignment.VEC16
+    t = torch.zeros(4, 8)
+    h = TensorHandle.of(t)
+    assert h.meta.shape == (4, 8) and h.address == t.data_ptr() and h.alignment >= Alignment.VEC16
+    ctx = ExecutionContext.current()
+    assert ctx.policy is not None and ctx.stream >= 0
+    assert BroadcastShape((4, 1, 6), (5, 6)).result == s(4, 5, 6)
+    with pytest.raises(ShapeError):
+        BroadcastShape((4, 3), (5,)).result
+    assert ReshapeShape((4, 6), (InferDim, 3)).result == (8, 3) and ReshapeShape((4, 6), (2, 12)).result == (2, 12)
+    with pytest.raises(ShapeError):
+        ReshapeShape((4, 6), (InferDim, 5)).result
+    x = torch.arange(24).reshape(4, 6)
+    assert torch.equal(idx[Slice(1, 3), ...].apply(x), x[1:3]) and torch.equal(idx[..., Slice(0, 6, 2)].apply(x), x[:, 0:6:2])
+    with pytest.raises(ShapeError):
+        idx[Slice(2, 9)].apply(x)
+    p = unary_plan(TensorMeta.of(t), TensorMeta.of(t))
+    assert isinstance(p, UnaryIterationPlan) and p.input is p.operands[0]
