@@ -273,3 +273,35 @@ class HubApi:
     def from_pretrained(self, repo: str, filename: str = "model.safetensors"):
         from ..io import load_safetensors
         return load_safetensors(self.path(repo, filename))
+
+
+class Collate:
+    """A batch-assembly policy as an object (crates/incin-data/src/loader.rs ``Collate``): ``Collate()`` stacks samples
+    field by field like :func:`default_collate`; ``Collate(pad_value=0)`` first pads variable-length leading axes of each
+    field to the longest sample of the batch (token sequences), and ``Collate(fn)`` wraps any function."""
+
+    def __init__(self, fn: Callable | None = None, pad_value=None):
+        self.fn, self.pad_value = fn, pad_value
+
+    def __call__(self, samples: Sequence):
+        if self.fn is not None:
+            return self.fn(samples)
+        if self.pad_value is None:
+            return default_collate(samples)
+        first = samples[0]
+        fields = list(zip(*samples)) if isinstance(first, (tuple, list)) else [samples]
+        out = []
+        for col in fields:
+            col = [torch.as_tensor(c) for c in col]
+            if col[0].dim() == 0 or len({c.shape[0] for c in col}) == 1:
+                out.append(torch.stack(col))
+                continue
+            n = max(c.shape[0] for c in col)
+            padded = [torch.cat([c, c.new_full((n - c.shape[0],) + tuple(c.shape[1:]), self.pad_value)]) for c in col]
+            out.append(torch.stack(padded))
+        return tuple(out) if isinstance(first, (tuple, list)) else out[0]
+
+
+def from_pretrained(repo: str, filename: str = "model.safetensors", cache_dir=None):
+    """Tensors of a cached hub checkpoint (``HubApi(cache_dir).from_pretrained``)."""
+    return HubApi(cache_dir).from_pretrained(repo, filename)

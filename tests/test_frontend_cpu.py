@@ -589,3 +589,16 @@ def test_descriptor_vocabulary_axis_mask_alignment_handles_and_index_objects():
         idx[Slice(2, 9)].apply(x)
     p = unary_plan(TensorMeta.of(t), TensorMeta.of(t))
     assert isinstance(p, UnaryIterationPlan) and p.input is p.operands[0]
+
+
+def test_collate_objects_and_hub_lookup(tmp_path):
+    from incin_b200.data import Collate, DataLoader, TensorDataset, from_pretrained
+    pad = Collate(pad_value=-1)
+    b = pad([(torch.tensor([1, 2, 3]), torch.tensor(0)), (torch.tensor([4]), torch.tensor(1))])
+    assert b[0].tolist() == [[1, 2, 3], [4, -1, -1]] and b[1].tolist() == [0, 1]
+    assert Collate()([(torch.ones(2), 1), (torch.zeros(2), 0)])[0].shape == (2, 2)
+    assert Collate(lambda s: len(s))([1, 2, 3]) == 3
+    ds = TensorDataset(torch.arange(10.0).unsqueeze(1), torch.arange(10))
+    assert [x[1].tolist() for x in DataLoader(ds, 4, collate=Collate())] == [[0, 1, 2, 3], [4, 5, 6, 7], [8, 9]]
+    with pytest.raises(FileNotFoundError):                     # offline: only what is already in the cache resolves
+        from_pretrained("nobody/nothing", cache_dir=tmp_path)
