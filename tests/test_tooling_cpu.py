@@ -759,3 +759,22 @@ def test_saved_tensors_extend_liveness_and_bounded_plan_tuner():
     assert one.iterations_evaluated == 1 and one.best == "baseline" and one.speedup_ratio == 1.0
     with pytest.raises(ValueError):
         G.BoundedPlanTuner(max_iterations=0)
+
+
+def test_cli_doc_clippy_and_fix(tmp_path):
+    root = str(Path(__file__).resolve().parent.parent)
+    run = lambda *a: subprocess.run([sys.executable, "-m", "incin_b200", *a], capture_output=True, text=True, cwd=root, timeout=300)
+    d = run("doc", "tensor.from_raw")
+    assert d.returncode == 0 and "from_raw" in d.stdout and "Nothing is copied" in d.stdout
+    assert run("doc", "no.such.thing").returncode == 1
+    clean = run("clippy")                                                  # the package itself is clean
+    assert clean.returncode == 0 and "0 finding(s)" in clean.stdout
+    bad = tmp_path / "bad.py"
+    bad.write_text("def f(x=[]):\n    try:\n        pass\n    except:\n        pass\n")
+    c = run("clippy", str(bad))
+    assert c.returncode == 1 and "mutable default" in c.stdout and "bare `except:`" in c.stdout and "[fix:" not in c.stdout
+    f = run("fix", str(bad))
+    assert f.returncode == 1 and "[fix: `except Exception:`]" in f.stdout
+    broken = tmp_path / "broken.py"
+    broken.write_text("def f(:\n")
+    assert "error" in run("clippy", str(broken)).stdout
