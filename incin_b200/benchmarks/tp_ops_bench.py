@@ -124,10 +124,15 @@ def main():
         a = (torch.randn(M, cols, device=dev) * 0.1).bfloat16()
         flops = 2.0 * M * H * cols
         roof = max(flops / (args.gemm_peak_tflops * 1e12), link / 770e9) * 1e3
-        arms = [("nccl", 0)] + [("fused", int(c)) for c in args.copy_ctas.split(",")]
+        # a count, 0 (the per-call model) or "tune" (measured under the collective tuning contract, then timed)
+        arms = [("nccl", 0)] + [("fused", c if c == "tune" else int(c)) for c in args.copy_ctas.split(",")]
         ref = {}
         for mode, cc in arms:
-            tp = TensorParallel(dev, None, max_rows_per_rank=Ml, max_cols=max(H, cols), mode=mode, copy_ctas=cc)
+            tuned = cc == "tune"
+            tp = TensorParallel(dev, None, max_rows_per_rank=Ml, max_cols=max(H, cols), mode=mode, copy_ctas=0 if tuned else cc)
+            if tuned:
+                tp.tune_copy_ctas("gather", x, w_col)
+                tp.tune_copy_ctas("scatter", a, w_row)
             ag = _time(lambda: tp.gather_gemm(x, w_col), args.iters, dev)
             rs = _time(lambda: tp.gemm_scatter(a, w_row), args.iters, dev)
             G.check_status(dev)
@@ -142,7 +147,8 @@ def main():
                 assert e_ag == 0.0 and e_rs < 2e-2, (e_ag, e_rs)
             if rank == 0:
                 base = {"tp": world, "rows_per_rank": Ml, "hidden": H, "shard_cols": cols, "mode": mode,
-                        "copy_ctas": tp.copy_ctas if mode == "fused" else None, "link_mb_per_gpu": link / 2 ** 20,
+                        "copy_ctas": (sorted(tp._tuned.items()) if tuned else tp.copy_ctas) if mode == "fused" else None,
+                        "link_mb_per_gpu": link / 2 ** 20,
                         "roofline_ms": roof}
                 print(json.dumps({**base, "op": "all_gather_gemm", "ms": ag, "link_gbs": link / ag / 1e6,
                                   "of_roofline": roof / ag}), flush=True)

@@ -81,6 +81,7 @@ class TensorParallel:
             raise ValueError("rows per rank must be a multiple of 128 (one GEMM tile never straddles two owners)")
         self.rows, self.cols = max_rows_per_rank, max_cols
         self.copy_ctas = copy_ctas          # 0 = choose per call from the copy volume and the GEMM size
+        self._tuned: dict[tuple, int] = {}  # (op, rows per rank, K, N) -> copy CTAs committed by tune_copy_ctas
         shard_bytes = max_rows_per_rank * max_cols * 2
         ex = dict(session=session, ranks=ranks)
         self.shard = [SymmetricBuffer(shard_bytes, device).exchange(group, **ex) for _ in range(2)]
@@ -114,7 +115,57 @@ class TensorParallel:
     LINK_GBS = 650.0
     GEMM_TFLOPS = 1200.0
 
-    def _copy_ctas(self, copy_bytes: float, link_bytes: float, flops: float, push: bool = False) -> int:
+    def tune_copy_ctas(self, op: str, x: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False,
+                       candidates=(12, 20, 32, 44), samples: int = 3):
+        """Measure the copy-CTA count of one fused op for one shape under the collective tuning contract
+        (:mod:`incin_b200.tuning.collective`): every rank of the group times the same candidates in the same order,
+        the sample reports are exchanged, a candidate's score is the median over samples of the MAX over ranks, every
+        rank votes, and the winner is committed only if the votes agree.  Later calls of ``gather_gemm`` /
+        ``gemm_scatter`` with this shape use the committed count.  ``op``: ``"gather"`` (x = this rank's shard) or
+        ``"scatter"`` (x = the full rows).  Collective: every rank of the group must call it with the same arguments."""
+        import json
+        from ..tuning import collective as CT
+        assert self.mode == "fused" and op in ("gather", "scatter")
+        run = (lambda: self.gather_gemm(x, w, b_mn=b_mn)) if op == "gather" else (lambda: self.gemm_scatter(x, w, b_mn=b_mn))
+        N = w.shape[1] if b_mn else w.shape[0]
+        key = (op, x.shape[0] if op == "gather" else x.shape[0] // self.world, x.shape[1], N)
+        saved, reports = self.copy_ctas, []
+        try:
+            for c in candidates:
+                self.copy_ctas = int(c)
+                run()                                                # warm-up (and buffer parities advance in lockstep)
+                times = []
+                for _ in range(samples):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    run()
+                    e1.record()
+                    e1.synchronize()
+                    times.append(int(e0.elapsed_time(e1) * 1e6))
+                cand = CT.CollectiveCandidate(CT.CollectiveAlgorithm.ONE_SHOT_P2P, channels=int(c))
+                reports.append(CT.SampleReport(self.rank, cand.token(), tuple(times)))
+        finally:
+            self.copy_ctas = saved
+        mine = json.dumps([(r.rank, r.candidate, r.samples_ns) for r in reports])
+        everyone = self._exchange(mine)
+        all_reports = [CT.SampleReport(rk, cd, tuple(sm)) for blob in everyone for rk, cd, sm in json.loads(blob)]
+        vote = CT.local_vote(self.rank, all_reports)
+        votes = [CT.CommitVote(*json.loads(v)) for v in self._exchange(json.dumps([vote.rank, vote.candidate]))]
+        committed = CT.commit(self.world, all_reports, votes)       # raises TuningDisagreement unless unanimous
+        by_token = {CT.CollectiveCandidate(CT.CollectiveAlgorithm.ONE_SHOT_P2P, channels=int(c)).token(): int(c) for c in candidates}
+        self._tuned[key] = by_token[committed.candidate]
+        return committed
+
+    def _exchange(self, text: str) -> list[str]:
+        """One string per rank of the group, over the session's control channel when there is one."""
+        if self.session is not None and self.session.ctx is not None:
+            blobs = self.session.allgather(text.encode().ljust(4096, b"\0"), self.ranks)
+            return [b.rstrip(b"\0").decode() for b in blobs]
+        out = [None] * self.world
+        dist.all_gather_object(out, text, group=self.group)
+        return out
+
+    def _copy_ctas(self, copy_bytes: float, link_bytes: float, flops: float, push: bool = False, key=None) -> int:
         """Who moves the data of a fused launch.  By default the number of CTAs of the launch that copy instead of
         computing: the count that minimises ``max(copy time, link time, GEMM time on the remaining SMs)``.  Negative
         (``INCIN_TP_COPY=warps``): one extra warp in every compute CTA moves the data and no SM is taken from the
@@ -124,6 +175,8 @@ class TensorParallel:
         so dedicated CTAs, which keep that back-pressure on SMs that do nothing else, stay the default."""
         if self.copy_ctas:
             return self.copy_ctas
+        if key is not None and key in self._tuned:
+            return self._tuned[key]
         if os.environ.get("INCIN_TP_COPY", "ctas") == "warps":
             return -max(1, int(os.environ.get("INCIN_TP_COPY_STAGES", "2")))   # operand stages that become the copy ring
         best, best_t = 8, float("inf")
@@ -176,7 +229,7 @@ class TensorParallel:
         G.gemm(gathered, w, out, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=ldc, b_mn=b_mn, c_offset=c_offset,
                gather={"world": self.world, "rank": self.rank, "rows_per_rank": Ml, "src": src, "flags": flags,
                        "copy_ctas": self._copy_ctas((self.world - 1) * Ml * Kd * 2, (self.world - 1) * Ml * Kd * 2,
-                                                    2.0 * M * N * Kd)})
+                                                    2.0 * M * N * Kd, key=("gather", Ml, Kd, N))})
         return out, gathered
 
     def gemm_scatter(self, a: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False,
@@ -206,7 +259,8 @@ class TensorParallel:
         G.gemm(a, w, stage, M=M, N=N, K=Kd, lda=Kd, ldb=(N if b_mn else Kd), ldc=N, b_mn=b_mn,
                scatter={"world": self.world, "rank": self.rank, "rows_per_rank": Ml, "dst": buf.ptrs,
                         "slot_stride": Ml * N, "ready": ready,
-                        "copy_ctas": self._copy_ctas(remote, remote, 2.0 * M * N * Kd, push=True)})
+                        "copy_ctas": self._copy_ctas(remote, remote, 2.0 * M * N * Kd, push=True,
+                                                     key=("scatter", Ml, Kd, N))})
         self.barrier()   # every peer's tiles for my rows have landed in my slot buffer
         out = torch.empty(Ml, N, dtype=torch.bfloat16, device=self.device)
         nat.check(nat.cuda().incin_slot_reduce(buf.ptr, Ml * N, self.world, nat.ptr(residual), out.data_ptr(), Ml, N, N,

@@ -49,6 +49,16 @@ def main():
         dist.all_reduce(part)
         out[f"gemm_rs_{it}"] = rel(ys, part[rank * Ml:(rank + 1) * Ml] + res.float())
 
+    # ---- the copy-CTA count of a shape, measured under the collective tuning contract (same candidates on every
+    # rank, median of the max over ranks, unanimous commit); the committed count is then what the op launches with
+    committed = tp.tune_copy_ctas("gather", x_full[rank * Ml:(rank + 1) * Ml].contiguous(), w, candidates=(4, 8), samples=2)
+    out["tuned_gather"] = {"candidate": committed.candidate, "world": committed.world, "picked": tp._tuned[("gather", Ml, Kd, N)]}
+    y2, _ = tp.gather_gemm(x_full[rank * Ml:(rank + 1) * Ml].contiguous(), w)
+    out["ag_gemm_tuned"] = rel(y2, x_full.float() @ w.float().t())
+    tp.tune_copy_ctas("scatter", a, w, candidates=(4, 8), samples=2)
+    out["tuned_scatter_picked"] = tp._tuned[("scatter", Ml, Kd, N)]
+    G.check_status()
+
     # ---- model level
     # the first model runs under the repo's own control plane (plan agreed before any peer mapping, handles over the
     # rendezvous channel, every fused launch checked against the plan cursor); the second on the torch.distributed plumbing
@@ -95,6 +105,7 @@ def main():
         ok = ok and all(abs(a - b) < 5e-2 for a, b in zip(r["loss_ref"], r["loss_tp"])) and r["loss_tp"][-1] < r["loss_tp"][0]
         ok = ok and r["q_w_diff"] < 5e-2 and r["embed_diff"] < 5e-2
     ok = ok and out.get("plan_validated_launches", 0) >= 4 * 8 * 2 and out.get("plan_completed_each_step", False)
+    ok = ok and out["tuned_gather"]["picked"] in (4, 8) and out["tuned_gather"]["world"] == world and out["tuned_scatter_picked"] in (4, 8)
     out["ok"] = ok
     if rank == 0:
         print("TP_RESULT " + json.dumps(out), flush=True)
