@@ -82,6 +82,10 @@ class TensorParallel:
         self.rows, self.cols = max_rows_per_rank, max_cols
         self.copy_ctas = copy_ctas          # 0 = choose per call from the copy volume and the GEMM size
         self._tuned: dict[tuple, int] = {}  # (op, rows per rank, K, N) -> copy CTAs committed by tune_copy_ctas
+        # INCIN_TP_AUTOTUNE=1: a shape seen for the first time outside a graph capture is tuned on the spot (every rank
+        # of the group reaches the same op in the same order, so the measurement is collective by construction)
+        self.autotune = os.environ.get("INCIN_TP_AUTOTUNE") == "1"
+        self._tuning = False
         shard_bytes = max_rows_per_rank * max_cols * 2
         ex = dict(session=session, ranks=ranks)
         self.shard = [SymmetricBuffer(shard_bytes, device).exchange(group, **ex) for _ in range(2)]
@@ -130,6 +134,7 @@ class TensorParallel:
         N = w.shape[1] if b_mn else w.shape[0]
         key = (op, x.shape[0] if op == "gather" else x.shape[0] // self.world, x.shape[1], N)
         saved, reports = self.copy_ctas, []
+        self._tuning = True
         try:
             for c in candidates:
                 self.copy_ctas = int(c)
@@ -146,6 +151,7 @@ class TensorParallel:
                 reports.append(CT.SampleReport(self.rank, cand.token(), tuple(times)))
         finally:
             self.copy_ctas = saved
+            self._tuning = False
         mine = json.dumps([(r.rank, r.candidate, r.samples_ns) for r in reports])
         everyone = self._exchange(mine)
         all_reports = [CT.SampleReport(rk, cd, tuple(sm)) for blob in everyone for rk, cd, sm in json.loads(blob)]
@@ -155,6 +161,11 @@ class TensorParallel:
         by_token = {CT.CollectiveCandidate(CT.CollectiveAlgorithm.ONE_SHOT_P2P, channels=int(c)).token(): int(c) for c in candidates}
         self._tuned[key] = by_token[committed.candidate]
         return committed
+
+    def _maybe_tune(self, op: str, x, w, b_mn: bool, key) -> None:
+        if self.autotune and not self._tuning and not self.copy_ctas and key not in self._tuned and \
+                not torch.cuda.is_current_stream_capturing():
+            self.tune_copy_ctas(op, x.detach(), w.detach(), b_mn=b_mn)
 
     def _exchange(self, text: str) -> list[str]:
         """One string per rank of the group, over the session's control channel when there is one."""
@@ -210,6 +221,7 @@ class TensorParallel:
             return out, gathered
         if Ml % 128 or Ml > self.rows or Kd > self.cols or Kd % 8:
             raise ValueError(f"shard [{Ml}, {Kd}] does not fit the tensor-parallel buffers [{self.rows}, {self.cols}]")
+        self._maybe_tune("gather", x_shard, w, b_mn, ("gather", Ml, Kd, w.shape[1] if b_mn else w.shape[0]))
         p = self._shard_parity
         self._shard_parity ^= 1
         buf = self.shard[p]
@@ -248,6 +260,7 @@ class TensorParallel:
             return out if residual is None else out + residual
         if M % self.world or Ml % 128 or Ml > self.rows or N > self.cols or N % 8:
             raise ValueError(f"product [{M}, {N}] does not fit the tensor-parallel buffers")
+        self._maybe_tune("scatter", a, w, b_mn, ("scatter", Ml, Kd, N))
         p = self._slot_parity
         self._slot_parity ^= 1
         buf = self.slots[p]
