@@ -74,6 +74,12 @@ def main():
         tpm = TensorParallel(dev, max_rows_per_rank=B * T // world, max_cols=cfg.d_model, session=sess,
                              plan=tensor_parallel_plan(cfg, session.mesh, rank, B * T) if sess else None,
                              ranks=list(range(world)) if sess else None)
+        if sess is not None:
+            # the same measurement with the reports and votes travelling over the session's control channel
+            xs = torch.randn(B * T // world, cfg.d_model, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(dev)
+            ws = (torch.randn(384, cfg.d_model, generator=torch.Generator().manual_seed(6)) * 0.1).to(torch.bfloat16).to(dev)
+            c2 = tpm.tune_copy_ctas("gather", xs, ws, candidates=(4, 8), samples=2)
+            out["tuned_over_session"] = c2.world == world and tpm._tuned[("gather", B * T // world, cfg.d_model, 384)] in (4, 8)
         gg = torch.Generator().manual_seed(3)
         tok = torch.randint(0, cfg.vocab_size, (B, T), generator=gg).to(dev)
         tgt = torch.randint(0, cfg.vocab_size, (B, T), generator=gg).to(dev)
@@ -105,6 +111,7 @@ def main():
         ok = ok and all(abs(a - b) < 5e-2 for a, b in zip(r["loss_ref"], r["loss_tp"])) and r["loss_tp"][-1] < r["loss_tp"][0]
         ok = ok and r["q_w_diff"] < 5e-2 and r["embed_diff"] < 5e-2
     ok = ok and out.get("plan_validated_launches", 0) >= 4 * 8 * 2 and out.get("plan_completed_each_step", False)
+    ok = ok and out.get("tuned_over_session", False)
     ok = ok and out["tuned_gather"]["picked"] in (4, 8) and out["tuned_gather"]["world"] == world and out["tuned_scatter_picked"] in (4, 8)
     out["ok"] = ok
     if rank == 0:
