@@ -170,6 +170,8 @@ class TensorParallel:
     def _exchange(self, text: str) -> list[str]:
         """One string per rank of the group, over the session's control channel when there is one."""
         if self.session is not None and self.session.ctx is not None:
+            if len(text.encode()) > 4096:     # the control channel gathers equal-size blobs
+                raise ValueError("tuning report too large for one control message: fewer candidates or samples")
             blobs = self.session.allgather(text.encode().ljust(4096, b"\0"), self.ranks)
             return [b.rstrip(b"\0").decode() for b in blobs]
         out = [None] * self.world
