@@ -111,7 +111,45 @@ class TopologyProbe(Protocol):
 
 
 class CudaTopologyProbe:
-    """Real probe: CUDA device properties + peer-access capability (NVSwitch answers HIGH_BANDWIDTH)."""
+    """Real probe: CUDA device properties + peer-access capability, refined by NVML where it is importable: a pair that
+    NVML reports as NVLink-connected is HIGH_BANDWIDTH, a pair that can only reach each other's memory over PCIe is
+    PEER_CAPABLE, a pair without peer access bounces through the host.  NVML is only READ (P2P status queries);
+    ``nvml`` takes a stand-in module for tests."""
+
+    def __init__(self, nvml=None):
+        self._nvml, self._nvml_ready = nvml, nvml is not None
+        if nvml is None:
+            try:
+                import pynvml
+                pynvml.nvmlInit()
+                self._nvml, self._nvml_ready = pynvml, True
+            except Exception:           # no NVML on this machine: peer access alone decides
+                self._nvml, self._nvml_ready = None, False
+
+    def _nvlink(self, a: int, b: int) -> bool | None:
+        """True / False from NVML, None when NVML cannot say."""
+        if not self._nvml_ready:
+            return None
+        n = self._nvml
+        try:
+            ha, hb = self._handle(a), self._handle(b)
+            return n.nvmlDeviceGetP2PStatus(ha, hb, n.NVML_P2P_CAPS_INDEX_NVLINK) == n.NVML_P2P_STATUS_OK
+        except Exception:
+            return None
+
+    def _handle(self, cuda_index: int):
+        """NVML handle of a CUDA device: by UUID where both sides know it (NVML numbers every GPU of the machine, CUDA
+        only the visible ones), by index otherwise."""
+        n = self._nvml
+        by_uuid = getattr(n, "nvmlDeviceGetHandleByUUID", None)
+        if by_uuid is not None:
+            try:
+                import torch
+                uuid = str(torch.cuda.get_device_properties(cuda_index).uuid)
+                return by_uuid(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+            except Exception:
+                pass
+        return n.nvmlDeviceGetHandleByIndex(cuda_index)
 
     def identity(self, device: DeviceId) -> DeviceIdentity | None:
         import torch
@@ -129,7 +167,10 @@ class CudaTopologyProbe:
             ok = torch.cuda.can_device_access_peer(a.index, b.index)
         except Exception:
             return LinkClass.UNREACHABLE
-        return LinkClass.HIGH_BANDWIDTH if ok else LinkClass.HOST_BOUNCE
+        if not ok:
+            return LinkClass.HOST_BOUNCE
+        nvlink = self._nvlink(a.index, b.index)
+        return LinkClass.PEER_CAPABLE if nvlink is False else LinkClass.HIGH_BANDWIDTH
 
 
 class BindErrorKind(enum.Enum):

@@ -437,3 +437,28 @@ def test_copy_cta_heuristic_balances_copy_link_and_gemm():
             del os.environ["INCIN_TP_COPY"]
         else:
             os.environ["INCIN_TP_COPY"] = old
+
+
+def test_cuda_topology_probe_reads_link_classes_from_nvml(monkeypatch):
+    """NVLink-connected pairs are HIGH_BANDWIDTH, PCIe-only peers PEER_CAPABLE, no peer access HOST_BOUNCE; NVML is only
+    queried (a stand-in module plays it here) and its absence falls back to peer access alone."""
+    import types
+    from incin_b200.core import Cuda
+    from incin_b200.parallel import mesh as M
+    calls = []
+    fake = types.SimpleNamespace(NVML_P2P_CAPS_INDEX_NVLINK=2, NVML_P2P_STATUS_OK=0,
+                                 nvmlDeviceGetHandleByIndex=lambda i: ("h", i))
+
+    def status(ha, hb, cap):
+        calls.append((ha[1], hb[1], cap))
+        return 0 if {ha[1], hb[1]} == {0, 1} else 5          # only GPUs 0 and 1 share NVLink
+    fake.nvmlDeviceGetP2PStatus = status
+    monkeypatch.setattr(torch.cuda, "can_device_access_peer", lambda a, b: (a, b) != (0, 3) and (a, b) != (3, 0))
+    probe = M.CudaTopologyProbe(nvml=fake)
+    assert probe.link(Cuda(0), Cuda(0)) is M.LinkClass.SAME_DEVICE
+    assert probe.link(Cuda(0), Cuda(1)) is M.LinkClass.HIGH_BANDWIDTH
+    assert probe.link(Cuda(0), Cuda(2)) is M.LinkClass.PEER_CAPABLE
+    assert probe.link(Cuda(0), Cuda(3)) is M.LinkClass.HOST_BOUNCE
+    assert all(cap == 2 for _, _, cap in calls) and (0, 3, 2) not in calls        # no NVML query without peer access
+    broken = types.SimpleNamespace(nvmlDeviceGetHandleByIndex=lambda i: (_ for _ in ()).throw(RuntimeError("nvml down")))
+    assert M.CudaTopologyProbe(nvml=broken).link(Cuda(0), Cuda(2)) is M.LinkClass.HIGH_BANDWIDTH   # NVML cannot say
