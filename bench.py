@@ -20,6 +20,8 @@ One rank prints one JSON line.
 
 After the two timed regions (which are unchanged by it) the same line carries an ``extra`` object with the other
 benchmark configurations, measured on the same box, device-timed, max over ranks, synthetic data:
+  * 1 GPU: the CPU MLP (784-256-10, batch 64, SGD, 100 steps on the host's C++ tape autograd; steps/s next to PyTorch
+    CPU and the largest difference between the two loss curves; wall-clock, no GPU involved);
   * 1 GPU: the causal attention micro-benchmark (B 8, H 32, S 4096, D 128: TFLOP/s, and max abs error against an fp32
     CPU reference of one slice) next to PyTorch SDPA, and a table of the step's GEMM shapes against cuBLAS;
   * N > 1 GPUs: Llama-1.1B with tensor parallelism over the N GPUs (16 x 2048 tokens), fused-collective arm and NCCL arm;
@@ -167,6 +169,17 @@ def extra_measurements(args, world: int, rank: int, device, ctx=None) -> dict:
             return [{"shape": r["shape"], "mnk": [r["M"], r["N"], r["K"]], "layout": r["kind"], "ms": r["ms"],
                      "tflops": r["tflops"], "cublas_ms": r["cublas_ms"], "cublas_tflops": r["cublas_tflops"]} for r in rows]
 
+        def cpu_mlp():
+            from incin_b200.models import mlp
+            ours, t_ours = min((mlp.train_native(steps=100) for _ in range(3)), key=lambda r: r[1])
+            lib, t_lib = min((mlp.train_torch(steps=100) for _ in range(3)), key=lambda r: r[1])
+            return {"config": "CPU MLP 784-256(ReLU)-10, batch 64, fp32, seed 0, softmax cross-entropy, SGD lr 0.01, "
+                              "100 steps; host only (C++ tape autograd), best of 3",
+                    "steps_per_s": round(100 / t_ours, 1), "torch_cpu_steps_per_s": round(100 / t_lib, 1),
+                    "loss_first": ours[0], "loss_last": ours[-1],
+                    "max_loss_diff_vs_torch_cpu": max(abs(a - b) for a, b in zip(ours, lib))}
+
+        guarded("cpu_mlp_784_256_10", cpu_mlp)
         guarded("attention_b8_h32_s4096_d128", attention)
         guarded("gemm_vs_cublas", gemm)
     else:

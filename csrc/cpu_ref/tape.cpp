@@ -7,12 +7,18 @@
 // reverse, calls each closure once and ACCUMULATES contributions per input id
 // (fan-out sums), draining the tape.  A non-finite gradient is reported
 // according to the NaN policy instead of being silently propagated.
+#include <unistd.h>
+
 #include <atomic>
+#include <condition_variable>
+#include <mutex>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
 #include <functional>
+#include <algorithm>
 #include <memory>
+#include <thread>
 #include <unordered_map>
 #include <vector>
 
@@ -73,41 +79,201 @@ void push(Node n) {
   if (g_tape.grad_mode) g_tape.nodes.push_back(std::move(n));
 }
 
+// C[M,N] += A[M,K] * B[K,N].  A is addressed through (a_rs, a_cs) so a transposed left operand needs no copy; B
+// and C are row-major.  Every output element accumulates its K products one at a time in ascending k, with
+// separate multiply and add (the file is compiled without contraction), so the result does not depend on the
+// tile sizes, on the instruction set the loader picked, or on how rows were split over threads.
+typedef float v8f __attribute__((vector_size(32), aligned(4), may_alias));
+
+// MR rows by NV*8 columns held in vector registers over the whole K loop
+template <int MR, int NV>
+__attribute__((always_inline)) inline void gemm_tile_v(const float* A, int64_t a_rs, int64_t a_cs, const float* B,
+                                                       int64_t ldb, float* C, int64_t ldc, int64_t K) {
+  v8f acc[MR][NV];
+  for (int r = 0; r < MR; ++r)
+    for (int c = 0; c < NV; ++c) acc[r][c] = *(const v8f*)(C + r * ldc + 8 * c);
+  for (int64_t k = 0; k < K; ++k) {
+    v8f b[NV];
+    for (int c = 0; c < NV; ++c) b[c] = *(const v8f*)(B + k * ldb + 8 * c);
+    for (int r = 0; r < MR; ++r) {
+      const float a = A[r * a_rs + k * a_cs];
+      const v8f av = {a, a, a, a, a, a, a, a};
+      for (int c = 0; c < NV; ++c) acc[r][c] += av * b[c];
+    }
+  }
+  for (int r = 0; r < MR; ++r)
+    for (int c = 0; c < NV; ++c) *(v8f*)(C + r * ldc + 8 * c) = acc[r][c];
+}
+
+template <int MR>
+__attribute__((always_inline)) inline void gemm_tile_1(const float* A, int64_t a_rs, int64_t a_cs, const float* B,
+                                                       int64_t ldb, float* C, int64_t ldc, int64_t K) {
+  for (int r = 0; r < MR; ++r) {
+    float acc = C[r * ldc];
+    for (int64_t k = 0; k < K; ++k) acc += A[r * a_rs + k * a_cs] * B[k * ldb];
+    C[r * ldc] = acc;
+  }
+}
+
+// NV*8 columns at a time: the K x 16 panel of B stays in cache while every row block of [i0, i1) passes over it
+template <int NV>
+__attribute__((always_inline)) inline void gemm_panel(const float* A, int64_t a_rs, int64_t a_cs, const float* B,
+                                                      float* C, int64_t i0, int64_t i1, int64_t N, int64_t K) {
+  constexpr int MR = 4;
+  int64_t i = i0;
+  for (; i + MR <= i1; i += MR) gemm_tile_v<MR, NV>(A + i * a_rs, a_rs, a_cs, B, N, C + i * N, N, K);
+  for (; i < i1; ++i) gemm_tile_v<1, NV>(A + i * a_rs, a_rs, a_cs, B, N, C + i * N, N, K);
+}
+
+__attribute__((target_clones("avx2", "avx", "default"))) void gemm_rows(const float* A, int64_t a_rs, int64_t a_cs,
+                                                                        const float* B, float* C, int64_t i0,
+                                                                        int64_t i1, int64_t N, int64_t K) {
+  int64_t j = 0;
+  for (; j + 16 <= N; j += 16) gemm_panel<2>(A, a_rs, a_cs, B + j, C + j, i0, i1, N, K);
+  for (; j + 8 <= N; j += 8) gemm_panel<1>(A, a_rs, a_cs, B + j, C + j, i0, i1, N, K);
+  for (; j < N; ++j)
+    for (int64_t i = i0; i < i1; ++i) gemm_tile_1<1>(A + i * a_rs, a_rs, a_cs, B + j, N, C + i * N + j, N, K);
+}
+
+// A small pool of sleeping workers splits the rows of one product.  Starting threads per product costs about as
+// much as the products of a small MLP; waking sleeping ones costs a few microseconds.  A forked child has no
+// workers (threads do not survive fork) and computes on the calling thread.
+class RowPool {
+ public:
+  static RowPool& get() {
+    static RowPool p;
+    return p;
+  }
+  // runs fn(lo, hi) over [0, M) in `parts` row ranges whose sizes are multiples of `align`
+  void run(int64_t M, int64_t parts, int64_t align, const std::function<void(int64_t, int64_t)>& fn) {
+    parts = std::min<int64_t>(parts, (int64_t)workers_.size() + 1);
+    if (parts <= 1 || owner_ != getpid() || busy_.exchange(true)) {  // nested or concurrent callers run inline
+      fn(0, M);
+      return;
+    }
+    const int64_t per = ((M + parts - 1) / parts + align - 1) / align * align;
+    {
+      std::lock_guard<std::mutex> l(m_);
+      fn_ = &fn;
+      M_ = M;
+      per_ = per;
+      next_.store(1);
+      n_parts_ = (M + per - 1) / per;
+      pending_.store(n_parts_ - 1);
+      ++gen_;
+    }
+    cv_.notify_all();
+    fn(0, std::min(M, per));
+    for (int spins = 0; pending_.load(std::memory_order_acquire) > 0; ++spins)
+      if (spins > 2000) std::this_thread::yield();
+    busy_.store(false);
+  }
+
+ private:
+  RowPool() : owner_(getpid()) {
+    const unsigned hc = std::max(1u, std::thread::hardware_concurrency());
+    for (unsigned i = 1; i < std::min(hc, 8u); ++i) workers_.emplace_back([this] { work(); });
+  }
+  ~RowPool() {
+    if (owner_ == getpid()) {
+      {
+        std::lock_guard<std::mutex> l(m_);
+        stop_ = true;
+      }
+      cv_.notify_all();
+      for (auto& t : workers_) t.join();
+    } else {
+      for (auto& t : workers_) t.detach();
+    }
+  }
+  void work() {
+    uint64_t seen = 0;
+    for (;;) {
+      const std::function<void(int64_t, int64_t)>* fn;
+      int64_t M, per, n_parts;
+      {
+        std::unique_lock<std::mutex> l(m_);
+        cv_.wait(l, [&] { return stop_ || gen_ != seen; });
+        if (stop_) return;
+        seen = gen_;
+        fn = fn_;
+        M = M_;
+        per = per_;
+        n_parts = n_parts_;
+      }
+      for (;;) {
+        const int64_t part = next_.fetch_add(1);
+        if (part >= n_parts) break;
+        (*fn)(part * per, std::min(M, (part + 1) * per));
+        pending_.fetch_sub(1, std::memory_order_release);
+      }
+    }
+  }
+  std::vector<std::thread> workers_;
+  std::mutex m_;
+  std::condition_variable cv_;
+  const std::function<void(int64_t, int64_t)>* fn_ = nullptr;
+  int64_t M_ = 0, per_ = 0, n_parts_ = 0;
+  std::atomic<int64_t> next_{0}, pending_{0};
+  std::atomic<bool> busy_{false};
+  uint64_t gen_ = 0;
+  bool stop_ = false;
+  pid_t owner_;
+};
+
+void gemm_acc(const float* A, int64_t a_rs, int64_t a_cs, const float* B, float* C, int64_t M, int64_t N,
+              int64_t K) {
+  const int64_t flops = 2 * M * N * K;
+  const int64_t parts = std::min<int64_t>({8, M / 8, flops >> 20});
+  if (parts <= 1) {
+    gemm_rows(A, a_rs, a_cs, B, C, 0, M, N, K);
+    return;
+  }
+  RowPool::get().run(M, parts, 4,
+                     [&](int64_t lo, int64_t hi) { gemm_rows(A, a_rs, a_cs, B, C, lo, hi, N, K); });
+}
+
+// out[C,R] = in[R,C]^T in 16x16 blocks (both sides stay within a few cache lines per block)
+void transpose(const float* in, float* out, int64_t R, int64_t Cn) {
+  constexpr int64_t TB = 16;
+  for (int64_t r0 = 0; r0 < R; r0 += TB)
+    for (int64_t c0 = 0; c0 < Cn; c0 += TB)
+      for (int64_t r = r0; r < std::min(R, r0 + TB); ++r)
+        for (int64_t c = c0; c < std::min(Cn, c0 + TB); ++c) out[c * R + r] = in[r * Cn + c];
+}
+
 // y[M,N] = x[M,K] * w[N,K]^T + b[N]
 TP linear(const TP& x, const TP& w, const TP& b) {
   const int64_t M = x->rows, K = x->cols, N = w->rows;
   TP y = make(M, N, true);
-  // y[i, :] = b + sum_k x[i, k] * wt[k, :]: the inner loop runs over independent outputs, so it vectorises
-  // without reassociating the reduction (bit-stable across compilers, unlike a dot-product inner loop)
-  std::vector<float> wt((size_t)(K * N));
-  for (int64_t j = 0; j < N; ++j)
-    for (int64_t k = 0; k < K; ++k) wt[(size_t)(k * N + j)] = w->v[(size_t)(j * K + k)];
-  for (int64_t i = 0; i < M; ++i) {
-    float* yr = &y->v[(size_t)(i * N)];
-    for (int64_t j = 0; j < N; ++j) yr[j] = b ? b->v[(size_t)j] : 0.f;
-    const float* xr = &x->v[(size_t)(i * K)];
-    for (int64_t k = 0; k < K; ++k) {
-      const float xv = xr[k];
-      const float* wr = &wt[(size_t)(k * N)];
-      for (int64_t j = 0; j < N; ++j) yr[j] += xv * wr[j];
-    }
+  // The vector loop runs over the columns of a row-major right operand, so one side has to be transposed:
+  // either w (N*K elements) for y = x * w^T, or x and the result (M*(K+N)) for y^T = w * x^T.  Both forms add
+  // the K products of an output in the same order; the cheaper transposition wins.
+  if (M * (K + N) < N * K) {
+    std::vector<float> xt((size_t)(K * M)), yt((size_t)(N * M));
+    transpose(x->v.data(), xt.data(), M, K);
+    for (int64_t j = 0; j < N; ++j)
+      for (int64_t i = 0; i < M; ++i) yt[(size_t)(j * M + i)] = b ? b->v[(size_t)j] : 0.f;
+    gemm_acc(w->v.data(), K, 1, xt.data(), yt.data(), N, M, K);
+    transpose(yt.data(), y->v.data(), N, M);
+  } else {
+    std::vector<float> wt((size_t)(K * N));
+    transpose(w->v.data(), wt.data(), N, K);
+    for (int64_t i = 0; i < M; ++i)
+      for (int64_t j = 0; j < N; ++j) y->v[(size_t)(i * N + j)] = b ? b->v[(size_t)j] : 0.f;
+    gemm_acc(x->v.data(), K, 1, wt.data(), y->v.data(), M, N, K);
   }
   std::vector<uint64_t> ins = {x->id, w->id};
   if (b) ins.push_back(b->id);
   push({y->id, ins, [x, w, b, M, N, K](const std::vector<float>& g) {
           std::vector<std::vector<float>> out;
-          std::vector<float> dx((size_t)(M * K), 0.f), dw((size_t)(N * K), 0.f);
-          for (int64_t i = 0; i < M; ++i)
-            for (int64_t j = 0; j < N; ++j) {
-              const float gy = g[(size_t)(i * N + j)];
-              if (gy == 0.f) continue;
-              const float *xr = &x->v[(size_t)(i * K)], *wr = &w->v[(size_t)(j * K)];
-              float *dxr = &dx[(size_t)(i * K)], *dwr = &dw[(size_t)(j * K)];
-              for (int64_t k = 0; k < K; ++k) {
-                dxr[k] += gy * wr[k];
-                dwr[k] += gy * xr[k];
-              }
-            }
+          // dx[M,K] = g[M,N] * w[N,K] (skipped for an input that takes no gradient); dw[N,K] = g^T[N,M] * x[M,K]
+          std::vector<float> dx, dw((size_t)(N * K), 0.f);
+          if (x->requires_grad) {
+            dx.assign((size_t)(M * K), 0.f);
+            gemm_acc(g.data(), N, 1, w->v.data(), dx.data(), M, K, N);
+          }
+          gemm_acc(g.data(), 1, N, x->v.data(), dw.data(), N, K, M);
           out.push_back(std::move(dx));
           out.push_back(std::move(dw));
           if (b) {
@@ -170,6 +336,7 @@ void backward(const TP& root) {
     auto contrib = it->backward(g->second);
     for (size_t i = 0; i < it->ins.size() && i < contrib.size(); ++i) {
       auto& c = contrib[i];
+      if (c.empty()) continue;  // this input takes no gradient
       if (g_tape.nan_policy)
         for (float f : c)
           if (!std::isfinite(f)) {

@@ -31,7 +31,8 @@ NVCC_FLAGS = [
     "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-O3",
 ]
-CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-pthread", "-Wall", "-Wno-unused-function"]
+# no contraction: the CPU oracle promises the same bits whatever instruction set a multi-versioned loop runs on
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-pthread", "-ffp-contract=off", "-Wall", "-Wno-unused-function"]
 
 
 def _nvcc() -> str | None:

@@ -58,7 +58,7 @@ def train_torch(steps: int = 100, lr: float = 0.01, seed: int = 0) -> tuple[list
     for _ in range(steps):
         hdn = torch.relu(x @ ps[0].t() + ps[1])
         loss = torch.nn.functional.cross_entropy(hdn @ ps[2].t() + ps[3], y)
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
         grads = torch.autograd.grad(loss, ps)
         with torch.no_grad():
             for p, g in zip(ps, grads):

@@ -413,6 +413,62 @@ def test_native_mlp_benchmark_matches_pytorch_cpu():
     assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5
 
 
+def test_native_tape_linear_shapes_gradients_and_fork():
+    """The tape's linear op against PyTorch fp32 on shapes that reach both transposition choices, the vector tiles,
+    the scalar column tail and the row pool; an input without gradient gets none; a forked child (which has no
+    pool threads) computes the same losses."""
+    import ctypes as C
+    import os
+    from incin_b200 import _native as nat
+    from incin_b200.models.mlp import train_native
+    h = nat.host()
+    for f in ("incin_tape_tensor", "incin_tape_linear", "incin_tape_cross_entropy"):
+        getattr(h, f).restype = C.c_int64
+    h.incin_tape_tensor.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int]
+    h.incin_tape_linear.argtypes = [C.c_int64] * 3
+    h.incin_tape_cross_entropy.argtypes = [C.c_int64, C.c_void_p]
+    h.incin_tape_backward.argtypes = [C.c_int64]
+    h.incin_tape_read.argtypes = h.incin_tape_grad.argtypes = [C.c_int64, C.c_void_p]
+    g = torch.Generator().manual_seed(0)
+    for m, n, k, x_grad in ((7, 13, 37, True), (64, 300, 200, False), (33, 520, 96, True), (128, 10, 64, True)):
+        h.incin_tape_reset()
+        x = torch.randn(m, k, generator=g)
+        w = torch.randn(n, k, generator=g) / k ** 0.5
+        b = torch.randn(n, generator=g)
+        t = torch.randint(0, n, (m,), generator=g)
+        hx = h.incin_tape_tensor(x.data_ptr(), m, k, int(x_grad))
+        hw = h.incin_tape_tensor(w.data_ptr(), n, k, 1)
+        hb = h.incin_tape_tensor(b.data_ptr(), 1, n, 1)
+        hy = h.incin_tape_linear(hx, hw, hb)
+        loss = h.incin_tape_cross_entropy(hy, t.data_ptr())
+        assert hy and loss and h.incin_tape_backward(loss) == 0
+        y = torch.empty(m, n)
+        h.incin_tape_read(hy, y.data_ptr())
+        xr, wr, br = (v.clone().requires_grad_() for v in (x, w, b))
+        ref = xr @ wr.t() + br
+        torch.nn.functional.cross_entropy(ref, t).backward()
+        assert torch.allclose(y, ref.detach(), atol=2e-5, rtol=1e-5)
+        for hnd, want in ((hw, wr.grad), (hb, br.grad.view(1, n)), (hx, xr.grad)):
+            got = torch.zeros_like(want)
+            rc = h.incin_tape_grad(hnd, got.data_ptr())
+            if hnd == hx and not x_grad:
+                assert rc == 2
+            else:
+                assert rc == 0 and torch.allclose(got, want, atol=2e-6, rtol=1e-4), (m, n, k)
+    h.incin_tape_reset()
+    a, _ = train_native(steps=3)
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", DeprecationWarning)   # the fork is the point of this check
+        pid = os.fork()
+    if pid == 0:
+        try:
+            os._exit(0 if train_native(steps=3)[0] == a else 3)
+        finally:
+            os._exit(4)
+    assert os.waitstatus_to_exitcode(os.waitpid(pid, 0)[1]) == 0
+
+
 def test_linear_cross_entropy_cpu_twin_and_model_loss():
     """Off the GPU the fused LM-head loss is linear followed by cross_entropy over the first `num_classes` columns, and
     the GPT-2 model routes its training loss through it."""
