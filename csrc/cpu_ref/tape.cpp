@@ -83,56 +83,82 @@ void push(Node n) {
 // and C are row-major.  Every output element accumulates its K products one at a time in ascending k, with
 // separate multiply and add (the file is compiled without contraction), so the result does not depend on the
 // tile sizes, on the instruction set the loader picked, or on how rows were split over threads.
-typedef float v8f __attribute__((vector_size(32), aligned(4), may_alias));
+// Vector types reach the templates through a traits struct: as template arguments themselves they would lose
+// `aligned(4)` (loads from any float address) and `may_alias`.
+struct Vec8 {
+  typedef float type __attribute__((vector_size(32), aligned(4), may_alias));
+};
+struct Vec16 {
+  typedef float type __attribute__((vector_size(64), aligned(4), may_alias));
+};
 
-// MR rows by NV*8 columns held in vector registers over the whole K loop
-template <int MR, int NV>
+// MR rows by NV vectors of columns held in registers over the whole K loop
+template <class VT, int MR, int NV>
 __attribute__((always_inline)) inline void gemm_tile_v(const float* A, int64_t a_rs, int64_t a_cs, const float* B,
                                                        int64_t ldb, float* C, int64_t ldc, int64_t K) {
-  v8f acc[MR][NV];
+  typedef typename VT::type V;
+  constexpr int W = sizeof(V) / sizeof(float);
+  V acc[MR][NV];
   for (int r = 0; r < MR; ++r)
-    for (int c = 0; c < NV; ++c) acc[r][c] = *(const v8f*)(C + r * ldc + 8 * c);
+    for (int c = 0; c < NV; ++c) acc[r][c] = *(const V*)(C + r * ldc + W * c);
   for (int64_t k = 0; k < K; ++k) {
-    v8f b[NV];
-    for (int c = 0; c < NV; ++c) b[c] = *(const v8f*)(B + k * ldb + 8 * c);
+    V b[NV];
+    for (int c = 0; c < NV; ++c) b[c] = *(const V*)(B + k * ldb + W * c);
     for (int r = 0; r < MR; ++r) {
-      const float a = A[r * a_rs + k * a_cs];
-      const v8f av = {a, a, a, a, a, a, a, a};
+      const V av = A[r * a_rs + k * a_cs] - V{};  // scalar op vector broadcasts; x - (+0) is x for every x
       for (int c = 0; c < NV; ++c) acc[r][c] += av * b[c];
     }
   }
   for (int r = 0; r < MR; ++r)
-    for (int c = 0; c < NV; ++c) *(v8f*)(C + r * ldc + 8 * c) = acc[r][c];
+    for (int c = 0; c < NV; ++c) *(V*)(C + r * ldc + W * c) = acc[r][c];
 }
 
-template <int MR>
-__attribute__((always_inline)) inline void gemm_tile_1(const float* A, int64_t a_rs, int64_t a_cs, const float* B,
-                                                       int64_t ldb, float* C, int64_t ldc, int64_t K) {
-  for (int r = 0; r < MR; ++r) {
-    float acc = C[r * ldc];
-    for (int64_t k = 0; k < K; ++k) acc += A[r * a_rs + k * a_cs] * B[k * ldb];
-    C[r * ldc] = acc;
+__attribute__((always_inline)) inline void gemm_col(const float* A, int64_t a_rs, int64_t a_cs, const float* B,
+                                                    int64_t ldb, float* C, int64_t ldc, int64_t i0, int64_t i1,
+                                                    int64_t K) {
+  for (int64_t i = i0; i < i1; ++i) {
+    float acc = C[i * ldc];
+    for (int64_t k = 0; k < K; ++k) acc += A[i * a_rs + k * a_cs] * B[k * ldb];
+    C[i * ldc] = acc;
   }
 }
 
-// NV*8 columns at a time: the K x 16 panel of B stays in cache while every row block of [i0, i1) passes over it
-template <int NV>
+// NV vectors of columns at a time: that K-deep panel of B stays in cache while every row block of [i0, i1) passes
+template <class VT, int NV>
 __attribute__((always_inline)) inline void gemm_panel(const float* A, int64_t a_rs, int64_t a_cs, const float* B,
                                                       float* C, int64_t i0, int64_t i1, int64_t N, int64_t K) {
   constexpr int MR = 4;
   int64_t i = i0;
-  for (; i + MR <= i1; i += MR) gemm_tile_v<MR, NV>(A + i * a_rs, a_rs, a_cs, B, N, C + i * N, N, K);
-  for (; i < i1; ++i) gemm_tile_v<1, NV>(A + i * a_rs, a_rs, a_cs, B, N, C + i * N, N, K);
+  for (; i + MR <= i1; i += MR) gemm_tile_v<VT, MR, NV>(A + i * a_rs, a_rs, a_cs, B, N, C + i * N, N, K);
+  for (; i < i1; ++i) gemm_tile_v<VT, 1, NV>(A + i * a_rs, a_rs, a_cs, B, N, C + i * N, N, K);
 }
 
-__attribute__((target_clones("avx2", "avx", "default"))) void gemm_rows(const float* A, int64_t a_rs, int64_t a_cs,
-                                                                        const float* B, float* C, int64_t i0,
-                                                                        int64_t i1, int64_t N, int64_t K) {
+template <class VT>
+__attribute__((always_inline)) inline void gemm_rows_impl(const float* A, int64_t a_rs, int64_t a_cs, const float* B,
+                                                          float* C, int64_t i0, int64_t i1, int64_t N, int64_t K) {
+  constexpr int W = sizeof(typename VT::type) / sizeof(float);
   int64_t j = 0;
-  for (; j + 16 <= N; j += 16) gemm_panel<2>(A, a_rs, a_cs, B + j, C + j, i0, i1, N, K);
-  for (; j + 8 <= N; j += 8) gemm_panel<1>(A, a_rs, a_cs, B + j, C + j, i0, i1, N, K);
-  for (; j < N; ++j)
-    for (int64_t i = i0; i < i1; ++i) gemm_tile_1<1>(A + i * a_rs, a_rs, a_cs, B + j, N, C + i * N + j, N, K);
+  for (; j + 2 * W <= N; j += 2 * W) gemm_panel<VT, 2>(A, a_rs, a_cs, B + j, C + j, i0, i1, N, K);
+  for (; j + W <= N; j += W) gemm_panel<VT, 1>(A, a_rs, a_cs, B + j, C + j, i0, i1, N, K);
+  for (; j + 8 <= N; j += 8) gemm_panel<Vec8, 1>(A, a_rs, a_cs, B + j, C + j, i0, i1, N, K);
+  for (; j < N; ++j) gemm_col(A, a_rs, a_cs, B + j, N, C + j, N, i0, i1, K);
+}
+
+// 256-bit tiles for AVX2 / AVX / baseline (the loader picks the clone), 512-bit tiles where the CPU has AVX-512
+__attribute__((target_clones("avx2", "avx", "default"))) void gemm_rows_256(const float* A, int64_t a_rs,
+                                                                            int64_t a_cs, const float* B, float* C,
+                                                                            int64_t i0, int64_t i1, int64_t N,
+                                                                            int64_t K) {
+  gemm_rows_impl<Vec8>(A, a_rs, a_cs, B, C, i0, i1, N, K);
+}
+__attribute__((target("avx512f"))) void gemm_rows_512(const float* A, int64_t a_rs, int64_t a_cs, const float* B,
+                                                      float* C, int64_t i0, int64_t i1, int64_t N, int64_t K) {
+  gemm_rows_impl<Vec16>(A, a_rs, a_cs, B, C, i0, i1, N, K);
+}
+void gemm_rows(const float* A, int64_t a_rs, int64_t a_cs, const float* B, float* C, int64_t i0, int64_t i1,
+               int64_t N, int64_t K) {
+  static const bool wide = __builtin_cpu_supports("avx512f");
+  (wide ? gemm_rows_512 : gemm_rows_256)(A, a_rs, a_cs, B, C, i0, i1, N, K);
 }
 
 // A small pool of sleeping workers splits the rows of one product.  Starting threads per product costs about as
