@@ -468,10 +468,7 @@ norm_bwd_param_final(const float* __restrict__ scratch, float* __restrict__ dgam
 // The row is held as the raw 16-byte loads (bf16) and unpacked where it is used; the per-column accumulators of each
 // warp live in shared memory (element (it, i, lane) at it*256 + i*32 + lane: a warp touches 32 different banks), which
 // keeps the kernel under 85 registers so that three blocks (24 warps) per SM have loads in flight.
-// CSUM: a third accumulator takes the column sums of the dx this kernel writes (the incoming residual gradient
-// included): that is the bias gradient of the linear layer whose output entered the residual stream in front of this
-// norm, which then needs no column-sum launch of its own.
-template <bool RMS, int ITER, bool CSUM = false>
+template <bool RMS, int ITER>
 __global__ void __launch_bounds__(NORM_WARPS * 32, 3)
 norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                       const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
@@ -480,18 +477,16 @@ norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
                       long long rows_per) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float acc_smem[];                     // [NORM_WARPS][NA][ITER * 256]
+  extern __shared__ float acc_smem[];                     // [NORM_WARPS][2][ITER * 256]
   constexpr int W = ITER * 256;
-  constexpr int NA = CSUM ? 3 : 2;
+  constexpr int NA = 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* gacc = acc_smem + (warp * NA + 0) * W;
   float* bacc = acc_smem + (warp * NA + 1) * W;
-  float* cacc = acc_smem + (warp * NA + (CSUM ? 2 : 0)) * W;   // only touched when CSUM
 #pragma unroll
   for (int j = lane; j < W; j += 32) {
     gacc[j] = 0.f;
     bacc[j] = 0.f;
-    if (CSUM) cacc[j] = 0.f;
   }
   __syncwarp();
   const long long r0 = (long long)blockIdx.x * rows_per;
@@ -550,10 +545,6 @@ norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
           for (int i = 0; i < 8; ++i) o[i] += a[i];
         }
         store8(dx + r * C + c, o);
-        if (CSUM) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) cacc[it * 256 + i * 32 + lane] += o[i];
-        }
       }
     }
   }
@@ -562,16 +553,164 @@ norm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
   for (int j = threadIdx.x; j < W; j += NORM_WARPS * 32) {
     const int c = (j & ~255) + (j & 31) * 8 + ((j >> 5) & 7);
     if (c < C) {
-      float a = 0.f, bsum = 0.f, csum = 0.f;
+      float a = 0.f, bsum = 0.f;
 #pragma unroll
       for (int w = 0; w < NORM_WARPS; ++w) {
         a += acc_smem[(w * NA + 0) * W + j];
         bsum += acc_smem[(w * NA + 1) * W + j];
-        if (CSUM) csum += acc_smem[(w * NA + 2) * W + j];
       }
       scratch[((long long)blockIdx.x * NA + 0) * C + c] = a;
       scratch[((long long)blockIdx.x * NA + 1) * C + c] = bsum;
-      if (CSUM) scratch[((long long)blockIdx.x * NA + 2) * C + c] = csum;
+    }
+  }
+}
+
+// The one-pass backward that also produces the column sums of the dx it writes (the incoming residual gradient
+// included): that is the bias gradient of the linear layer whose output entered the residual stream in front of this
+// norm, which then needs no column-sum launch of its own.  Three partial sums per column, and a two-stage pipeline:
+// a warp has only a few rows to work through, so in the kernel above the memory system idles while every warp computes
+// and the warps idle while every load is in flight.  Here a warp requests its next row (x, dy and the incoming residual
+// gradient, with that row's mean and rstd) before it starts on the current one.  The second set of row registers
+// costs occupancy: two blocks of 7 warps per SM (128 registers), each warp with up to two rows in flight; 7 rather
+// than 8 because 8192 rows over 148 SMs are then exactly four rows per warp.
+__device__ __forceinline__ uint4 ld_issue_here(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+template <int ITER>
+struct NormRow {
+  uint4 x[ITER], d[ITER], a[ITER];
+  float mean, rstd;
+};
+
+template <bool RMS, int ITER, int CW>
+__global__ void __launch_bounds__(CW * 32, 2)
+norm_bwd_colsum_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                       const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                       const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dx_add,
+                       __nv_bfloat16* __restrict__ dx, float* __restrict__ scratch, long long rows, int C,
+                       long long rows_per) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float acc_smem[];                     // [CW][3][ITER * 256]
+  constexpr int W = ITER * 256;
+  constexpr int NA = 3;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* gacc = acc_smem + (warp * NA + 0) * W;
+  float* bacc = acc_smem + (warp * NA + 1) * W;
+  float* cacc = acc_smem + (warp * NA + 2) * W;
+#pragma unroll
+  for (int j = lane; j < W; j += 32) {
+    gacc[j] = 0.f;
+    bacc[j] = 0.f;
+    cacc[j] = 0.f;
+  }
+  __syncwarp();
+  const long long r0 = (long long)blockIdx.x * rows_per;
+  const long long r1 = r0 + rows_per < rows ? r0 + rows_per : rows;
+  const float inv_c = 1.f / C;
+  auto fetch = [&](NormRow<ITER>& R, long long r) {
+    R.mean = RMS ? 0.f : mean_in[r];
+    R.rstd = rstd_in[r];
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const int c = it * 256 + lane * 8;
+      const bool in = c < C;
+      const uint4 zero = make_uint4(0, 0, 0, 0);
+      // volatile: the request must be issued here, ahead of the work on the current row, and not where the
+      // compiler would otherwise sink it to (next to its first use, which would undo the pipeline)
+      R.x[it] = in ? ld_issue_here(x + r * C + c) : zero;
+      R.d[it] = in ? ld_issue_here(dy + r * C + c) : zero;   // d = 0 past C
+      R.a[it] = (in && dx_add) ? ld_issue_here(dx_add + r * C + c) : zero;
+    }
+  };
+  NormRow<ITER> cur, nxt;
+  long long r = r0 + warp;
+  if (r < r1) fetch(cur, r);
+  for (; r < r1; r += CW) {
+    if (r + CW < r1) fetch(nxt, r + CW);
+    const float rstd = cur.rstd;
+    const float nmr = -cur.mean * rstd;   // xhat = x * rstd + nmr
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      float f[8], d[8], g[8];
+      unpack8(cur.x[it], f);
+      unpack8(cur.d[it], d);
+      if (it * 256 + lane * 8 < C) {
+        load8(gamma + it * 256 + lane * 8, g);   // from L1: the two blocks of an SM leave it most of its capacity
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) g[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        f[i] = fmaf(f[i], rstd, nmr);   // xhat
+        const float gd = g[i] * d[i];
+        s1 += gd;
+        s2 = fmaf(gd, f[i], s2);
+      }
+      // accumulators as float2 (columns 2p, 2p + 1 of this lane's eight): half the shared-memory instructions of a
+      // scalar layout, and 32 lanes x 8 bytes are still conflict-free
+#pragma unroll
+      for (int p2 = 0; p2 < 4; ++p2) {
+        float2* ga = reinterpret_cast<float2*>(gacc) + it * 128 + p2 * 32 + lane;
+        float2* ba = reinterpret_cast<float2*>(bacc) + it * 128 + p2 * 32 + lane;
+        float2 gv = *ga, bv = *ba;
+        gv.x = fmaf(d[2 * p2], f[2 * p2], gv.x);
+        gv.y = fmaf(d[2 * p2 + 1], f[2 * p2 + 1], gv.y);
+        bv.x += d[2 * p2];
+        bv.y += d[2 * p2 + 1];
+        *ga = gv;
+        *ba = bv;
+      }
+    }
+    s1 = RMS ? 0.f : warp_sum(s1) * inv_c;
+    s2 = warp_sum(s2) * inv_c;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const int c = it * 256 + lane * 8;
+      if (c < C) {
+        float f[8], d[8], g[8], a[8], o[8];
+        unpack8(cur.x[it], f);
+        unpack8(cur.d[it], d);
+        load8(gamma + c, g);
+        unpack8(cur.a[it], a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float xh = fmaf(f[i], rstd, nmr);
+          o[i] = fmaf(rstd, fmaf(-xh, s2, g[i] * d[i] - s1), a[i]);
+        }
+        store8(dx + r * C + c, o);
+#pragma unroll
+        for (int p2 = 0; p2 < 4; ++p2) {
+          float2* ca = reinterpret_cast<float2*>(cacc) + it * 128 + p2 * 32 + lane;
+          float2 cv = *ca;
+          cv.x += o[2 * p2];
+          cv.y += o[2 * p2 + 1];
+          *ca = cv;
+        }
+      }
+    }
+    cur = nxt;
+  }
+  __syncthreads();
+  // the 8 warps' accumulators are added in warp order
+  for (int j = threadIdx.x; j < W; j += CW * 32) {
+    const int c = (j & ~255) + ((j & 63) >> 1) * 8 + ((j >> 6) & 3) * 2 + (j & 1);   // float2 layout above
+    if (c < C) {
+      float a = 0.f, bsum = 0.f, csum = 0.f;
+#pragma unroll
+      for (int w = 0; w < CW; ++w) {
+        a += acc_smem[(w * NA + 0) * W + j];
+        bsum += acc_smem[(w * NA + 1) * W + j];
+        csum += acc_smem[(w * NA + 2) * W + j];
+      }
+      scratch[((long long)blockIdx.x * NA + 0) * C + c] = a;
+      scratch[((long long)blockIdx.x * NA + 1) * C + c] = bsum;
+      scratch[((long long)blockIdx.x * NA + 2) * C + c] = csum;
     }
   }
 }
@@ -586,6 +725,18 @@ static long long fused_rows_per(long long rows, int C) {
   if (cap > 444) cap = 444;   // three blocks per SM: one wave
   if (blocks > cap) blocks = cap;
   return (rows + blocks - 1) / blocks;
+}
+
+// the pipelined kernel with column sums runs two blocks per SM: one wave of 296
+constexpr int COLSUM_WARPS = 7;   // 2 x 7 warps per SM: 8192 rows over 148 SMs are four rows per warp, none idle
+static long long colsum_rows_per(long long rows) {
+  long long blocks = (rows + COLSUM_WARPS - 1) / COLSUM_WARPS;
+  if (blocks > 296) blocks = 296;
+  return (rows + blocks - 1) / blocks;
+}
+static int colsum_chunks(long long rows) {
+  const long long rp = colsum_rows_per(rows);
+  return (int)((rows + rp - 1) / rp);
 }
 
 static int param_chunks(long long rows, int C) {
@@ -607,11 +758,12 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, con
   if (dxsum && !(dgamma && fused_bwd_ok(C))) return INCIN_ERR_ARGUMENT;   // column sums of dx: one-pass kernel only
   if (dgamma && fused_bwd_ok(C)) {
     if (!scratch) return INCIN_ERR_ARGUMENT;
-    const long long rp = fused_rows_per(rows, C);
-    const int chunks = param_chunks(rows, C);
+    const long long rp = dxsum ? colsum_rows_per(rows) : fused_rows_per(rows, C);
+    const int chunks = dxsum ? colsum_chunks(rows) : param_chunks(rows, C);
     const int iters = (C + 255) / 256;
     const int na = dxsum ? 3 : 2;
-    const size_t acc_bytes = (size_t)NORM_WARPS * na * iters * 256 * sizeof(float);   // 8 KB per 256 columns and sum
+    const int warps = dxsum ? COLSUM_WARPS : NORM_WARPS;
+    const size_t acc_bytes = (size_t)warps * na * iters * 256 * sizeof(float);   // 8 KB per 256 columns and sum
     static PerDeviceFlags attr_set[10];   // per kernel (RMS is a template argument here) and per device
     bool attr_ok = true;
     auto go = [&](auto kern) {
@@ -619,14 +771,14 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, con
         attr_ok = false;   // nothing was launched: the partial sums must not be reduced either
         return;
       }
-      launch_pdl(kern, dim3((unsigned)chunks), dim3(NORM_WARPS * 32), acc_bytes, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+      launch_pdl(kern, dim3((unsigned)chunks), dim3(warps * 32), acc_bytes, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                  (const __nv_bfloat16*)gamma, mean, rstd, (const __nv_bfloat16*)dx_add, (__nv_bfloat16*)dx, scratch, rows, C, rp);
     };
     if (dxsum) {
-      if (iters == 1) go(norm_bwd_fused_kernel<RMS, 1, true>);
-      else if (iters == 2) go(norm_bwd_fused_kernel<RMS, 2, true>);
-      else if (iters == 3) go(norm_bwd_fused_kernel<RMS, 3, true>);
-      else go(norm_bwd_fused_kernel<RMS, 4, true>);
+      if (iters == 1) go(norm_bwd_colsum_kernel<RMS, 1, COLSUM_WARPS>);
+      else if (iters == 2) go(norm_bwd_colsum_kernel<RMS, 2, COLSUM_WARPS>);
+      else if (iters == 3) go(norm_bwd_colsum_kernel<RMS, 3, COLSUM_WARPS>);
+      else go(norm_bwd_colsum_kernel<RMS, 4, COLSUM_WARPS>);
     } else if (iters == 1) go(norm_bwd_fused_kernel<RMS, 1>);
     else if (iters == 2) go(norm_bwd_fused_kernel<RMS, 2>);
     else if (iters == 3) go(norm_bwd_fused_kernel<RMS, 3>);
@@ -689,7 +841,7 @@ extern "C" int incin_layernorm_bwd(const void* dy, const void* x, const void* ga
 // gradient of the linear layer in front of this norm on the residual stream.  C % 8 == 0 and C <= 1024 (the one-pass
 // kernel); scratch holds incin_layernorm_bwd_colsum_scratch_floats(rows, C) floats.
 extern "C" long long incin_layernorm_bwd_colsum_scratch_floats(long long rows, int C) {
-  return (long long)param_chunks(rows, C) * 3 * C;
+  return (long long)colsum_chunks(rows) * 3 * C;
 }
 
 extern "C" int incin_layernorm_bwd_colsum(const void* dy, const void* x, const void* gamma, const float* mean,

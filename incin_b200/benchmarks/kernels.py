@@ -147,6 +147,14 @@ def bench_bandwidth(args) -> None:
     dgs, dbs = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
     rec("layernorm_bwd 8192x768 (+residual gradient)",
         timeit(lambda: K.layernorm_bwd(ys, x, g, means, rstds, ys, dgs, dbs)), 4 * x.numel() * 2)
+    dcs = torch.zeros(C, device="cuda")
+    rec("layernorm_bwd 8192x768 (+residual gradient, + column sums of dx)",
+        timeit(lambda: K.layernorm_bwd(ys, x, g, means, rstds, ys, dgs, dbs, dcs)), 4 * x.numel() * 2)
+    # what a plain device copy of the same bytes reaches at this size (launch ramp and tail included)
+    x2, x4 = torch.empty_like(x), torch.empty(2, *x.shape, dtype=x.dtype, device="cuda")
+    x4s = torch.empty_like(x4)
+    rec("copy 8192x768 (torch copy_, bytes of layernorm_fwd)", timeit(lambda: x2.copy_(x)), 2 * x.numel() * 2)
+    rec("copy 2x8192x768 (torch copy_, bytes of layernorm_bwd)", timeit(lambda: x4s.copy_(x4)), 4 * x.numel() * 2)
     rec("layernorm_fwd 65536x4096", timeit(lambda: K.layernorm_fwd(xb, gb, None, 1e-5)), 2 * xb.numel() * 2)
     y, mean, rstd = K.layernorm_fwd(xb, gb, None, 1e-5)
     dg = torch.zeros(big_c, device="cuda")

@@ -221,6 +221,9 @@ def test_layernorm_backward_also_returns_the_column_sums_of_dx(C):
     dg1, db1 = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
     cs = torch.full((C,), 3.0, device="cuda")                       # accumulates on top of what is there
     dx1 = K.layernorm_bwd(dy, x, gamma, mean, rstd, res, dg1, db1, cs)
-    assert torch.equal(dx0, dx1) and torch.equal(dg0, dg1) and torch.equal(db0, db1)
+    # the one-pass kernel with column sums is its own kernel (pipelined, other summation order): close, not equal
+    check_close(dx1, dx0.float(), rtol=1.6e-2, atol_rms=1e-2, what=f"dx, C={C}")
+    check_close(dg1, dg0, rtol=1e-3, atol_rms=1e-3, what=f"dgamma, C={C}")
+    check_close(db1, db0, rtol=1e-3, atol_rms=1e-3, what=f"dbeta, C={C}")
     want = dx0.float().sum(0) + 3.0
     check_close(cs, want, rtol=1e-2, atol_rms=1e-2, what=f"column sums of dx, C={C}")
