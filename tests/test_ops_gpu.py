@@ -201,6 +201,28 @@ def test_linear_cross_entropy_fused():
     assert w.main_grad[V:].abs().max().item() == 0.0      # padded vocabulary rows get no gradient
 
 
+@pytest.mark.parametrize("rows,C", [(5, 8), (300, 256), (8192, 512), (1001, 1000)])
+def test_pipelined_norm_backward_edges(rows, C):
+    """The pipelined one-pass backward with column sums on its edge cases (fewer rows than warps, a partly filled last
+    group of 256 columns, no incoming residual gradient) against fp32 autograd."""
+    from _tol import check_close
+    from incin_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(rows * 7 + C)
+    x = torch.randn(rows, C, generator=g).bfloat16().cuda()
+    dy = torch.randn(rows, C, generator=g).bfloat16().cuda()
+    gamma = (torch.rand(C, generator=g) + 0.5).bfloat16().cuda()
+    beta = torch.zeros(C).bfloat16().cuda()
+    _, mean, rstd = K.layernorm_fwd(x, gamma, beta, 1e-5)
+    dg, db, cs = (torch.zeros(C, device="cuda") for _ in range(3))
+    dx = K.layernorm_bwd(dy, x, gamma, mean, rstd, None, dg, db, cs)
+    xr, gr, br = x.float().requires_grad_(), gamma.float().requires_grad_(), beta.float().requires_grad_()
+    torch.nn.functional.layer_norm(xr, (C,), gr, br, 1e-5).backward(dy.float())
+    check_close(dx, xr.grad, rtol=1.6e-2, atol_rms=1.5e-2, what=f"dx {rows}x{C}")
+    check_close(dg, gr.grad, rtol=5e-3, atol_rms=5e-3, what=f"dgamma {rows}x{C}")
+    check_close(db, br.grad, rtol=5e-3, atol_rms=5e-3, what=f"dbeta {rows}x{C}")
+    check_close(cs, dx.float().sum(0), rtol=1e-2, atol_rms=1e-2, what=f"column sums {rows}x{C}")
+
+
 @pytest.mark.parametrize("C", [768, 1024, 2048, 100])
 def test_layernorm_backward_also_returns_the_column_sums_of_dx(C):
     """The bias gradient of the linear in front of a norm is the column sum of the norm's input gradient: it comes out
