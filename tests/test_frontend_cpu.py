@@ -466,7 +466,19 @@ def test_native_tape_linear_shapes_gradients_and_fork():
             os._exit(0 if train_native(steps=3)[0] == a else 3)
         finally:
             os._exit(4)
-    assert os.waitstatus_to_exitcode(os.waitpid(pid, 0)[1]) == 0
+    import signal
+    import time
+    deadline = time.monotonic() + 60.0          # a child that never returns fails the test instead of hanging it
+    while True:
+        done, status = os.waitpid(pid, os.WNOHANG)
+        if done:
+            break
+        if time.monotonic() > deadline:
+            os.kill(pid, signal.SIGKILL)
+            os.waitpid(pid, 0)
+            pytest.fail("forked child did not finish")
+        time.sleep(0.01)
+    assert os.waitstatus_to_exitcode(status) == 0
 
 
 def test_linear_cross_entropy_cpu_twin_and_model_loss():
