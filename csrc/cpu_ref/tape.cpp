@@ -172,77 +172,77 @@ class RowPool {
   }
   // runs fn(lo, hi) over [0, M) in `parts` row ranges whose sizes are multiples of `align`
   void run(int64_t M, int64_t parts, int64_t align, const std::function<void(int64_t, int64_t)>& fn) {
-    parts = std::min<int64_t>(parts, (int64_t)workers_.size() + 1);
+    parts = std::min<int64_t>(parts, (int64_t)workers_->size() + 1);
     if (parts <= 1 || owner_ != getpid() || busy_.exchange(true)) {  // nested or concurrent callers run inline
       fn(0, M);
       return;
     }
     const int64_t per = ((M + parts - 1) / parts + align - 1) / align * align;
+    const int64_t n_parts = (M + per - 1) / per;
     {
       std::lock_guard<std::mutex> l(m_);
       fn_ = &fn;
       M_ = M;
       per_ = per;
-      next_.store(1);
-      n_parts_ = (M + per - 1) / per;
-      pending_.store(n_parts_ - 1);
-      ++gen_;
+      n_parts_ = n_parts;
+      next_part_ = 1;   // part 0 is the caller's
+      pending_.store(n_parts - 1);
     }
     cv_.notify_all();
     fn(0, std::min(M, per));
+    // the caller takes parts too, then waits for the ones the workers hold.  A part is claimed under the mutex
+    // together with the job it belongs to, and this function returns only after every claimed part has finished
+    // with no part left to claim, so a worker that wakes late never sees a job of an earlier call.
+    for (;;) {
+      int64_t part;
+      {
+        std::lock_guard<std::mutex> l(m_);
+        if (next_part_ >= n_parts_) break;
+        part = next_part_++;
+      }
+      fn(part * per, std::min(M, (part + 1) * per));
+      pending_.fetch_sub(1, std::memory_order_release);
+    }
     for (int spins = 0; pending_.load(std::memory_order_acquire) > 0; ++spins)
       if (spins > 2000) std::this_thread::yield();
     busy_.store(false);
   }
 
  private:
-  RowPool() : owner_(getpid()) {
+  RowPool() : workers_(new std::vector<std::thread>), owner_(getpid()) {
     const unsigned hc = std::max(1u, std::thread::hardware_concurrency());
-    for (unsigned i = 1; i < std::min(hc, 8u); ++i) workers_.emplace_back([this] { work(); });
+    for (unsigned i = 1; i < std::min(hc, 8u); ++i) workers_->emplace_back([this] { work(); });
   }
   ~RowPool() {
-    if (owner_ == getpid()) {
-      {
-        std::lock_guard<std::mutex> l(m_);
-        stop_ = true;
-      }
-      cv_.notify_all();
-      for (auto& t : workers_) t.join();
-    } else {
-      for (auto& t : workers_) t.detach();
+    if (owner_ != getpid()) return;   // a forked child has no such threads: their handles are left alone
+    {
+      std::lock_guard<std::mutex> l(m_);
+      stop_ = true;
     }
+    cv_.notify_all();
+    for (auto& t : *workers_) t.join();
+    delete workers_;
   }
   void work() {
-    uint64_t seen = 0;
+    std::unique_lock<std::mutex> l(m_);
     for (;;) {
-      const std::function<void(int64_t, int64_t)>* fn;
-      int64_t M, per, n_parts;
-      {
-        std::unique_lock<std::mutex> l(m_);
-        cv_.wait(l, [&] { return stop_ || gen_ != seen; });
-        if (stop_) return;
-        seen = gen_;
-        fn = fn_;
-        M = M_;
-        per = per_;
-        n_parts = n_parts_;
-      }
-      for (;;) {
-        const int64_t part = next_.fetch_add(1);
-        if (part >= n_parts) break;
-        (*fn)(part * per, std::min(M, (part + 1) * per));
-        pending_.fetch_sub(1, std::memory_order_release);
-      }
+      cv_.wait(l, [&] { return stop_ || next_part_ < n_parts_; });
+      if (stop_) return;
+      const int64_t part = next_part_++, M = M_, per = per_;
+      const std::function<void(int64_t, int64_t)>* fn = fn_;
+      l.unlock();
+      (*fn)(part * per, std::min(M, (part + 1) * per));
+      pending_.fetch_sub(1, std::memory_order_release);
+      l.lock();
     }
   }
-  std::vector<std::thread> workers_;
+  std::vector<std::thread>* workers_;
   std::mutex m_;
   std::condition_variable cv_;
   const std::function<void(int64_t, int64_t)>* fn_ = nullptr;
-  int64_t M_ = 0, per_ = 0, n_parts_ = 0;
-  std::atomic<int64_t> next_{0}, pending_{0};
+  int64_t M_ = 0, per_ = 0, n_parts_ = 0, next_part_ = 0;   // guarded by m_
+  std::atomic<int64_t> pending_{0};
   std::atomic<bool> busy_{false};
-  uint64_t gen_ = 0;
   bool stop_ = false;
   pid_t owner_;
 };
