@@ -179,7 +179,27 @@ def extra_measurements(args, world: int, rank: int, device, ctx=None) -> dict:
                     "loss_first": ours[0], "loss_last": ours[-1],
                     "max_loss_diff_vs_torch_cpu": max(abs(a - b) for a, b in zip(ours, lib))}
 
-        guarded("cpu_mlp_784_256_10", cpu_mlp)
+        def cpu_mlp_bounded():
+            # host threads only; bounded so that nothing on the host can hold back the line this program prints
+            import threading
+            box: dict = {}
+
+            def work():
+                try:
+                    box["row"] = cpu_mlp()
+                except Exception as e:   # noqa: BLE001
+                    box["err"] = e
+
+            t = threading.Thread(target=work, daemon=True)
+            t.start()
+            t.join(120.0)
+            if "err" in box:
+                raise box["err"]
+            if "row" not in box:
+                raise TimeoutError("CPU MLP did not finish within 120 s")
+            return box["row"]
+
+        guarded("cpu_mlp_784_256_10", cpu_mlp_bounded)
         guarded("attention_b8_h32_s4096_d128", attention)
         guarded("gemm_vs_cublas", gemm)
     else:
